@@ -1,0 +1,248 @@
+// k44_oracle.cpp — TEST INFRASTRUCTURE ONLY. CPU restatement of the SNNtome wave-executor maths.
+//
+// This file is the checker that the CUDA path is compared against. It is never linked into, imported
+// by or called from the shipped library; only the test-suite, the smoke check and the benchmark's
+// CPU-baseline leg load it.
+//
+// PARITY UNPINNED for output values: the reference ships no golden vectors, no fixtures and no CPU
+// executor for this path, and its licence forbids compiling or running it. What *is* pinned:
+//   * FNV-1a-64 against the published known-answer vectors (tests/test_oracle.py),
+//   * FP16 conversion against numpy.float16 for all 65536 bit patterns and random floats,
+//   * the wave arithmetic against a numpy float64 restatement and numpy.matmul in the dense case.
+//
+// Each function cites the reference location whose behaviour it restates (paths relative to the
+// reference project root). Nothing here was copied; the arithmetic is written from the formulas.
+//
+// Build: see oracle/Makefile (g++ -O3 -march=native -fopenmp -shared -fPIC).
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+// ---- FP16 <-> FP32, round to nearest even, subnormals kept, overflow -> inf --------------------
+// Behaviour described by wavec/k44_plan_types.hpp:21-87; written independently around the
+// "scale into the target grid and let the FPU round" idea instead of manual mantissa surgery.
+inline uint16_t f32_to_f16_rte(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    const uint32_t sign = (u >> 16) & 0x8000u;
+    const uint32_t absu = u & 0x7fffffffu;
+    if (absu >= 0x7f800000u) {                       // inf / nan
+        if (absu == 0x7f800000u) return (uint16_t)(sign | 0x7c00u);
+        // the reference keeps the top mantissa bits and forces the payload non-zero
+        return (uint16_t)(sign | 0x7c00u | ((absu & 0x007fffffu) >> 13) | 1u);
+    }
+    if (absu >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u);   // >= 65520 rounds to inf
+    if (absu < 0x38800000u) {                        // below the smallest normal half: subnormal grid
+        // the half subnormal grid has spacing 2^-24: round |f| * 2^24 to an integer, RTE.
+        float a;
+        std::memcpy(&a, &absu, 4);
+        const float scaled = a * 16777216.0f;        // exact (power of two), <= 1024
+        const float r = std::nearbyintf(scaled);     // default rounding mode = RTE
+        return (uint16_t)(sign | (uint32_t)r);       // r == 1024 lands on the smallest normal: correct
+    }
+    // normal range: add half an ulp of the 10-bit mantissa (plus the tie-to-even correction)
+    const uint32_t lsb = (absu >> 13) & 1u;
+    const uint32_t rounded = absu + 0x0fffu + lsb;
+    return (uint16_t)(sign | ((rounded - 0x38000000u) >> 13));
+}
+
+inline float f16_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    const uint32_t em = h & 0x7fffu;
+    uint32_t u;
+    if (em >= 0x7c00u) {
+        u = sign | 0x7f800000u | ((em & 0x3ffu) << 13);
+    } else if (em >= 0x0400u) {
+        u = sign | ((em << 13) + 0x38000000u);
+    } else {
+        const float v = (float)em * (1.0f / 16777216.0f);   // exact
+        std::memcpy(&u, &v, 4);
+        u |= sign;
+    }
+    float f;
+    std::memcpy(&f, &u, 4);
+    return f;
+}
+
+// Activation set of kernels/cuda/kernel44_cuda_pack.cuh:54-58 evaluated in double, plus value 5
+// (exact erf GELU) which the reference does not have.
+inline double activate(double v, int act) {
+    switch (act) {
+    case 1: return v > 0.0 ? v : 0.0;
+    case 2: return 1.0 / (1.0 + std::exp(-v));
+    case 3: return v / (1.0 + std::exp(-v));
+    case 4: return v > 0.1 * v ? v : 0.1 * v;
+    case 5: return 0.5 * v * (1.0 + std::erf(v * 0.70710678118654752440));
+    default: return v;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+// FNV-1a 64-bit — wavec/k44_tcff_io.hpp:10-17 (standard offset basis and prime).
+uint64_t k44o_fnv1a64(const uint8_t *data, uint64_t len) {
+    uint64_t h = 14695981039346656037ull;
+    for (uint64_t i = 0; i < len; ++i) {
+        h = (h ^ data[i]) * 1099511628211ull;
+    }
+    return h;
+}
+
+void k44o_f32_to_f16(const float *src, uint16_t *dst, uint64_t n) {
+    for (uint64_t i = 0; i < n; ++i) dst[i] = f32_to_f16_rte(src[i]);
+}
+
+void k44o_f16_to_f32(const uint16_t *src, float *dst, uint64_t n) {
+    for (uint64_t i = 0; i < n; ++i) dst[i] = f16_to_f32(src[i]);
+}
+
+// Row-major [cout][B] <-> the file's 16x16 tile order — wavec/k44_plan_types.hpp:363-394.
+// A weight row is cut into 8-half (16-byte) vectors. Tiles are 16 neurons x 16 synapses, walked
+// neuron-block major; inside a tile the 32 vectors are ordered (k_half, neuron): vector v holds
+// neuron (v & 15), synapse half (v >> 4).
+void k44o_rowmajor_to_wmma(const uint16_t *row_major, uint16_t *wmma, uint32_t cout, uint32_t B) {
+    const uint32_t kt = B / 16;
+    for (uint32_t nb = 0; nb < cout / 16; ++nb)
+        for (uint32_t kb = 0; kb < kt; ++kb)
+            for (uint32_t v = 0; v < 32; ++v) {
+                const uint32_t neuron = nb * 16 + (v & 15);
+                const uint32_t k0 = kb * 16 + (v >> 4) * 8;
+                std::memcpy(wmma + (((uint64_t)nb * kt + kb) * 32 + v) * 8,
+                            row_major + (uint64_t)neuron * B + k0, 16);
+            }
+}
+
+void k44o_wmma_to_rowmajor(const uint16_t *wmma, uint16_t *row_major, uint32_t cout, uint32_t B) {
+    const uint32_t kt = B / 16;
+    for (uint32_t nb = 0; nb < cout / 16; ++nb)
+        for (uint32_t kb = 0; kb < kt; ++kb)
+            for (uint32_t v = 0; v < 32; ++v) {
+                const uint32_t neuron = nb * 16 + (v & 15);
+                const uint32_t k0 = kb * 16 + (v >> 4) * 8;
+                std::memcpy(row_major + (uint64_t)neuron * B + k0,
+                            wmma + (((uint64_t)nb * kt + kb) * 32 + v) * 8, 16);
+            }
+}
+
+// One wave over a 1-D token layout, in place on the canvas.
+//
+//   Y[y_off + tile_off_Y[t] + out_j*pitch + c] =
+//       f16_rte( epilogue( bias[j] + sum_s W[j][s] * X[x_base + tile_off_X[t] + idx[j/G][s] + c] ) )
+//
+// Semantics: kernels/cuda/kernel44_cuda_pack.cuh:190-216 (addressing, bias-initialised accumulator),
+// :69-126 (epilogue: residual added BEFORE the activation when a cout map is present, AFTER it
+// otherwise; optional uint16 output-row remap), wavec/k44_plan_types.hpp:498-516 (64-column tiles).
+// Operands are the FP16-quantised values; accumulation is in double ("stage 2" of
+// whitepaper/sparse_wmma_kernel/tests/error_collapse_test.cpp:297-347), so the only rounding is
+// the final store. Padded synapse slots are consumed as stored (index 0, weight 0), exactly like
+// the reference kernels do.
+//
+// rows_begin/rows_end restrict the neurons computed (sampled checks on very large waves).
+// Returns 0, or -1 if an index would leave the canvas (nothing is written in that case).
+int k44o_wave_forward(uint16_t *canvas, uint64_t canvas_elems, const uint16_t *w_row_major,
+                      const uint32_t *idx, const uint16_t *bias, const uint16_t *cout_map,
+                      uint32_t cout, uint32_t group, uint32_t B, int act, int has_residual,
+                      uint64_t y_off, uint64_t res_off, uint64_t x_base_off, uint32_t pitch,
+                      const uint32_t *tile_off_x, const uint32_t *tile_off_y, uint32_t num_tiles,
+                      uint32_t rows_begin, uint32_t rows_end) {
+    if (rows_end > cout) rows_end = cout;
+    // bounds check first: every read and write must stay inside the canvas
+    uint32_t max_idx = 0;
+    for (uint64_t i = (uint64_t)(rows_begin / group) * B; i < (uint64_t)((rows_end + group - 1) / group) * B; ++i)
+        if (idx[i] > max_idx) max_idx = idx[i];
+    for (uint32_t t = 0; t < num_tiles; ++t) {
+        if (x_base_off + tile_off_x[t] + max_idx + 64 > canvas_elems) return -1;
+    }
+    for (uint32_t j = rows_begin; j < rows_end; ++j) {
+        const uint64_t out_j = cout_map ? cout_map[j] : j;
+        for (uint32_t t = 0; t < num_tiles; ++t) {
+            if (y_off + tile_off_y[t] + out_j * pitch + 64 > canvas_elems) return -1;
+            if (has_residual && res_off + tile_off_y[t] + out_j * pitch + 64 > canvas_elems) return -1;
+        }
+    }
+    // All reads come from earlier waves' regions, all writes go to this wave's region; a snapshot
+    // of the outputs is staged so that a plan that (incorrectly) aliases them still behaves like
+    // the GPU's "read old data" order as far as possible. Writes are applied at the end.
+    const int64_t nrows = (int64_t)rows_end - (int64_t)rows_begin;
+    std::vector<uint16_t> out((size_t)(nrows > 0 ? nrows : 0) * num_tiles * 64);
+#pragma omp parallel
+    {
+        std::vector<double> wrow(B);
+        std::vector<double> acc(64);
+#pragma omp for schedule(dynamic, 4)
+        for (int64_t jj = 0; jj < nrows; ++jj) {
+            const uint32_t j = rows_begin + (uint32_t)jj;
+            const uint32_t *irow = idx + (uint64_t)(j / group) * B;
+            for (uint32_t s = 0; s < B; ++s) wrow[s] = (double)f16_to_f32(w_row_major[(uint64_t)j * B + s]);
+            const double b = bias ? (double)f16_to_f32(bias[j]) : 0.0;
+            const uint64_t out_j = cout_map ? cout_map[j] : j;
+            for (uint32_t t = 0; t < num_tiles; ++t) {
+                for (int c = 0; c < 64; ++c) acc[c] = b;
+                const uint16_t *xt = canvas + x_base_off + tile_off_x[t];
+                for (uint32_t s = 0; s < B; ++s) {
+                    const double w = wrow[s];
+                    const uint16_t *xr = xt + irow[s];
+                    for (int c = 0; c < 64; ++c) acc[c] += w * (double)f16_to_f32(xr[c]);
+                }
+                const uint16_t *rr = has_residual ? canvas + res_off + tile_off_y[t] + out_j * pitch : nullptr;
+                uint16_t *o = out.data() + ((size_t)jj * num_tiles + t) * 64;
+                for (int c = 0; c < 64; ++c) {
+                    double v = acc[c];
+                    const double r = rr ? (double)f16_to_f32(rr[c]) : 0.0;
+                    if (rr && cout_map) v += r;
+                    v = activate(v, act);
+                    if (rr && !cout_map) v += r;
+                    o[c] = f32_to_f16_rte((float)v);
+                }
+            }
+        }
+    }
+    for (int64_t jj = 0; jj < nrows; ++jj) {
+        const uint32_t j = rows_begin + (uint32_t)jj;
+        const uint64_t out_j = cout_map ? cout_map[j] : j;
+        for (uint32_t t = 0; t < num_tiles; ++t)
+            std::memcpy(canvas + y_off + tile_off_y[t] + out_j * pitch,
+                        out.data() + ((size_t)jj * num_tiles + t) * 64, 128);
+    }
+    return 0;
+}
+
+// Same arithmetic but with FP32 accumulation in 16-synapse chunks followed by the FP16 store —
+// "stage 3" of whitepaper/sparse_wmma_kernel/tests/error_collapse_test.cpp:297-347. Used only for
+// the sanity band on expected GPU-vs-exact error, never as the parity reference.
+void k44o_dot_stage3(const uint16_t *w, const uint16_t *x, uint32_t B, float bias, float *out) {
+    float acc = bias;
+    for (uint32_t s0 = 0; s0 < B; s0 += 16) {
+        float part = 0.0f;
+        for (uint32_t s = s0; s < s0 + 16 && s < B; ++s) part += f16_to_f32(w[s]) * f16_to_f32(x[s]);
+        acc += part;
+    }
+    *out = f16_to_f32(f32_to_f16_rte(acc));
+}
+
+int k44o_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+void k44o_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+}  // extern "C"
