@@ -1,0 +1,110 @@
+/* Native additions of libk44wavec.so: build a wave plan from arrays or a .tcff file, keep inputs and
+ * outputs on the device, run on a caller-supplied CUDA stream.
+ *
+ * These have no counterpart in the reference ABI; they exist because the reference's only execution
+ * entry point (wavec_gpu_infer_f32, wavec/k44_wave_executor.cu:972-986) moves every input and output
+ * through host FP32 arrays with blocking copies (:146-176), which would dominate the wave time.
+ * Plan fields mirror K44ExecCmd / K44WavePlan (wavec/k44_plan_types.hpp:603-693).
+ *
+ * All functions return 0 on success and a negative value on failure unless stated otherwise; the
+ * message of the last failure on the calling thread is returned by k44b_last_error().
+ */
+#ifndef K44B_H
+#define K44B_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct k44b_wave_desc {
+    uint32_t cout;            /* padded output rows, multiple of 16 (K44ExecCmd::Cout) */
+    uint32_t logical_cout;    /* rows that carry neurons (K44ExecCmd::logical_Cout) */
+    uint32_t cin;             /* informational (K44ExecCmd::Cin) */
+    uint32_t group;           /* neurons sharing one gather list (K44ExecCmd::cluster_size) */
+    uint32_t fan_in;          /* padded synapses per neuron, multiple of 8 (K44ExecCmd::B) */
+    uint32_t fan_in_raw;      /* slots >= fan_in_raw must carry zero weights (K44ExecCmd::B_raw) */
+    int32_t act;              /* 0 none, 1 relu, 2 sigmoid, 3 silu, 4 leaky-relu(0.1), 5 gelu(erf) */
+    uint32_t has_residual;
+    uint64_t y_off;           /* canvas element offset of output row 0 */
+    uint64_t src_off;         /* informational */
+    uint64_t res_off;         /* canvas element offset of residual row 0 */
+    uint64_t x_base_off;      /* added to every entry of idx */
+    const uint32_t *idx;      /* host [cout/group][fan_in] FP16-element offsets, or NULL when run_rows is given */
+    const uint32_t *run_rows; /* host [cout/group][fan_in/run_len] first canvas row of every run, or NULL */
+    uint32_t run_len;         /* rows per run (run_rows form) */
+    uint32_t weights_on_device; /* 0: `weights` is a host pointer, 1: device pointer on the plan's device */
+    const uint16_t *weights;  /* row-major [cout][fan_in] FP16 bit patterns */
+    const uint16_t *bias;     /* host [cout] FP16 or NULL */
+    const uint16_t *cout_map; /* host [cout] logical row -> stored row, or NULL */
+    const char *name;         /* optional */
+} k44b_wave_desc;
+
+typedef struct k44b_wave_info_t {
+    uint32_t cout, group, fan_in, box_rows;   /* box_rows: rows fetched per TMA box, 0 on the index path */
+    int32_t path;                             /* 0 FMA kernel, 1 tcgen05 kernel */
+    uint32_t n_tile;                          /* columns per tile on the tcgen05 path */
+    uint64_t synapses;                        /* logical_cout * fan_in_raw */
+    uint64_t weight_bytes;                    /* packed size on the device */
+} k44b_wave_info_t;
+
+/* Create an empty plan bound to `device`: allocates and zeroes the canvas (canvas_elems FP16, rows of
+ * `pitch` elements, pitch a multiple of 64). force_path: -1 automatic, 0 FMA kernel only, 1 tcgen05
+ * wherever the gather structure allows. Returns NULL on failure. */
+void *k44b_plan_create(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t columns, int force_path);
+/* Pack one wave onto the device (weights re-tiled, gather table analysed into row runs). Host and
+ * device source arrays may be released when the call returns. */
+int k44b_plan_add_wave(void *plan, const k44b_wave_desc *wave);
+/* Declare the dense input / output tensors used by k44b_infer_f32. */
+int k44b_plan_set_io(void *plan, uint64_t input_off, uint32_t input_c, uint64_t output_off, uint32_t output_c, uint32_t width);
+/* Build a pure-wave plan from a TCFFv1.0 file (pitch from its geometry tag, else pitch_hint). */
+void *k44b_plan_from_tcff(const char *path, uint32_t pitch_hint, int device, int force_path);
+void k44b_plan_destroy(void *plan);
+
+/* Device pointer to canvas element 0 (FP16). Valid until the plan is destroyed. */
+void *k44b_canvas_ptr(void *plan);
+uint64_t k44b_canvas_elems(void *plan);
+int k44b_num_waves(void *plan);
+int k44b_wave_info(void *plan, int wave, k44b_wave_info_t *out);
+/* Queue every wave on `stream` (a cudaStream_t; NULL = default stream). Does not synchronise. */
+int k44b_execute(void *plan, void *stream);
+/* Queue one wave (0-based) on `stream`. */
+int k44b_execute_wave(void *plan, int wave, void *stream);
+/* Host FP16 in / out in canvas layout: h_in is [input_c][pitch], h_out is [output_c][pitch] (either may be
+ * NULL to skip that copy). Copies and waves run on `stream`; returns once the output has arrived.
+ * out_gpu_ms = device time of the waves only. Use pinned host memory for asynchronous copies. */
+int k44b_infer_f16(void *plan, const uint16_t *h_in, uint16_t *h_out, float *out_gpu_ms, void *stream);
+/* Synchronise the plan's device and fetch-and-clear the kernels' status word (0 = ok). Returns -1 and
+ * sets the error text when the status is non-zero. */
+int k44b_status(void *plan, uint32_t *status);
+/* Same contract as wavec_gpu_infer_f32 for a native plan. */
+int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, int out_elems, float *out_gpu_ms);
+/* Number of kernels this plan has launched so far. */
+uint64_t k44b_launch_count(void *plan);
+/* Unpack wave `wave`'s device weights to row-major [cout][fan_in] FP16 at device pointer d_dst. */
+int k44b_wave_weights_rowmajor(void *plan, int wave, void *d_dst);
+
+/* Handle-based plans (wavec_*): device used by wavec_gpu_init_plan, and access to the executor's plan. */
+int k44b_set_device(void *wavec_handle, int device);
+int k44b_set_force_path(void *wavec_handle, int force_path);
+void *k44b_handle_plan(void *wavec_handle);   /* plan pointer usable with the k44b_* calls above, or NULL */
+
+/* Utilities */
+const char *k44b_last_error(void);
+const char *k44b_version(void);
+/* dst[i] = FP16(scale * N(0,1)) from a stateless hash of (seed, i); dst is a device pointer. */
+int k44b_fill_normal_f16(void *d_dst, uint64_t n, uint64_t seed, float scale, void *stream);
+/* Host helpers (no device needed): FNV-1a-64, FP32->FP16 RTE, 16x16-tile weight order. */
+uint64_t k44b_fnv1a64(const uint8_t *data, uint64_t len);
+void k44b_f32_to_f16(const float *src, uint16_t *dst, uint64_t n);
+void k44b_rowmajor_to_wmma(const uint16_t *src, uint16_t *dst, uint32_t cout, uint32_t fan_in);
+void k44b_wmma_to_rowmajor(const uint16_t *src, uint16_t *dst, uint32_t cout, uint32_t fan_in);
+/* Host-only gather analysis: returns rows per box (8/16/32/64) when the tcgen05 path applies, 0 when
+ * it does not; out_box_rows (optional, capacity in entries) receives the run table. */
+int k44b_analyze_gather(const k44b_wave_desc *wave, uint32_t pitch, uint64_t canvas_elems, uint32_t *out_box_rows,
+                        uint64_t capacity, uint64_t *out_count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,406 @@
+// extern "C" surface of libk44wavec.so: the reference-compatible wavec_* calls (include/k44wavec.h)
+// and the native k44b_* additions (include/k44b.h).
+#include <memory>
+#include <mutex>
+
+#include "../../include/k44b.h"
+#include "../../include/k44wavec.h"
+#include "k44_exec.hpp"
+#include "k44_graph.hpp"
+#include "k44_tcff.hpp"
+
+using namespace k44b;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int set_error(const std::string &m) {
+    g_last_error = m;
+    return -1;
+}
+
+struct NativePlan {
+    Executor exec;
+};
+
+struct Handle {
+    WaveGraph graph;
+    std::unique_ptr<NativePlan> gpu;
+    int device = 0;
+    int force_path = -1;
+};
+
+Handle *H(void *p) { return static_cast<Handle *>(p); }
+NativePlan *P(void *p) { return static_cast<NativePlan *>(p); }
+
+bool ensure_compiled(Handle *h) {
+    if (h->graph.compiled) return true;
+    if (!h->graph.compile()) {
+        set_error(h->graph.error);
+        return false;
+    }
+    return true;
+}
+
+int add_linear_common(void *handle, const char *name, const char *in, const char *out, int din, int dout, int act,
+                      std::vector<uint16_t> &&w, const float *bias, const char *res) {
+    Handle *h = H(handle);
+    if (!h) return set_error("null handle");
+    return h->graph.add_linear(name, in, out, din, dout, act, std::move(w), bias, res) ? 0 : set_error(h->graph.error);
+}
+
+int unsupported(void *handle, const char *what) {
+    if (!handle) return set_error("null handle");
+    return set_error(std::string(what) + " is not part of the wave path implemented by this library");
+}
+
+bool desc_to_wave(const k44b_wave_desc *d, HostWave &w, std::string &err) {
+    if (!d) { err = "null wave descriptor"; return false; }
+    if (!d->weights) { err = "wave descriptor has no weights"; return false; }
+    if (!d->idx && !d->run_rows) { err = "wave descriptor has neither an index table nor a run table"; return false; }
+    if (d->cout == 0 || d->group == 0 || d->cout % d->group || d->fan_in == 0 || d->fan_in % 8u || d->cout % 16u) {
+        err = "wave descriptor has inconsistent dimensions";
+        return false;
+    }
+    w.name = d->name ? d->name : "wave";
+    w.cout = d->cout; w.logical_cout = d->logical_cout ? d->logical_cout : d->cout; w.cin = d->cin;
+    w.group = d->group; w.fan_in = d->fan_in; w.fan_in_raw = d->fan_in_raw ? d->fan_in_raw : d->fan_in;
+    w.act = d->act; w.has_residual = d->has_residual != 0; w.has_bias = d->bias != nullptr;
+    w.y_off = d->y_off; w.src_off = d->src_off; w.res_off = d->res_off; w.x_base_off = d->x_base_off;
+    const size_t groups = d->cout / d->group;
+    if (d->idx) w.idx.assign(d->idx, d->idx + groups * d->fan_in);
+    if (d->run_rows) {
+        if (d->run_len == 0 || d->fan_in % d->run_len) { err = "run length must divide the fan-in"; return false; }
+        w.run_len = d->run_len;
+        w.run_rows.assign(d->run_rows, d->run_rows + groups * (d->fan_in / d->run_len));
+    }
+    if (d->weights_on_device) {
+        w.dev_weights_rowmajor = d->weights;
+    } else {
+        w.w_wmma.resize((size_t)d->cout * d->fan_in);
+        rowmajor_to_wmma(d->weights, w.w_wmma.data(), d->cout, d->fan_in);
+    }
+    if (d->bias) w.bias.assign(d->bias, d->bias + d->cout);
+    if (d->cout_map) w.cout_map.assign(d->cout_map, d->cout_map + d->cout);
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---------------------------------------------------------------------------------------------------
+// reference-compatible surface
+// ---------------------------------------------------------------------------------------------------
+void *wavec_create(int max_B_per_wave, int default_S, int kv_cache_max_seq, int fold_rmsnorm_gamma) {
+    Handle *h = new (std::nothrow) Handle();
+    if (!h) return nullptr;
+    h->graph.max_b_per_wave = (uint32_t)std::max(0, max_B_per_wave);
+    h->graph.forced_group = (uint32_t)std::max(0, default_S);
+    h->graph.kv_cache_max_seq = (uint32_t)std::max(0, kv_cache_max_seq);
+    h->graph.fold_rmsnorm_gamma = fold_rmsnorm_gamma != 0;
+    return h;
+}
+
+void wavec_destroy(void *handle) { delete H(handle); }
+
+int wavec_gpu_release(void *handle) {
+    if (!handle) return set_error("null handle");
+    H(handle)->gpu.reset();
+    return 0;
+}
+
+int wavec_add_input(void *handle, const char *name, int c, int h, int w, int is_1d) {
+    if (!handle) return set_error("null handle");
+    return H(handle)->graph.add_input(name, c, h, w, is_1d) ? 0 : set_error(H(handle)->graph.error);
+}
+
+int wavec_add_flatten(void *handle, const char *, const char *, const char *) { return unsupported(handle, "flatten"); }
+
+int wavec_add_conv2d(void *handle, const char *name, const char *in, const char *out, int cin, int cout, int kh, int kw,
+                     int stride, int pad, int act, const float *w_f32, const float *bias_f32, const char *res) {
+    if (kh != 1 || kw != 1 || stride != 1 || pad != 0) return unsupported(handle, "spatial convolution");
+    return wavec_add_linear_f32(handle, name, in, out, cin, cout, act, w_f32, bias_f32, res);
+}
+
+int wavec_add_conv2d_f16(void *handle, const char *name, const char *in, const char *out, int cin, int cout, int kh, int kw,
+                         int stride, int pad, int act, const uint16_t *w_f16, const float *bias_f32, const char *res) {
+    if (kh != 1 || kw != 1 || stride != 1 || pad != 0) return unsupported(handle, "spatial convolution");
+    return wavec_add_linear_f16(handle, name, in, out, cin, cout, act, w_f16, bias_f32, res);
+}
+
+int wavec_add_linear_f32(void *handle, const char *name, const char *in, const char *out, int din, int dout, int act,
+                         const float *w_f32, const float *bias_f32, const char *res) {
+    if (din <= 0 || dout <= 0) return set_error("add_linear: bad dimensions");
+    std::vector<uint16_t> w((size_t)din * dout, 0);
+    if (w_f32) for (size_t i = 0; i < w.size(); ++i) w[i] = float_to_half(w_f32[i]);
+    return add_linear_common(handle, name, in, out, din, dout, act, std::move(w), bias_f32, res);
+}
+
+int wavec_add_linear_f16(void *handle, const char *name, const char *in, const char *out, int din, int dout, int act,
+                         const uint16_t *w_f16, const float *bias_f32, const char *res) {
+    if (din <= 0 || dout <= 0) return set_error("add_linear: bad dimensions");
+    std::vector<uint16_t> w((size_t)din * dout, 0);
+    if (w_f16) std::memcpy(w.data(), w_f16, w.size() * 2);
+    return add_linear_common(handle, name, in, out, din, dout, act, std::move(w), bias_f32, res);
+}
+
+int wavec_add_linear_bf16(void *handle, const char *name, const char *in, const char *out, int din, int dout, int act,
+                          const uint16_t *w_bf16, const float *bias_f32, const char *res) {
+    if (din <= 0 || dout <= 0) return set_error("add_linear: bad dimensions");
+    std::vector<uint16_t> w((size_t)din * dout, 0);
+    if (w_bf16) for (size_t i = 0; i < w.size(); ++i) w[i] = float_to_half(bf16_to_float(w_bf16[i]));
+    return add_linear_common(handle, name, in, out, din, dout, act, std::move(w), bias_f32, res);
+}
+
+int wavec_add_upconv2x2(void *handle, const char *, const char *, const char *, int, int, const float *, const float *) {
+    return unsupported(handle, "transposed convolution");
+}
+int wavec_add_maxpool(void *handle, const char *, const char *, const char *, int, int, int) { return unsupported(handle, "max-pool"); }
+int wavec_add_upsample2x(void *handle, const char *, const char *, const char *) { return unsupported(handle, "upsample"); }
+int wavec_add_rmsnorm(void *handle, const char *, const char *, const char *, int, float, const float *, int) {
+    return unsupported(handle, "RMSNorm");
+}
+int wavec_add_swiglu(void *handle, const char *, const char *, const char *, const char *) { return unsupported(handle, "SwiGLU"); }
+int wavec_add_rope_gqa_attn(void *handle, const char *, const char *, const char *, const char *, const char *, int, int, int,
+                            float, int) {
+    return unsupported(handle, "RoPE / attention");
+}
+
+int wavec_add_split(void *handle, const char *name, const char *in, int n, const char **outs) {
+    if (!handle || n <= 0 || !in || !outs) return set_error("add_split: bad arguments");
+    std::vector<std::string> o(outs, outs + n);
+    return H(handle)->graph.add_topology(GraphNode::SPLIT, name, {in}, o) ? 0 : set_error(H(handle)->graph.error);
+}
+
+int wavec_add_slice(void *handle, const char *name, const char *in, int n, const char **outs, const int *sizes) {
+    if (!handle || n <= 0 || !in || !outs) return set_error("add_slice: bad arguments");
+    std::vector<std::string> o(outs, outs + n);
+    std::vector<uint32_t> sz;
+    if (sizes) for (int i = 0; i < n; ++i) sz.push_back((uint32_t)std::max(0, sizes[i]));
+    return H(handle)->graph.add_topology(GraphNode::SLICE, name, {in}, o, sz) ? 0 : set_error(H(handle)->graph.error);
+}
+
+int wavec_add_concat(void *handle, const char *name, int n, const char **ins, const char *out) {
+    if (!handle || n <= 0 || !ins || !out) return set_error("add_concat: bad arguments");
+    std::vector<std::string> i(ins, ins + n);
+    return H(handle)->graph.add_topology(GraphNode::CONCAT, name, i, {out}) ? 0 : set_error(H(handle)->graph.error);
+}
+
+int wavec_set_output(void *handle, const char *out) {
+    if (!handle || !out) return set_error("set_output: bad arguments");
+    H(handle)->graph.output_tensor = out;
+    H(handle)->graph.compiled = false;
+    return 0;
+}
+
+int wavec_set_reuse_canvas(void *handle, int on) {
+    if (!handle) return set_error("null handle");
+    H(handle)->graph.reuse_canvas = on != 0;
+    H(handle)->graph.compiled = false;
+    return 0;
+}
+
+int wavec_set_batch_size(void *handle, int batch) {
+    if (!handle) return set_error("null handle");
+    H(handle)->graph.batch_size = (uint32_t)std::max(1, batch);
+    H(handle)->graph.compiled = false;
+    return 0;
+}
+
+int wavec_set_target_preset(void *handle, const char *preset) {
+    if (!handle) return set_error("null handle");
+    H(handle)->graph.target = preset_from_name(preset);
+    H(handle)->graph.compiled = false;
+    return 0;
+}
+
+int wavec_compile(void *handle) {
+    if (!handle) return set_error("null handle");
+    return H(handle)->graph.compile() ? 0 : set_error(H(handle)->graph.error);
+}
+
+const char *wavec_get_summary_json(void *handle) {
+    if (!handle || !ensure_compiled(H(handle))) return "{}";
+    return H(handle)->graph.summary_json.c_str();
+}
+
+int wavec_save_tcff_ex(void *handle, const char *path, const char *prefix, int /*include_canvas*/, int include_geometry) {
+    if (!handle || !path) return set_error("save_tcff: bad arguments");
+    if (!ensure_compiled(H(handle))) return -1;
+    std::string err;
+    return tcff_save(H(handle)->graph.plan, path, prefix, include_geometry != 0, err) ? 0 : set_error(err);
+}
+
+int wavec_save_tcff(void *handle, const char *path, const char *prefix) { return wavec_save_tcff_ex(handle, path, prefix, 1, 1); }
+
+int wavec_load_tcff_weights(void *handle, const char *path) {
+    if (!handle || !path) return set_error("load_tcff_weights: bad arguments");
+    if (!ensure_compiled(H(handle))) return -1;
+    std::string err;
+    return tcff_load_into(H(handle)->graph.plan, path, err) ? 0 : set_error(err);
+}
+
+int wavec_gpu_init_plan(void *handle) {
+    Handle *h = H(handle);
+    if (!h) return set_error("null handle");
+    if (!ensure_compiled(h)) return -1;
+    std::unique_ptr<NativePlan> p(new NativePlan());
+    if (!p->exec.init(h->graph.plan, h->device, h->force_path)) return set_error(p->exec.err);
+    h->gpu = std::move(p);
+    return 0;
+}
+
+int wavec_gpu_infer_f32(void *handle, const float *h_in, int in_elems, float *h_out, int out_elems, float *out_gpu_ms) {
+    if (!handle || !h_in || !h_out) return set_error("gpu_infer_f32: bad arguments");
+    Handle *h = H(handle);
+    if (!h->gpu) return set_error("gpu_infer_f32: wavec_gpu_init_plan has not been called");
+    return h->gpu->exec.infer_f32(h_in, in_elems, h_out, out_elems, out_gpu_ms) ? 0 : set_error(h->gpu->exec.err);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// native surface
+// ---------------------------------------------------------------------------------------------------
+void *k44b_plan_create(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t columns, int force_path) {
+    std::unique_ptr<NativePlan> p(new NativePlan());
+    if (!p->exec.begin(device, canvas_elems, pitch, columns, force_path)) {
+        set_error(p->exec.err);
+        return nullptr;
+    }
+    return p.release();
+}
+
+int k44b_plan_add_wave(void *plan, const k44b_wave_desc *wave) {
+    if (!plan) return set_error("null plan");
+    HostWave w;
+    std::string err;
+    if (!desc_to_wave(wave, w, err)) return set_error(err);
+    return P(plan)->exec.add_wave(w) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_plan_set_io(void *plan, uint64_t input_off, uint32_t input_c, uint64_t output_off, uint32_t output_c, uint32_t width) {
+    if (!plan) return set_error("null plan");
+    Executor &e = P(plan)->exec;
+    if (input_off + (uint64_t)input_c * e.pitch() > e.canvas_elems() || output_off + (uint64_t)output_c * e.pitch() > e.canvas_elems() ||
+        width > e.pitch())
+        return set_error("input / output region leaves the canvas");
+    e.set_io(input_off, input_c, output_off, output_c, width);
+    return 0;
+}
+
+void *k44b_plan_from_tcff(const char *path, uint32_t pitch_hint, int device, int force_path) {
+    if (!path) { set_error("null path"); return nullptr; }
+    HostPlan hp;
+    std::string err;
+    if (!tcff_to_plan(path, pitch_hint, hp, err)) { set_error(err); return nullptr; }
+    std::unique_ptr<NativePlan> p(new NativePlan());
+    if (!p->exec.init(hp, device, force_path)) { set_error(p->exec.err); return nullptr; }
+    return p.release();
+}
+
+void k44b_plan_destroy(void *plan) { delete P(plan); }
+
+void *k44b_canvas_ptr(void *plan) { return plan ? (void *)P(plan)->exec.canvas() : nullptr; }
+uint64_t k44b_canvas_elems(void *plan) { return plan ? P(plan)->exec.canvas_elems() : 0; }
+int k44b_num_waves(void *plan) { return plan ? (int)P(plan)->exec.num_waves() : -1; }
+
+int k44b_wave_info(void *plan, int wave, k44b_wave_info_t *out) {
+    if (!plan || !out || wave < 0 || (size_t)wave >= P(plan)->exec.num_waves()) return set_error("wave_info: bad arguments");
+    const DeviceWave &w = P(plan)->exec.wave((size_t)wave);
+    out->cout = w.args.cout; out->group = w.args.group; out->fan_in = w.args.fan_in;
+    out->box_rows = w.args.gather_mode == GATHER_BOX ? w.args.box_h : 0;
+    out->path = w.path; out->n_tile = w.path == PATH_UMMA ? w.desc.n_tile : 64;
+    out->synapses = w.synapses; out->weight_bytes = w.weight_bytes;
+    return 0;
+}
+
+int k44b_execute(void *plan, void *stream) {
+    if (!plan) return set_error("null plan");
+    return P(plan)->exec.execute((cudaStream_t)stream) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_execute_wave(void *plan, int wave, void *stream) {
+    if (!plan || wave < 0) return set_error("execute_wave: bad arguments");
+    return P(plan)->exec.execute_wave((size_t)wave, (cudaStream_t)stream) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_infer_f16(void *plan, const uint16_t *h_in, uint16_t *h_out, float *out_gpu_ms, void *stream) {
+    if (!plan) return set_error("null plan");
+    return P(plan)->exec.infer_f16(h_in, h_out, out_gpu_ms, (cudaStream_t)stream) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_status(void *plan, uint32_t *status) {
+    if (!plan) return set_error("null plan");
+    uint32_t st = 0;
+    if (!P(plan)->exec.read_status(&st)) return set_error(P(plan)->exec.err);
+    if (status) *status = st;
+    return st == 0 ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, int out_elems, float *out_gpu_ms) {
+    if (!plan || !h_in || !h_out) return set_error("infer_f32: bad arguments");
+    return P(plan)->exec.infer_f32(h_in, in_elems, h_out, out_elems, out_gpu_ms) ? 0 : set_error(P(plan)->exec.err);
+}
+
+uint64_t k44b_launch_count(void *plan) { return plan ? P(plan)->exec.launches() : 0; }
+
+int k44b_wave_weights_rowmajor(void *plan, int wave, void *d_dst) {
+    if (!plan || !d_dst || wave < 0) return set_error("wave_weights_rowmajor: bad arguments");
+    return P(plan)->exec.weights_to_rowmajor((size_t)wave, d_dst) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_set_device(void *handle, int device) {
+    if (!handle || device < 0) return set_error("set_device: bad arguments");
+    H(handle)->device = device;
+    return 0;
+}
+
+int k44b_set_force_path(void *handle, int force_path) {
+    if (!handle) return set_error("null handle");
+    H(handle)->force_path = force_path;
+    return 0;
+}
+
+void *k44b_handle_plan(void *handle) { return handle ? (void *)H(handle)->gpu.get() : nullptr; }
+
+const char *k44b_last_error(void) { return g_last_error.c_str(); }
+const char *k44b_version(void) { return "k44b 0.1 (sm_100a)"; }
+
+int k44b_fill_normal_f16(void *d_dst, uint64_t n, uint64_t seed, float scale, void *stream) {
+    if (!d_dst) return set_error("fill_normal_f16: null pointer");
+    const cudaError_t e = launch_fill_normal_f16((__half *)d_dst, n, seed, scale, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : set_error(std::string("fill_normal_f16: ") + cudaGetErrorString(e));
+}
+
+uint64_t k44b_fnv1a64(const uint8_t *data, uint64_t len) { return fnv1a64(data, (size_t)len); }
+
+void k44b_f32_to_f16(const float *src, uint16_t *dst, uint64_t n) {
+    for (uint64_t i = 0; i < n; ++i) dst[i] = float_to_half(src[i]);
+}
+
+void k44b_rowmajor_to_wmma(const uint16_t *src, uint16_t *dst, uint32_t cout, uint32_t fan_in) { rowmajor_to_wmma(src, dst, cout, fan_in); }
+void k44b_wmma_to_rowmajor(const uint16_t *src, uint16_t *dst, uint32_t cout, uint32_t fan_in) { wmma_to_rowmajor(src, dst, cout, fan_in); }
+
+int k44b_analyze_gather(const k44b_wave_desc *wave, uint32_t pitch, uint64_t canvas_elems, uint32_t *out_box_rows, uint64_t capacity,
+                        uint64_t *out_count) {
+    if (!wave || pitch == 0) return set_error("analyze_gather: bad arguments");
+    HostWave w;
+    w.cout = wave->cout; w.group = wave->group; w.fan_in = wave->fan_in;
+    w.fan_in_raw = wave->fan_in_raw ? wave->fan_in_raw : wave->fan_in;
+    w.x_base_off = wave->x_base_off;
+    if (w.cout == 0 || w.group == 0 || w.cout % w.group || w.fan_in == 0) return set_error("analyze_gather: inconsistent dimensions");
+    const size_t groups = w.cout / w.group;
+    if (wave->idx) w.idx.assign(wave->idx, wave->idx + groups * w.fan_in);
+    else if (wave->run_rows && wave->run_len && w.fan_in % wave->run_len == 0) {
+        w.run_len = wave->run_len;
+        w.run_rows.assign(wave->run_rows, wave->run_rows + groups * (w.fan_in / wave->run_len));
+    } else return set_error("analyze_gather: no gather table");
+    const GatherPlan gp = analyze_gather(w, pitch, canvas_elems);
+    if (out_count) *out_count = gp.box_rows.size();
+    if (!gp.box_ok) { g_last_error = gp.why_not; return 0; }
+    if (out_box_rows) std::memcpy(out_box_rows, gp.box_rows.data(), std::min<uint64_t>(capacity, gp.box_rows.size()) * 4);
+    return (int)gp.box_h;
+}
+
+}  // extern "C"

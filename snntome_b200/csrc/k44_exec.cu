@@ -1,0 +1,433 @@
+// Plan -> device packer and wave scheduler (see k44_exec.hpp).
+#include "k44_exec.hpp"
+
+#include <cstdlib>
+
+namespace k44b {
+
+const char *status_string(uint32_t st) {
+    if (st == 0) return "ok";
+    if (st & ST_BAD_INDEX) return "gather offset outside the canvas";
+    if (st & ST_TIMEOUT_DRAIN) return "timed out draining in-flight copies";
+    if (st & ST_TIMEOUT_PRODUCER) return "producer timed out waiting for a free stage";
+    if (st & ST_TIMEOUT_MMA) return "MMA issuer timed out waiting for operands";
+    if (st & ST_TIMEOUT_EPILOGUE) return "epilogue timed out waiting for an accumulator";
+    return "unknown kernel status";
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host analysis
+// ---------------------------------------------------------------------------------------------------
+bool validate_wave(const HostWave &w, uint32_t pitch, uint32_t num_tiles, uint64_t canvas_elems, std::string &err) {
+    auto bad = [&](const std::string &m) { err = "wave '" + w.name + "': " + m; return false; };
+    if (w.cout == 0 || w.cout % 16u) return bad("row count must be a positive multiple of 16");
+    if (w.group == 0 || w.cout % w.group) return bad("group size must divide the row count");
+    if (w.fan_in == 0 || w.fan_in % 8u) return bad("fan-in must be a positive multiple of 8");
+    if (w.fan_in_raw > w.fan_in) return bad("raw fan-in exceeds the padded fan-in");
+    if (pitch == 0 || pitch % 64u || num_tiles * 64u != pitch) return bad("row pitch must be a multiple of 64");
+    if (w.y_off % 8u || w.res_off % 8u) return bad("output / residual offsets must be multiples of 8 elements");
+    if (w.y_off + (uint64_t)w.cout * pitch > canvas_elems) return bad("output rows leave the canvas");
+    if (w.has_residual && w.res_off + (uint64_t)w.cout * pitch > canvas_elems) return bad("residual rows leave the canvas");
+    const uint32_t groups = w.cout / w.group;
+    if (!w.run_rows.empty()) {
+        if (w.run_len == 0 || w.fan_in % w.run_len) return bad("run length must divide the fan-in");
+        if (w.run_rows.size() != (size_t)groups * (w.fan_in / w.run_len)) return bad("run table has the wrong size");
+        const uint64_t rows = canvas_elems / pitch;
+        for (uint32_t r : w.run_rows)
+            if ((uint64_t)r + w.run_len > rows) return bad("a run leaves the canvas");
+    } else {
+        if (w.idx.size() != (size_t)groups * w.fan_in) return bad("gather table has the wrong size");
+        uint32_t mx = 0;
+        for (uint32_t v : w.idx) mx = std::max(mx, v);
+        if (w.x_base_off + (uint64_t)mx + pitch > canvas_elems) return bad("a gather offset leaves the canvas");
+    }
+    if (!w.bias.empty() && w.bias.size() != w.cout) return bad("bias has the wrong size");
+    if (!w.cout_map.empty()) {
+        if (w.cout_map.size() != w.cout) return bad("row map has the wrong size");
+        for (uint16_t m : w.cout_map)
+            if (w.y_off + ((uint64_t)m + 1) * pitch > canvas_elems) return bad("row map target leaves the canvas");
+    }
+    if (w.act < 0 || w.act > ACT_GELU) return bad("unknown activation");
+    return true;
+}
+
+GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_elems) {
+    GatherPlan gp;
+    const uint32_t groups = w.cout / w.group;
+    const uint64_t total_rows = canvas_elems / pitch;
+    if (!(w.group % kTileM == 0u || groups == 1u)) {
+        gp.why_not = "group size is not a multiple of 128 neurons";
+        return gp;
+    }
+    struct Run { uint32_t row, len; };
+    std::vector<std::vector<Run>> runs(groups);
+    if (!w.run_rows.empty()) {
+        const uint32_t per = w.fan_in / w.run_len;
+        for (uint32_t g = 0; g < groups; ++g)
+            for (uint32_t r = 0; r < per; ++r) runs[g].push_back({w.run_rows[(size_t)g * per + r], w.run_len});
+    } else {
+        for (uint32_t g = 0; g < groups; ++g) {
+            const uint32_t *row_idx = w.idx.data() + (size_t)g * w.fan_in;
+            auto &rg = runs[g];
+            for (uint32_t s = 0; s < w.fan_in; ++s) {
+                uint64_t row;
+                if (s < w.fan_in_raw) {
+                    const uint64_t e = w.x_base_off + row_idx[s];
+                    if (e % pitch) { gp.why_not = "gather offsets are not row aligned (token / pixel shift)"; return gp; }
+                    row = e / pitch;
+                } else {
+                    // zero-weight padding slot: free to continue the previous run while it stays inside the canvas
+                    row = (!rg.empty() && (uint64_t)rg.back().row + rg.back().len < total_rows) ? (uint64_t)rg.back().row + rg.back().len : 0;
+                }
+                if (!rg.empty() && (uint64_t)rg.back().row + rg.back().len == row) ++rg.back().len;
+                else rg.push_back({(uint32_t)row, 1u});
+            }
+        }
+    }
+    uint32_t h = 64;
+    for (auto &rg : runs)
+        for (auto &r : rg)
+            while (h >= 8 && r.len % h) h >>= 1;
+    const uint32_t tail = (kStageK - w.fan_in % kStageK) % kStageK;
+    while (h >= 8 && tail % h) h >>= 1;
+    if (h < 8) { gp.why_not = "runs are not made of whole 8-row blocks"; return gp; }
+    gp.box_h = h;
+    gp.boxes_per_group = (w.fan_in + tail) / h;
+    gp.box_rows.reserve((size_t)groups * gp.boxes_per_group);
+    for (auto &rg : runs) {
+        for (auto &r : rg)
+            for (uint32_t o = 0; o < r.len; o += h) gp.box_rows.push_back(r.row + o);
+        for (uint32_t o = 0; o < tail; o += h) gp.box_rows.push_back(0u);
+    }
+    for (uint32_t r : gp.box_rows)
+        if ((uint64_t)r + h > total_rows) { gp.why_not = "a run leaves the canvas"; gp.box_rows.clear(); return gp; }
+    gp.box_ok = true;
+    return gp;
+}
+
+// tcgen05 shared-memory operand descriptors (64-bit): start address >> 4 in bits 0-13, leading-dimension
+// byte offset >> 4 in bits 16-29, stride-dimension byte offset >> 4 in bits 32-45, descriptor version 1 in
+// bits 46-47, layout type in bits 61-63 (2 = 128-byte swizzle).
+static uint64_t smem_desc_bits(uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+    return ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) | ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) |
+           ((uint64_t)layout << 61);
+}
+
+UmmaDesc make_umma_desc(uint32_t n_tile, int variant) {
+    UmmaDesc d;
+    d.n_tile = n_tile;
+    // A = weights, K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart; a K=16 step
+    // moves 32 bytes along the row.
+    d.a_base = smem_desc_bits(16, 1024, 2);
+    d.a_k_step = 32 >> 4;
+    // B = substrate tile, MN-major (columns contiguous), 128-byte swizzle: each synapse row is 128 bytes (64
+    // columns); 8-row groups 1024 bytes apart (stride dimension = K); further 64-column blocks 8 KiB apart
+    // (leading dimension = N). A K=16 step moves 16 rows = 2048 bytes.
+    d.b_base = (variant == 1) ? smem_desc_bits(1024, kStageK * 128u, 2) : smem_desc_bits(kStageK * 128u, 1024, 2);
+    d.b_k_step = 2048 >> 4;
+    // instruction descriptor: FP32 accumulate (bit 4), A/B FP16 (0), A K-major (bit 15 = 0), B MN-major
+    // (bit 16 = 1), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+    d.idesc = (1u << 4) | (1u << 16) | ((n_tile >> 3) << 17) | ((kTileM >> 4) << 24);
+    d.wait_cycles = 4000000000ull;     // about two seconds at boost clock
+    return d;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// executor
+// ---------------------------------------------------------------------------------------------------
+bool Executor::check(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return true;
+    err = std::string(what) + ": " + cudaGetErrorString(e);
+    return false;
+}
+
+void Executor::release() {
+    if (device_ >= 0) cudaSetDevice(device_);
+    for (auto &w : waves_) {
+        cudaFree(w.d_weights); cudaFree(w.d_gather); cudaFree(w.d_bias); cudaFree(w.d_map); cudaFree(w.d_idx_table);
+    }
+    waves_.clear();
+    cudaFree(canvas_); canvas_ = nullptr;
+    cudaFree(d_status_); d_status_ = nullptr;
+    cudaFree(d_in_f32_); d_in_f32_ = nullptr;
+    cudaFree(d_out_f32_); d_out_f32_ = nullptr;
+    if (ev0_) { cudaEventDestroy(ev0_); ev0_ = nullptr; }
+    if (ev1_) { cudaEventDestroy(ev1_); ev1_ = nullptr; }
+    canvas_elems_ = 0;
+}
+
+bool Executor::begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t columns, int force_path) {
+    release();
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) return fail("no CUDA device: this library has no CPU path");
+    if (device < 0 || device >= count) return fail("device ordinal out of range");
+    if (!check(cudaSetDevice(device), "cudaSetDevice")) return false;
+    cudaDeviceProp prop{};
+    if (!check(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties")) return false;
+    if (prop.major != 10) return fail(std::string("device '") + prop.name + "' is not sm_100: kernels are built for B200 only");
+    device_ = device;
+    num_sms_ = prop.multiProcessorCount;
+    force_path_ = force_path;
+    if (const char *e = std::getenv("K44B_FORCE_PATH")) {
+        if (!std::strcmp(e, "fma")) force_path_ = 0;
+        else if (!std::strcmp(e, "umma")) force_path_ = 1;
+    }
+    if (pitch == 0 || pitch % 64u) return fail("row pitch must be a multiple of 64");
+    if (canvas_elems == 0 || canvas_elems % 8u) return fail("canvas size must be a positive multiple of 8 elements");
+    pitch_ = pitch; columns_ = columns ? columns : pitch; canvas_elems_ = canvas_elems;
+    if (!check(cudaMalloc(&canvas_, canvas_elems * sizeof(__half)), "canvas allocation")) { canvas_ = nullptr; return false; }
+    if (!check(cudaMemset(canvas_, 0, canvas_elems * sizeof(__half)), "canvas clear")) return false;
+    if (!check(cudaMalloc(&d_status_, 256), "status allocation")) return false;
+    if (!check(cudaMemset(d_status_, 0, 256), "status clear")) return false;
+    if (!check(cudaEventCreate(&ev0_), "event") || !check(cudaEventCreate(&ev1_), "event")) return false;
+    if (!check(umma_kernel_setup(), "kernel attribute setup")) return false;
+    return true;
+}
+
+bool Executor::make_tensor_map(DeviceWave &dw) {
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn)
+            return fail("cuTensorMapEncodeTiled is not available from the driver");
+        encode = (EncodeFn)fn;
+    }
+    const cuuint64_t dims[2] = {pitch_, canvas_elems_ / pitch_};
+    const cuuint64_t strides[1] = {(cuuint64_t)pitch_ * 2u};
+    const cuuint32_t box[2] = {64u, dw.args.box_h};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = encode(&dw.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, canvas_, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return true;
+}
+
+bool Executor::add_wave(const HostWave &w) {
+    if (!ready()) return fail("executor not initialised");
+    if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
+    const uint32_t tiles64 = pitch_ / 64u;
+    if (!validate_wave(w, pitch_, tiles64, canvas_elems_, err)) return false;
+    if (w.w_wmma.empty() && !w.dev_weights_rowmajor) return fail("wave '" + w.name + "' has no weights");
+    if (!w.w_wmma.empty() && w.w_wmma.size() != (size_t)w.cout * w.fan_in) return fail("wave '" + w.name + "': weight block has the wrong size");
+    // padding slots must carry zero weights (the packer is free to point them at any row)
+    if (!w.w_wmma.empty() && w.fan_in_raw < w.fan_in) {
+        for (uint32_t j = 0; j < w.cout; ++j)
+            for (uint32_t s = w.fan_in_raw; s < w.fan_in; ++s)
+                if (w.w_wmma[wmma_vec_index(j, s >> 3, w.fan_in) * 8u + (s & 7u)] & 0x7fffu)
+                    return fail("wave '" + w.name + "': non-zero weight in a padding slot");
+    }
+
+    DeviceWave dw;
+    dw.name = w.name;
+    dw.synapses = (uint64_t)w.logical_cout * w.fan_in_raw;
+    WaveArgs &a = dw.args;
+    a.canvas = canvas_; a.canvas_elems = canvas_elems_; a.status = d_status_;
+    a.y_off = w.y_off; a.res_off = w.res_off; a.x_base_off = w.x_base_off;
+    a.cout = w.cout; a.group = w.group; a.fan_in = w.fan_in;
+    a.num_kstages = (w.fan_in + kStageK - 1) / kStageK;
+    a.pitch = pitch_; a.num_col_tiles64 = tiles64;
+    a.act = w.act; a.has_residual = w.has_residual ? 1 : 0;
+    const uint32_t groups = w.cout / w.group;
+    a.mtiles_per_group = groups == 1 ? (w.cout + kTileM - 1) / kTileM : std::max(1u, w.group / kTileM);
+
+    // ---- weights: container order or device row-major -> tiled ----
+    const uint32_t mtiles = (w.cout + kTileM - 1) / kTileM;
+    dw.weight_bytes = (uint64_t)mtiles * a.num_kstages * kStageWBytes;
+    if (!check(cudaMalloc(&dw.d_weights, dw.weight_bytes), "weight allocation")) return false;
+    bool ok = true;
+    if (w.dev_weights_rowmajor) {
+        ok = check(launch_repack_rowmajor_to_tiled((const uint4 *)w.dev_weights_rowmajor, (uint4 *)dw.d_weights, w.cout, w.fan_in, nullptr), "weight repack") &&
+             check(cudaDeviceSynchronize(), "weight repack");   // the caller may reuse its buffer on return
+    } else {
+        void *stage = nullptr;
+        const size_t bytes = w.w_wmma.size() * 2;
+        ok = check(cudaMalloc(&stage, bytes), "staging allocation") &&
+             check(cudaMemcpy(stage, w.w_wmma.data(), bytes, cudaMemcpyHostToDevice), "weight upload") &&
+             check(launch_repack_wmma_to_tiled((const uint4 *)stage, (uint4 *)dw.d_weights, w.cout, w.fan_in, nullptr), "weight repack") &&
+             check(cudaDeviceSynchronize(), "weight repack");
+        cudaFree(stage);
+    }
+    a.w_tiles = (const uint4 *)dw.d_weights;
+
+    // ---- gather tables ----
+    GatherPlan gp;
+    if (ok) gp = analyze_gather(w, pitch_, canvas_elems_);
+    if (ok && gp.box_ok) {
+        const size_t bytes = gp.box_rows.size() * 4;
+        ok = check(cudaMalloc(&dw.d_gather, bytes), "run table allocation") &&
+             check(cudaMemcpy(dw.d_gather, gp.box_rows.data(), bytes, cudaMemcpyHostToDevice), "run table upload");
+        a.gather = (const uint32_t *)dw.d_gather;
+        a.gather_mode = GATHER_BOX;
+        a.box_h = gp.box_h; a.boxes_per_group = gp.boxes_per_group;
+        a.x_base_off = 0;                 // box rows are absolute canvas rows
+        dw.umma_capable = true;
+    } else if (ok) {
+        dw.fma_reason = gp.why_not;
+        if (w.idx.empty()) { ok = fail("wave '" + w.name + "': run table unusable (" + gp.why_not + ") and no index table given"); }
+        else {
+            const size_t bytes = w.idx.size() * 4;
+            ok = check(cudaMalloc(&dw.d_gather, bytes), "index table allocation") &&
+                 check(cudaMemcpy(dw.d_gather, w.idx.data(), bytes, cudaMemcpyHostToDevice), "index table upload");
+            a.gather = (const uint32_t *)dw.d_gather;
+            a.gather_mode = GATHER_IDX;
+        }
+    }
+    if (ok && !w.bias.empty() && w.has_bias) {
+        ok = check(cudaMalloc(&dw.d_bias, w.bias.size() * 2), "bias allocation") &&
+             check(cudaMemcpy(dw.d_bias, w.bias.data(), w.bias.size() * 2, cudaMemcpyHostToDevice), "bias upload");
+        a.bias = (const __half *)dw.d_bias;
+    }
+    if (ok && !w.cout_map.empty()) {
+        ok = check(cudaMalloc(&dw.d_map, w.cout_map.size() * 2), "row map allocation") &&
+             check(cudaMemcpy(dw.d_map, w.cout_map.data(), w.cout_map.size() * 2, cudaMemcpyHostToDevice), "row map upload");
+        a.cout_map = (const uint16_t *)dw.d_map;
+    }
+    // ---- path and tile shape ----
+    if (ok) {
+        dw.path = (dw.umma_capable && force_path_ != 0) ? PATH_UMMA : PATH_FMA;
+        if (dw.path == PATH_UMMA) {
+            uint32_t n_tile = 64;
+            for (uint32_t cand : {256u, 128u})
+                if (tiles64 % (cand / 64u) == 0u && (uint64_t)mtiles * (tiles64 / (cand / 64u)) >= (uint64_t)num_sms_) { n_tile = cand; break; }
+            if (const char *e = std::getenv("K44B_N_TILE")) {
+                const uint32_t v = (uint32_t)std::atoi(e);
+                if ((v == 64 || v == 128 || v == 256) && tiles64 % (v / 64u) == 0u) n_tile = v;
+            }
+            int variant = 0;
+            if (const char *e = std::getenv("K44B_UMMA_VARIANT")) variant = std::atoi(e);
+            dw.desc = make_umma_desc(n_tile, variant);
+            ok = make_tensor_map(dw);
+        }
+    }
+    if (!ok) {
+        cudaFree(dw.d_weights); cudaFree(dw.d_gather); cudaFree(dw.d_bias); cudaFree(dw.d_map);
+        return false;
+    }
+    waves_.push_back(dw);
+    return true;
+}
+
+void Executor::set_io(uint64_t in_off, uint32_t in_c, uint64_t out_off, uint32_t out_c, uint32_t width) {
+    in_off_ = in_off; in_c_ = in_c; out_off_ = out_off; out_c_ = out_c; io_width_ = width;
+}
+
+bool Executor::init(const HostPlan &plan, int device, int force_path) {
+    if (!begin(device, plan.canvas_elems, plan.layout.channel_stride, plan.layout.width, force_path)) return false;
+    for (const auto &w : plan.waves)
+        if (!add_wave(w)) { std::string keep = err; release(); err = keep; return false; }
+    set_io(plan.input_off, plan.input_c, plan.output_off, plan.logical_output_c ? plan.logical_output_c : plan.output_c, plan.layout.width);
+    if ((uint64_t)in_off_ + (uint64_t)in_c_ * pitch_ > canvas_elems_ || (uint64_t)out_off_ + (uint64_t)out_c_ * pitch_ > canvas_elems_) {
+        release();
+        return fail("plan input / output region leaves the canvas");
+    }
+    return true;
+}
+
+bool Executor::execute(cudaStream_t stream) {
+    if (!ready()) return fail("executor not initialised");
+    for (auto &w : waves_) {
+        const cudaError_t e = (w.path == PATH_UMMA) ? launch_wave_umma(w.args, w.desc, w.tmap, num_sms_, stream)
+                                                    : launch_wave_fma(w.args, stream);
+        ++launches_;
+        if (e != cudaSuccess) return check(e, ("launch of wave '" + w.name + "'").c_str());
+    }
+    return true;
+}
+
+bool Executor::execute_wave(size_t i, cudaStream_t stream) {
+    if (!ready()) return fail("executor not initialised");
+    if (i >= waves_.size()) return fail("wave index out of range");
+    DeviceWave &w = waves_[i];
+    const cudaError_t e = (w.path == PATH_UMMA) ? launch_wave_umma(w.args, w.desc, w.tmap, num_sms_, stream)
+                                                : launch_wave_fma(w.args, stream);
+    ++launches_;
+    return check(e, ("launch of wave '" + w.name + "'").c_str());
+}
+
+// Host FP16 in / out without any conversion: the input rows are copied straight into the canvas and the
+// output rows straight out of it (both in canvas layout, `pitch` elements per row). With pinned host
+// buffers the copies are asynchronous on `stream`; the call returns after the output has arrived.
+bool Executor::infer_f16(const uint16_t *h_in, uint16_t *h_out, float *gpu_ms, cudaStream_t stream) {
+    if (!ready()) return fail("executor not initialised");
+    if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
+    const size_t in_b = (size_t)in_c_ * pitch_ * 2, out_b = (size_t)out_c_ * pitch_ * 2;
+    if (h_in && in_b && !check(cudaMemcpyAsync(canvas_ + in_off_, h_in, in_b, cudaMemcpyHostToDevice, stream), "input upload")) return false;
+    if (!check(cudaEventRecord(ev0_, stream), "event record")) return false;
+    if (!execute(stream)) return false;
+    if (!check(cudaEventRecord(ev1_, stream), "event record")) return false;
+    if (h_out && out_b && !check(cudaMemcpyAsync(h_out, canvas_ + out_off_, out_b, cudaMemcpyDeviceToHost, stream), "output download")) return false;
+    if (!check(cudaStreamSynchronize(stream), "wave execution")) return false;
+    float t = 0.f;
+    cudaEventElapsedTime(&t, ev0_, ev1_);
+    if (gpu_ms) *gpu_ms = t;
+    uint32_t st = 0;
+    if (!check(cudaMemcpy(&st, d_status_, 4, cudaMemcpyDeviceToHost), "status read")) return false;
+    if (st) { cudaMemset(d_status_, 0, 4); return fail(std::string("kernel status: ") + status_string(st)); }
+    return true;
+}
+
+bool Executor::read_status(uint32_t *status) {
+    if (!ready()) return fail("executor not initialised");
+    uint32_t st = 0;
+    if (!check(cudaSetDevice(device_), "cudaSetDevice") || !check(cudaDeviceSynchronize(), "synchronise") ||
+        !check(cudaMemcpy(&st, d_status_, 4, cudaMemcpyDeviceToHost), "status read"))
+        return false;
+    if (status) *status = st;
+    if (st) { cudaMemset(d_status_, 0, 4); err = std::string("kernel status: ") + status_string(st); }
+    return true;
+}
+
+bool Executor::execute_timed(float *ms) {
+    if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
+    if (!check(cudaEventRecord(ev0_, nullptr), "event record")) return false;
+    if (!execute(nullptr)) return false;
+    if (!check(cudaEventRecord(ev1_, nullptr), "event record") || !check(cudaEventSynchronize(ev1_), "wave execution")) return false;
+    float t = 0.f;
+    cudaEventElapsedTime(&t, ev0_, ev1_);
+    if (ms) *ms = t;
+    uint32_t st = 0;
+    if (!read_status(&st)) return false;
+    return st == 0;
+}
+
+// Host FP32 in / out, the contract of the reference's infer_f32 (wavec/k44_wave_executor.cu:599-618):
+// input is dense [C][W] FP32, converted to FP16 RTE into the padded input rows; gpu_ms covers the waves
+// only; at most out_elems values are copied back. The FP32<->FP16 layout conversion runs on the device.
+bool Executor::infer_f32(const float *h_in, int in_elems, float *h_out, int out_elems, float *gpu_ms) {
+    if (!ready()) return fail("executor not initialised");
+    if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
+    const size_t in_n = (size_t)in_c_ * io_width_, out_n = (size_t)out_c_ * io_width_;
+    if (in_elems < 0 || (size_t)in_elems < in_n) return fail("input has fewer elements than the plan's input tensor");
+    if (!d_in_f32_ && !check(cudaMalloc(&d_in_f32_, std::max<size_t>(in_n, 1) * 4), "input staging")) return false;
+    if (!d_out_f32_ && !check(cudaMalloc(&d_out_f32_, std::max<size_t>(out_n, 1) * 4), "output staging")) return false;
+    if (!check(cudaMemcpyAsync(d_in_f32_, h_in, in_n * 4, cudaMemcpyHostToDevice, nullptr), "input upload")) return false;
+    if (!check(launch_f32_to_canvas(d_in_f32_, canvas_ + in_off_, in_c_, io_width_, pitch_, nullptr), "input conversion")) return false;
+    ++launches_;
+    if (!check(cudaEventRecord(ev0_, nullptr), "event record")) return false;
+    if (!execute(nullptr)) return false;
+    if (!check(cudaEventRecord(ev1_, nullptr), "event record")) return false;
+    if (!check(launch_canvas_to_f32(canvas_ + out_off_, d_out_f32_, out_c_, io_width_, pitch_, nullptr), "output conversion")) return false;
+    ++launches_;
+    const size_t copy_n = std::min((size_t)std::max(out_elems, 0), out_n);
+    if (!check(cudaMemcpy(h_out, d_out_f32_, copy_n * 4, cudaMemcpyDeviceToHost), "output download")) return false;
+    float t = 0.f;
+    cudaEventElapsedTime(&t, ev0_, ev1_);
+    if (gpu_ms) *gpu_ms = t;
+    uint32_t st = 0;
+    if (!read_status(&st)) return false;
+    return st == 0;
+}
+
+bool Executor::weights_to_rowmajor(size_t wave, void *d_dst) {
+    if (wave >= waves_.size()) return fail("wave index out of range");
+    const auto &w = waves_[wave];
+    return check(launch_tiled_to_rowmajor((const uint4 *)w.d_weights, (uint4 *)d_dst, w.args.cout, w.args.fan_in, nullptr), "weight unpack") &&
+           check(cudaDeviceSynchronize(), "weight unpack");
+}
+
+}  // namespace k44b

@@ -1,0 +1,93 @@
+// Wave executor: owns the device copy of a plan (packed weights, gather tables, canvas) and runs the
+// wave list. Counterpart of the reference's K44GpuExecutorState (wavec/k44_wave_executor.cu:265-619)
+// with three differences that matter to callers: no call ever terminates the process (errors are
+// returned with a message), execution can be queued on a caller-supplied stream, and the canvas can
+// be reached as a device pointer so that inputs and outputs need not travel through host FP32.
+#pragma once
+#include <string>
+#include <vector>
+
+#include "k44_host.hpp"
+#include "k44_kernels.cuh"
+
+namespace k44b {
+
+// Gather description derived from a wave's index table (or given directly as runs).
+struct GatherPlan {
+    bool box_ok = false;                 // every run is made of whole boxes of `box_h` rows
+    uint32_t box_h = 0;                  // 8, 16, 32 or 64
+    uint32_t boxes_per_group = 0;        // == 64/box_h * ceil(fan_in/64)
+    std::vector<uint32_t> box_rows;      // [groups][boxes_per_group] canvas row numbers
+    std::string why_not;                 // reason the tensor-core path cannot be used
+};
+
+// Pure host analysis (unit-testable without a device).
+GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_elems);
+bool validate_wave(const HostWave &w, uint32_t pitch, uint32_t num_tiles, uint64_t canvas_elems, std::string &err);
+UmmaDesc make_umma_desc(uint32_t n_tile, int variant);
+
+struct DeviceWave {
+    std::string name;
+    WaveArgs args;
+    UmmaDesc desc;
+    CUtensorMap tmap;
+    int path = PATH_FMA;
+    bool umma_capable = false;
+    std::string fma_reason;
+    void *d_weights = nullptr, *d_gather = nullptr, *d_bias = nullptr, *d_map = nullptr;
+    uint32_t *d_idx_table = nullptr;     // expanded table kept for the FMA path when boxes are used too
+    uint64_t synapses = 0;               // logical_cout * fan_in_raw
+    uint64_t weight_bytes = 0;
+};
+
+class Executor {
+  public:
+    ~Executor() { release(); }
+    std::string err;
+
+    // force_path: -1 choose per wave, 0 always FMA, 1 tensor cores wherever the gather allows
+    bool begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t columns, int force_path);
+    bool add_wave(const HostWave &w);
+    void set_io(uint64_t in_off, uint32_t in_c, uint64_t out_off, uint32_t out_c, uint32_t width);
+    bool init(const HostPlan &plan, int device, int force_path);   // begin + add_wave* + set_io
+    void release();
+
+    bool execute(cudaStream_t stream);                             // queue every wave; no sync
+    bool execute_wave(size_t wave, cudaStream_t stream);          // queue one wave; no sync
+    // host FP16 rows in canvas layout ([input_c][pitch] in, [output_c][pitch] out), copies on `stream`
+    bool infer_f16(const uint16_t *h_in, uint16_t *h_out, float *gpu_ms, cudaStream_t stream);
+    bool execute_timed(float *ms);                                 // default stream, event-timed, synchronous
+    bool infer_f32(const float *h_in, int in_elems, float *h_out, int out_elems, float *gpu_ms);
+    bool read_status(uint32_t *status);                            // synchronises the device
+    bool weights_to_rowmajor(size_t wave, void *d_dst);            // unpack check: tiled -> [cout][fan_in]
+
+    bool ready() const { return canvas_ != nullptr; }
+    __half *canvas() const { return canvas_; }
+    uint64_t canvas_elems() const { return canvas_elems_; }
+    size_t num_waves() const { return waves_.size(); }
+    const DeviceWave &wave(size_t i) const { return waves_[i]; }
+    int device() const { return device_; }
+    uint32_t pitch() const { return pitch_; }
+    uint64_t launches() const { return launches_; }
+
+  private:
+    bool fail(const std::string &m) { err = m; return false; }
+    bool check(cudaError_t e, const char *what);
+    bool make_tensor_map(DeviceWave &dw);
+
+    int device_ = -1, num_sms_ = 148, force_path_ = -1;
+    __half *canvas_ = nullptr;
+    uint64_t canvas_elems_ = 0;
+    uint32_t pitch_ = 0, columns_ = 0;
+    uint32_t *d_status_ = nullptr;
+    std::vector<DeviceWave> waves_;
+    uint64_t in_off_ = 0, out_off_ = 0;
+    uint32_t in_c_ = 0, out_c_ = 0, io_width_ = 0;
+    float *d_in_f32_ = nullptr, *d_out_f32_ = nullptr;
+    cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+    uint64_t launches_ = 0;
+};
+
+const char *status_string(uint32_t st);
+
+}  // namespace k44b

@@ -1,0 +1,477 @@
+// Wave kernels for sm_100a.
+//
+//  * k44_wave_umma_kernel — the hot path. Persistent, warp-specialised, one CTA per SM.
+//      warp 0   producer: per 64-synapse stage one linear bulk copy of the packed weight block and
+//               one TMA box per run of substrate rows (128-byte swizzle), completing on an mbarrier;
+//      warp 1   a single thread issues tcgen05.mma (M=128 neurons, N=64..256 columns, K=16) with
+//               FP32 accumulators in tensor memory, double-buffered across tiles;
+//      warps 2-5 epilogue: tcgen05.ld -> bias -> activation -> residual -> FP16 RTE -> canvas rows.
+//    Replaces the roles of the reference's three mma.sync kernels and its tcgen05 prototype
+//    (kernels/cuda/kernel44_cuda_pack.cuh:242-286, 370-391, 438-623) for run-structured gathers.
+//  * k44_wave_fma_kernel — general FP32-FMA path (any gather table, any element alignment, any group
+//    size); also the cross-check for the tensor-core path.
+//  * packer / conversion kernels.
+//
+// Every wait on a barrier is bounded in time; on expiry the kernel records a status bit, drains its
+// own copies, frees its tensor memory and returns.
+#include "k44_kernels.cuh"
+#include "k44_ptx.cuh"
+
+namespace k44b {
+
+// ---------------------------------------------------------------------------------------------------
+// fused epilogue (semantics of kernels/cuda/kernel44_cuda_pack.cuh:54-58, 69-126; GELU added)
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float apply_act(float v, int act) {
+    switch (act) {
+    case 1: return fmaxf(v, 0.0f);
+    case 2: return 1.0f / (1.0f + __expf(-v));
+    case 3: return v / (1.0f + __expf(-v));
+    case 4: return fmaxf(v, 0.1f * v);
+    case 5: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    default: return v;
+    }
+}
+
+// residual goes in before the activation when an output-row map is present, after it otherwise
+__device__ __forceinline__ float finish_value(float acc, float bias, float res, int act, bool has_res, bool has_map) {
+    float v = acc + bias;
+    if (has_res && has_map) v += res;
+    v = apply_act(v, act);
+    if (has_res && !has_map) v += res;
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// FMA path
+// ---------------------------------------------------------------------------------------------------
+// CTA = 256 threads = 16 neurons x one 64-column tile. Per 64-synapse stage the 64 gathered rows
+// (2-byte loads: offsets may have any alignment — this is what lets a tap be a token shift) and the
+// 16x64 weight block are staged in shared memory; thread (q, c) accumulates neurons 4q..4q+3 for
+// column c.
+constexpr int kFmaRows = 16;
+
+__global__ void __launch_bounds__(256) k44_wave_fma_kernel(const WaveArgs a) {
+    __shared__ __half xs[kStageK][64];
+    __shared__ __align__(16) __half ws[kFmaRows][kStageK];
+    __shared__ uint64_t offs[kStageK];
+
+    const uint32_t tile = blockIdx.x;                     // 64-column tile
+    const uint32_t j0 = blockIdx.y * kFmaRows;            // first neuron
+    const uint32_t g = j0 / a.group;
+    const uint32_t tid = threadIdx.x, c = tid & 63u, q = tid >> 6;
+    const __half *xbase = a.canvas + a.x_base_off + (uint64_t)tile * 64u;
+    const uint64_t x_limit = a.canvas_elems - a.x_base_off - (uint64_t)tile * 64u;   // exclusive bound for off + 64
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    bool bad = false;
+    for (uint32_t ks = 0; ks < a.num_kstages; ++ks) {
+        if (tid < kStageK) {
+            const uint32_t s = ks * kStageK + tid;
+            uint64_t off = 0;
+            if (s < a.fan_in) {
+                if (a.gather_mode == GATHER_IDX) {
+                    off = a.gather[(uint64_t)g * a.fan_in + s];
+                } else {
+                    const uint32_t row = a.gather[(uint64_t)g * a.boxes_per_group + s / a.box_h] + s % a.box_h;
+                    off = (uint64_t)row * a.pitch;
+                }
+            }
+            if (off + 64u > x_limit) { off = 0; bad = true; }   // record and skip instead of faulting
+            offs[tid] = off;
+        } else if (tid < kStageK + 128) {
+            const uint32_t v = tid - kStageK, r = v >> 3, k8 = v & 7u;   // 16 rows x 8 vectors
+            const uint4 wv = a.w_tiles[tiled_vec_index(j0 + r, ks * 8u + k8, a.num_kstages)];
+            *reinterpret_cast<uint4 *>(&ws[r][k8 * 8]) = wv;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (uint32_t k = q; k < kStageK; k += 4) xs[k][c] = xbase[offs[k] + c];
+        __syncthreads();
+#pragma unroll 8
+        for (uint32_t k = 0; k < kStageK; ++k) {
+            const float x = __half2float(xs[k][c]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[i] = fmaf(__half2float(ws[q * 4 + i][k]), x, acc[i]);
+        }
+        __syncthreads();
+    }
+    if (bad) atomicOr(a.status, (uint32_t)ST_BAD_INDEX);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t j = j0 + q * 4 + i;
+        if (j >= a.cout) continue;
+        const uint32_t oj = a.cout_map ? a.cout_map[j] : j;
+        const uint64_t o = (uint64_t)oj * a.pitch + (uint64_t)tile * 64u + c;
+        const float b = a.bias ? __half2float(a.bias[j]) : 0.0f;
+        const float r = a.has_residual ? __half2float(a.canvas[a.res_off + o]) : 0.0f;
+        a.canvas[a.y_off + o] = __float2half_rn(finish_value(acc[i], b, r, a.act, a.has_residual != 0, a.cout_map != nullptr));
+    }
+}
+
+cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s) {
+    dim3 grid(a.num_col_tiles64, (a.cout + kFmaRows - 1) / kFmaRows);
+    k44_wave_fma_kernel<<<grid, 256, 0, s>>>(a);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------------
+// tcgen05 path
+// ---------------------------------------------------------------------------------------------------
+constexpr int kUmmaThreads = 192;
+
+template <int N_TILE>
+struct UmmaCfg {
+    static constexpr int kColBlocks = N_TILE / 64;
+    static constexpr uint32_t kXBytes = (uint32_t)kColBlocks * kStageK * 128u;        // 8 KiB per 64 columns
+    static constexpr uint32_t kStageBytes = kStageWBytes + kXBytes;
+    static constexpr int kStages = (N_TILE == 64) ? 8 : (N_TILE == 128 ? 6 : 4);
+    static constexpr uint32_t kTmemCols = 2u * N_TILE;
+    static constexpr uint32_t kSmemBytes = 1024u /*alignment slack*/ + (uint32_t)kStages * kStageBytes + 256u;
+};
+
+template <int N_TILE>
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a, const UmmaDesc d) {
+    using Cfg = UmmaCfg<N_TILE>;
+    constexpr int STAGES = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows of 128 bytes
+    const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    const uint32_t w_smem = smem_base;
+    const uint32_t x_smem = smem_base + (uint32_t)STAGES * kStageWBytes;
+    const uint32_t ctl = x_smem + (uint32_t)STAGES * Cfg::kXBytes;
+    const uint32_t full_bar = ctl, empty_bar = ctl + 8u * STAGES;
+    const uint32_t tfull_bar = ctl + 16u * STAGES, tempty_bar = tfull_bar + 16u;
+    uint8_t *ctl_ptr = smem_raw + (ctl - ptx::smem_addr(smem_raw));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ctl_ptr + 16 * STAGES + 32);
+    volatile uint32_t *abort_word = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t tiles_n = a.num_col_tiles64 / Cfg::kColBlocks;
+    const uint32_t mtiles = (a.cout + kTileM - 1) / kTileM;
+    const uint32_t total_tiles = mtiles * tiles_n;
+    const uint32_t mtiles_per_group = a.mtiles_per_group;
+    const uint32_t boxes_per_stage = kStageK / a.box_h;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar + 8u * s, 1);
+            ptx::mbar_init(empty_bar + 8u * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(tfull_bar + 8u * b, 1);
+            ptx::mbar_init(tempty_bar + 8u * b, 128);
+        }
+        *abort_word = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_addr(const_cast<uint32_t *>(tmem_slot)), Cfg::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+        const long long t0 = clock64();
+        for (uint32_t it = 0;; ++it) {
+            if (ptx::mbar_try_wait(bar, parity)) return true;
+            if ((it & 31u) == 31u) {
+                if (*abort_word != 0u) return false;
+                if ((unsigned long long)(clock64() - t0) > d.wait_cycles) return false;
+            }
+        }
+    };
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) ptx::prefetch_tensormap(&tmap);
+        const uint64_t pol_w = ptx::policy_evict_first();   // weights are streamed once
+        const uint64_t pol_x = ptx::policy_evict_last();    // substrate rows are shared between groups
+        uint32_t issued = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const uint32_t mt = tile / tiles_n, ct = tile % tiles_n;
+            const uint32_t *rows = a.gather + (uint64_t)(mt / mtiles_per_group) * a.boxes_per_group;
+            const uint4 *wsrc = a.w_tiles + (uint64_t)mt * a.num_kstages * (kStageWBytes / 16u);
+            uint32_t cached = 0;
+            for (uint32_t ks = 0; ks < a.num_kstages && ok; ++ks) {
+                const uint32_t stage = issued % STAGES, ph = (issued / STAGES) & 1u;
+                if (lane == 0) {
+                    ok = wait(empty_bar + 8u * stage, ph ^ 1u);
+                    if (ok) {
+                        ptx::mbar_arrive_expect_tx(full_bar + 8u * stage, Cfg::kStageBytes);
+                        ptx::bulk_g2s(w_smem + stage * kStageWBytes, wsrc + (uint64_t)ks * (kStageWBytes / 16u), kStageWBytes,
+                                      full_bar + 8u * stage, pol_w);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                for (uint32_t b = 0; b < boxes_per_stage; ++b) {
+                    const uint32_t bi = ks * boxes_per_stage + b;
+                    if ((bi & 31u) == 0u) cached = (bi + lane < a.boxes_per_group) ? __ldg(rows + bi + lane) : 0u;
+                    const uint32_t row = __shfl_sync(0xffffffffu, cached, bi & 31u);
+                    if (lane == 0) {
+#pragma unroll
+                        for (int cb = 0; cb < Cfg::kColBlocks; ++cb)
+                            ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + (uint32_t)cb * (kStageK * 128u) + b * a.box_h * 128u,
+                                             &tmap, (int32_t)(ct * N_TILE + cb * 64), (int32_t)row, full_bar + 8u * stage, pol_x);
+                    }
+                }
+                ++issued;
+            }
+        }
+        if (!ok && lane == 0) {
+            if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PRODUCER);
+            *abort_word = 1u;
+            // wait (bounded) for copies already in flight before this CTA's shared memory goes away
+            const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0u;
+            for (uint32_t i = first; i < issued; ++i) {
+                const long long t0 = clock64();
+                bool done = false;
+                while (!done && (unsigned long long)(clock64() - t0) < d.wait_cycles)
+                    done = ptx::mbar_try_wait(full_bar + 8u * (i % STAGES), (i / STAGES) & 1u);
+                if (!done) atomicOr(a.status, (uint32_t)ST_TIMEOUT_DRAIN);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t consumed = 0, iter = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+                const uint32_t acc = iter & 1u;
+                ok = wait(tempty_bar + 8u * acc, ((iter >> 1) & 1u) ^ 1u);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * N_TILE;
+                for (uint32_t ks = 0; ks < a.num_kstages; ++ks) {
+                    const uint32_t stage = consumed % STAGES, ph = (consumed / STAGES) & 1u;
+                    ok = wait(full_bar + 8u * stage, ph);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+                    const uint64_t a0 = d.a_base | (uint64_t)(((w_smem + stage * kStageWBytes) >> 4) & 0x3fffu);
+                    const uint64_t b0 = d.b_base | (uint64_t)(((x_smem + stage * Cfg::kXBytes) >> 4) & 0x3fffu);
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < kStageK / 16u; ++k4)
+                        ptx::umma_f16(d_tmem, a0 + (uint64_t)(k4 * d.a_k_step), b0 + (uint64_t)(k4 * d.b_k_step), d.idesc,
+                                      (ks | k4) != 0u ? 1u : 0u);
+                    ptx::umma_commit(empty_bar + 8u * stage);      // stage reusable once these MMAs retire
+                    ++consumed;
+                }
+                if (ok) ptx::umma_commit(tfull_bar + 8u * acc);     // accumulator complete
+            }
+            if (!ok) {
+                if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_MMA);
+                *abort_word = 1u;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue ----------------
+        const uint32_t quarter = warp & 3u;                  // TMEM lanes this warp may read
+        const bool has_map = a.cout_map != nullptr;
+        uint32_t iter = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+            const uint32_t mt = tile / tiles_n, ct = tile % tiles_n, acc = iter & 1u;
+            ok = wait(tfull_bar + 8u * acc, (iter >> 1) & 1u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t j = mt * kTileM + quarter * 32u + lane;
+            const bool live = j < a.cout;
+            const uint32_t oj = (live && has_map) ? a.cout_map[j] : j;
+            const float bias = (live && a.bias) ? __half2float(a.bias[j]) : 0.0f;
+            const uint64_t o = (uint64_t)oj * a.pitch + (uint64_t)ct * N_TILE;
+#pragma unroll 1
+            for (uint32_t c0 = 0; c0 < (uint32_t)N_TILE; c0 += 32u) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * N_TILE + c0, v);
+                ptx::tmem_ld_wait();
+                if (live) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(a.canvas + a.y_off + o + c0);
+                    const uint4 *rsrc = reinterpret_cast<const uint4 *>(a.canvas + a.res_off + o + c0);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        if (a.has_residual) {
+                            const uint4 rv = rsrc[q4];
+                            const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(rh[e]); r[2 * e] = f.x; r[2 * e + 1] = f.y; }
+                        }
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float lo = finish_value(__uint_as_float(v[q4 * 8 + 2 * e]), bias, r[2 * e], a.act, a.has_residual != 0, has_map);
+                            const float hi = finish_value(__uint_as_float(v[q4 * 8 + 2 * e + 1]), bias, r[2 * e + 1], a.act, a.has_residual != 0, has_map);
+                            const __half2 h2 = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
+                            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
+                        }
+                        dst[q4] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(tempty_bar + 8u * acc);
+        }
+        if (!ok && lane == 0) {
+            if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_EPILOGUE);
+            *abort_word = 1u;
+        }
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+cudaError_t umma_kernel_setup() {
+    cudaError_t e;
+    e = cudaFuncSetAttribute(k44_wave_umma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)UmmaCfg<64>::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(k44_wave_umma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)UmmaCfg<128>::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k44_wave_umma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)UmmaCfg<256>::kSmemBytes);
+}
+
+cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s) {
+    const uint32_t mtiles = (a.cout + kTileM - 1) / kTileM;
+    const uint32_t tiles = mtiles * (a.num_col_tiles64 / (d.n_tile / 64u));
+    const uint32_t grid = tiles < (uint32_t)num_sms ? tiles : (uint32_t)num_sms;
+    switch (d.n_tile) {
+    case 64: k44_wave_umma_kernel<64><<<grid, kUmmaThreads, UmmaCfg<64>::kSmemBytes, s>>>(tmap, a, d); break;
+    case 128: k44_wave_umma_kernel<128><<<grid, kUmmaThreads, UmmaCfg<128>::kSmemBytes, s>>>(tmap, a, d); break;
+    case 256: k44_wave_umma_kernel<256><<<grid, kUmmaThreads, UmmaCfg<256>::kSmemBytes, s>>>(tmap, a, d); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------------
+// packer kernels: one thread per 16-byte destination vector
+// ---------------------------------------------------------------------------------------------------
+template <int SRC>   // 0: container (16x16-tile) order, 1: row-major
+__global__ void k44_repack_to_tiled_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, uint32_t cout,
+                                           uint32_t fan_in, uint32_t num_kstages, uint64_t total) {
+    for (uint64_t v = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; v < total; v += (uint64_t)gridDim.x * blockDim.x) {
+        // invert tiled_vec_index: v = ((mt*KS + ks)*128 + r)*8 + pos
+        const uint32_t pos = (uint32_t)(v & 7u), r = (uint32_t)((v >> 3) & 127u);
+        const uint64_t blk = v >> 10;
+        const uint32_t ks = (uint32_t)(blk % num_kstages), mt = (uint32_t)(blk / num_kstages);
+        const uint32_t j = mt * 128u + r, k8 = ks * 8u + (pos ^ (r & 7u));
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (j < cout && k8 * 8u < fan_in) {
+            const uint64_t si = SRC == 0 ? (((uint64_t)(j >> 4) * (fan_in >> 4) + (k8 >> 1)) * 32u + ((k8 & 1u) << 4) + (j & 15u))
+                                         : ((uint64_t)j * (fan_in >> 3) + k8);
+            val = src[si];
+        }
+        dst[v] = val;
+    }
+}
+
+static inline uint32_t grid_for(uint64_t total, int block) {
+    const uint64_t g = (total + block - 1) / block;
+    return (uint32_t)(g < 148ull * 16ull ? (g ? g : 1) : 148ull * 16ull);
+}
+
+cudaError_t launch_repack_wmma_to_tiled(const uint4 *src, uint4 *dst, uint32_t cout, uint32_t fan_in, cudaStream_t s) {
+    const uint32_t ks = (fan_in + kStageK - 1) / kStageK, mt = (cout + kTileM - 1) / kTileM;
+    const uint64_t total = (uint64_t)mt * ks * 1024u;
+    k44_repack_to_tiled_kernel<0><<<grid_for(total, 256), 256, 0, s>>>(src, dst, cout, fan_in, ks, total);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_repack_rowmajor_to_tiled(const uint4 *src, uint4 *dst, uint32_t cout, uint32_t fan_in, cudaStream_t s) {
+    const uint32_t ks = (fan_in + kStageK - 1) / kStageK, mt = (cout + kTileM - 1) / kTileM;
+    const uint64_t total = (uint64_t)mt * ks * 1024u;
+    k44_repack_to_tiled_kernel<1><<<grid_for(total, 256), 256, 0, s>>>(src, dst, cout, fan_in, ks, total);
+    return cudaGetLastError();
+}
+
+__global__ void k44_tiled_to_rowmajor_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, uint32_t fan_in,
+                                             uint32_t num_kstages, uint64_t total) {
+    const uint32_t v8 = fan_in >> 3;
+    for (uint64_t v = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; v < total; v += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t j = (uint32_t)(v / v8), k8 = (uint32_t)(v % v8);
+        dst[v] = src[tiled_vec_index(j, k8, num_kstages)];
+    }
+}
+
+cudaError_t launch_tiled_to_rowmajor(const uint4 *src, uint4 *dst, uint32_t cout, uint32_t fan_in, cudaStream_t s) {
+    const uint32_t ks = (fan_in + kStageK - 1) / kStageK;
+    const uint64_t total = (uint64_t)cout * (fan_in >> 3);
+    k44_tiled_to_rowmajor_kernel<<<grid_for(total, 256), 256, 0, s>>>(src, dst, fan_in, ks, total);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host-I/O helpers: dense F32 [rows][width] <-> canvas rows (FP16, row pitch), on the device
+// (the reference does this on the host: wavec/k44_wave_executor.cu:146-176)
+// ---------------------------------------------------------------------------------------------------
+__global__ void k44_f32_to_canvas_kernel(const float *__restrict__ src, __half *__restrict__ dst, uint32_t width,
+                                         uint32_t pitch, uint64_t total) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t row = i / pitch;
+        const uint32_t col = (uint32_t)(i % pitch);
+        dst[i] = __float2half_rn(col < width ? src[row * width + col] : 0.0f);
+    }
+}
+
+__global__ void k44_canvas_to_f32_kernel(const __half *__restrict__ src, float *__restrict__ dst, uint32_t width,
+                                         uint32_t pitch, uint64_t total) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t row = i / width;
+        const uint32_t col = (uint32_t)(i % width);
+        dst[i] = __half2float(src[row * pitch + col]);
+    }
+}
+
+cudaError_t launch_f32_to_canvas(const float *src, __half *dst, uint32_t rows, uint32_t width, uint32_t pitch, cudaStream_t s) {
+    const uint64_t total = (uint64_t)rows * pitch;
+    k44_f32_to_canvas_kernel<<<grid_for(total, 256), 256, 0, s>>>(src, dst, width, pitch, total);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_canvas_to_f32(const __half *src, float *dst, uint32_t rows, uint32_t width, uint32_t pitch, cudaStream_t s) {
+    const uint64_t total = (uint64_t)rows * width;
+    k44_canvas_to_f32_kernel<<<grid_for(total, 256), 256, 0, s>>>(src, dst, width, pitch, total);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------------
+// counter-based normal fill (synthetic weights of plans too large to generate on the host)
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+__global__ void k44_fill_normal_f16_kernel(__half *dst, uint64_t n, uint64_t seed, float scale) {
+    // each thread produces one Box-Muller pair
+    for (uint64_t p = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; 2 * p < n; p += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t h = mix64(seed ^ (p * 0xD1342543DE82EF95ull));
+        const float u1 = ((uint32_t)(h >> 40) + 1u) * (1.0f / 16777217.0f);      // (0,1]
+        const float u2 = (uint32_t)(h & 0xffffffu) * (1.0f / 16777216.0f);
+        const float rad = sqrtf(-2.0f * __logf(u1)) * scale;
+        float sn, cs;
+        __sincosf(6.28318530718f * u2, &sn, &cs);
+        dst[2 * p] = __float2half_rn(rad * cs);
+        if (2 * p + 1 < n) dst[2 * p + 1] = __float2half_rn(rad * sn);
+    }
+}
+
+cudaError_t launch_fill_normal_f16(__half *dst, uint64_t n, uint64_t seed, float scale, cudaStream_t s) {
+    k44_fill_normal_f16_kernel<<<grid_for((n + 1) / 2, 256), 256, 0, s>>>(dst, n, seed, scale);
+    return cudaGetLastError();
+}
+
+}  // namespace k44b

@@ -1,0 +1,86 @@
+// Device-side contracts of the wave kernels: packed weight layout, gather tables, launch wrappers.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace k44b {
+
+// ---- packed ("tiled") weight layout --------------------------------------------------------------
+// Weights of a wave are stored as [m_tile][k_stage] blocks of 16 KiB: 128 neurons x 64 synapses of
+// FP16, i.e. 128 rows of 128 bytes. Inside a block the 16-byte chunk c (0..7) of row r sits at chunk
+// position c ^ (r & 7) — the 128-byte shared-memory swizzle — so that one linear bulk copy of a block
+// lands in shared memory already in the K-major SWIZZLE_128B operand layout of tcgen05.mma.
+// Rows >= cout and synapses >= fan_in are zero.
+constexpr uint32_t kTileM = 128;       // neurons per tile
+constexpr uint32_t kStageK = 64;       // synapses per pipeline stage
+constexpr uint32_t kStageWBytes = kTileM * kStageK * 2;
+
+__host__ __device__ inline uint64_t tiled_vec_index(uint32_t j, uint32_t k8, uint32_t num_kstages) {
+    const uint32_t mt = j >> 7, r = j & 127u, ks = k8 >> 3, c = k8 & 7u;
+    return (((uint64_t)mt * num_kstages + ks) * 128u + r) * 8u + (c ^ (r & 7u));
+}
+
+enum GatherMode : int {
+    GATHER_IDX = 0,    // one 32-bit FP16-element offset per synapse (general; any alignment)
+    GATHER_BOX = 1,    // runs of `box_h` consecutive rows: one 32-bit row number per box
+};
+
+enum WavePath : int { PATH_FMA = 0, PATH_UMMA = 1 };
+
+// Status word written by kernels instead of trapping or hanging.
+enum KernelStatus : uint32_t {
+    ST_OK = 0,
+    ST_TIMEOUT_PRODUCER = 1u << 0,
+    ST_TIMEOUT_MMA = 1u << 1,
+    ST_TIMEOUT_EPILOGUE = 1u << 2,
+    ST_TIMEOUT_DRAIN = 1u << 3,
+    ST_BAD_INDEX = 1u << 4,
+};
+
+struct WaveArgs {
+    // tensors
+    const uint4 *w_tiles = nullptr;
+    const uint32_t *gather = nullptr;     // idx table or box-row table
+    const __half *bias = nullptr;         // may be null
+    const uint16_t *cout_map = nullptr;   // may be null
+    __half *canvas = nullptr;
+    uint32_t *status = nullptr;
+    // geometry
+    uint64_t canvas_elems = 0;
+    uint64_t y_off = 0, res_off = 0, x_base_off = 0;
+    uint32_t cout = 0, group = 0, fan_in = 0;
+    uint32_t mtiles_per_group = 1;        // 128-neuron tiles sharing one gather list (tensor-core path)
+    uint32_t num_kstages = 0;             // ceil(fan_in / 64)
+    uint32_t pitch = 0, num_col_tiles64 = 0;
+    int gather_mode = GATHER_IDX;
+    uint32_t box_h = 0, boxes_per_group = 0;
+    int act = 0;
+    int has_residual = 0;
+};
+
+// tcgen05 operand descriptors are assembled on the host (see k44_exec.cu) and passed in.
+struct UmmaDesc {
+    uint64_t a_base = 0, b_base = 0;      // descriptor bits without the start address
+    uint32_t a_k_step = 0, b_k_step = 0;  // start-address increment per K=16 step, 16-byte units
+    uint32_t idesc = 0;
+    uint32_t n_tile = 64;
+    unsigned long long wait_cycles = 0;   // bound for every barrier wait
+};
+
+cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s);
+cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
+cudaError_t umma_kernel_setup();       // opt in to large dynamic shared memory (once per device)
+
+// packer kernels
+cudaError_t launch_repack_wmma_to_tiled(const uint4 *src_wmma, uint4 *dst, uint32_t cout, uint32_t fan_in, cudaStream_t s);
+cudaError_t launch_repack_rowmajor_to_tiled(const uint4 *src_rows, uint4 *dst, uint32_t cout, uint32_t fan_in, cudaStream_t s);
+cudaError_t launch_tiled_to_rowmajor(const uint4 *src_tiled, uint4 *dst_rows, uint32_t cout, uint32_t fan_in, cudaStream_t s);
+// host f32 [C][W] <-> canvas rows (FP16, pitch), on the device
+cudaError_t launch_f32_to_canvas(const float *src, __half *dst, uint32_t rows, uint32_t width, uint32_t pitch, cudaStream_t s);
+cudaError_t launch_canvas_to_f32(const __half *src, float *dst, uint32_t rows, uint32_t width, uint32_t pitch, cudaStream_t s);
+// counter-based normal fill: element i gets scale * N(0,1) from a stateless hash of (seed, i)
+cudaError_t launch_fill_normal_f16(__half *dst, uint64_t n, uint64_t seed, float scale, cudaStream_t s);
+
+}  // namespace k44b

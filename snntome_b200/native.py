@@ -1,0 +1,222 @@
+"""Native plan API (include/k44b.h): device-resident canvas, caller-supplied stream, plans built from
+arrays or a `.tcff` file. PyTorch is used only to view device memory and to name streams."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import numpy as np
+
+from ._lib import WaveDesc, WaveInfo, get_lib, last_error
+from .plan import Plan, Wave
+
+PATH_AUTO, PATH_FMA, PATH_UMMA = -1, 0, 1
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+class _CudaView:
+    """Minimal __cuda_array_interface__ carrier so that torch can wrap a raw device pointer."""
+
+    def __init__(self, ptr: int, n: int, typestr: str, keepalive):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 3}
+        self._keepalive = keepalive
+
+
+def _ptr(a: Optional[np.ndarray]):
+    return a.ctypes.data if a is not None else None
+
+
+def wave_desc(w: Wave, *, device_weights_ptr: int = 0, run_rows: Optional[np.ndarray] = None, run_len: int = 0):
+    """Fill a k44b_wave_desc from a `Wave`. Returns (desc, keepalive list)."""
+    d = WaveDesc()
+    d.cout, d.logical_cout, d.cin, d.group = w.cout, w.logical_cout, w.cin, w.group
+    d.fan_in, d.fan_in_raw, d.act, d.has_residual = w.fan_in, w.fan_in_raw, int(w.act), int(bool(w.has_residual))
+    d.y_off, d.src_off, d.res_off, d.x_base_off = int(w.y_off), int(w.src_off), int(w.res_off), int(w.x_base_off)
+    keep = [w]
+    if run_rows is not None:
+        rr = np.ascontiguousarray(run_rows, dtype=np.uint32)
+        keep.append(rr)
+        d.run_rows, d.run_len, d.idx = rr.ctypes.data, int(run_len), None
+    else:
+        d.idx = _ptr(w.idx)
+    if device_weights_ptr:
+        d.weights, d.weights_on_device = device_weights_ptr, 1
+    else:
+        d.weights, d.weights_on_device = _ptr(w.weights), 0
+    d.bias = _ptr(w.bias)
+    d.cout_map = _ptr(w.cout_map)
+    name = (w.name or "wave").encode()
+    keep.append(name)
+    d.name = name
+    return d, keep
+
+
+class NativePlan:
+    def __init__(self, ptr: int, owned: bool = True, keepalive=None):
+        self._lib = get_lib()
+        self._ptr = ptr
+        self._owned = owned
+        self._keepalive = keepalive
+
+    # -- construction ------------------------------------------------------------------------------
+    @classmethod
+    def create(cls, canvas_elems: int, pitch: int, columns: int, device: int = 0, force_path: int = PATH_AUTO) -> "NativePlan":
+        lib = get_lib()
+        p = lib.k44b_plan_create(int(device), int(canvas_elems), int(pitch), int(columns), int(force_path))
+        if not p:
+            raise NativeError(f"plan_create: {last_error()}")
+        return cls(p)
+
+    @classmethod
+    def from_plan(cls, plan: Plan, device: int = 0, force_path: int = PATH_AUTO) -> "NativePlan":
+        np_ = cls.create(plan.canvas_elems, plan.pitch, plan.columns, device, force_path)
+        for w in plan.waves:
+            np_.add_wave(w)
+        np_.set_io(plan.input_off, plan.input_c, plan.output_off, plan.output_c, plan.columns)
+        return np_
+
+    @classmethod
+    def from_tcff(cls, path, pitch_hint: int = 0, device: int = 0, force_path: int = PATH_AUTO) -> "NativePlan":
+        lib = get_lib()
+        p = lib.k44b_plan_from_tcff(str(path).encode(), int(pitch_hint), int(device), int(force_path))
+        if not p:
+            raise NativeError(f"plan_from_tcff: {last_error()}")
+        return cls(p)
+
+    def add_wave(self, w: Wave, **kw) -> None:
+        d, keep = wave_desc(w, **kw)
+        rc = self._lib.k44b_plan_add_wave(self._ptr, ctypes.byref(d))
+        del keep
+        if rc != 0:
+            raise NativeError(f"add_wave: {last_error()}")
+
+    def add_wave_desc(self, d: WaveDesc) -> None:
+        if self._lib.k44b_plan_add_wave(self._ptr, ctypes.byref(d)) != 0:
+            raise NativeError(f"add_wave: {last_error()}")
+
+    def set_io(self, input_off: int, input_c: int, output_off: int, output_c: int, width: int) -> None:
+        if self._lib.k44b_plan_set_io(self._ptr, int(input_off), int(input_c), int(output_off), int(output_c), int(width)) != 0:
+            raise NativeError(f"set_io: {last_error()}")
+
+    def close(self) -> None:
+        if self._ptr and self._owned:
+            self._lib.k44b_plan_destroy(self._ptr)
+        self._ptr = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- inspection ----------------------------------------------------------------------------------
+    @property
+    def num_waves(self) -> int:
+        return self._lib.k44b_num_waves(self._ptr)
+
+    @property
+    def canvas_elems(self) -> int:
+        return int(self._lib.k44b_canvas_elems(self._ptr))
+
+    def wave_info(self, i: int) -> WaveInfo:
+        info = WaveInfo()
+        if self._lib.k44b_wave_info(self._ptr, i, ctypes.byref(info)) != 0:
+            raise NativeError(f"wave_info: {last_error()}")
+        return info
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.k44b_launch_count(self._ptr))
+
+    def canvas_tensor(self):
+        """The canvas as a torch.float16 CUDA tensor (zero-copy view)."""
+        import torch
+        view = _CudaView(self._lib.k44b_canvas_ptr(self._ptr), self.canvas_elems, "<f2", self)
+        return torch.as_tensor(view, device="cuda")
+
+    # -- execution -----------------------------------------------------------------------------------
+    def execute(self, stream=None) -> None:
+        """Queue all waves. `stream`: a torch.cuda.Stream, a raw cudaStream_t integer, or None for torch's
+        current stream."""
+        if stream is None:
+            import torch
+            sp = torch.cuda.current_stream().cuda_stream
+        elif hasattr(stream, "cuda_stream"):
+            sp = stream.cuda_stream
+        else:
+            sp = int(stream)
+        if self._lib.k44b_execute(self._ptr, ctypes.c_void_p(sp)) != 0:
+            raise NativeError(f"execute: {last_error()}")
+
+    def _stream_ptr(self, stream) -> int:
+        if stream is None:
+            import torch
+            return torch.cuda.current_stream().cuda_stream
+        return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+    def execute_wave(self, wave: int, stream=None) -> None:
+        if self._lib.k44b_execute_wave(self._ptr, int(wave), ctypes.c_void_p(self._stream_ptr(stream))) != 0:
+            raise NativeError(f"execute_wave: {last_error()}")
+
+    def infer_f16(self, h_in_ptr: int, h_out_ptr: int, stream=None) -> float:
+        """Host FP16 buffers (raw addresses, canvas layout, ideally pinned) -> device waves -> host."""
+        ms = ctypes.c_float(0.0)
+        rc = self._lib.k44b_infer_f16(self._ptr, ctypes.c_void_p(h_in_ptr), ctypes.c_void_p(h_out_ptr), ctypes.byref(ms),
+                                      ctypes.c_void_p(self._stream_ptr(stream)))
+        if rc != 0:
+            raise NativeError(f"infer_f16: {last_error()}")
+        return float(ms.value)
+
+    def status(self) -> int:
+        st = ctypes.c_uint32(0)
+        rc = self._lib.k44b_status(self._ptr, ctypes.byref(st))
+        if rc != 0:
+            raise NativeError(f"status {st.value:#x}: {last_error()}")
+        return st.value
+
+    def infer_f32(self, x: np.ndarray, out_elems: int):
+        x32 = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty(out_elems, dtype=np.float32)
+        ms = ctypes.c_float(0.0)
+        f32p = ctypes.POINTER(ctypes.c_float)
+        rc = self._lib.k44b_infer_f32(self._ptr, x32.ctypes.data_as(f32p), int(x32.size), out.ctypes.data_as(f32p), int(out.size), ctypes.byref(ms))
+        if rc != 0:
+            raise NativeError(f"infer_f32: {last_error()}")
+        return out, float(ms.value)
+
+    def weights_rowmajor(self, wave: int):
+        """Unpack wave `wave`'s packed device weights to a [cout, fan_in] uint16 torch tensor."""
+        import torch
+        info = self.wave_info(wave)
+        t = torch.empty((info.cout, info.fan_in), dtype=torch.int16, device="cuda")
+        if self._lib.k44b_wave_weights_rowmajor(self._ptr, wave, ctypes.c_void_p(t.data_ptr())) != 0:
+            raise NativeError(f"weights_rowmajor: {last_error()}")
+        return t
+
+
+def fill_normal_f16(tensor, seed: int, scale: float) -> None:
+    """Fill a CUDA float16 tensor with scale*N(0,1) from a stateless hash (library kernel)."""
+    import torch
+    lib = get_lib()
+    rc = lib.k44b_fill_normal_f16(ctypes.c_void_p(tensor.data_ptr()), tensor.numel(), int(seed), float(scale),
+                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    if rc != 0:
+        raise NativeError(f"fill_normal_f16: {last_error()}")
+
+
+def analyze_gather(w: Wave, pitch: int, canvas_elems: int):
+    """Host-only: returns (rows per box or 0, run table as uint32 array)."""
+    lib = get_lib()
+    d, keep = wave_desc(w)
+    cap = (w.cout // w.group) * ((w.fan_in + 63) // 64 * 64 // 8)
+    out = np.zeros(cap, dtype=np.uint32)
+    cnt = ctypes.c_uint64(0)
+    h = lib.k44b_analyze_gather(ctypes.byref(d), int(pitch), int(canvas_elems), out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)),
+                                cap, ctypes.byref(cnt))
+    del keep
+    if h < 0:
+        raise NativeError(f"analyze_gather: {last_error()}")
+    return h, out[: cnt.value].copy()

@@ -1,0 +1,227 @@
+"""GPU parity: the CUDA wave executor, called through the C ABI, against the CPU oracle on the same
+seeded inputs. Tolerance for outputs is rtol 2e-3 / atol 1e-3 (FP16 operands, FP32 accumulation on
+the device, double accumulation in the oracle); plan decoding, weight packing and container bytes
+are compared exactly."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from snntome_b200 import native, synth
+from snntome_b200.native import PATH_AUTO, PATH_FMA, PATH_UMMA, NativePlan
+from snntome_b200.plan import ACT_GELU, ACT_LEAKY_RELU, ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, Plan, Wave
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 2e-3, 1e-3
+
+
+def run_gpu(plan, x_bits, force_path=PATH_AUTO, expect_path=None):
+    import torch
+    npn = NativePlan.from_plan(plan, device=0, force_path=force_path)
+    if expect_path is not None:
+        for i in range(npn.num_waves):
+            assert npn.wave_info(i).path == expect_path, f"wave {i} took path {npn.wave_info(i).path}"
+    canvas = npn.canvas_tensor()
+    x = torch.from_numpy(np.ascontiguousarray(x_bits).view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    canvas[plan.input_off: plan.input_off + x.numel()] = x
+    npn.execute()
+    assert npn.status() == 0
+    out = canvas.cpu().numpy().view(np.uint16)
+    npn.close()
+    return out
+
+
+def check(plan, got_canvas, want_canvas):
+    for w in plan.waves:
+        a, b = w.y_off, w.y_off + w.cout * plan.pitch
+        ok, err, k = O.compare(got_canvas[a:b], want_canvas[a:b], RTOL, ATOL)
+        assert ok, f"wave {w.name}: max abs err {err} at element {k} (row {k // plan.pitch}, col {k % plan.pitch})"
+
+
+@pytest.mark.parametrize("group", [128, 16])
+def test_config0_fma_path(group):
+    plan = synth.config0(group=group)
+    x = synth.random_input(plan, 11)
+    check(plan, run_gpu(plan, x, PATH_FMA, expect_path=PATH_FMA), O.run_plan(plan, x))
+
+
+def test_config0_tensor_core_path():
+    plan = synth.config0(group=128)
+    x = synth.random_input(plan, 11)
+    check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_UMMA), O.run_plan(plan, x))
+
+
+def test_config0_group16_falls_back_to_fma_automatically():
+    plan = synth.config0(group=16)
+    x = synth.random_input(plan, 12)
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_FMA), O.run_plan(plan, x))
+
+
+def test_ultra_sparse_rule_scaled_down():
+    """Fan-in 4096 = 64 runs of 64 rows, groups of 128, ReLU, 64 columns — the benchmark plan's
+    connectivity at a size the oracle finishes quickly."""
+    plan = synth.config2_scaled(input_rows=32768, cout=1024, waves=2)
+    x = synth.random_input(plan, 13, dist="normal")
+    want = O.run_plan(plan, x)
+    check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_UMMA), want)
+    check(plan, run_gpu(plan, x, PATH_FMA, expect_path=PATH_FMA), want)
+
+
+@pytest.mark.parametrize("act", [ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, ACT_LEAKY_RELU, ACT_GELU])
+@pytest.mark.parametrize("path", [PATH_FMA, PATH_UMMA])
+def test_dense_chain_all_activations(act, path):
+    plan = synth.dense_chain(seed=act + 20, dims=[192, 384, 200], columns=64, act=act, weight_std=0.08)
+    x = synth.random_input(plan, 14)
+    check(plan, run_gpu(plan, x, path, expect_path=path), O.run_plan(plan, x))
+
+
+@pytest.mark.parametrize("path", [PATH_FMA, PATH_UMMA])
+def test_ragged_sizes_and_tail_stage(path):
+    # fan-in 96 (half-filled last stage), 80 output rows (partial 128-row tile), one group
+    plan = synth.dense_chain(seed=31, dims=[96, 80, 130], columns=64, act=ACT_SILU, weight_std=0.1, group=0)
+    for w in plan.waves:                      # single group per wave so the tensor-core path applies
+        w.idx = w.idx[:1].copy()
+        w.group = w.cout
+    x = synth.random_input(plan, 15)
+    check(plan, run_gpu(plan, x, path, expect_path=path), O.run_plan(plan, x))
+
+
+@pytest.mark.parametrize("path", [PATH_FMA, PATH_UMMA])
+@pytest.mark.parametrize("with_map", [False, True])
+def test_residual_and_row_map(path, with_map):
+    plan = synth.dense_chain(seed=41, dims=[128, 128, 128], columns=64, act=ACT_RELU, weight_std=0.1, residual_from={2: 1})
+    if with_map:
+        rng = np.random.default_rng(5)
+        plan.waves[1].cout_map = rng.permutation(plan.waves[1].cout).astype(np.uint16)
+    x = synth.random_input(plan, 16, dist="normal")
+    check(plan, run_gpu(plan, x, path, expect_path=path), O.run_plan(plan, x))
+
+
+@pytest.mark.parametrize("columns,n_tile", [(64, 64), (128, 128), (256, 256), (512, 256), (192, 64), (320, 64)])
+def test_column_tiles(columns, n_tile, monkeypatch):
+    monkeypatch.setenv("K44B_N_TILE", str(n_tile))
+    plan = synth.sparse_plan(seed=51 + columns, input_rows=2048, waves=2, cout=256, runs=8, run_len=32, columns=columns,
+                             group=128, act=ACT_RELU)
+    x = synth.random_input(plan, 17)
+    want = O.run_plan(plan, x)
+    check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_UMMA), want)
+    check(plan, run_gpu(plan, x, PATH_FMA), want)
+
+
+@pytest.mark.parametrize("run_len", [8, 16, 32, 64])
+def test_run_lengths(run_len):
+    plan = synth.sparse_plan(seed=60 + run_len, input_rows=4096, waves=1, cout=384, runs=256 // run_len, run_len=run_len,
+                             columns=64, group=128, act=ACT_NONE)
+    x = synth.random_input(plan, 18)
+    check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_UMMA), O.run_plan(plan, x))
+
+
+def test_token_shift_offsets_use_general_path():
+    """Element-granular gather offsets (a tap that is the same row read a few tokens earlier)."""
+    rng = np.random.default_rng(70)
+    pitch, rows_in, cout, B, group = 256, 64, 128, 64, 128
+    shifts = rng.integers(0, 8, size=B)
+    rows = rng.integers(1, rows_in, size=B)
+    idx = (rows * pitch - shifts).astype(np.uint32)[None, :]
+    w = synth.f16_bits(rng.normal(0, 0.2, (cout, B)))
+    wave = Wave(cout=cout, group=group, fan_in=B, idx=idx, weights=w, bias=None, y_off=rows_in * pitch, act=ACT_GELU)
+    plan = Plan(canvas_elems=(rows_in + cout) * pitch, pitch=pitch, columns=200, input_off=0, input_c=rows_in,
+                output_off=rows_in * pitch, output_c=cout, waves=[wave])
+    x = synth.random_input(plan, 19)
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_FMA), O.run_plan(plan, x))
+
+
+def test_minimum_size_wave():
+    plan = synth.dense_chain(seed=80, dims=[8, 3], columns=1, act=ACT_SIGMOID)
+    assert plan.waves[0].cout == 16 and plan.waves[0].fan_in == 64
+    x = synth.random_input(plan, 20)
+    want = O.run_plan(plan, x)
+    check(plan, run_gpu(plan, x, PATH_FMA), want)
+    plan.waves[0].idx = plan.waves[0].idx[:1].copy()
+    plan.waves[0].group = 16
+    check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_UMMA), want)
+
+
+def test_weight_packing_is_bit_exact():
+    import torch
+    plan = synth.dense_chain(seed=90, dims=[160, 208], columns=64)
+    npn = NativePlan.from_plan(plan)
+    got = npn.weights_rowmajor(0).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, plan.waves[0].weights)
+    # device-resident row-major source takes the other packer kernel
+    w = plan.waves[0]
+    dev = torch.from_numpy(w.weights.view(np.int16)).cuda()
+    np2 = NativePlan.create(plan.canvas_elems, plan.pitch, plan.columns)
+    np2.add_wave(w, device_weights_ptr=dev.data_ptr())
+    assert np.array_equal(np2.weights_rowmajor(0).cpu().numpy().view(np.uint16), w.weights)
+
+
+def test_run_table_form_equals_index_form():
+    plan = synth.config0()
+    x = synth.random_input(plan, 21)
+    base = run_gpu(plan, x, PATH_UMMA)
+    import torch
+    npn = NativePlan.create(plan.canvas_elems, plan.pitch, plan.columns, force_path=PATH_UMMA)
+    for wi, w in enumerate(plan.waves):
+        starts = synth.run_starts(1234, wi, w.cout // w.group, 16, 16, 4096 + wi * 1024).astype(np.uint32)
+        npn.add_wave(w, run_rows=starts, run_len=16)
+        assert npn.wave_info(wi).box_rows == 16
+    canvas = npn.canvas_tensor()
+    xt = torch.from_numpy(x.view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    canvas[: xt.numel()] = xt
+    npn.execute()
+    assert npn.status() == 0
+    assert np.array_equal(canvas.cpu().numpy().view(np.uint16), base)
+
+
+def test_wavec_surface_end_to_end(tmp_path):
+    """compile -> save .tcff -> fresh graph -> load -> infer_f32 through the reference-shaped API, and
+    the same file through the native loader."""
+    from snntome_b200.wavec import WaveGraph
+    rng = np.random.default_rng(100)
+    dims, cols = [256, 512, 128], 48
+    ws = [rng.normal(0, 0.05, (dims[i + 1], dims[i])).astype(np.float32) for i in range(2)]
+    bs = [rng.normal(0, 0.1, dims[i + 1]).astype(np.float32) for i in range(2)]
+
+    def build(weights):
+        g = WaveGraph(batch_size=cols)
+        g.add_input("x", dims[0], 1, 1, is_1d=True)
+        g.add_linear("fc1", "x", "h", dims[0], dims[1], weights[0], bs[0], act="silu")
+        g.add_linear("fc2", "h", "y", dims[1], dims[2], weights[1], bs[1], act=None)
+        g.set_output("y")
+        return g
+
+    g = build(ws)
+    plan = g.compile()
+    path = tmp_path / "mlp.tcff"
+    plan.save_tcff(path)
+    g2 = build([np.zeros_like(w) for w in ws])
+    plan2 = g2.compile()
+    plan2.load_tcff_weights(path)
+    x = rng.uniform(-1, 1, (dims[0], 1, cols)).astype(np.float32)
+    y, ms = plan2.infer_f32(x)
+    assert y.shape == (dims[2], 1, cols) and ms > 0
+    # oracle on the FP16-quantised operands
+    xq = O.f16_to_f32(O.f32_to_f16(x[:, 0, :])).astype(np.float64)
+    w1 = O.f16_to_f32(O.f32_to_f16(ws[0])).astype(np.float64)
+    w2 = O.f16_to_f32(O.f32_to_f16(ws[1])).astype(np.float64)
+    b1 = O.f16_to_f32(O.f32_to_f16(bs[0])).astype(np.float64)
+    b2 = O.f16_to_f32(O.f32_to_f16(bs[1])).astype(np.float64)
+    h = w1 @ xq + b1[:, None]
+    h = O.f16_to_f32(O.f32_to_f16((h / (1 + np.exp(-h))).astype(np.float32))).astype(np.float64)
+    want = O.f32_to_f16((w2 @ h + b2[:, None]).astype(np.float32))
+    ok, err, k = O.compare(O.f32_to_f16(y[:, 0, :]), want, RTOL, ATOL)
+    assert ok, (err, k)
+    # native loader on the same file: no graph needed
+    npn = NativePlan.from_tcff(path)
+    assert npn.num_waves == 2
+    y2, _ = npn.infer_f32(x, dims[2] * cols)
+    assert np.array_equal(y2.reshape(dims[2], cols), y[:, 0, :])
+
+
+def test_bad_plan_is_rejected_before_launch():
+    plan = synth.config0()
+    plan.waves[0].idx[3, 7] = plan.canvas_elems
+    with pytest.raises(native.NativeError, match="leaves the canvas"):
+        NativePlan.from_plan(plan)
