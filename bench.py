@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Benchmark of the wave-executor hot path on the ultra-sparse plan.
+
+Workload (synthetic, seeded; stands in for the benchmark text's "ultra-sparse large plan"): FP16 substrate
+with 40,000,000 input rows of 64 columns, 4 waves x 1,048,576 neurons, fan-in 4096 = 64 runs of 64 consecutive
+rows with uniform aligned starts over the input and earlier waves, groups of 128 neurons sharing their runs,
+weights N(0, 1/4096), no bias, ReLU, 64 columns (batch) per GPU. One step = one pass of all 4 waves.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scale S]
+
+Under torchrun each rank runs its own replica on its own 64 columns (weak scaling, no data-path
+collective); time is the maximum over ranks, value the aggregate over all ranks.
+
+Prints one JSON line: metric = effective synaptic TFLOP/s (2 * synapses * columns / s).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SEED = 2024
+FULL = dict(input_rows=40_000_000, waves=4, cout=1 << 20, runs=64, run_len=64, columns=64, group=128)
+
+
+def workload(scale: float) -> dict:
+    """scale < 1 shrinks rows and neurons proportionally (development only; the default is the full plan)."""
+    w = dict(FULL)
+    if scale != 1.0:
+        w["input_rows"] = max(65536, int(FULL["input_rows"] * scale) // 64 * 64)
+        w["cout"] = max(1024, int(FULL["cout"] * scale) // 128 * 128)
+    return w
+
+
+def algorithmic_bytes_per_wave(w: dict) -> float:
+    """Weights once + run table + every group's gathered rows once + output rows (no bias in this plan)."""
+    fan_in = w["runs"] * w["run_len"]
+    groups = w["cout"] // w["group"]
+    return (w["cout"] * fan_in * 2 + groups * w["runs"] * 8 + groups * fan_in * w["columns"] * 2 + w["cout"] * w["columns"] * 2)
+
+
+def flops_per_wave(w: dict) -> float:
+    return 2.0 * w["cout"] * w["runs"] * w["run_len"] * w["columns"]
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_starts_table(wave: int, w: dict) -> np.ndarray:
+    from snntome_b200 import synth
+    rows_avail = w["input_rows"] + wave * w["cout"]
+    return synth.run_starts(SEED, wave, w["cout"] // w["group"], w["runs"], w["run_len"], rows_avail).astype(np.uint32)
+
+
+def build_device_plan(w: dict, device: int):
+    """Plan built in memory: weights are generated on the device wave by wave (row-major), packed by the
+    library, and the row-major copy is dropped."""
+    import torch
+    from snntome_b200._lib import WaveDesc
+    from snntome_b200.native import NativePlan, fill_normal_f16
+    pitch = 64
+    fan_in = w["runs"] * w["run_len"]
+    total_rows = w["input_rows"] + w["waves"] * w["cout"]
+    plan = NativePlan.create(total_rows * pitch, pitch, w["columns"], device=device)
+    scratch = torch.empty((w["cout"], fan_in), dtype=torch.float16, device=f"cuda:{device}")
+    for wi in range(w["waves"]):
+        fill_normal_f16(scratch, SEED * 1000 + wi, (1.0 / fan_in) ** 0.5)
+        torch.cuda.synchronize()
+        starts = run_starts_table(wi, w)
+        d = WaveDesc()
+        d.cout = d.logical_cout = w["cout"]
+        d.cin = w["input_rows"] + wi * w["cout"]
+        d.group, d.fan_in, d.fan_in_raw, d.act, d.has_residual = w["group"], fan_in, fan_in, 1, 0
+        d.y_off = (w["input_rows"] + wi * w["cout"]) * pitch
+        d.run_rows, d.run_len = starts.ctypes.data, w["run_len"]
+        d.weights, d.weights_on_device = scratch.data_ptr(), 1
+        d.name = f"wave{wi}".encode()
+        plan.add_wave_desc(d)
+    del scratch
+    torch.cuda.empty_cache()
+    plan.set_io(0, w["input_rows"], (w["input_rows"] + (w["waves"] - 1) * w["cout"]) * pitch, w["cout"], w["columns"])
+    return plan
+
+
+def cpu_baseline(w: dict, seconds_target: float = 15.0, threads: int | None = None) -> dict:
+    """The oracle (a port: the reference has no CPU implementation of this path) timed on this host on a bounded
+    sample: whole 128-neuron groups of one wave with the full fan-in and 64 columns, gathering from a reduced
+    substrate."""
+    from oracle import oracle as O
+    from snntome_b200 import synth
+    from snntome_b200.plan import Plan, Wave, expand_runs
+    L = O.lib()
+    if threads:
+        L.k44o_set_num_threads(threads)
+    cores = L.k44o_num_threads()
+    fan_in = w["runs"] * w["run_len"]
+    rows = 1 << 20                                   # 128 MiB substrate sample (far beyond the CPU caches)
+    groups = max(1, min(64, int(2 * cores)))
+    cout = groups * w["group"]
+    rng = np.random.default_rng(SEED)
+    starts = synth.run_starts(SEED, 0, groups, w["runs"], w["run_len"], rows)
+    wave = Wave(cout=cout, group=w["group"], fan_in=fan_in, idx=expand_runs(starts, w["run_len"], 64),
+                weights=synth.f16_bits(rng.normal(0, (1.0 / fan_in) ** 0.5, (cout, fan_in))), bias=None, y_off=rows * 64, act=1)
+    plan = Plan(canvas_elems=(rows + cout) * 64, pitch=64, columns=64, input_off=0, input_c=rows, output_off=rows * 64,
+                output_c=cout, waves=[wave])
+    canvas = np.zeros(plan.canvas_elems, dtype=np.uint16)
+    canvas[: rows * 64] = synth.f16_bits(rng.normal(0, 1, rows * 64).astype(np.float32))
+    O.wave_forward(canvas, wave, plan, rows=(0, w["group"]))          # warm-up on one group
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        O.wave_forward(canvas, wave, plan)
+        reps += 1
+        if time.perf_counter() - t0 > seconds_target / 2 or reps >= 8:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    flops = 2.0 * cout * fan_in * 64
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port", "seconds_per_rep": dt,
+            "sample": f"{cout} neurons ({groups} groups of {w['group']}) of one wave, fan-in {fan_in}, 64 columns, "
+                      f"substrate sample of {rows} rows; double accumulation, OpenMP over neurons"}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scale", type=float, default=float(os.environ.get("K44B_BENCH_SCALE", "1.0")))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    w = workload(args.scale)
+    warmup = max(3, args.warmup)
+    cfg = {"workload": "ultra-sparse plan: 40M-row FP16 substrate, 4 waves x 1M neurons, fan-in 4096 as 64 runs of 64 rows, "
+                       "groups of 128, ReLU, 64 columns per GPU",
+           "input_rows": w["input_rows"], "neurons_per_wave": w["cout"], "waves": w["waves"], "fan_in": w["runs"] * w["run_len"],
+           "run_len": w["run_len"], "group": w["group"], "columns_per_gpu": w["columns"], "global_columns": w["columns"] * world,
+           "parallelism": f"column replicas x{world} (plan replicated, no collective)",
+           "l2_policy": "weights streamed per step (34 GB) exceed the 126 MB L2; no explicit flush", "scale": args.scale}
+
+    if args.impl == "reference":
+        # The reference has no CPU implementation of this path and may not be compiled or run; the timed CPU arm is
+        # the oracle port with all host threads, on rank 0 only.
+        if rank != 0:
+            return
+        steps = max(1, min(args.steps, 3))
+        vals = [cpu_baseline(w, seconds_target=20.0) for _ in range(1)]
+        cb = vals[0]
+        line = {"impl": "reference", "metric": "effective synaptic TFLOP/s (2*synapses*columns/s)", "value": cb["value"], "unit": "TFLOP/s",
+                "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f16 operands, f64 accumulate (CPU)", "data": "synthetic", "config": cfg,
+                "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    from snntome_b200.native import fill_normal_f16
+    plan = build_device_plan(w, local_rank)
+    canvas = plan.canvas_tensor()
+    in_elems = w["input_rows"] * 64
+    fill_normal_f16(canvas[:in_elems], SEED + 77 + rank, 1.0)
+    torch.cuda.synchronize()
+    nw = plan.num_waves
+    paths = [plan.wave_info(i).path for i in range(nw)]
+    stream = torch.cuda.current_stream()
+
+    # ---- device-resident throughput ----
+    sampler = ClockSampler(local_rank)       # started before the warm-up: nvidia-smi needs ~0.1 s to deliver its first sample
+    sampler.start()
+    for _ in range(warmup):
+        plan.execute(stream)
+    assert plan.status() == 0
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(nw + 1)] for _ in range(args.steps)]
+    barrier()
+    l0 = plan.launch_count
+    t_start = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record(stream)
+    for s in range(args.steps):
+        ev[s][0].record(stream)
+        for i in range(nw):
+            plan.execute_wave(i, stream)
+            ev[s][i + 1].record(stream)
+    t_end.record(stream)
+    barrier()
+    launches = plan.launch_count - l0
+    assert plan.status() == 0
+    total_ms = t_start.elapsed_time(t_end)
+    wave_ms = [[ev[s][i].elapsed_time(ev[s][i + 1]) for i in range(nw)] for s in range(args.steps)]
+    if dist is not None:
+        t = torch.tensor([total_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    flops_step = flops_per_wave(w) * nw
+    value = flops_step * world / (ms_per_step * 1e-3) / 1e12
+    bytes_wave = algorithmic_bytes_per_wave(w)
+    avg_wave_ms = float(np.mean(wave_ms))
+    peak, peak_kind = measured_peaks()
+    achieved = bytes_wave / (avg_wave_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "k44_wave_umma_kernel<64>" if paths[0] == 1 else "k44_wave_fma_kernel",
+                "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                "algorithmic_bytes_per_launch": bytes_wave, "avg_launch_ms": avg_wave_ms,
+                "per_wave_ms": [float(np.mean([wave_ms[s][i] for s in range(args.steps)])) for i in range(nw)], "traffic": None}
+
+    # ---- end to end through the C ABI with host buffers (pinned FP16 in canvas layout) ----
+    e2e = None
+    if not args.no_e2e:
+        out_rows = w["cout"]
+        h_in = torch.empty(in_elems, dtype=torch.float16).pin_memory()
+        h_in.copy_(canvas[:in_elems])
+        h_out = torch.empty(out_rows * 64, dtype=torch.float16).pin_memory()
+        e_steps = max(2, min(args.steps, 5))
+        plan.infer_f16(h_in.data_ptr(), h_out.data_ptr(), stream)      # warm-up
+        barrier()
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(e_steps):
+            plan.infer_f16(h_in.data_ptr(), h_out.data_ptr(), stream)
+        t1.record(stream)
+        barrier()
+        e_ms = t0.elapsed_time(t1)
+        if dist is not None:
+            t = torch.tensor([e_ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
+        e2e = {"value": flops_step * world / (e_ms / e_steps * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e_ms / e_steps,
+               "steps": e_steps, "h2d_bytes_per_step": in_elems * 2, "d2h_bytes_per_step": out_rows * 64 * 2,
+               "api": "k44b_infer_f16 (host FP16 rows in, last wave's rows out, pinned memory)",
+               "checksum": float(h_out[: 64 * 1024].float().abs().sum().item())}
+        del h_in, h_out
+
+    clocks = sampler.stop()                  # samples span warm-up, the timed steps and the end-to-end steps
+    cb = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cb = cpu_baseline(w)
+    if rank == 0:
+        line = {"metric": "effective synaptic TFLOP/s (2*synapses*columns/s)", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+                "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic", "config": cfg,
+                "hbm_gbs_algorithmic": bytes_wave * nw * world / (ms_per_step * 1e-3) / 1e9, "roofline": roofline, "cpu_baseline": cb,
+                "e2e": e2e, "gpu_launches": int(launches), "kernel_paths": paths, "clocks": clocks}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

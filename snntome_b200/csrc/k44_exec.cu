@@ -53,8 +53,19 @@ bool validate_wave(const HostWave &w, uint32_t pitch, uint32_t num_tiles, uint64
 
 GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_elems) {
     GatherPlan gp;
-    const uint32_t groups = w.cout / w.group;
+    uint32_t groups = w.cout / w.group;
     const uint64_t total_rows = canvas_elems / pitch;
+    // Groups whose gather lists are all identical (every dense layer) behave like one big group.
+    if (groups > 1u) {
+        bool same = true;
+        if (!w.run_rows.empty()) {
+            const size_t per = w.run_rows.size() / groups;
+            for (uint32_t g = 1; g < groups && same; ++g) same = std::equal(w.run_rows.begin(), w.run_rows.begin() + per, w.run_rows.begin() + g * per);
+        } else {
+            for (uint32_t g = 1; g < groups && same; ++g) same = std::equal(w.idx.begin(), w.idx.begin() + w.fan_in, w.idx.begin() + (size_t)g * w.fan_in);
+        }
+        if (same) { groups = 1u; gp.shared_by_all = true; }
+    }
     if (!(w.group % kTileM == 0u || groups == 1u)) {
         gp.why_not = "group size is not a multiple of 128 neurons";
         return gp;
@@ -233,7 +244,6 @@ bool Executor::add_wave(const HostWave &w) {
     a.pitch = pitch_; a.num_col_tiles64 = tiles64;
     a.act = w.act; a.has_residual = w.has_residual ? 1 : 0;
     const uint32_t groups = w.cout / w.group;
-    a.mtiles_per_group = groups == 1 ? (w.cout + kTileM - 1) / kTileM : std::max(1u, w.group / kTileM);
 
     // ---- weights: container order or device row-major -> tiled ----
     const uint32_t mtiles = (w.cout + kTileM - 1) / kTileM;
@@ -265,6 +275,8 @@ bool Executor::add_wave(const HostWave &w) {
         a.gather_mode = GATHER_BOX;
         a.box_h = gp.box_h; a.boxes_per_group = gp.boxes_per_group;
         a.x_base_off = 0;                 // box rows are absolute canvas rows
+        a.mtiles_per_group = (groups == 1u || gp.shared_by_all) ? (w.cout + kTileM - 1) / kTileM : std::max(1u, w.group / kTileM);
+        if (gp.shared_by_all) a.group = w.cout;   // the run table holds a single list
         dw.umma_capable = true;
     } else if (ok) {
         dw.fma_reason = gp.why_not;
