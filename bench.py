@@ -179,6 +179,151 @@ def cpu_baseline(w: dict, seconds_target: float = 15.0, threads: int | None = No
                       f"substrate sample of {rows} rows; double accumulation, OpenMP over neurons"}
 
 
+
+# ------------------------------------------------------------------------------------------------------------
+# second workload: dense decoder compiled to waves (Llama-3.2-1B shapes), decode batch 64
+# ------------------------------------------------------------------------------------------------------------
+DECODER = dict(hidden=2048, layers=16, heads=32, kv_heads=8, head_dim=64, ffn=8192, vocab=128256, columns=64)
+
+
+def build_decoder_plan(cfg: dict, device: int, seed: int = 7):
+    """Every linear of the decoder is one wave whose neurons gather the full input width (one run). Only the
+    wave chain is built: attention, RMSNorm, RoPE and the SwiGLU product are not waves, so `o` reads the q rows
+    and `down` reads the gate rows as stand-ins of the same shape. Weights N(0, 0.01^2) generated on the device."""
+    import torch
+    from snntome_b200._lib import WaveDesc
+    from snntome_b200.native import NativePlan, fill_normal_f16
+    H, F, V = cfg["hidden"], cfg["ffn"], cfg["vocab"]
+    KV = cfg["kv_heads"] * cfg["head_dim"]
+    pitch = 64
+    rows = {}
+    cur = 0
+    for name, n in [("x0", H), ("x1", H), ("q", H), ("k", KV), ("v", KV), ("h", H), ("g", F), ("u", F), ("logits", V)]:
+        rows[name] = cur
+        cur += n
+    plan = NativePlan.create(cur * pitch, pitch, cfg["columns"], device=device)
+    scratch = torch.empty(max(V * H, F * H), dtype=torch.float16, device=f"cuda:{device}")
+    params = 0
+    counter = [0]
+
+    def add(name, src, dst, cin, cout, act=0, res=None):
+        nonlocal params
+        wv = scratch[: cout * cin]
+        fill_normal_f16(wv, seed * 100003 + counter[0], 0.01)
+        counter[0] += 1
+        torch.cuda.synchronize()
+        groups = cout // 128
+        starts = np.full((groups, 1), rows[src], dtype=np.uint32)
+        d = WaveDesc()
+        d.cout = d.logical_cout = cout
+        d.cin, d.group, d.fan_in, d.fan_in_raw, d.act = cin, 128, cin, cin, act
+        d.has_residual = 1 if res else 0
+        d.y_off = rows[dst] * pitch
+        d.src_off = rows[src] * pitch
+        d.res_off = rows[res] * pitch if res else 0
+        d.run_rows, d.run_len = starts.ctypes.data, cin
+        d.weights, d.weights_on_device = wv.data_ptr(), 1
+        d.name = name.encode()
+        plan.add_wave_desc(d)
+        params += cout * cin
+
+    x_in, x_out = "x0", "x1"
+    for layer in range(cfg["layers"]):
+        add(f"L{layer}.q", x_in, "q", H, H)
+        add(f"L{layer}.k", x_in, "k", H, KV)
+        add(f"L{layer}.v", x_in, "v", H, KV)
+        add(f"L{layer}.o", "q", "h", H, H, res=x_in)
+        add(f"L{layer}.gate", "h", "g", H, F, act=3)
+        add(f"L{layer}.up", "h", "u", H, F)
+        add(f"L{layer}.down", "g", x_out, F, H, res="h")
+        x_in, x_out = x_out, x_in
+    add("lm_head", x_in, "logits", H, V)
+    del scratch
+    torch.cuda.empty_cache()
+    plan.set_io(0, H, rows["logits"] * pitch, V, cfg["columns"])
+    return plan, params, rows
+
+
+def decode_main(args) -> None:
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = dict(DECODER, layers=args.layers)
+    from snntome_b200.native import fill_normal_f16
+    plan, params, rows = build_decoder_plan(cfg, local_rank)
+    canvas = plan.canvas_tensor()
+    fill_normal_f16(canvas[: cfg["hidden"] * 64], 99 + rank, 1.0)
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
+    nw = plan.num_waves
+    warmup = max(3, args.warmup)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(warmup):
+        plan.execute_graph(stream)
+    assert plan.status() == 0
+    # weights (2.47 GB) exceed the 126 MB L2, so every step streams them from HBM again
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    l0 = plan.launch_count
+    t0.record(stream)
+    for _ in range(args.steps):
+        plan.execute_graph(stream)
+    t1.record(stream)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches = plan.launch_count - l0
+    assert plan.status() == 0
+    ms = t0.elapsed_time(t1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+    # per-wave breakdown with direct launches (not part of the timed region)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(nw + 1)]
+    for rep in range(2):
+        ev[0].record(stream)
+        for i in range(nw):
+            plan.execute_wave(i, stream)
+            ev[i + 1].record(stream)
+    torch.cuda.synchronize()
+    wave_us = [ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(nw)]
+    clocks = sampler.stop()
+    peak, kind = measured_peaks()
+    bytes_step = params * 2.0
+    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    infos = [plan.wave_info(i) for i in range(nw)]
+    if rank == 0:
+        line = {"metric": "decode tok/s (wave chain of a 1B dense decoder, batch 64 per GPU)", "value": cfg["columns"] * world / (ms_step * 1e-3),
+                "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+                "config": {"workload": "dense decoder as waves: hidden 2048, 32/8 heads x 64, FFN 8192, vocab 128256, one wave per linear, "
+                                       "64 columns per GPU; wave chain only (no attention / norm / rope kernels)",
+                           "layers": cfg["layers"], "waves_per_step": nw, "params": params, "launch": "one CUDA graph per step",
+                           "l2_policy": "2.47 GB of weights per step exceed the 126 MB L2; no explicit flush"},
+                "roofline": {"bound": "hbm", "kernel": "whole step (k44_wave_umma_kernel<64> small-wave and streaming variants)", "achieved": achieved,
+                             "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s", "frac": achieved / peak, "algorithmic_bytes_per_step": bytes_step,
+                             "traffic": None},
+                "per_wave_us_direct_launch": {"layer0": wave_us[:7], "lm_head": wave_us[-1], "sum": sum(wave_us)},
+                "k_splits": {"layer0": [i.k_splits for i in infos[:7]], "lm_head": infos[-1].k_splits},
+                "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -186,9 +331,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", type=float, default=float(os.environ.get("K44B_BENCH_SCALE", "1.0")))
+    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode"])
+    ap.add_argument("--layers", type=int, default=16, help="decode workload: decoder layers (16 = the 1B shape)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
+    if args.workload == "decode":
+        return decode_main(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

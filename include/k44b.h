@@ -44,6 +44,7 @@ typedef struct k44b_wave_info_t {
     uint32_t cout, group, fan_in, box_rows;   /* box_rows: rows fetched per TMA box, 0 on the index path */
     int32_t path;                             /* 0 FMA kernel, 1 tcgen05 kernel */
     uint32_t n_tile;                          /* columns per tile on the tcgen05 path */
+    uint32_t k_splits;                        /* K splits per tile (partial sums meet in FP32 scratch) */
     uint64_t synapses;                        /* logical_cout * fan_in_raw */
     uint64_t weight_bytes;                    /* packed size on the device */
 } k44b_wave_info_t;
@@ -68,6 +69,9 @@ int k44b_num_waves(void *plan);
 int k44b_wave_info(void *plan, int wave, k44b_wave_info_t *out);
 /* Queue every wave on `stream` (a cudaStream_t; NULL = default stream). Does not synchronise. */
 int k44b_execute(void *plan, void *stream);
+/* Same as k44b_execute, but the wave list is captured once into a CUDA graph and replayed with a single
+ * launch. The first call on a plan builds the graph (do not issue it inside a stream capture). */
+int k44b_execute_graph(void *plan, void *stream);
 /* Queue one wave (0-based) on `stream`. */
 int k44b_execute_wave(void *plan, int wave, void *stream);
 /* Host FP16 in / out in canvas layout: h_in is [input_c][pitch], h_out is [output_c][pitch] (either may be
@@ -79,6 +83,9 @@ int k44b_infer_f16(void *plan, const uint16_t *h_in, uint16_t *h_out, float *out
 int k44b_status(void *plan, uint32_t *status);
 /* Same contract as wavec_gpu_infer_f32 for a native plan. */
 int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, int out_elems, float *out_gpu_ms);
+/* Development aid: 16 SM-clock timestamps recorded by CTA 0 of the last tcgen05 wave kernel when the
+ * library runs with K44B_DEBUG_MODE=16 (all zero otherwise). */
+int k44b_debug_trace(void *plan, long long *out16);
 /* Number of kernels this plan has launched so far. */
 uint64_t k44b_launch_count(void *plan);
 /* Unpack wave `wave`'s device weights to row-major [cout][fan_in] FP16 at device pointer d_dst. */

@@ -25,7 +25,7 @@ class WaveInfo(ctypes.Structure):
     """k44b_wave_info_t (include/k44b.h)."""
     _fields_ = [
         ("cout", c_uint32), ("group", c_uint32), ("fan_in", c_uint32), ("box_rows", c_uint32),
-        ("path", c_int32), ("n_tile", c_uint32), ("synapses", c_uint64), ("weight_bytes", c_uint64),
+        ("path", c_int32), ("n_tile", c_uint32), ("k_splits", c_uint32), ("synapses", c_uint64), ("weight_bytes", c_uint64),
     ]
 
 
@@ -74,10 +74,12 @@ PROTOTYPES = {
     "k44b_num_waves": (c_int, [c_void_p]),
     "k44b_wave_info": (c_int, [c_void_p, c_int, POINTER(WaveInfo)]),
     "k44b_execute": (c_int, [c_void_p, c_void_p]),
+    "k44b_execute_graph": (c_int, [c_void_p, c_void_p]),
     "k44b_execute_wave": (c_int, [c_void_p, c_int, c_void_p]),
     "k44b_infer_f16": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(c_float), c_void_p]),
     "k44b_status": (c_int, [c_void_p, POINTER(c_uint32)]),
     "k44b_infer_f32": (c_int, [c_void_p, _f32p, c_int, _f32p, c_int, _f32p]),
+    "k44b_debug_trace": (c_int, [c_void_p, POINTER(ctypes.c_longlong)]),
     "k44b_launch_count": (c_uint64, [c_void_p]),
     "k44b_wave_weights_rowmajor": (c_int, [c_void_p, c_int, c_void_p]),
     "k44b_set_device": (c_int, [c_void_p, c_int]),

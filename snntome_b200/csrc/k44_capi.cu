@@ -311,6 +311,7 @@ int k44b_wave_info(void *plan, int wave, k44b_wave_info_t *out) {
     out->cout = w.args.cout; out->group = w.args.group; out->fan_in = w.args.fan_in;
     out->box_rows = w.args.gather_mode == GATHER_BOX ? w.args.box_h : 0;
     out->path = w.path; out->n_tile = w.path == PATH_UMMA ? w.desc.n_tile : 64;
+    out->k_splits = w.path == PATH_UMMA ? w.args.k_splits : 1;
     out->synapses = w.synapses; out->weight_bytes = w.weight_bytes;
     return 0;
 }
@@ -318,6 +319,11 @@ int k44b_wave_info(void *plan, int wave, k44b_wave_info_t *out) {
 int k44b_execute(void *plan, void *stream) {
     if (!plan) return set_error("null plan");
     return P(plan)->exec.execute((cudaStream_t)stream) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_execute_graph(void *plan, void *stream) {
+    if (!plan) return set_error("null plan");
+    return P(plan)->exec.execute_graph((cudaStream_t)stream) ? 0 : set_error(P(plan)->exec.err);
 }
 
 int k44b_execute_wave(void *plan, int wave, void *stream) {
@@ -341,6 +347,11 @@ int k44b_status(void *plan, uint32_t *status) {
 int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, int out_elems, float *out_gpu_ms) {
     if (!plan || !h_in || !h_out) return set_error("infer_f32: bad arguments");
     return P(plan)->exec.infer_f32(h_in, in_elems, h_out, out_elems, out_gpu_ms) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_debug_trace(void *plan, long long *out16) {
+    if (!plan || !out16) return set_error("debug_trace: bad arguments");
+    return P(plan)->exec.read_trace(out16) ? 0 : set_error(P(plan)->exec.err);
 }
 
 uint64_t k44b_launch_count(void *plan) { return plan ? P(plan)->exec.launches() : 0; }

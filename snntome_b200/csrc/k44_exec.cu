@@ -158,6 +158,10 @@ void Executor::release() {
         cudaFree(w.d_weights); cudaFree(w.d_gather); cudaFree(w.d_bias); cudaFree(w.d_map); cudaFree(w.d_idx_table);
     }
     waves_.clear();
+    drop_graph();
+    cudaFree(d_scratch_); d_scratch_ = nullptr;
+    cudaFree(d_counters_); d_counters_ = nullptr;
+    scratch_tiles_ = 0;
     cudaFree(canvas_); canvas_ = nullptr;
     cudaFree(d_status_); d_status_ = nullptr;
     cudaFree(d_in_f32_); d_in_f32_ = nullptr;
@@ -312,8 +316,24 @@ bool Executor::add_wave(const HostWave &w) {
             }
             int variant = 0;
             if (const char *e = std::getenv("K44B_UMMA_VARIANT")) variant = std::atoi(e);
+            // Small waves (fewer tiles than SMs): 64-column tiles, two CTAs per SM, and the fan-in cut into
+            // K splits so that every SM streams a share of the weights.
+            uint32_t splits = 1;
+            bool small = (uint64_t)mtiles * (tiles64 / (n_tile / 64u)) < (uint64_t)num_sms_;
+            if (const char *e = std::getenv("K44B_SMALL_WAVE")) small = std::atoi(e) != 0;
+            if (small) {
+                n_tile = 64;
+                const uint32_t tiles = mtiles * tiles64, cap = 2u * (uint32_t)num_sms_;
+                splits = std::max(1u, std::min(cap / tiles, a.num_kstages / 2u));   // all items resident at once: no second round
+                if (const char *e = std::getenv("K44B_SPLITS")) splits = std::max(1u, std::min((uint32_t)std::atoi(e), a.num_kstages));
+            }
+            a.kstages_per_split = (a.num_kstages + splits - 1) / splits;
+            a.k_splits = (a.num_kstages + a.kstages_per_split - 1) / a.kstages_per_split;
             dw.desc = make_umma_desc(n_tile, variant);
-            ok = make_tensor_map(dw);
+            dw.desc.small_wave = small ? 1u : 0u;
+            if (const char *e = std::getenv("K44B_DEBUG_MODE")) dw.desc.debug = (uint32_t)std::atoi(e);
+            if (a.k_splits > 1) ok = reserve_scratch((size_t)mtiles * tiles64);
+            ok = ok && make_tensor_map(dw);
         }
     }
     if (!ok) {
@@ -321,6 +341,7 @@ bool Executor::add_wave(const HostWave &w) {
         return false;
     }
     waves_.push_back(dw);
+    drop_graph();
     return true;
 }
 
@@ -340,25 +361,74 @@ bool Executor::init(const HostPlan &plan, int device, int force_path) {
     return true;
 }
 
+// Split-K partial sums of every wave meet in one shared FP32 scratch area (waves run one after another).
+// Both the scratch and the per-tile arrival counters are zero between launches: the finishing CTA clears them.
+bool Executor::reserve_scratch(size_t tiles) {
+    if (tiles <= scratch_tiles_) return true;
+    if (!check(cudaDeviceSynchronize(), "synchronise")) return false;
+    cudaFree(d_scratch_); cudaFree(d_counters_);
+    d_scratch_ = nullptr; d_counters_ = nullptr; scratch_tiles_ = 0;
+    const size_t sb = tiles * 64u * kTileM * sizeof(float), cb = tiles * sizeof(uint32_t);
+    if (!check(cudaMalloc(&d_scratch_, sb), "split-K scratch allocation") || !check(cudaMalloc(&d_counters_, cb), "split-K counter allocation"))
+        return false;
+    if (!check(cudaMemset(d_scratch_, 0, sb), "scratch clear") || !check(cudaMemset(d_counters_, 0, cb), "counter clear")) return false;
+    scratch_tiles_ = tiles;
+    drop_graph();
+    return true;
+}
+
+void Executor::drop_graph() {
+    if (graph_exec_) { cudaGraphExecDestroy(graph_exec_); graph_exec_ = nullptr; }
+}
+
+bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
+    cudaError_t e;
+    if (w.path == PATH_UMMA) {
+        w.args.scratch = d_scratch_;
+        w.args.counters = d_counters_;
+        e = launch_wave_umma(w.args, w.desc, w.tmap, num_sms_, stream);
+    } else {
+        e = launch_wave_fma(w.args, stream);
+    }
+    ++launches_;
+    return check(e, ("launch of wave '" + w.name + "'").c_str());
+}
+
 bool Executor::execute(cudaStream_t stream) {
     if (!ready()) return fail("executor not initialised");
-    for (auto &w : waves_) {
-        const cudaError_t e = (w.path == PATH_UMMA) ? launch_wave_umma(w.args, w.desc, w.tmap, num_sms_, stream)
-                                                    : launch_wave_fma(w.args, stream);
-        ++launches_;
-        if (e != cudaSuccess) return check(e, ("launch of wave '" + w.name + "'").c_str());
-    }
+    for (auto &w : waves_)
+        if (!launch_one(w, stream)) return false;
     return true;
+}
+
+// The wave list is a fixed sequence: capture it once into a CUDA graph and replay it with one launch call.
+bool Executor::execute_graph(cudaStream_t stream) {
+    if (!ready()) return fail("executor not initialised");
+    if (!graph_exec_) {
+        cudaStream_t cap = nullptr;
+        if (!check(cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking), "capture stream")) return false;
+        cudaGraph_t g = nullptr;
+        bool ok = check(cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal), "begin capture");
+        const uint64_t before = launches_;
+        if (ok) {
+            ok = execute(cap);
+            const cudaError_t e = cudaStreamEndCapture(cap, &g);
+            if (ok) ok = check(e, "end capture");
+        }
+        launches_ = before;                    // capturing is not launching
+        if (ok) ok = check(cudaGraphInstantiate(&graph_exec_, g, 0), "graph instantiate");
+        if (g) cudaGraphDestroy(g);
+        cudaStreamDestroy(cap);
+        if (!ok) { graph_exec_ = nullptr; return false; }
+    }
+    launches_ += waves_.size();
+    return check(cudaGraphLaunch(graph_exec_, stream), "graph launch");
 }
 
 bool Executor::execute_wave(size_t i, cudaStream_t stream) {
     if (!ready()) return fail("executor not initialised");
     if (i >= waves_.size()) return fail("wave index out of range");
-    DeviceWave &w = waves_[i];
-    const cudaError_t e = (w.path == PATH_UMMA) ? launch_wave_umma(w.args, w.desc, w.tmap, num_sms_, stream)
-                                                : launch_wave_fma(w.args, stream);
-    ++launches_;
-    return check(e, ("launch of wave '" + w.name + "'").c_str());
+    return launch_one(waves_[i], stream);
 }
 
 // Host FP16 in / out without any conversion: the input rows are copied straight into the canvas and the
@@ -392,6 +462,12 @@ bool Executor::read_status(uint32_t *status) {
     if (status) *status = st;
     if (st) { cudaMemset(d_status_, 0, 4); err = std::string("kernel status: ") + status_string(st); }
     return true;
+}
+
+bool Executor::read_trace(long long *out16) {
+    if (!ready()) return fail("executor not initialised");
+    return check(cudaDeviceSynchronize(), "synchronise") &&
+           check(cudaMemcpy(out16, reinterpret_cast<char *>(d_status_) + 8, 16 * sizeof(long long), cudaMemcpyDeviceToHost), "trace read");
 }
 
 bool Executor::execute_timed(float *ms) {

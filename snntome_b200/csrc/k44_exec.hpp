@@ -55,11 +55,13 @@ class Executor {
 
     bool execute(cudaStream_t stream);                             // queue every wave; no sync
     bool execute_wave(size_t wave, cudaStream_t stream);          // queue one wave; no sync
+    bool execute_graph(cudaStream_t stream);                      // replay the wave list as one CUDA graph
     // host FP16 rows in canvas layout ([input_c][pitch] in, [output_c][pitch] out), copies on `stream`
     bool infer_f16(const uint16_t *h_in, uint16_t *h_out, float *gpu_ms, cudaStream_t stream);
     bool execute_timed(float *ms);                                 // default stream, event-timed, synchronous
     bool infer_f32(const float *h_in, int in_elems, float *h_out, int out_elems, float *gpu_ms);
     bool read_status(uint32_t *status);                            // synchronises the device
+    bool read_trace(long long *out16);                             // development aid: kernel milestone clocks
     bool weights_to_rowmajor(size_t wave, void *d_dst);            // unpack check: tiled -> [cout][fan_in]
 
     bool ready() const { return canvas_ != nullptr; }
@@ -75,6 +77,9 @@ class Executor {
     bool fail(const std::string &m) { err = m; return false; }
     bool check(cudaError_t e, const char *what);
     bool make_tensor_map(DeviceWave &dw);
+    bool reserve_scratch(size_t tiles);
+    bool launch_one(DeviceWave &w, cudaStream_t stream);
+    void drop_graph();
 
     int device_ = -1, num_sms_ = 148, force_path_ = -1;
     __half *canvas_ = nullptr;
@@ -87,6 +92,10 @@ class Executor {
     float *d_in_f32_ = nullptr, *d_out_f32_ = nullptr;
     cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
     uint64_t launches_ = 0;
+    float *d_scratch_ = nullptr;
+    uint32_t *d_counters_ = nullptr;
+    size_t scratch_tiles_ = 0;
+    cudaGraphExec_t graph_exec_ = nullptr;
 };
 
 const char *status_string(uint32_t st);

@@ -120,20 +120,134 @@ cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s) {
 // ---------------------------------------------------------------------------------------------------
 constexpr int kUmmaThreads = 192;
 
-template <int N_TILE>
+// STAGES_SEL == 0: deep pipeline, one CTA per SM (streaming waves with many tiles).
+// STAGES_SEL == 1: 4 stages, two CTAs per SM (small waves: more CTAs in flight, split-K).
+template <int N_TILE, int STAGES_SEL>
 struct UmmaCfg {
     static constexpr int kColBlocks = N_TILE / 64;
     static constexpr uint32_t kXBytes = (uint32_t)kColBlocks * kStageK * 128u;        // 8 KiB per 64 columns
     static constexpr uint32_t kStageBytes = kStageWBytes + kXBytes;
-    static constexpr int kStages = (N_TILE == 64) ? 8 : (N_TILE == 128 ? 6 : 4);
+    static constexpr int kStages = STAGES_SEL == 1 ? 4 : ((N_TILE == 64) ? 8 : (N_TILE == 128 ? 6 : 4));
+    static constexpr int kCtasPerSm = STAGES_SEL == 1 ? 2 : 1;
     static constexpr uint32_t kTmemCols = 2u * N_TILE;
-    static constexpr uint32_t kSmemBytes = 1024u /*alignment slack*/ + (uint32_t)kStages * kStageBytes + 256u;
+    static constexpr uint32_t kOutStageBytes = 128u * 80u;                           // epilogue staging: 128 rows x (64 + 16 pad) bytes
+    static constexpr uint32_t kSmemBytes = 1024u /*alignment slack*/ + (uint32_t)kStages * kStageBytes + 256u + kOutStageBytes;
 };
 
-template <int N_TILE>
-__global__ void __launch_bounds__(kUmmaThreads, 1)
+__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Shared by the direct and the split-K epilogue: 32 accumulator values of one neuron -> FP16 row segment.
+__device__ __forceinline__ void store_row_segment(const WaveArgs &a, const float (&v)[32], float bias, bool has_map, uint64_t elem_off) {
+    uint4 *dst = reinterpret_cast<uint4 *>(a.canvas + a.y_off + elem_off);
+    const uint4 *rsrc = reinterpret_cast<const uint4 *>(a.canvas + a.res_off + elem_off);
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+        float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (a.has_residual) {
+            const uint4 rv = rsrc[q4];
+            const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(rh[e]); r[2 * e] = f.x; r[2 * e + 1] = f.y; }
+        }
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float lo = finish_value(v[q4 * 8 + 2 * e], bias, r[2 * e], a.act, a.has_residual != 0, has_map);
+            const float hi = finish_value(v[q4 * 8 + 2 * e + 1], bias, r[2 * e + 1], a.act, a.has_residual != 0, has_map);
+            const __half2 h2 = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
+            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+        dst[q4] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+}
+
+// Branch-free activation for the tensor-core epilogue: the activation kind is a template parameter so that the
+// 32 values a thread converts are independent straight-line code (a per-element runtime switch serialises them
+// behind branch latency when only one warp runs per scheduler).
+template <int ACT>
+__device__ __forceinline__ float act_fast(float v) {
+    if (ACT == 1) return fmaxf(v, 0.0f);
+    if (ACT == 2) return __fdividef(1.0f, 1.0f + __expf(-v));
+    if (ACT == 3) return __fdividef(v, 1.0f + __expf(-v));
+    if (ACT == 4) return fmaxf(v, 0.1f * v);
+    if (ACT == 5) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    return v;
+}
+
+// Each thread converts its 32 values (one neuron, 32 columns) to FP16 and parks them in a padded shared-memory
+// slot; the warp then writes the 32 rows back as whole 64-byte pieces (8 rows per instruction), so that every
+// global store fills complete 32-byte sectors. Must be called by all 32 lanes of a warp.
+template <int ACT, bool RES, bool MAP>
+__device__ __forceinline__ void stage_and_store_t(const WaveArgs &a, const float (&v)[32], float bias, bool live, uint32_t oj,
+                                                  uint64_t col0, uint8_t *wstage, uint32_t lane) {
+    uint4 *slot = reinterpret_cast<uint4 *>(wstage + lane * 80u);
+    uint32_t pk[16];
+    if (RES) {
+        const uint4 *rsrc = reinterpret_cast<const uint4 *>(a.canvas + a.res_off + (uint64_t)oj * a.pitch + col0);
+        uint4 rv[4];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) rv[q4] = live ? rsrc[q4] : make_uint4(0, 0, 0, 0);
+        const __half2 *rh = reinterpret_cast<const __half2 *>(rv);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const float2 r = __half22float2(rh[e]);
+            float lo = v[2 * e] + bias, hi = v[2 * e + 1] + bias;
+            if (MAP) { lo += r.x; hi += r.y; }
+            lo = act_fast<ACT>(lo); hi = act_fast<ACT>(hi);
+            if (!MAP) { lo += r.x; hi += r.y; }
+            const __half2 h2 = __floats2half2_rn(lo, hi);
+            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const __half2 h2 = __floats2half2_rn(act_fast<ACT>(v[2 * e] + bias), act_fast<ACT>(v[2 * e + 1] + bias));
+            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) slot[q4] = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+    __syncwarp();
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+        const uint32_t r = 8u * i + (lane >> 2), piece = lane & 3u;
+        const uint32_t oj_r = __shfl_sync(0xffffffffu, oj, r);
+        const int live_r = __shfl_sync(0xffffffffu, live ? 1 : 0, r);
+        const uint4 val = *reinterpret_cast<const uint4 *>(wstage + r * 80u + piece * 16u);
+        if (live_r) *reinterpret_cast<uint4 *>(a.canvas + a.y_off + (uint64_t)oj_r * a.pitch + col0 + piece * 8u) = val;
+    }
+    __syncwarp();
+}
+
+template <int ACT>
+__device__ __forceinline__ void stage_and_store_a(const WaveArgs &a, const float (&v)[32], float bias, bool has_map, bool live, uint32_t oj,
+                                                  uint64_t col0, uint8_t *wstage, uint32_t lane) {
+    if (!a.has_residual) stage_and_store_t<ACT, false, false>(a, v, bias, live, oj, col0, wstage, lane);
+    else if (has_map) stage_and_store_t<ACT, true, true>(a, v, bias, live, oj, col0, wstage, lane);
+    else stage_and_store_t<ACT, true, false>(a, v, bias, live, oj, col0, wstage, lane);
+}
+
+// One uniform branch per 32 values instead of one per value.
+__device__ __forceinline__ void stage_and_store(const WaveArgs &a, const float (&v)[32], float bias, bool has_map, bool live, uint32_t oj,
+                                                uint64_t col0, uint8_t *wstage, uint32_t lane) {
+    switch (a.act) {
+    case 1: stage_and_store_a<1>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    case 2: stage_and_store_a<2>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    case 3: stage_and_store_a<3>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    case 4: stage_and_store_a<4>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    case 5: stage_and_store_a<5>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    default: stage_and_store_a<0>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    }
+}
+
+// Work item = (neuron tile, column tile, K split). With splits == 1 the epilogue writes the canvas directly.
+// With splits > 1 every item adds its partial accumulator into an FP32 scratch tile ([column][neuron] so that
+// a warp's 32 neurons are contiguous), and the item that arrives last at the tile's counter applies the
+// epilogue, stores the rows and leaves scratch and counter zeroed for the next launch. Nobody waits.
+template <int N_TILE, int STAGES_SEL>
+__global__ void __launch_bounds__(kUmmaThreads, UmmaCfg<N_TILE, STAGES_SEL>::kCtasPerSm)
 k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a, const UmmaDesc d) {
-    using Cfg = UmmaCfg<N_TILE>;
+    using Cfg = UmmaCfg<N_TILE, STAGES_SEL>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows of 128 bytes
@@ -146,11 +260,19 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
     uint8_t *ctl_ptr = smem_raw + (ctl - ptx::smem_addr(smem_raw));
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ctl_ptr + 16 * STAGES + 32);
     volatile uint32_t *abort_word = tmem_slot + 1;
+    volatile uint32_t *last_flag = tmem_slot + 2;
+    volatile uint32_t *epi_ok = tmem_slot + 4;       // two slots, alternating per item
+    uint8_t *out_stage = ctl_ptr + 256;              // 128 rows x 80 bytes, one 32-row block per epilogue warp
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    // development aid (debug bit 16): CTA 0 records SM-clock timestamps of its milestones after the status word
+    const bool trace = (d.debug & 16u) && blockIdx.x == 0;
+    auto stamp = [&](int slot) { if (trace) reinterpret_cast<volatile long long *>(a.status + 2)[slot] = clock64(); };
+    if (threadIdx.x == 0) stamp(0);
     const uint32_t tiles_n = a.num_col_tiles64 / Cfg::kColBlocks;
     const uint32_t mtiles = (a.cout + kTileM - 1) / kTileM;
-    const uint32_t total_tiles = mtiles * tiles_n;
+    const uint32_t splits = a.k_splits;
+    const uint32_t total_items = mtiles * tiles_n * splits;
     const uint32_t mtiles_per_group = a.mtiles_per_group;
     const uint32_t boxes_per_stage = kStageK / a.box_h;
 
@@ -166,7 +288,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         *abort_word = 0;
         ptx::fence_mbar_init();
     }
-    if (warp == 1) {
+    if (warp == 1 && !(d.debug & 2u)) {
         ptx::tmem_alloc(ptx::smem_addr(const_cast<uint32_t *>(tmem_slot)), Cfg::kTmemCols);
         ptx::tmem_relinquish();
     }
@@ -174,6 +296,12 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) stamp(1);
+    if (d.debug & 1u) {
+        __syncthreads();
+        if (warp == 1 && !(d.debug & 2u)) ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+        return;
+    }
 
     auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
         const long long t0 = clock64();
@@ -185,6 +313,13 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
             }
         }
     };
+    // item -> (tile, split) and the split's K-stage range
+    auto decode = [&](uint32_t item, uint32_t &tile, uint32_t &ks0, uint32_t &ks1) {
+        tile = item / splits;
+        const uint32_t sp = item % splits;
+        ks0 = sp * a.kstages_per_split;
+        ks1 = min(a.num_kstages, ks0 + a.kstages_per_split);
+    };
 
     if (warp == 0) {
         // ---------------- producer ----------------
@@ -193,17 +328,19 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         const uint64_t pol_x = ptx::policy_evict_last();    // substrate rows are shared between groups
         uint32_t issued = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (uint32_t item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            uint32_t tile, ks0, ks1;
+            decode(item, tile, ks0, ks1);
             const uint32_t mt = tile / tiles_n, ct = tile % tiles_n;
             const uint32_t *rows = a.gather + (uint64_t)(mt / mtiles_per_group) * a.boxes_per_group;
             const uint4 *wsrc = a.w_tiles + (uint64_t)mt * a.num_kstages * (kStageWBytes / 16u);
-            uint32_t cached = 0;
-            for (uint32_t ks = 0; ks < a.num_kstages && ok; ++ks) {
+            uint32_t cached = 0, cached_base = 0xffffffffu;
+            for (uint32_t ks = ks0; ks < ks1 && ok; ++ks) {
                 const uint32_t stage = issued % STAGES, ph = (issued / STAGES) & 1u;
                 if (lane == 0) {
                     ok = wait(empty_bar + 8u * stage, ph ^ 1u);
                     if (ok) {
-                        ptx::mbar_arrive_expect_tx(full_bar + 8u * stage, Cfg::kStageBytes);
+                        ptx::mbar_arrive_expect_tx(full_bar + 8u * stage, (d.debug & 4u) ? kStageWBytes : Cfg::kStageBytes);
                         ptx::bulk_g2s(w_smem + stage * kStageWBytes, wsrc + (uint64_t)ks * (kStageWBytes / 16u), kStageWBytes,
                                       full_bar + 8u * stage, pol_w);
                     }
@@ -212,18 +349,23 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                 if (!ok) break;
                 for (uint32_t b = 0; b < boxes_per_stage; ++b) {
                     const uint32_t bi = ks * boxes_per_stage + b;
-                    if ((bi & 31u) == 0u) cached = (bi + lane < a.boxes_per_group) ? __ldg(rows + bi + lane) : 0u;
+                    if ((bi & ~31u) != cached_base) {          // whole warp fetches the next 32 run rows
+                        cached_base = bi & ~31u;
+                        cached = (cached_base + lane < a.boxes_per_group) ? __ldg(rows + cached_base + lane) : 0u;
+                    }
                     const uint32_t row = __shfl_sync(0xffffffffu, cached, bi & 31u);
-                    if (lane == 0) {
+                    if (lane == 0 && !(d.debug & 4u)) {
 #pragma unroll
                         for (int cb = 0; cb < Cfg::kColBlocks; ++cb)
                             ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + (uint32_t)cb * (kStageK * 128u) + b * a.box_h * 128u,
                                              &tmap, (int32_t)(ct * N_TILE + cb * 64), (int32_t)row, full_bar + 8u * stage, pol_x);
                     }
                 }
+                if (issued == 0 && lane == 0) stamp(2);
                 ++issued;
             }
         }
+        if (lane == 0) stamp(9);
         if (!ok && lane == 0) {
             if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PRODUCER);
             *abort_word = 1u;
@@ -242,27 +384,31 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         if (lane == 0) {
             uint32_t consumed = 0, iter = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+            for (uint32_t item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++iter) {
+                uint32_t tile, ks0, ks1;
+                decode(item, tile, ks0, ks1);
                 const uint32_t acc = iter & 1u;
                 ok = wait(tempty_bar + 8u * acc, ((iter >> 1) & 1u) ^ 1u);
                 if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * N_TILE;
-                for (uint32_t ks = 0; ks < a.num_kstages; ++ks) {
+                for (uint32_t ks = ks0; ks < ks1; ++ks) {
                     const uint32_t stage = consumed % STAGES, ph = (consumed / STAGES) & 1u;
                     ok = wait(full_bar + 8u * stage, ph);
                     if (!ok) break;
+                    if (consumed == 0) stamp(3);
                     ptx::tc_fence_after();
                     const uint64_t a0 = d.a_base | (uint64_t)(((w_smem + stage * kStageWBytes) >> 4) & 0x3fffu);
                     const uint64_t b0 = d.b_base | (uint64_t)(((x_smem + stage * Cfg::kXBytes) >> 4) & 0x3fffu);
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < kStageK / 16u; ++k4)
                         ptx::umma_f16(d_tmem, a0 + (uint64_t)(k4 * d.a_k_step), b0 + (uint64_t)(k4 * d.b_k_step), d.idesc,
-                                      (ks | k4) != 0u ? 1u : 0u);
+                                      (ks != ks0 || k4 != 0u) ? 1u : 0u);
                     ptx::umma_commit(empty_bar + 8u * stage);      // stage reusable once these MMAs retire
                     ++consumed;
                 }
                 if (ok) ptx::umma_commit(tfull_bar + 8u * acc);     // accumulator complete
+                if (iter == 0) stamp(4);
             }
             if (!ok) {
                 if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_MMA);
@@ -276,48 +422,81 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         const bool has_map = a.cout_map != nullptr;
         uint32_t iter = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+        for (uint32_t item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++iter) {
+            uint32_t tile, ks0, ks1;
+            decode(item, tile, ks0, ks1);
             const uint32_t mt = tile / tiles_n, ct = tile % tiles_n, acc = iter & 1u;
-            ok = wait(tfull_bar + 8u * acc, (iter >> 1) & 1u);
-            ok = __all_sync(0xffffffffu, ok);
+            // one thread waits (bounded) and tells the other 127, so that all four warps take the same branch
+            if (threadIdx.x == 64u) epi_ok[iter & 1u] = wait(tfull_bar + 8u * acc, (iter >> 1) & 1u) ? 1u : 0u;
+            epilogue_bar_sync();
+            ok = epi_ok[iter & 1u] != 0u;
             if (!ok) break;
+            if (iter == 0 && threadIdx.x == 64u) stamp(5);
             ptx::tc_fence_after();
-            const uint32_t j = mt * kTileM + quarter * 32u + lane;
+            const uint32_t r_in_tile = quarter * 32u + lane;
+            const uint32_t j = mt * kTileM + r_in_tile;
             const bool live = j < a.cout;
             const uint32_t oj = (live && has_map) ? a.cout_map[j] : j;
             const float bias = (live && a.bias) ? __half2float(a.bias[j]) : 0.0f;
             const uint64_t o = (uint64_t)oj * a.pitch + (uint64_t)ct * N_TILE;
+            if (splits == 1u) {
 #pragma unroll 1
-            for (uint32_t c0 = 0; c0 < (uint32_t)N_TILE; c0 += 32u) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * N_TILE + c0, v);
-                ptx::tmem_ld_wait();
-                if (live) {
-                    uint4 *dst = reinterpret_cast<uint4 *>(a.canvas + a.y_off + o + c0);
-                    const uint4 *rsrc = reinterpret_cast<const uint4 *>(a.canvas + a.res_off + o + c0);
+                for (uint32_t c0 = 0; c0 < (uint32_t)N_TILE; c0 += 32u) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * N_TILE + c0, v);
+                    ptx::tmem_ld_wait();
+                    float f[32];
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        if (a.has_residual) {
-                            const uint4 rv = rsrc[q4];
-                            const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(rh[e]); r[2 * e] = f.x; r[2 * e + 1] = f.y; }
-                        }
-                        uint32_t pk[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float lo = finish_value(__uint_as_float(v[q4 * 8 + 2 * e]), bias, r[2 * e], a.act, a.has_residual != 0, has_map);
-                            const float hi = finish_value(__uint_as_float(v[q4 * 8 + 2 * e + 1]), bias, r[2 * e + 1], a.act, a.has_residual != 0, has_map);
-                            const __half2 h2 = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
-                            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
-                        }
-                        dst[q4] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                    }
+                    for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
+                    if (d.debug & 32u) { if (live) store_row_segment(a, f, bias, has_map, o + c0); }
+                    else if (!(d.debug & 8u)) stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
                 }
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(tempty_bar + 8u * acc);
+                if (iter == 0 && threadIdx.x == 64u) stamp(6);
+            } else if (d.debug & 8u) {
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(tempty_bar + 8u * acc);
+            } else {
+                float *sc = a.scratch + (uint64_t)tile * (N_TILE * kTileM) + r_in_tile;
+#pragma unroll 1
+                for (uint32_t c0 = 0; c0 < (uint32_t)N_TILE; c0 += 32u) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * N_TILE + c0, v);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) atomicAdd(sc + (uint64_t)(c0 + e) * kTileM, __uint_as_float(v[e]));
+                }
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(tempty_bar + 8u * acc);      // accumulator free: the next item's MMAs may start
+                if (iter == 0 && threadIdx.x == 64u) stamp(6);
+                __threadfence();
+                if (iter == 0 && threadIdx.x == 64u) stamp(10);
+                epilogue_bar_sync();
+                if (threadIdx.x == 64u) {
+                    const uint32_t prev = atomicAdd(a.counters + tile, 1u);
+                    *last_flag = (prev == splits - 1u) ? 1u : 0u;
+                }
+                epilogue_bar_sync();
+                if (*last_flag != 0u) {
+                    __threadfence();
+#pragma unroll 1
+                    for (uint32_t c0 = 0; c0 < (uint32_t)N_TILE; c0 += 32u) {
+                        float f[32];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            float *p = sc + (uint64_t)(c0 + e) * kTileM;
+                            f[e] = __ldcg(p);
+                            __stcg(p, 0.0f);
+                        }
+                        if (d.debug & 32u) { if (live) store_row_segment(a, f, bias, has_map, o + c0); }
+                        else stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
+                    }
+                    if (threadIdx.x == 64u) a.counters[tile] = 0u;
+                }
+                if (iter == 0 && threadIdx.x == 64u) stamp(7);
+                epilogue_bar_sync();                          // last_flag is rewritten by the next item
             }
-            ptx::tc_fence_before();
-            ptx::mbar_arrive(tempty_bar + 8u * acc);
         }
         if (!ok && lane == 0) {
             if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_EPILOGUE);
@@ -326,32 +505,48 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
     }
     ptx::tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) stamp(8);
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
 }
 
+template <int N_TILE, int SEL>
+static cudaError_t umma_attr() {
+    return cudaFuncSetAttribute(k44_wave_umma_kernel<N_TILE, SEL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)UmmaCfg<N_TILE, SEL>::kSmemBytes);
+}
+
 cudaError_t umma_kernel_setup() {
     cudaError_t e;
-    e = cudaFuncSetAttribute(k44_wave_umma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)UmmaCfg<64>::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(k44_wave_umma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)UmmaCfg<128>::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(k44_wave_umma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)UmmaCfg<256>::kSmemBytes);
+    if ((e = umma_attr<64, 0>()) != cudaSuccess) return e;
+    if ((e = umma_attr<128, 0>()) != cudaSuccess) return e;
+    if ((e = umma_attr<256, 0>()) != cudaSuccess) return e;
+    return umma_attr<64, 1>();
+}
+
+template <int N_TILE, int SEL>
+static cudaError_t umma_launch(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s) {
+    using Cfg = UmmaCfg<N_TILE, SEL>;
+    const uint32_t mtiles = (a.cout + kTileM - 1) / kTileM;
+    const uint32_t items = mtiles * (a.num_col_tiles64 / (N_TILE / 64u)) * a.k_splits;
+    const uint32_t cap = (uint32_t)num_sms * Cfg::kCtasPerSm;
+    const uint32_t grid = items < cap ? items : cap;
+    k44_wave_umma_kernel<N_TILE, SEL><<<grid, kUmmaThreads, Cfg::kSmemBytes, s>>>(tmap, a, d);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s) {
-    const uint32_t mtiles = (a.cout + kTileM - 1) / kTileM;
-    const uint32_t tiles = mtiles * (a.num_col_tiles64 / (d.n_tile / 64u));
-    const uint32_t grid = tiles < (uint32_t)num_sms ? tiles : (uint32_t)num_sms;
+    if (a.k_splits == 0 || a.kstages_per_split == 0) return cudaErrorInvalidValue;
+    if (a.k_splits > 1 && (!a.scratch || !a.counters)) return cudaErrorInvalidValue;
+    if (d.small_wave) return d.n_tile == 64 ? umma_launch<64, 1>(a, d, tmap, num_sms, s) : cudaErrorInvalidValue;
     switch (d.n_tile) {
-    case 64: k44_wave_umma_kernel<64><<<grid, kUmmaThreads, UmmaCfg<64>::kSmemBytes, s>>>(tmap, a, d); break;
-    case 128: k44_wave_umma_kernel<128><<<grid, kUmmaThreads, UmmaCfg<128>::kSmemBytes, s>>>(tmap, a, d); break;
-    case 256: k44_wave_umma_kernel<256><<<grid, kUmmaThreads, UmmaCfg<256>::kSmemBytes, s>>>(tmap, a, d); break;
+    case 64: return umma_launch<64, 0>(a, d, tmap, num_sms, s);
+    case 128: return umma_launch<128, 0>(a, d, tmap, num_sms, s);
+    case 256: return umma_launch<256, 0>(a, d, tmap, num_sms, s);
     default: return cudaErrorInvalidValue;
     }
-    return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -58,6 +58,10 @@ struct WaveArgs {
     uint32_t box_h = 0, boxes_per_group = 0;
     int act = 0;
     int has_residual = 0;
+    // split-K (tensor-core path): partial sums meet in an FP32 scratch tile, the last arrival finishes the rows
+    uint32_t k_splits = 1, kstages_per_split = 0;
+    float *scratch = nullptr;             // [tiles][N_TILE][128] FP32, all zero between launches
+    uint32_t *counters = nullptr;         // [tiles], all zero between launches
 };
 
 // tcgen05 operand descriptors are assembled on the host (see k44_exec.cu) and passed in.
@@ -66,7 +70,9 @@ struct UmmaDesc {
     uint32_t a_k_step = 0, b_k_step = 0;  // start-address increment per K=16 step, 16-byte units
     uint32_t idesc = 0;
     uint32_t n_tile = 64;
+    uint32_t small_wave = 0;              // 1: 4-stage, two-CTAs-per-SM variant (N_TILE 64 only)
     unsigned long long wait_cycles = 0;   // bound for every barrier wait
+    uint32_t debug = 0;                   // development switches (0 in production)
 };
 
 cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s);

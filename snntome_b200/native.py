@@ -157,6 +157,11 @@ class NativePlan:
             return torch.cuda.current_stream().cuda_stream
         return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
 
+    def execute_graph(self, stream=None) -> None:
+        """Replay all waves as one CUDA graph (built on first use)."""
+        if self._lib.k44b_execute_graph(self._ptr, ctypes.c_void_p(self._stream_ptr(stream))) != 0:
+            raise NativeError(f"execute_graph: {last_error()}")
+
     def execute_wave(self, wave: int, stream=None) -> None:
         if self._lib.k44b_execute_wave(self._ptr, int(wave), ctypes.c_void_p(self._stream_ptr(stream))) != 0:
             raise NativeError(f"execute_wave: {last_error()}")

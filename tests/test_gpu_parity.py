@@ -217,7 +217,9 @@ def test_wavec_surface_end_to_end(tmp_path):
     npn = NativePlan.from_tcff(path)
     assert npn.num_waves == 2
     y2, _ = npn.infer_f32(x, dims[2] * cols)
-    assert np.array_equal(y2.reshape(dims[2], cols), y[:, 0, :])
+    # split-K partial sums are combined with FP32 atomics, whose order varies from run to run
+    ok, err, k = O.compare(O.f32_to_f16(y2.reshape(dims[2], cols)), O.f32_to_f16(y[:, 0, :]), RTOL, ATOL)
+    assert ok, (err, k)
 
 
 def test_bad_plan_is_rejected_before_launch():
@@ -225,3 +227,58 @@ def test_bad_plan_is_rejected_before_launch():
     plan.waves[0].idx[3, 7] = plan.canvas_elems
     with pytest.raises(native.NativeError, match="leaves the canvas"):
         NativePlan.from_plan(plan)
+
+
+@pytest.mark.parametrize("splits", [0, 2, 3, 7, 32])
+def test_split_k_small_waves(splits, monkeypatch):
+    """Waves with fewer 128-neuron tiles than SMs cut their fan-in into K splits whose partial sums meet in an
+    FP32 scratch tile; the scratch must come back zeroed (second run equals the first)."""
+    import torch
+    if splits:
+        monkeypatch.setenv("K44B_SPLITS", str(splits))
+    plan = synth.dense_chain(seed=110, dims=[2048, 320, 512, 200], columns=64, act=ACT_SILU, weight_std=0.03,
+                             residual_from={3: 0})
+    x = synth.random_input(plan, 22)
+    want = O.run_plan(plan, x)
+    npn = NativePlan.from_plan(plan, force_path=PATH_UMMA)
+    infos = [npn.wave_info(i) for i in range(npn.num_waves)]
+    assert all(i.path == PATH_UMMA for i in infos)
+    assert infos[0].k_splits > 1
+    if splits:
+        assert infos[0].k_splits == min(splits, 32) or infos[0].k_splits == -(-32 // -(-32 // splits))
+    canvas = npn.canvas_tensor()
+    xt = torch.from_numpy(x.view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    results = []
+    for rep in range(3):
+        canvas.zero_()
+        canvas[: xt.numel()] = xt
+        if rep == 2:
+            npn.execute_graph()
+        else:
+            npn.execute()
+        assert npn.status() == 0
+        results.append(canvas.cpu().numpy().view(np.uint16))
+        check(plan, results[-1], want)
+    # FP32 atomics commute only up to rounding: repeated runs agree within the parity tolerance, checked above;
+    # with a single split the result is bit-stable
+    npn.close()
+
+
+def test_graph_replay_equals_direct_launches():
+    import torch
+    plan = synth.config0()
+    x = synth.random_input(plan, 23)
+    npn = NativePlan.from_plan(plan)
+    canvas = npn.canvas_tensor()
+    xt = torch.from_numpy(x.view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    canvas[: xt.numel()] = xt
+    npn.execute()
+    assert npn.status() == 0
+    a = canvas.cpu().numpy().view(np.uint16).copy()
+    before = npn.launch_count
+    for _ in range(3):
+        canvas[xt.numel():].zero_()
+        npn.execute_graph()
+    assert npn.status() == 0
+    assert npn.launch_count == before + 3 * npn.num_waves
+    assert np.array_equal(canvas.cpu().numpy().view(np.uint16), a)
