@@ -91,6 +91,34 @@ uint64_t k44b_launch_count(void *plan);
 /* Unpack wave `wave`'s device weights to row-major [cout][fan_in] FP16 at device pointer d_dst. */
 int k44b_wave_weights_rowmajor(void *plan, int wave, void *d_dst);
 
+/* One tensor-core wave that allocates nothing. This entry point has no counterpart in the reference.
+ *
+ * For callers that may not let the library allocate device memory: processes whose HBM is entirely owned by
+ * the host framework's arena, callers under a fixed memory budget, and latency-critical sections that cannot
+ * take the device-wide synchronisation of cudaMalloc / cudaFree. Everything the wave touches is passed in as
+ * device pointers owned by the caller; the split-K partial sums, arrival counters and status word live in a
+ * fixed array inside the library image (about 2 MiB per GPU, present for the life of the process).
+ *
+ *   d_canvas         FP16 canvas holding the gathered rows and receiving the output rows (rows of `pitch`)
+ *   d_weights_tiled  weights in the library's packed order: [cout/128 rounded up][ceil(fan_in/64)] blocks of
+ *                    16 KiB; inside a block neuron row r (0..127) is 128 bytes and the 16-byte chunk c of its 64
+ *                    synapses sits at chunk position c ^ (r & 7); rows >= cout and synapses >= fan_in are zero
+ *   d_box_rows       [cout/group][ceil(fan_in/64) * 64/rows_per_box] first canvas row of every box of
+ *                    `rows_per_box` consecutive rows (what k44b_analyze_gather returns)
+ *   d_bias           [cout] FP16 or NULL;  act as in k44b_wave_desc;  y_off = element offset of output row 0
+ *   k_splits         1..ceil(fan_in/64): how many CTAs share one output tile's fan-in
+ *
+ * Limits: (cout/128 rounded up) * (pitch/64) <= K44B_STATIC_MAX_TILES, otherwise the call fails with a message
+ * naming the limit; no residual and no row map. The first call on a device resolves the array's address and
+ * sets kernel attributes: make that call outside any stream capture. Every call uses the same array and
+ * clears the part it needs first, so two calls that overlap on one GPU (different streams or threads) race.
+ * The call queues its work on `stream` and returns after the wave has finished and its status was checked.
+ * Returns 0, or -1 with a message copied to `err` (if given). Calls no cudaMalloc / cudaFree. */
+#define K44B_STATIC_MAX_TILES 64
+int k44b_wave_forward_static(void *d_canvas, uint64_t canvas_elems, uint32_t pitch, const void *d_weights_tiled,
+                             const uint32_t *d_box_rows, uint32_t rows_per_box, const uint16_t *d_bias, uint32_t cout, uint32_t group,
+                             uint32_t fan_in, int act, uint64_t y_off, uint32_t k_splits, void *stream, char *err, uint32_t err_capacity);
+
 /* Handle-based plans (wavec_*): device used by wavec_gpu_init_plan, and access to the executor's plan. */
 int k44b_set_device(void *wavec_handle, int device);
 int k44b_set_force_path(void *wavec_handle, int force_path);

@@ -82,6 +82,8 @@ PROTOTYPES = {
     "k44b_debug_trace": (c_int, [c_void_p, POINTER(ctypes.c_longlong)]),
     "k44b_launch_count": (c_uint64, [c_void_p]),
     "k44b_wave_weights_rowmajor": (c_int, [c_void_p, c_int, c_void_p]),
+    "k44b_wave_forward_static": (c_int, [c_void_p, c_uint64, c_uint32, c_void_p, c_void_p, c_uint32, c_void_p, c_uint32, c_uint32, c_uint32,
+                                         c_int, c_uint64, c_uint32, c_void_p, c_char_p, c_uint32]),
     "k44b_set_device": (c_int, [c_void_p, c_int]),
     "k44b_set_force_path": (c_int, [c_void_p, c_int]),
     "k44b_handle_plan": (c_void_p, [c_void_p]),
