@@ -324,6 +324,146 @@ def decode_main(args) -> None:
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------------------
+# third workload: cluster-pruned 8B decoder, neuron-sharded per wave with an all-gather of the wave's rows
+# ------------------------------------------------------------------------------------------------------------
+PRUNED = dict(hidden=4096, layers=32, kv=1024, ffn=14336, vocab=128256, columns=256, cluster=32, keep=0.10)
+
+
+def sharded_main(args) -> None:
+    """Llama-3-8B shaped wave chain; every 128-neuron group keeps 10 % of its 32-row input clusters (uniform,
+    seeded); the lm_head stays dense. Rank r owns rows [r*cout/n, (r+1)*cout/n) of every wave and only their
+    weights; after each wave the rows are all-gathered in place on the replicated canvas (NCCL over NVLink)."""
+    import torch
+    import torch.distributed as dist
+    from snntome_b200 import shard, synth
+    from snntome_b200._lib import WaveDesc
+    from snntome_b200.native import NativePlan, fill_normal_f16
+    rank = int(os.environ.get("RANK", "0")); local_rank = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = dict(PRUNED, layers=args.layers if args.layers != 16 else PRUNED["layers"])
+    H, F, V, KV, C = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["kv"], cfg["columns"]
+    pitch = C
+    rows, cur = {}, 0
+    for name, n in [("x0", H), ("x1", H), ("q", H), ("k", KV), ("v", KV), ("h", H), ("g", F), ("u", F), ("logits", V)]:
+        rows[name] = cur; cur += n
+    plan = NativePlan.create(cur * pitch, pitch, C, device=local_rank)
+    waves = []       # (y_off, cout_total, block_elems)
+    kept_params = 0
+    scratch = torch.empty(max(V // world * H, 1), dtype=torch.float16, device="cuda")
+
+    def add(name, wi, src, dst, cin, cout, act=0, res=None, dense=False):
+        nonlocal kept_params
+        blk = cout // world
+        assert cout % world == 0 and blk % 128 == 0, f"{name}: {cout} rows do not split into {world} blocks of whole 128-neuron groups"
+        r0 = rank * blk
+        groups = blk // 128
+        if dense:
+            fan_in, run_len = cin, cin
+            starts = np.full((groups, 1), rows[src], dtype=np.uint32)
+        else:
+            clusters = cin // cfg["cluster"]
+            keep = max(2, int(round(cfg["keep"] * clusters / 2)) * 2)
+            fan_in, run_len = keep * cfg["cluster"], cfg["cluster"]
+            ctr = (np.arange(groups * keep, dtype=np.uint64) + np.uint64((r0 // 128) * keep))
+            starts = (rows[src] + synth.uniform_int(SEED + 5, wi, ctr, clusters).astype(np.int64) * cfg["cluster"]).astype(np.uint32).reshape(groups, keep)
+            starts.sort(axis=1)
+        wv = scratch[: blk * fan_in]
+        fill_normal_f16(wv, SEED * 7919 + wi * 64 + rank, 0.01)
+        torch.cuda.synchronize()
+        d = WaveDesc()
+        d.cout = d.logical_cout = blk
+        d.cin, d.group, d.fan_in, d.fan_in_raw, d.act = cin, 128, fan_in, fan_in, act
+        d.has_residual = 1 if res else 0
+        d.y_off = (rows[dst] + r0) * pitch
+        d.res_off = (rows[res] + r0) * pitch if res else 0
+        d.run_rows, d.run_len = starts.ctypes.data, run_len
+        d.weights, d.weights_on_device = wv.data_ptr(), 1
+        d.name = name.encode()
+        plan.add_wave_desc(d)
+        waves.append((rows[dst] * pitch, cout * pitch, blk * pitch))
+        kept_params += cout * fan_in
+
+    x_in, x_out, wi = "x0", "x1", 0
+    for layer in range(cfg["layers"]):
+        for name, src, dst, cin, cout, act, res in [("q", x_in, "q", H, H, 0, None), ("k", x_in, "k", H, KV, 0, None), ("v", x_in, "v", H, KV, 0, None),
+                                                    ("o", "q", "h", H, H, 0, x_in), ("gate", "h", "g", H, F, 3, None), ("up", "h", "u", H, F, 0, None),
+                                                    ("down", "g", x_out, F, H, 0, "h")]:
+            add(f"L{layer}.{name}", wi, src, dst, cin, cout, act, res); wi += 1
+        x_in, x_out = x_out, x_in
+    # vocab 128256 = 1002 groups of 128: pad the sharded lm_head to a multiple of world*128 rows would change the shape,
+    # so it is split only when it divides evenly; otherwise every rank computes the whole (replicated) lm_head.
+    lm_sharded = (V % (world * 128) == 0)
+    if lm_sharded:
+        add("lm_head", wi, x_in, "logits", H, V, dense=True)
+    else:
+        w_save, r_save = world, rank
+        world_, rank_ = world, rank
+        world, rank = 1, 0
+        scratch = torch.empty(V * H, dtype=torch.float16, device="cuda") if scratch.numel() < V * H else scratch
+        add("lm_head", wi, x_in, "logits", H, V, dense=True)
+        world, rank = world_, rank_
+    del scratch
+    torch.cuda.empty_cache()
+    canvas = plan.canvas_tensor()
+    fill_normal_f16(canvas[: H * pitch], 4242, 1.0)       # same input on every rank (replicated canvas)
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
+    nw = plan.num_waves
+
+    def step():
+        for i in range(nw):
+            plan.execute_wave(i, stream)
+            y_off, total, blk = waves[i]
+            if world > 1 and blk != total:
+                out = canvas[y_off: y_off + total]
+                dist.all_gather_into_tensor(out, out[rank * blk: (rank + 1) * blk])
+
+    warmup = max(3, args.warmup)
+    sampler = ClockSampler(local_rank); sampler.start()
+    for _ in range(warmup):
+        step()
+    assert plan.status() == 0
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    l0 = plan.launch_count
+    t0.record(stream)
+    for _ in range(args.steps):
+        step()
+    t1.record(stream)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    assert plan.status() == 0
+    ms = t0.elapsed_time(t1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+    ms_step = ms / args.steps
+    clocks = sampler.stop()
+    checksum = float(canvas[rows["logits"] * pitch: rows["logits"] * pitch + 4096].float().abs().sum().item())
+    gather_bytes = sum(total * 2 * (world - 1) // world for (_, total, blk) in waves if blk != total)
+    if rank == 0:
+        peak, kind = measured_peaks()
+        bytes_rank = kept_params * 2.0 / (world if lm_sharded else 1)
+        line = {"metric": "decode tok/s (cluster-pruned 8B wave chain, neuron-sharded, batch 256)", "value": C / (ms_step * 1e-3), "unit": "tok/s",
+                "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+                "config": {"workload": "Llama-3-8B shaped wave chain, 90 % of 32-row input clusters removed per 128-neuron group, dense lm_head, "
+                                       "batch 256; rows of every wave split over the ranks, per-wave in-place NCCL all-gather",
+                           "layers": cfg["layers"], "waves_per_step": nw, "kept_params": kept_params, "lm_head_sharded": lm_sharded,
+                           "allgather_bytes_received_per_rank_per_step": gather_bytes},
+                "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9, "peak": peak,
+                             "peak_kind": f"of {kind}", "unit": "GB/s", "frac": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9 / peak, "traffic": None},
+                "cpu_baseline": None, "e2e": None, "gpu_launches": int(plan.launch_count - l0), "checksum": checksum, "clocks": clocks}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -331,13 +471,15 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", type=float, default=float(os.environ.get("K44B_BENCH_SCALE", "1.0")))
-    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode"])
+    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "pruned-sharded"])
     ap.add_argument("--layers", type=int, default=16, help="decode workload: decoder layers (16 = the 1B shape)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     if args.workload == "decode":
         return decode_main(args)
+    if args.workload == "pruned-sharded":
+        return sharded_main(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -1,0 +1,65 @@
+"""Two-GPU check of neuron sharding with the real kernels: each rank runs its rows of every wave on its own
+GPU and the rows are all-gathered in place over NCCL. Skipped where fewer than two GPUs are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from snntome_b200 import shard, synth
+from snntome_b200.plan import ACT_RELU
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _plan():
+    return synth.sparse_plan(seed=81, input_rows=2048, waves=3, cout=1024, runs=8, run_len=32, columns=128, group=128, act=ACT_RELU)
+
+
+def _worker(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    from snntome_b200.native import NativePlan
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        plan = _plan()
+        x = synth.random_input(plan, 82)
+        mine = shard.shard_plan(plan, rank, world)
+        npn = NativePlan.from_plan(mine, device=rank)
+        canvas = npn.canvas_tensor()
+        xt = torch.from_numpy(x.view(np.int16).reshape(-1)).cuda().view(torch.float16)
+        canvas[: xt.numel()] = xt
+        runner = shard.NeuronShardedRunner(plan, rank, world, canvas, lambda i: npn.execute_wave(i))
+        runner.run()
+        assert npn.status() == 0
+        np.save(os.path.join(out_dir, f"canvas{rank}.npy"), canvas.cpu().numpy().view(np.uint16))
+        npn.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_neuron_sharding_matches_oracle(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    plan = _plan()
+    want = O.run_plan(plan, synth.random_input(plan, 82))
+    for r in range(2):
+        got = np.load(tmp_path / f"canvas{r}.npy")
+        for w in plan.waves:
+            a, b = w.y_off, w.y_off + w.cout * plan.pitch
+            ok, err, k = O.compare(got[a:b], want[a:b], 2e-3, 1e-3)
+            assert ok, (r, w.name, err, k)
+    assert np.array_equal(np.load(tmp_path / "canvas0.npy"), np.load(tmp_path / "canvas1.npy"))
