@@ -38,6 +38,11 @@ typedef struct k44b_wave_desc {
     const uint16_t *bias;     /* host [cout] FP16 or NULL */
     const uint16_t *cout_map; /* host [cout] logical row -> stored row, or NULL */
     const char *name;         /* optional */
+    /* Receptive-field token shift (optional): entry s of a group (one per synapse when `idx` is given, one per
+     * run when `run_rows` is given) reads its row that many columns earlier; columns whose position inside
+     * their frame of `frame_len` columns (0 = the whole row) is below the shift read zero. */
+    const uint8_t *shifts;
+    uint32_t frame_len;
 } k44b_wave_desc;
 
 typedef struct k44b_wave_info_t {

@@ -146,6 +146,12 @@ void k44o_wmma_to_rowmajor(const uint16_t *wmma, uint16_t *row_major, uint32_t c
 // the final store. Padded synapse slots are consumed as stored (index 0, weight 0), exactly like
 // the reference kernels do.
 //
+// Token shift (the receptive-field variant; the reference expresses a shifted tap as an element-granular
+// offset, kernels/cuda/kernel44_cuda_pack.cuh:153-159, wavec/k44_plan_types.hpp:592-600): when `shifts` is given,
+// synapse s of group g reads its row `shifts[g*B+s]` columns earlier, and — causal padding, which the flat
+// offsets of the reference cannot express — columns whose position inside their frame of `frame_len` columns
+// is smaller than the shift read zero instead of the previous frame's tail (frame_len 0: one frame per row).
+//
 // rows_begin/rows_end restrict the neurons computed (sampled checks on very large waves).
 // Returns 0, or -1 if an index would leave the canvas (nothing is written in that case).
 int k44o_wave_forward(uint16_t *canvas, uint64_t canvas_elems, const uint16_t *w_row_major,
@@ -153,7 +159,7 @@ int k44o_wave_forward(uint16_t *canvas, uint64_t canvas_elems, const uint16_t *w
                       uint32_t cout, uint32_t group, uint32_t B, int act, int has_residual,
                       uint64_t y_off, uint64_t res_off, uint64_t x_base_off, uint32_t pitch,
                       const uint32_t *tile_off_x, const uint32_t *tile_off_y, uint32_t num_tiles,
-                      uint32_t rows_begin, uint32_t rows_end) {
+                      uint32_t rows_begin, uint32_t rows_end, const uint8_t *shifts, uint32_t frame_len) {
     if (rows_end > cout) rows_end = cout;
     // bounds check first: every read and write must stay inside the canvas
     uint32_t max_idx = 0;
@@ -191,7 +197,16 @@ int k44o_wave_forward(uint16_t *canvas, uint64_t canvas_elems, const uint16_t *w
                 for (uint32_t s = 0; s < B; ++s) {
                     const double w = wrow[s];
                     const uint16_t *xr = xt + irow[s];
-                    for (int c = 0; c < 64; ++c) acc[c] += w * (double)f16_to_f32(xr[c]);
+                    if (!shifts) {
+                        for (int c = 0; c < 64; ++c) acc[c] += w * (double)f16_to_f32(xr[c]);
+                    } else {
+                        const uint32_t sh = shifts[(uint64_t)(j / group) * B + s];
+                        const uint32_t flen = frame_len ? frame_len : pitch;
+                        for (int c = 0; c < 64; ++c) {
+                            const uint32_t col = tile_off_x[t] % pitch + (uint32_t)c;     // column inside the row
+                            if (col % flen >= sh) acc[c] += w * (double)f16_to_f32(xr[(int64_t)c - (int64_t)sh]);
+                        }
+                    }
                 }
                 const uint16_t *rr = has_residual ? canvas + res_off + tile_off_y[t] + out_j * pitch : nullptr;
                 uint16_t *o = out.data() + ((size_t)jj * num_tiles + t) * 64;

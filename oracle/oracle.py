@@ -74,7 +74,7 @@ def lib() -> ctypes.CDLL:
             u16p, ctypes.c_uint64, u16p, u32p, u16p, u16p,
             ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, ctypes.c_int,
             ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32,
-            u32p, u32p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32]
+            u32p, u32p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, u8p, ctypes.c_uint32]
         L.k44o_wave_forward.restype = ctypes.c_int
         L.k44o_dot_stage3.argtypes = [u16p, u16p, ctypes.c_uint32, ctypes.c_float, f32p]
         L.k44o_num_threads.restype = ctypes.c_int
@@ -153,13 +153,18 @@ def wave_forward(canvas: np.ndarray, wave, plan, rows: tuple[int, int] | None = 
     assert canvas.dtype == np.uint16 and canvas.flags.c_contiguous
     toff = plan.tile_offsets()
     r0, r1 = rows if rows is not None else (0, wave.cout)
+    shifts = getattr(wave, "shifts", None)
+    if shifts is not None:
+        shifts = np.ascontiguousarray(shifts, dtype=np.uint8)
+        assert shifts.shape == wave.idx.shape
     rc = lib().k44o_wave_forward(
         _p(canvas, u16p), canvas.size, _p(wave.weights, u16p), _p(wave.idx, u32p),
         _p(wave.bias, u16p) if wave.bias is not None else None,
         _p(wave.cout_map, u16p) if wave.cout_map is not None else None,
         wave.cout, wave.group, wave.fan_in, int(wave.act), 1 if wave.has_residual else 0,
         wave.y_off, wave.res_off, wave.x_base_off, plan.pitch,
-        _p(toff, u32p), _p(toff, u32p), toff.size, r0, r1)
+        _p(toff, u32p), _p(toff, u32p), toff.size, r0, r1,
+        _p(shifts, u8p) if shifts is not None else None, int(getattr(wave, "frame_len", 0) or 0))
     if rc != 0:
         raise IndexError("oracle: gather or store offset outside the canvas")
 
@@ -188,9 +193,16 @@ def wave_forward_numpy(canvas: np.ndarray, wave, plan) -> None:
     out_rows = []
     ncols = plan.pitch
     col = np.arange(ncols, dtype=np.int64)
+    shifts = getattr(wave, "shifts", None)
+    flen = int(getattr(wave, "frame_len", 0) or 0) or ncols
     for j in range(wave.cout):
         irow = wave.idx[j // wave.group].astype(np.int64) + wave.x_base_off
-        x = cv[irow[:, None] + col[None, :]].astype(np.float64)          # [B, pitch]
+        if shifts is None:
+            x = cv[irow[:, None] + col[None, :]].astype(np.float64)          # [B, pitch]
+        else:
+            sh = shifts[j // wave.group].astype(np.int64)
+            x = cv[np.maximum(irow[:, None] + col[None, :] - sh[:, None], 0)].astype(np.float64)
+            x = np.where((col[None, :] % flen) >= sh[:, None], x, 0.0)
         w = wave.weights[j].view(np.float16).astype(np.float64)
         acc = w @ x
         if wave.bias is not None:

@@ -18,6 +18,7 @@ class WaveDesc(ctypes.Structure):
         ("y_off", c_uint64), ("src_off", c_uint64), ("res_off", c_uint64), ("x_base_off", c_uint64),
         ("idx", c_void_p), ("run_rows", c_void_p), ("run_len", c_uint32), ("weights_on_device", c_uint32),
         ("weights", c_void_p), ("bias", c_void_p), ("cout_map", c_void_p), ("name", c_char_p),
+        ("shifts", c_void_p), ("frame_len", c_uint32),
     ]
 
 

@@ -83,6 +83,11 @@ bool desc_to_wave(const k44b_wave_desc *d, HostWave &w, std::string &err) {
     }
     if (d->bias) w.bias.assign(d->bias, d->bias + d->cout);
     if (d->cout_map) w.cout_map.assign(d->cout_map, d->cout_map + d->cout);
+    if (d->shifts) {
+        const size_t n = d->run_rows ? groups * (d->fan_in / d->run_len) : groups * d->fan_in;
+        w.shifts.assign(d->shifts, d->shifts + n);
+    }
+    w.frame_len = d->frame_len;
     return true;
 }
 

@@ -41,6 +41,12 @@ bool validate_wave(const HostWave &w, uint32_t pitch, uint32_t num_tiles, uint64
         for (uint32_t v : w.idx) mx = std::max(mx, v);
         if (w.x_base_off + (uint64_t)mx + pitch > canvas_elems) return bad("a gather offset leaves the canvas");
     }
+    if (!w.shifts.empty()) {
+        const size_t want = w.run_rows.empty() ? (size_t)groups * w.fan_in : w.run_rows.size();
+        if (w.shifts.size() != want) return bad("shift table has the wrong size");
+        const uint32_t flen = w.frame_len ? w.frame_len : pitch;
+        if (pitch % flen) return bad("frame length must divide the row pitch");
+    }
     if (!w.bias.empty() && w.bias.size() != w.cout) return bad("bias has the wrong size");
     if (!w.cout_map.empty()) {
         if (w.cout_map.size() != w.cout) return bad("row map has the wrong size");
@@ -58,11 +64,11 @@ GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_ele
     // Groups whose gather lists are all identical (every dense layer) behave like one big group.
     if (groups > 1u) {
         bool same = true;
-        if (!w.run_rows.empty()) {
-            const size_t per = w.run_rows.size() / groups;
-            for (uint32_t g = 1; g < groups && same; ++g) same = std::equal(w.run_rows.begin(), w.run_rows.begin() + per, w.run_rows.begin() + g * per);
-        } else {
-            for (uint32_t g = 1; g < groups && same; ++g) same = std::equal(w.idx.begin(), w.idx.begin() + w.fan_in, w.idx.begin() + (size_t)g * w.fan_in);
+        const size_t per_i = w.run_rows.empty() ? w.fan_in : w.run_rows.size() / groups;
+        const auto &tab = w.run_rows.empty() ? w.idx : w.run_rows;
+        for (uint32_t g = 1; g < groups && same; ++g) {
+            same = std::equal(tab.begin(), tab.begin() + per_i, tab.begin() + g * per_i);
+            if (same && !w.shifts.empty()) same = std::equal(w.shifts.begin(), w.shifts.begin() + per_i, w.shifts.begin() + g * per_i);
         }
         if (same) { groups = 1u; gp.shared_by_all = true; }
     }
@@ -70,31 +76,38 @@ GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_ele
         gp.why_not = "group size is not a multiple of 128 neurons";
         return gp;
     }
-    struct Run { uint32_t row, len; };
+    struct Run { uint32_t row, len, shift; };
     std::vector<std::vector<Run>> runs(groups);
     if (!w.run_rows.empty()) {
         const uint32_t per = w.fan_in / w.run_len;
         for (uint32_t g = 0; g < groups; ++g)
-            for (uint32_t r = 0; r < per; ++r) runs[g].push_back({w.run_rows[(size_t)g * per + r], w.run_len});
+            for (uint32_t r = 0; r < per; ++r)
+                runs[g].push_back({w.run_rows[(size_t)g * per + r], w.run_len, w.shifts.empty() ? 0u : w.shifts[(size_t)g * per + r]});
     } else {
         for (uint32_t g = 0; g < groups; ++g) {
             const uint32_t *row_idx = w.idx.data() + (size_t)g * w.fan_in;
+            const uint8_t *row_sh = w.shifts.empty() ? nullptr : w.shifts.data() + (size_t)g * w.fan_in;
             auto &rg = runs[g];
             for (uint32_t s = 0; s < w.fan_in; ++s) {
                 uint64_t row;
+                uint32_t sh = 0;
                 if (s < w.fan_in_raw) {
                     const uint64_t e = w.x_base_off + row_idx[s];
-                    if (e % pitch) { gp.why_not = "gather offsets are not row aligned (token / pixel shift)"; return gp; }
+                    if (e % pitch) { gp.why_not = "gather offsets are not row aligned (token / pixel shift given as raw offsets)"; return gp; }
                     row = e / pitch;
+                    sh = row_sh ? row_sh[s] : 0u;
                 } else {
                     // zero-weight padding slot: free to continue the previous run while it stays inside the canvas
                     row = (!rg.empty() && (uint64_t)rg.back().row + rg.back().len < total_rows) ? (uint64_t)rg.back().row + rg.back().len : 0;
+                    sh = rg.empty() ? 0u : rg.back().shift;
                 }
-                if (!rg.empty() && (uint64_t)rg.back().row + rg.back().len == row) ++rg.back().len;
-                else rg.push_back({(uint32_t)row, 1u});
+                if (!rg.empty() && (uint64_t)rg.back().row + rg.back().len == row && rg.back().shift == sh) ++rg.back().len;
+                else rg.push_back({(uint32_t)row, 1u, sh});
             }
         }
     }
+    for (auto &rg : runs)
+        for (auto &r : rg) gp.max_shift = std::max(gp.max_shift, r.shift);
     uint32_t h = 64;
     for (auto &rg : runs)
         for (auto &r : rg)
@@ -102,16 +115,19 @@ GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_ele
     const uint32_t tail = (kStageK - w.fan_in % kStageK) % kStageK;
     while (h >= 8 && tail % h) h >>= 1;
     if (h < 8) { gp.why_not = "runs are not made of whole 8-row blocks"; return gp; }
+    if (gp.max_shift > 0 && h < 16) { gp.why_not = "shifted runs must be made of whole 16-row blocks"; return gp; }
+    if (gp.max_shift > 8) { gp.why_not = "token shifts above 8 columns"; return gp; }
+    if (total_rows > kBoxRowMask) { gp.why_not = "canvas has more than 2^28 rows"; return gp; }
     gp.box_h = h;
     gp.boxes_per_group = (w.fan_in + tail) / h;
     gp.box_rows.reserve((size_t)groups * gp.boxes_per_group);
     for (auto &rg : runs) {
         for (auto &r : rg)
-            for (uint32_t o = 0; o < r.len; o += h) gp.box_rows.push_back(r.row + o);
+            for (uint32_t o = 0; o < r.len; o += h) gp.box_rows.push_back((r.row + o) | (r.shift << 28));
         for (uint32_t o = 0; o < tail; o += h) gp.box_rows.push_back(0u);
     }
     for (uint32_t r : gp.box_rows)
-        if ((uint64_t)r + h > total_rows) { gp.why_not = "a run leaves the canvas"; gp.box_rows.clear(); return gp; }
+        if ((uint64_t)(r & kBoxRowMask) + h > total_rows) { gp.why_not = "a run leaves the canvas"; gp.box_rows.clear(); return gp; }
     gp.box_ok = true;
     return gp;
 }
@@ -155,7 +171,7 @@ bool Executor::check(cudaError_t e, const char *what) {
 void Executor::release() {
     if (device_ >= 0) cudaSetDevice(device_);
     for (auto &w : waves_) {
-        cudaFree(w.d_weights); cudaFree(w.d_gather); cudaFree(w.d_bias); cudaFree(w.d_map); cudaFree(w.d_idx_table);
+        cudaFree(w.d_weights); cudaFree(w.d_gather); cudaFree(w.d_bias); cudaFree(w.d_map); cudaFree(w.d_idx_table); cudaFree(w.d_shifts);
     }
     waves_.clear();
     drop_graph();
@@ -215,9 +231,8 @@ bool Executor::make_tensor_map(DeviceWave &dw) {
     const cuuint64_t strides[1] = {(cuuint64_t)pitch_ * 2u};
     const cuuint32_t box[2] = {64u, dw.args.box_h};
     const cuuint32_t estr[2] = {1u, 1u};
-    const CUresult r = encode(&dw.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, canvas_, dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = encode(&dw.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, canvas_, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
     return true;
 }
@@ -291,8 +306,15 @@ bool Executor::add_wave(const HostWave &w) {
                  check(cudaMemcpy(dw.d_gather, w.idx.data(), bytes, cudaMemcpyHostToDevice), "index table upload");
             a.gather = (const uint32_t *)dw.d_gather;
             a.gather_mode = GATHER_IDX;
+            if (ok && !w.shifts.empty()) {
+                ok = check(cudaMalloc(&dw.d_shifts, w.shifts.size()), "shift table allocation") &&
+                     check(cudaMemcpy(dw.d_shifts, w.shifts.data(), w.shifts.size(), cudaMemcpyHostToDevice), "shift table upload");
+                a.shifts = (const uint8_t *)dw.d_shifts;
+            }
         }
     }
+    a.frame_len = w.frame_len;
+    a.has_shift = w.shifts.empty() ? 0u : 1u;
     if (ok && !w.bias.empty() && w.has_bias) {
         ok = check(cudaMalloc(&dw.d_bias, w.bias.size() * 2), "bias allocation") &&
              check(cudaMemcpy(dw.d_bias, w.bias.data(), w.bias.size() * 2, cudaMemcpyHostToDevice), "bias upload");
@@ -305,6 +327,10 @@ bool Executor::add_wave(const HostWave &w) {
     }
     // ---- path and tile shape ----
     if (ok) {
+        // Token-shifted runs stay on the FMA kernel: a shift of 1..7 columns would need either an unaligned
+        // shared-memory operand or an accumulator column offset that is not a multiple of the hardware's
+        // alignment, and tcgen05.mma rejects the latter with a misaligned-address fault.
+        if (gp.max_shift > 0) { dw.umma_capable = false; dw.fma_reason = "token-shifted runs"; }
         dw.path = (dw.umma_capable && force_path_ != 0) ? PATH_UMMA : PATH_FMA;
         if (dw.path == PATH_UMMA) {
             uint32_t n_tile = 64;
@@ -337,7 +363,7 @@ bool Executor::add_wave(const HostWave &w) {
         }
     }
     if (!ok) {
-        cudaFree(dw.d_weights); cudaFree(dw.d_gather); cudaFree(dw.d_bias); cudaFree(dw.d_map);
+        cudaFree(dw.d_weights); cudaFree(dw.d_gather); cudaFree(dw.d_bias); cudaFree(dw.d_map); cudaFree(dw.d_shifts);
         return false;
     }
     waves_.push_back(dw);

@@ -18,7 +18,8 @@ struct GatherPlan {
     bool shared_by_all = false;          // all groups had the same list: the table holds it once
     uint32_t box_h = 0;                  // 8, 16, 32 or 64
     uint32_t boxes_per_group = 0;        // == 64/box_h * ceil(fan_in/64)
-    std::vector<uint32_t> box_rows;      // [groups][boxes_per_group] canvas row numbers
+    std::vector<uint32_t> box_rows;      // [groups][boxes_per_group] canvas row | token shift << 28
+    uint32_t max_shift = 0;              // largest token shift of any run
     std::string why_not;                 // reason the tensor-core path cannot be used
 };
 
@@ -35,7 +36,7 @@ struct DeviceWave {
     int path = PATH_FMA;
     bool umma_capable = false;
     std::string fma_reason;
-    void *d_weights = nullptr, *d_gather = nullptr, *d_bias = nullptr, *d_map = nullptr;
+    void *d_weights = nullptr, *d_gather = nullptr, *d_bias = nullptr, *d_map = nullptr, *d_shifts = nullptr;
     uint32_t *d_idx_table = nullptr;     // expanded table kept for the FMA path when boxes are used too
     uint64_t synapses = 0;               // logical_cout * fan_in_raw
     uint64_t weight_bytes = 0;

@@ -186,6 +186,9 @@ struct HostWave {
     const void *dev_weights_rowmajor = nullptr;
     uint32_t run_len = 0;              // rows per run when `run_rows` is used
     std::vector<uint32_t> run_rows;    // [cout/group][fan_in/run_len] first row of every run
+    // Token shift: one entry per synapse (idx form) or per run (run form); empty = no shifts.
+    std::vector<uint8_t> shifts;
+    uint32_t frame_len = 0;            // columns per frame for the causal zero padding; 0 = whole row
 };
 
 struct HostPlan {

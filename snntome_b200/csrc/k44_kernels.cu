@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(256) k44_wave_fma_kernel(const WaveArgs a) {
     __shared__ __half xs[kStageK][64];
     __shared__ __align__(16) __half ws[kFmaRows][kStageK];
     __shared__ uint64_t offs[kStageK];
+    __shared__ uint32_t shs[kStageK];
 
     const uint32_t tile = blockIdx.x;                     // 64-column tile
     const uint32_t j0 = blockIdx.y * kFmaRows;            // first neuron
@@ -62,6 +63,8 @@ __global__ void __launch_bounds__(256) k44_wave_fma_kernel(const WaveArgs a) {
     const uint32_t tid = threadIdx.x, c = tid & 63u, q = tid >> 6;
     const __half *xbase = a.canvas + a.x_base_off + (uint64_t)tile * 64u;
     const uint64_t x_limit = a.canvas_elems - a.x_base_off - (uint64_t)tile * 64u;   // exclusive bound for off + 64
+    const uint32_t flen = a.frame_len ? a.frame_len : a.pitch;
+    const uint32_t col_in_frame = (tile * 64u + c) % flen;
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     bool bad = false;
@@ -69,24 +72,36 @@ __global__ void __launch_bounds__(256) k44_wave_fma_kernel(const WaveArgs a) {
         if (tid < kStageK) {
             const uint32_t s = ks * kStageK + tid;
             uint64_t off = 0;
+            uint32_t sh = 0;
             if (s < a.fan_in) {
                 if (a.gather_mode == GATHER_IDX) {
                     off = a.gather[(uint64_t)g * a.fan_in + s];
+                    if (a.shifts) sh = a.shifts[(uint64_t)g * a.fan_in + s];
                 } else {
-                    const uint32_t row = a.gather[(uint64_t)g * a.boxes_per_group + s / a.box_h] + s % a.box_h;
-                    off = (uint64_t)row * a.pitch;
+                    const uint32_t e = a.gather[(uint64_t)g * a.boxes_per_group + s / a.box_h];
+                    off = (uint64_t)((e & kBoxRowMask) + s % a.box_h) * a.pitch;
+                    sh = e >> 28;
                 }
             }
             if (off + 64u > x_limit) { off = 0; bad = true; }   // record and skip instead of faulting
             offs[tid] = off;
+            shs[tid] = sh;
         } else if (tid < kStageK + 128) {
             const uint32_t v = tid - kStageK, r = v >> 3, k8 = v & 7u;   // 16 rows x 8 vectors
             const uint4 wv = a.w_tiles[tiled_vec_index(j0 + r, ks * 8u + k8, a.num_kstages)];
             *reinterpret_cast<uint4 *>(&ws[r][k8 * 8]) = wv;
         }
         __syncthreads();
+        if (a.has_shift) {
 #pragma unroll 4
-        for (uint32_t k = q; k < kStageK; k += 4) xs[k][c] = xbase[offs[k] + c];
+            for (uint32_t k = q; k < kStageK; k += 4) {
+                const uint32_t sh = shs[k];
+                xs[k][c] = col_in_frame >= sh ? xbase[offs[k] + c - sh] : __float2half(0.0f);
+            }
+        } else {
+#pragma unroll 4
+            for (uint32_t k = q; k < kStageK; k += 4) xs[k][c] = xbase[offs[k] + c];
+        }
         __syncthreads();
 #pragma unroll 8
         for (uint32_t k = 0; k < kStageK; ++k) {
@@ -124,7 +139,7 @@ constexpr int kUmmaThreads = 192;
 // STAGES_SEL == 1: 4 stages, two CTAs per SM (small waves: more CTAs in flight, split-K).
 template <int N_TILE, int STAGES_SEL>
 struct UmmaCfg {
-    static constexpr int kColBlocks = N_TILE / 64;
+    static constexpr int kColBlocks = N_TILE / 64;                                    // 64-column blocks per tile
     static constexpr uint32_t kXBytes = (uint32_t)kColBlocks * kStageK * 128u;        // 8 KiB per 64 columns
     static constexpr uint32_t kStageBytes = kStageWBytes + kXBytes;
     static constexpr int kStages = STAGES_SEL == 1 ? 4 : ((N_TILE == 64) ? 8 : (N_TILE == 128 ? 6 : 4));
@@ -339,7 +354,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                 const uint32_t stage = issued % STAGES, ph = (issued / STAGES) & 1u;
                 if (lane == 0) {
                     ok = wait(empty_bar + 8u * stage, ph ^ 1u);
-                    if (ok) {
+                    if (ok) {   // weights first: they do not need the run table
                         ptx::mbar_arrive_expect_tx(full_bar + 8u * stage, (d.debug & 4u) ? kStageWBytes : Cfg::kStageBytes);
                         ptx::bulk_g2s(w_smem + stage * kStageWBytes, wsrc + (uint64_t)ks * (kStageWBytes / 16u), kStageWBytes,
                                       full_bar + 8u * stage, pol_w);
@@ -347,18 +362,32 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
-                for (uint32_t b = 0; b < boxes_per_stage; ++b) {
-                    const uint32_t bi = ks * boxes_per_stage + b;
-                    if ((bi & ~31u) != cached_base) {          // whole warp fetches the next 32 run rows
-                        cached_base = bi & ~31u;
-                        cached = (cached_base + lane < a.boxes_per_group) ? __ldg(rows + cached_base + lane) : 0u;
-                    }
-                    const uint32_t row = __shfl_sync(0xffffffffu, cached, bi & 31u);
-                    if (lane == 0 && !(d.debug & 4u)) {
+                // this stage's box entries (row | shift << 28); the whole warp fetches 32 entries at a time
+                uint32_t ent[8];
 #pragma unroll
-                        for (int cb = 0; cb < Cfg::kColBlocks; ++cb)
-                            ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + (uint32_t)cb * (kStageK * 128u) + b * a.box_h * 128u,
-                                             &tmap, (int32_t)(ct * N_TILE + cb * 64), (int32_t)row, full_bar + 8u * stage, pol_x);
+                for (uint32_t b = 0; b < 8u; ++b) {
+                    ent[b] = 0u;
+                    if (b < boxes_per_stage) {
+                        const uint32_t bi = ks * boxes_per_stage + b;
+                        if ((bi & ~31u) != cached_base) {
+                            cached_base = bi & ~31u;
+                            cached = (cached_base + lane < a.boxes_per_group) ? __ldg(rows + cached_base + lane) : 0u;
+                        }
+                        ent[b] = __shfl_sync(0xffffffffu, cached, bi & 31u);
+                    }
+                }
+                if (lane == 0) {
+                    if (!(d.debug & 4u)) {
+#pragma unroll
+                        for (uint32_t b = 0; b < 8u; ++b) {
+                            if (b < boxes_per_stage) {
+                                const uint32_t row = ent[b] & kBoxRowMask;
+#pragma unroll
+                                for (int cb = 0; cb < Cfg::kColBlocks; ++cb)
+                                    ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + (uint32_t)cb * (kStageK * 128u) + b * a.box_h * 128u, &tmap,
+                                                     (int32_t)(ct * N_TILE + cb * 64), (int32_t)row, full_bar + 8u * stage, pol_x);
+                            }
+                        }
                     }
                 }
                 if (issued == 0 && lane == 0) stamp(2);

@@ -24,8 +24,9 @@ __host__ __device__ inline uint64_t tiled_vec_index(uint32_t j, uint32_t k8, uin
 
 enum GatherMode : int {
     GATHER_IDX = 0,    // one 32-bit FP16-element offset per synapse (general; any alignment)
-    GATHER_BOX = 1,    // runs of `box_h` consecutive rows: one 32-bit row number per box
+    GATHER_BOX = 1,    // runs of `box_h` consecutive rows: one 32-bit entry per box = row | token shift << 28
 };
+constexpr uint32_t kBoxRowMask = 0x0fffffffu;   // canvas row of a box entry; the top 4 bits carry its token shift (0..8)
 
 enum WavePath : int { PATH_FMA = 0, PATH_UMMA = 1 };
 
@@ -58,6 +59,11 @@ struct WaveArgs {
     uint32_t box_h = 0, boxes_per_group = 0;
     int act = 0;
     int has_residual = 0;
+    // receptive-field token shift: a synapse reads its row `shift` columns earlier; columns whose position inside
+    // their frame is below the shift read zero
+    const uint8_t *shifts = nullptr;      // per synapse (GATHER_IDX only; box entries carry their own shift)
+    uint32_t frame_len = 0;               // columns per frame (0: the whole row)
+    uint32_t has_shift = 0;
     // split-K (tensor-core path): partial sums meet in an FP32 scratch tile, the last arrival finishes the rows
     uint32_t k_splits = 1, kstages_per_split = 0;
     float *scratch = nullptr;             // [tiles][N_TILE][128] FP32, all zero between launches

@@ -29,7 +29,8 @@ def _ptr(a: Optional[np.ndarray]):
     return a.ctypes.data if a is not None else None
 
 
-def wave_desc(w: Wave, *, device_weights_ptr: int = 0, run_rows: Optional[np.ndarray] = None, run_len: int = 0):
+def wave_desc(w: Wave, *, device_weights_ptr: int = 0, run_rows: Optional[np.ndarray] = None, run_len: int = 0,
+              run_shifts: Optional[np.ndarray] = None):
     """Fill a k44b_wave_desc from a `Wave`. Returns (desc, keepalive list)."""
     d = WaveDesc()
     d.cout, d.logical_cout, d.cin, d.group = w.cout, w.logical_cout, w.cin, w.group
@@ -40,8 +41,15 @@ def wave_desc(w: Wave, *, device_weights_ptr: int = 0, run_rows: Optional[np.nda
         rr = np.ascontiguousarray(run_rows, dtype=np.uint32)
         keep.append(rr)
         d.run_rows, d.run_len, d.idx = rr.ctypes.data, int(run_len), None
+        if run_shifts is not None:
+            rs = np.ascontiguousarray(run_shifts, dtype=np.uint8)
+            keep.append(rs)
+            d.shifts = rs.ctypes.data
     else:
         d.idx = _ptr(w.idx)
+        if w.shifts is not None:
+            d.shifts = _ptr(w.shifts)
+    d.frame_len = int(w.frame_len or 0)
     if device_weights_ptr:
         d.weights, d.weights_on_device = device_weights_ptr, 1
     else:

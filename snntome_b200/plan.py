@@ -74,6 +74,10 @@ class Wave:
     name: str = ""
     h_out: int = 1
     w_out: int = 1
+    # Receptive-field token shift: synapse s of group g reads its row `shifts[g][s]` columns (tokens) earlier;
+    # columns whose position inside their frame of `frame_len` columns is below the shift read zero.
+    shifts: Optional[np.ndarray] = None     # uint8 [cout // group, fan_in]
+    frame_len: int = 0                      # 0: the whole row is one frame
 
     def __post_init__(self):
         if not self.logical_cout:
@@ -86,6 +90,8 @@ class Wave:
             self.bias = np.ascontiguousarray(self.bias).view(np.uint16).reshape(self.cout)
         if self.cout_map is not None:
             self.cout_map = np.ascontiguousarray(self.cout_map, dtype=np.uint16).reshape(self.cout)
+        if self.shifts is not None:
+            self.shifts = np.ascontiguousarray(self.shifts, dtype=np.uint8).reshape(self.cout // self.group, self.fan_in)
 
     @property
     def synapses(self) -> int:

@@ -282,3 +282,46 @@ def test_graph_replay_equals_direct_launches():
     assert npn.status() == 0
     assert npn.launch_count == before + 3 * npn.num_waves
     assert np.array_equal(canvas.cpu().numpy().view(np.uint16), a)
+
+
+def shifted_plan(seed, *, rows_in=256, cout=256, runs=8, run_len=16, frames=2, frame_len=256, group=128, act=ACT_GELU, waves=2):
+    """Token-shift receptive-field plan: every run of `run_len` rows is read 0..7 tokens earlier, with zero
+    padding at the start of each frame (sequence)."""
+    rng = np.random.default_rng(seed)
+    pitch = frames * frame_len
+    fan_in = runs * run_len
+    ws, total = [], rows_in
+    for wi in range(waves):
+        groups = cout // group
+        starts = synth.run_starts(seed, wi, groups, runs, run_len, total)
+        from snntome_b200.plan import expand_runs
+        idx = expand_runs(starts, run_len, pitch)
+        sh_run = rng.integers(0, 8, size=(groups, runs)).astype(np.uint8)
+        shifts = np.repeat(sh_run, run_len, axis=1)
+        w = synth.f16_bits(rng.normal(0, (1.0 / fan_in) ** 0.5, (cout, fan_in)))
+        ws.append(Wave(cout=cout, group=group, fan_in=fan_in, idx=idx, weights=w, bias=None, y_off=total * pitch, act=act,
+                       shifts=shifts, frame_len=frame_len, name=f"shift{wi}"))
+        total += cout
+    return Plan(canvas_elems=total * pitch, pitch=pitch, columns=pitch, input_off=0, input_c=rows_in,
+                output_off=(total - cout) * pitch, output_c=cout, waves=ws)
+
+
+@pytest.mark.parametrize("group", [128, 16])
+def test_token_shift_plan_general_path(group):
+    plan = shifted_plan(120, group=group)
+    x = synth.random_input(plan, 24, dist="normal")
+    check(plan, run_gpu(plan, x, PATH_FMA, expect_path=PATH_FMA), O.run_plan(plan, x))
+
+
+def test_token_shift_runs_stay_on_general_path():
+    """Shifted runs are recognised as runs (one table entry per 16 rows, shift in its top bits) but execute on
+    the FMA kernel: tcgen05.mma cannot place its result at an accumulator column offset of 1..7."""
+    plan = shifted_plan(131, runs=8, run_len=16, frames=3, frame_len=256, cout=256)
+    x = synth.random_input(plan, 25, dist="normal")
+    check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_FMA), O.run_plan(plan, x))
+
+
+def test_token_shift_short_runs_fall_back():
+    plan = shifted_plan(140, runs=16, run_len=8)
+    x = synth.random_input(plan, 26, dist="normal")
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_FMA), O.run_plan(plan, x))

@@ -181,3 +181,29 @@ def test_tcff_python_roundtrip_and_corruption():
     bad[20] ^= 1
     with pytest.raises(ValueError):
         O.tcff_read(bytes(bad))
+
+
+def test_token_shift_oracle_twins_agree_and_pad_causally():
+    rng = np.random.default_rng(11)
+    pitch, frame, rows_in, cout, B = 128, 64, 40, 16, 64
+    idx = (rng.integers(0, rows_in, size=(1, B)) * pitch).astype(np.uint32)
+    shifts = rng.integers(0, 8, size=(1, B)).astype(np.uint8)
+    w = synth.f16_bits(rng.normal(0, 0.2, size=(cout, B)))
+    wave = Wave(cout=cout, group=16, fan_in=B, idx=idx, weights=w, bias=None, y_off=rows_in * pitch, act=ACT_GELU,
+                shifts=shifts, frame_len=frame)
+    plan = Plan(canvas_elems=(rows_in + cout) * pitch, pitch=pitch, columns=pitch, input_off=0, input_c=rows_in,
+                output_off=rows_in * pitch, output_c=cout, waves=[wave])
+    x = synth.random_input(plan, 5, dist="normal")
+    a = O.run_plan(plan, x)
+    b = O.run_plan(plan, x, use_numpy=True)
+    ok, err, k = O.compare(a, b, rtol=1e-3, atol=1e-6)
+    assert ok, (err, k)
+    # direct statement for one output element: column 64 is token 0 of the second frame -> only shift-0 taps contribute
+    X = x.view(np.float16).astype(np.float64).reshape(rows_in, pitch)
+    W = w.view(np.float16).astype(np.float64)
+    rows = idx[0] // pitch
+    for col in (64, 66, 3, 127):
+        acc = sum(W[5, s] * X[rows[s], col - shifts[0, s]] for s in range(B) if (col % frame) >= shifts[0, s])
+        want = np.float16(0.5 * acc * (1 + __import__("math").erf(acc * 0.7071067811865476)))
+        got = a[wave.y_off + 5 * pitch + col: wave.y_off + 5 * pitch + col + 1].view(np.float16)[0]
+        assert abs(float(got) - float(want)) <= 1e-3 + 2e-3 * abs(float(want))
