@@ -199,6 +199,7 @@ bool Executor::begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t
     device_ = device;
     num_sms_ = prop.multiProcessorCount;
     force_path_ = force_path;
+    if (const char *e = std::getenv("K44B_PDL")) pdl_ = std::atoi(e) != 0;
     if (const char *e = std::getenv("K44B_FORCE_PATH")) {
         if (!std::strcmp(e, "fma")) force_path_ = 0;
         else if (!std::strcmp(e, "umma")) force_path_ = 1;
@@ -347,18 +348,31 @@ bool Executor::add_wave(const HostWave &w) {
             uint32_t splits = 1;
             bool small = (uint64_t)mtiles * (tiles64 / (n_tile / 64u)) < (uint64_t)num_sms_;
             if (const char *e = std::getenv("K44B_SMALL_WAVE")) small = std::atoi(e) != 0;
+            bool cluster = false;
             if (small) {
                 n_tile = 64;
                 const uint32_t tiles = mtiles * tiles64, cap = 2u * (uint32_t)num_sms_;
                 splits = std::max(1u, std::min(cap / tiles, a.num_kstages / 2u));   // all items resident at once: no second round
-                if (const char *e = std::getenv("K44B_SPLITS")) splits = std::max(1u, std::min((uint32_t)std::atoi(e), a.num_kstages));
+                // preferred: the splits of a tile form a thread-block cluster (<= 8 CTAs, one CTA per SM) and add their
+                // partial sums through distributed shared memory instead of global scratch
+                cluster = tiles <= cap;
+                if (const char *e = std::getenv("K44B_CLUSTER")) cluster = cluster && std::atoi(e) != 0;
+                const char *es = std::getenv("K44B_SPLITS");
+                if (es) splits = std::max(1u, std::min((uint32_t)std::atoi(es), a.num_kstages));
+                if (cluster) {
+                    uint32_t s2 = 8;
+                    while (s2 > 1 && (s2 * tiles > cap || s2 * 2u > a.num_kstages)) s2 >>= 1;   // <= two CTAs per SM
+                    if (es) { s2 = 1; while (s2 * 2u <= std::min(splits, 8u)) s2 <<= 1; }
+                    splits = s2;
+                }
             }
             a.kstages_per_split = (a.num_kstages + splits - 1) / splits;
-            a.k_splits = (a.num_kstages + a.kstages_per_split - 1) / a.kstages_per_split;
+            a.k_splits = cluster ? splits : (a.num_kstages + a.kstages_per_split - 1) / a.kstages_per_split;
+            dw.use_cluster = cluster;
             dw.desc = make_umma_desc(n_tile, variant);
             dw.desc.small_wave = small ? 1u : 0u;
             if (const char *e = std::getenv("K44B_DEBUG_MODE")) dw.desc.debug = (uint32_t)std::atoi(e);
-            if (a.k_splits > 1) ok = reserve_scratch((size_t)mtiles * tiles64);
+            if (a.k_splits > 1 && !cluster) ok = reserve_scratch((size_t)mtiles * tiles64);
             ok = ok && make_tensor_map(dw);
         }
     }
@@ -366,8 +380,21 @@ bool Executor::add_wave(const HostWave &w) {
         cudaFree(dw.d_weights); cudaFree(dw.d_gather); cudaFree(dw.d_bias); cudaFree(dw.d_map); cudaFree(dw.d_shifts);
         return false;
     }
+    // canvas intervals for the scheduler's independence test
+    dw.write_lo = w.y_off; dw.write_hi = w.y_off + (uint64_t)w.cout * pitch_;
+    uint64_t lo = ~0ull, hi = 0;
+    if (gp.box_ok) {
+        for (uint32_t e : gp.box_rows) { const uint64_t r = e & kBoxRowMask; lo = std::min(lo, r * pitch_); hi = std::max(hi, (r + gp.box_h) * pitch_); }
+    } else {
+        for (uint32_t v : w.idx) { lo = std::min(lo, w.x_base_off + v); hi = std::max(hi, w.x_base_off + v + pitch_); }
+        if (lo >= 8) lo -= 8;                       // shifted taps read a few columns to the left
+    }
+    if (w.has_residual) { lo = std::min(lo, w.res_off); hi = std::max(hi, w.res_off + (uint64_t)w.cout * pitch_); }
+    dw.read_lo = lo; dw.read_hi = hi;
+    dw.groupable = dw.path == PATH_UMMA && dw.use_cluster && w.cout_map.empty();
     waves_.push_back(dw);
     drop_graph();
+    groups_valid_ = false;
     return true;
 }
 
@@ -407,9 +434,80 @@ void Executor::drop_graph() {
     if (graph_exec_) { cudaGraphExecDestroy(graph_exec_); graph_exec_ = nullptr; }
 }
 
+// Wave scheduler. Consecutive small waves that cannot observe each other (none reads or overwrites what another
+// one writes) share one launch: their clusters are numbered consecutively in one grid. A decoder layer's q, k, v
+// projections become one launch, gate and up another.
+void Executor::build_groups() {
+    groups_.clear();
+    auto overlaps = [](uint64_t a0, uint64_t a1, uint64_t b0, uint64_t b1) { return a0 < b1 && b0 < a1; };
+    bool allow = true;
+    if (const char *e = std::getenv("K44B_GROUP")) allow = std::atoi(e) != 0;
+    for (size_t i = 0; i < waves_.size(); ++i) {
+        DeviceWave &w = waves_[i];
+        bool joined = false;
+        if (allow && w.groupable && !groups_.empty()) {
+            LaunchGroup &g = groups_.back();
+            const DeviceWave &first = waves_[g.waves[0]];
+            bool ok = first.groupable && g.waves.size() < (size_t)kMaxGroupWaves && first.args.box_h == w.args.box_h;
+            for (size_t k = 0; ok && k < g.waves.size(); ++k) {
+                const DeviceWave &o = waves_[g.waves[k]];
+                ok = !overlaps(w.read_lo, w.read_hi, o.write_lo, o.write_hi) && !overlaps(w.write_lo, w.write_hi, o.write_lo, o.write_hi) &&
+                     !overlaps(w.write_lo, w.write_hi, o.read_lo, o.read_hi);
+            }
+            if (ok) {
+                uint32_t tiles = 0;
+                for (size_t k : g.waves) tiles += ((waves_[k].args.cout + kTileM - 1) / kTileM) * waves_[k].args.num_col_tiles64;
+                tiles += ((w.args.cout + kTileM - 1) / kTileM) * w.args.num_col_tiles64;
+                ok = tiles <= 2u * (uint32_t)num_sms_;
+            }
+            if (ok) { g.waves.push_back(i); joined = true; }
+        }
+        if (!joined) { groups_.push_back(LaunchGroup()); groups_.back().waves.push_back(i); }
+    }
+    for (auto &g : groups_) {
+        if (!waves_[g.waves[0]].use_cluster) continue;
+        uint32_t tiles = 0, min_ks = ~0u;
+        for (size_t k : g.waves) {
+            tiles += ((waves_[k].args.cout + kTileM - 1) / kTileM) * waves_[k].args.num_col_tiles64;
+            min_ks = std::min(min_ks, waves_[k].args.num_kstages);
+        }
+        uint32_t S = g.waves.size() == 1 ? waves_[g.waves[0]].args.k_splits : 8u;
+        if (g.waves.size() > 1)
+            while (S > 1 && (S * tiles > 2u * (uint32_t)num_sms_ || S * 2u > min_ks)) S >>= 1;
+        g.args = WaveGroupArgs();
+        g.args.count = (uint32_t)g.waves.size();
+        g.args.splits = S;
+        uint32_t first = 0;
+        for (size_t k = 0; k < g.waves.size(); ++k) {
+            DeviceWave &w = waves_[g.waves[k]];
+            w.args.k_splits = S;
+            w.args.kstages_per_split = (w.args.num_kstages + S - 1) / S;
+            g.args.w[k] = w.args;
+            g.args.first_cluster[k] = first;
+            first += ((w.args.cout + kTileM - 1) / kTileM) * w.args.num_col_tiles64;
+        }
+        g.args.total_clusters = first;
+    }
+    groups_valid_ = true;
+}
+
+bool Executor::launch_group(size_t gi, cudaStream_t stream) {
+    LaunchGroup &g = groups_[gi];
+    DeviceWave &w0 = waves_[g.waves[0]];
+    if (g.waves.size() == 1 && !w0.use_cluster) return launch_one(w0, stream);
+    ++launches_;
+    return check(launch_wave_umma_cluster(g.args, w0.desc, w0.tmap, pdl_, num_sms_, stream), ("launch of wave group starting at '" + w0.name + "'").c_str());
+}
+
 bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
     cudaError_t e;
-    if (w.path == PATH_UMMA) {
+    if (w.path == PATH_UMMA && w.use_cluster) {
+        WaveGroupArgs g;
+        g.count = 1; g.splits = w.args.k_splits;
+        g.w[0] = w.args;
+        g.total_clusters = ((w.args.cout + kTileM - 1) / kTileM) * w.args.num_col_tiles64;
+        e = launch_wave_umma_cluster(g, w.desc, w.tmap, pdl_, num_sms_, stream);
+    } else if (w.path == PATH_UMMA) {
         w.args.scratch = d_scratch_;
         w.args.counters = d_counters_;
         e = launch_wave_umma(w.args, w.desc, w.tmap, num_sms_, stream);
@@ -422,8 +520,9 @@ bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
 
 bool Executor::execute(cudaStream_t stream) {
     if (!ready()) return fail("executor not initialised");
-    for (auto &w : waves_)
-        if (!launch_one(w, stream)) return false;
+    if (!groups_valid_) build_groups();
+    for (size_t gi = 0; gi < groups_.size(); ++gi)
+        if (!launch_group(gi, stream)) return false;
     return true;
 }
 
@@ -447,13 +546,14 @@ bool Executor::execute_graph(cudaStream_t stream) {
         cudaStreamDestroy(cap);
         if (!ok) { graph_exec_ = nullptr; return false; }
     }
-    launches_ += waves_.size();
+    launches_ += groups_.size();
     return check(cudaGraphLaunch(graph_exec_, stream), "graph launch");
 }
 
 bool Executor::execute_wave(size_t i, cudaStream_t stream) {
     if (!ready()) return fail("executor not initialised");
     if (i >= waves_.size()) return fail("wave index out of range");
+    if (!groups_valid_) build_groups();     // fixes the split count a wave uses inside its group
     return launch_one(waves_[i], stream);
 }
 

@@ -34,11 +34,15 @@ struct DeviceWave {
     UmmaDesc desc;
     CUtensorMap tmap;
     int path = PATH_FMA;
+    bool use_cluster = false;            // small wave: K splits form a cluster and reduce through shared memory
     bool umma_capable = false;
     std::string fma_reason;
     void *d_weights = nullptr, *d_gather = nullptr, *d_bias = nullptr, *d_map = nullptr, *d_shifts = nullptr;
     uint32_t *d_idx_table = nullptr;     // expanded table kept for the FMA path when boxes are used too
     uint64_t synapses = 0;               // logical_cout * fan_in_raw
+    uint64_t read_lo = 0, read_hi = 0;   // canvas element interval this wave may read (gathers and residual)
+    uint64_t write_lo = 0, write_hi = 0; // canvas element interval it writes
+    bool groupable = false;              // may share a launch with independent neighbours
     uint64_t weight_bytes = 0;
 };
 
@@ -81,6 +85,11 @@ class Executor {
     bool reserve_scratch(size_t tiles);
     bool launch_one(DeviceWave &w, cudaStream_t stream);
     void drop_graph();
+    void build_groups();
+    bool launch_group(size_t gi, cudaStream_t stream);
+    struct LaunchGroup { std::vector<size_t> waves; WaveGroupArgs args; };
+    std::vector<LaunchGroup> groups_;
+    bool groups_valid_ = false;
 
     int device_ = -1, num_sms_ = 148, force_path_ = -1;
     __half *canvas_ = nullptr;
@@ -97,6 +106,7 @@ class Executor {
     uint32_t *d_counters_ = nullptr;
     size_t scratch_tiles_ = 0;
     cudaGraphExec_t graph_exec_ = nullptr;
+    bool pdl_ = true;                    // programmatic dependent launch between consecutive small waves
 };
 
 const char *status_string(uint32_t st);

@@ -362,32 +362,20 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
-                // this stage's box entries (row | shift << 28); the whole warp fetches 32 entries at a time
-                uint32_t ent[8];
-#pragma unroll
-                for (uint32_t b = 0; b < 8u; ++b) {
-                    ent[b] = 0u;
-                    if (b < boxes_per_stage) {
-                        const uint32_t bi = ks * boxes_per_stage + b;
-                        if ((bi & ~31u) != cached_base) {
-                            cached_base = bi & ~31u;
-                            cached = (cached_base + lane < a.boxes_per_group) ? __ldg(rows + cached_base + lane) : 0u;
-                        }
-                        ent[b] = __shfl_sync(0xffffffffu, cached, bi & 31u);
+                // one TMA box per run, issued right after its table lookup (the whole warp fetches 32 entries at a time;
+                // an entry is row | token shift << 28, the shift is only used by the FMA kernel)
+                for (uint32_t b = 0; b < boxes_per_stage; ++b) {
+                    const uint32_t bi = ks * boxes_per_stage + b;
+                    if ((bi & ~31u) != cached_base) {
+                        cached_base = bi & ~31u;
+                        cached = (cached_base + lane < a.boxes_per_group) ? __ldg(rows + cached_base + lane) : 0u;
                     }
-                }
-                if (lane == 0) {
-                    if (!(d.debug & 4u)) {
+                    const uint32_t row = __shfl_sync(0xffffffffu, cached, bi & 31u) & kBoxRowMask;
+                    if (lane == 0 && !(d.debug & 4u)) {
 #pragma unroll
-                        for (uint32_t b = 0; b < 8u; ++b) {
-                            if (b < boxes_per_stage) {
-                                const uint32_t row = ent[b] & kBoxRowMask;
-#pragma unroll
-                                for (int cb = 0; cb < Cfg::kColBlocks; ++cb)
-                                    ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + (uint32_t)cb * (kStageK * 128u) + b * a.box_h * 128u, &tmap,
-                                                     (int32_t)(ct * N_TILE + cb * 64), (int32_t)row, full_bar + 8u * stage, pol_x);
-                            }
-                        }
+                        for (int cb = 0; cb < Cfg::kColBlocks; ++cb)
+                            ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + (uint32_t)cb * (kStageK * 128u) + b * a.box_h * 128u, &tmap,
+                                             (int32_t)(ct * N_TILE + cb * 64), (int32_t)row, full_bar + 8u * stage, pol_x);
                     }
                 }
                 if (issued == 0 && lane == 0) stamp(2);
@@ -547,13 +535,6 @@ static cudaError_t umma_attr() {
                                 (int)UmmaCfg<N_TILE, SEL>::kSmemBytes);
 }
 
-cudaError_t umma_kernel_setup() {
-    cudaError_t e;
-    if ((e = umma_attr<64, 0>()) != cudaSuccess) return e;
-    if ((e = umma_attr<128, 0>()) != cudaSuccess) return e;
-    if ((e = umma_attr<256, 0>()) != cudaSuccess) return e;
-    return umma_attr<64, 1>();
-}
 
 template <int N_TILE, int SEL>
 static cudaError_t umma_launch(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s) {
@@ -576,6 +557,363 @@ cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtenso
     case 256: return umma_launch<256, 0>(a, d, tmap, num_sms, s);
     default: return cudaErrorInvalidValue;
     }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// tcgen05 path for small waves: one work item per CTA, K splits of a tile form a thread-block cluster
+// ---------------------------------------------------------------------------------------------------
+// A wave with fewer 128-neuron tiles than SMs (every linear of a decoder at decode batch sizes) cuts each
+// tile's fan-in into S = 1, 2, 4 or 8 splits. The S CTAs of a tile are launched as one cluster and combine
+// their FP32 partial accumulators through distributed shared memory: CTA r owns rows [r*128/S, (r+1)*128/S) of
+// the tile, every CTA writes the partial sums of those rows into the owner's receive buffer, one cluster
+// barrier later each owner adds its S partials, applies the epilogue and stores its rows. No global scratch,
+// no atomics, bit-reproducible. The kernel is also written for programmatic dependent launch: barrier set-up,
+// tensor-memory allocation and the weight copies of the first stages are issued before it waits for the
+// previous wave, because weights never depend on it.
+namespace smallwave {
+constexpr uint32_t kXBytes = kStageK * 128u;                         // one 64-column block
+constexpr uint32_t kStageBytes = kStageWBytes + kXBytes;             // 24 KiB
+constexpr uint32_t kRecvBytes = 64u * kTileM * 4u;                   // 32 KiB: [src rank][owned row][64 floats]
+constexpr uint32_t smem_bytes(int stages) { return 1024u + (uint32_t)stages * kStageBytes + kRecvBytes + 256u; }
+constexpr uint32_t kTmemCols = 64u;
+// 3 stages: two CTAs per SM (waves with up to 2 x SMs work items); 7 stages: one CTA per SM with a deep pipeline
+
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float x, float y, float z, float w) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+// Owner side of the exchange, compile-time split count: thread t of the 128 epilogue threads sums the S partial
+// rows for 64/S columns of one owned row, applies the epilogue and stores 16-byte pieces.
+template <int S, int ACT>
+__device__ __forceinline__ void finish_owned_t(const WaveArgs &a, const float *recv, uint32_t t, uint32_t mt, uint32_t ct, uint32_t rank) {
+    constexpr uint32_t rows_owned = kTileM / S, ncol = 64u / S;
+    const uint32_t row_local = t / S, col0 = (t % S) * ncol;
+    const uint32_t j = mt * kTileM + rank * rows_owned + row_local;
+    float v[ncol];
+#pragma unroll
+    for (uint32_t c = 0; c < ncol; c += 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (uint32_t src = 0; src < (uint32_t)S; ++src) {
+            const float4 p = *reinterpret_cast<const float4 *>(recv + ((size_t)(src * rows_owned + row_local) * 64u + col0 + c));
+            acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        }
+        v[c] = acc.x; v[c + 1] = acc.y; v[c + 2] = acc.z; v[c + 3] = acc.w;
+    }
+    if (j >= a.cout) return;
+    const bool has_map = a.cout_map != nullptr;
+    const uint32_t oj = has_map ? a.cout_map[j] : j;
+    const float bias = a.bias ? __half2float(a.bias[j]) : 0.0f;
+    const uint64_t o = (uint64_t)oj * a.pitch + (uint64_t)ct * 64u + col0;
+    __half *dst = a.canvas + a.y_off + o;
+#pragma unroll
+    for (uint32_t c = 0; c < ncol; c += 8) {
+        float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (a.has_residual) {
+            const uint4 rv = *reinterpret_cast<const uint4 *>(a.canvas + a.res_off + o + c);
+            const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(rh[e]); r[2 * e] = f.x; r[2 * e + 1] = f.y; }
+        }
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float lo = v[c + 2 * e] + bias, hi = v[c + 2 * e + 1] + bias;
+            if (has_map) { lo += r[2 * e]; hi += r[2 * e + 1]; }
+            lo = act_fast<ACT>(lo); hi = act_fast<ACT>(hi);
+            if (!has_map) { lo += r[2 * e]; hi += r[2 * e + 1]; }
+            const __half2 h2 = __floats2half2_rn(lo, hi);
+            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+        *reinterpret_cast<uint4 *>(dst + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+}
+
+template <int S>
+__device__ __forceinline__ void finish_owned(const WaveArgs &a, const float *recv, uint32_t t, uint32_t mt, uint32_t ct, uint32_t rank) {
+    switch (a.act) {
+    case 1: finish_owned_t<S, 1>(a, recv, t, mt, ct, rank); break;
+    case 2: finish_owned_t<S, 2>(a, recv, t, mt, ct, rank); break;
+    case 3: finish_owned_t<S, 3>(a, recv, t, mt, ct, rank); break;
+    case 4: finish_owned_t<S, 4>(a, recv, t, mt, ct, rank); break;
+    case 5: finish_owned_t<S, 5>(a, recv, t, mt, ct, rank); break;
+    default: finish_owned_t<S, 0>(a, recv, t, mt, ct, rank); break;
+    }
+}
+}  // namespace smallwave
+
+template <int kStages>
+__global__ void __launch_bounds__(kUmmaThreads, kStages <= 3 ? 2 : 1)
+k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ WaveGroupArgs grp, const UmmaDesc d) {
+    using namespace smallwave;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    const uint32_t w_smem = smem_base;
+    const uint32_t x_smem = smem_base + kStages * kStageWBytes;
+    const uint32_t recv_smem = x_smem + kStages * kXBytes;
+    const uint32_t ctl = recv_smem + kRecvBytes;
+    const uint32_t full_bar = ctl, empty_bar = ctl + 8u * kStages, tfull_bar = ctl + 16u * kStages;
+    uint8_t *base_ptr = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
+    float *recv = reinterpret_cast<float *>(base_ptr + kStages * kStageBytes);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + kStages * kStageBytes + kRecvBytes + 16 * kStages + 16);
+    volatile uint32_t *abort_word = tmem_slot + 1;
+    volatile uint32_t *epi_ok = tmem_slot + 2;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    // which wave of the group this cluster belongs to (uniform per CTA)
+    const uint32_t S = grp.splits;                         // == cluster size
+    const uint32_t cid = blockIdx.x / S;
+    uint32_t g = 0;
+#pragma unroll
+    for (uint32_t i = 1; i < (uint32_t)kMaxGroupWaves; ++i)
+        if (i < grp.count && cid >= grp.first_cluster[i]) g = i;
+    WaveArgs a = grp.w[0];
+    if (g == 1) a = grp.w[1];
+    else if (g == 2) a = grp.w[2];
+    else if (g == 3) a = grp.w[3];
+    const bool trace = (d.debug & 16u) && blockIdx.x == 0;       // development aid: milestone clocks of CTA 0
+    auto stamp = [&](int slot) { if (trace) reinterpret_cast<volatile long long *>(a.status + 2)[slot] = clock64(); };
+    if (threadIdx.x == 0) stamp(0);
+    const uint32_t tile = cid - grp.first_cluster[g], rank = cluster_rank();
+    const uint32_t tiles_n = a.num_col_tiles64;
+    const uint32_t mt = tile / tiles_n, ct = tile % tiles_n;
+    const uint32_t ks0 = rank * a.kstages_per_split;
+    const uint32_t ks1 = min(a.num_kstages, ks0 + a.kstages_per_split);   // may be empty for the last ranks
+    const uint32_t boxes_per_stage = kStageK / a.box_h;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(full_bar + 8u * s, 1);
+            ptx::mbar_init(empty_bar + 8u * s, 1);
+        }
+        ptx::mbar_init(tfull_bar, 1);
+        *abort_word = 0;
+        ptx::fence_mbar_init();
+        // weights of the first stages do not depend on the previous wave: start them before anything else
+        const uint64_t pol_w0 = ptx::policy_evict_first();
+        const uint4 *wsrc0 = a.w_tiles + (uint64_t)mt * a.num_kstages * (kStageWBytes / 16u);
+        const uint32_t nst0 = ks1 > ks0 ? ks1 - ks0 : 0u;
+        for (uint32_t i = 0; i < (nst0 < (uint32_t)kStages ? nst0 : (uint32_t)kStages); ++i) {
+            ptx::mbar_arrive_expect_tx(full_bar + 8u * i, kStageBytes);
+            ptx::bulk_g2s(w_smem + i * kStageWBytes, wsrc0 + (uint64_t)(ks0 + i) * (kStageWBytes / 16u), kStageWBytes, full_bar + 8u * i, pol_w0);
+        }
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_addr(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) stamp(1);
+    if (S > 1) cluster_arrive();            // phase A: "this CTA is alive"; waited for before the first remote write
+    grid_launch_dependents();               // the next wave may start its own set-up and weight prefetch
+
+    auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+        const long long t0 = clock64();
+        for (uint32_t it = 0;; ++it) {
+            if (ptx::mbar_try_wait(bar, parity)) return true;
+            if ((it & 31u) == 31u) {
+                if (*abort_word != 0u) return false;
+                if ((unsigned long long)(clock64() - t0) > d.wait_cycles) return false;
+            }
+        }
+    };
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) ptx::prefetch_tensormap(&tmap);
+        const uint64_t pol_w = ptx::policy_evict_first();
+        const uint64_t pol_x = ptx::policy_evict_last();
+        const uint32_t *rows = a.gather + (uint64_t)(mt / a.mtiles_per_group) * a.boxes_per_group;
+        const uint4 *wsrc = a.w_tiles + (uint64_t)mt * a.num_kstages * (kStageWBytes / 16u);
+        const uint32_t nst = ks1 > ks0 ? ks1 - ks0 : 0u;
+        const uint32_t pre = nst < (uint32_t)kStages ? nst : (uint32_t)kStages;
+        // (the weights of the first `pre` stages were issued by thread 0 during set-up)
+        if (lane == 0) stamp(2);
+        grid_dependency_wait();             // everything below reads rows the previous wave wrote
+        fence_proxy_async_global();
+        if (lane == 0) stamp(3);
+        uint32_t cached = 0, cached_base = 0xffffffffu;
+        bool ok = true;
+        uint32_t issued = 0;
+        for (uint32_t ks = ks0; ks < ks1 && ok; ++ks, ++issued) {
+            const uint32_t stage = issued % kStages, ph = (issued / kStages) & 1u;
+            if (issued >= pre) {
+                if (lane == 0) {
+                    ok = wait(empty_bar + 8u * stage, ph ^ 1u);
+                    if (ok) {
+                        ptx::mbar_arrive_expect_tx(full_bar + 8u * stage, kStageBytes);
+                        ptx::bulk_g2s(w_smem + stage * kStageWBytes, wsrc + (uint64_t)ks * (kStageWBytes / 16u), kStageWBytes, full_bar + 8u * stage, pol_w);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+            }
+            for (uint32_t b = 0; b < boxes_per_stage; ++b) {
+                const uint32_t bi = ks * boxes_per_stage + b;
+                if ((bi & ~31u) != cached_base) {
+                    cached_base = bi & ~31u;
+                    cached = (cached_base + lane < a.boxes_per_group) ? __ldg(rows + cached_base + lane) : 0u;
+                }
+                const uint32_t row = __shfl_sync(0xffffffffu, cached, bi & 31u) & kBoxRowMask;
+                if (lane == 0)
+                    ptx::tma_load_2d(x_smem + stage * kXBytes + b * a.box_h * 128u, &tmap, (int32_t)(ct * 64u), (int32_t)row, full_bar + 8u * stage, pol_x);
+            }
+            if (lane == 0 && issued == 0) stamp(4);
+        }
+        if (lane == 0) stamp(5);
+        if (!ok && lane == 0) {
+            if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PRODUCER);
+            *abort_word = 1u;
+            const uint32_t first = issued > (uint32_t)kStages ? issued - kStages : 0u;
+            for (uint32_t i = first; i < issued; ++i) {
+                const long long t0 = clock64();
+                bool done = false;
+                while (!done && (unsigned long long)(clock64() - t0) < d.wait_cycles)
+                    done = ptx::mbar_try_wait(full_bar + 8u * (i % kStages), (i / kStages) & 1u);
+                if (!done) atomicOr(a.status, (uint32_t)ST_TIMEOUT_DRAIN);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t consumed = 0;
+            for (uint32_t ks = ks0; ks < ks1; ++ks, ++consumed) {
+                const uint32_t stage = consumed % kStages, ph = (consumed / kStages) & 1u;
+                ok = wait(full_bar + 8u * stage, ph);
+                if (!ok) break;
+                if (consumed == 0) stamp(6);
+                ptx::tc_fence_after();
+                const uint64_t a0 = d.a_base | (uint64_t)(((w_smem + stage * kStageWBytes) >> 4) & 0x3fffu);
+                const uint64_t b0 = d.b_base | (uint64_t)(((x_smem + stage * kXBytes) >> 4) & 0x3fffu);
+#pragma unroll
+                for (uint32_t k4 = 0; k4 < kStageK / 16u; ++k4)
+                    ptx::umma_f16(tmem_base, a0 + (uint64_t)(k4 * d.a_k_step), b0 + (uint64_t)(k4 * d.b_k_step), d.idesc, (ks != ks0 || k4 != 0u) ? 1u : 0u);
+                ptx::umma_commit(empty_bar + 8u * stage);
+            }
+            stamp(7);
+            if (ok) ptx::umma_commit(tfull_bar);
+            else { if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_MMA); *abort_word = 1u; }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: partial sums to their owners ----------------
+        const uint32_t quarter = warp & 3u, r_in_tile = quarter * 32u + lane;
+        const bool has_k = ks1 > ks0;
+        if (threadIdx.x == 64u) epi_ok[0] = (!has_k || wait(tfull_bar, 0u)) ? 1u : 0u;
+        epilogue_bar_sync();
+        __syncwarp();
+        grid_dependency_wait();             // already satisfied (the operands depended on it); orders this thread's own accesses
+        const bool ok = epi_ok[0] != 0u;
+        if (threadIdx.x == 64u) stamp(8);
+        if (!ok && threadIdx.x == 64u) { if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_EPILOGUE); *abort_word = 1u; }
+        ptx::tc_fence_after();
+        const uint32_t rows_owned = kTileM / S;
+        const uint32_t owner = r_in_tile / rows_owned, row_local = r_in_tile % rows_owned;
+        // receive buffer of the owner: [src rank][row_local][64]
+        const uint32_t slot_off = ((rank * rows_owned + row_local) * 64u) * 4u;
+        if (S > 1) cluster_wait();          // phase A complete: every CTA of the cluster is running
+        if (threadIdx.x == 64u) stamp(9);
+        const uint32_t remote = S > 1 ? map_to_rank(recv_smem + slot_off, owner) : 0u;
+#pragma unroll 1
+        for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
+            uint32_t v[32];
+            if (has_k && ok) {
+                ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + c0, v);
+                ptx::tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) v[e] = 0u;
+            }
+            if (S > 1) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 4)
+                    st_cluster_v4(remote + (c0 + e) * 4u, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+            } else {
+                float *mine = recv + (size_t)r_in_tile * 64u + c0;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) mine[e] = __uint_as_float(v[e]);
+            }
+        }
+    }
+    // ---------------- exchange complete -> every CTA finishes the rows it owns ----------------
+    if (threadIdx.x == 64u) stamp(10);
+    ptx::tc_fence_before();
+    __syncwarp();
+    if (S > 1) {
+        if (warp < 2) cluster_wait();       // phase A (the epilogue warps waited for it above)
+        cluster_arrive();                   // phase B: my partial sums are written
+        cluster_wait();
+    } else {
+        __syncthreads();
+    }
+    if (threadIdx.x == 64u) stamp(11);
+    if (warp >= 2 && *abort_word == 0u) {
+        const uint32_t t = threadIdx.x - 64u;                       // 0..127
+        switch (S) {
+        case 1: finish_owned<1>(a, recv, t, mt, ct, rank); break;
+        case 2: finish_owned<2>(a, recv, t, mt, ct, rank); break;
+        case 4: finish_owned<4>(a, recv, t, mt, ct, rank); break;
+        default: finish_owned<8>(a, recv, t, mt, ct, rank); break;
+        }
+    }
+    if (threadIdx.x == 64u) stamp(12);
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+cudaError_t launch_wave_umma_cluster(const WaveGroupArgs &g, const UmmaDesc &d, const CUtensorMap &tmap, bool dependent_launch, int num_sms, cudaStream_t s) {
+    const uint32_t S = g.splits;
+    if (!(S == 1 || S == 2 || S == 4 || S == 8) || g.count == 0 || g.count > (uint32_t)kMaxGroupWaves || g.total_clusters == 0) return cudaErrorInvalidValue;
+    const uint32_t ctas = g.total_clusters * S;
+    const bool deep = false;                              // the 7-stage, one-CTA-per-SM variant lost to cluster placement stalls; kept for tuning
+    (void)num_sms;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas, 1, 1);
+    cfg.blockDim = dim3(kUmmaThreads, 1, 1);
+    cfg.dynamicSmemBytes = smallwave::smem_bytes(deep ? 7 : 3);
+    cfg.stream = s;
+    cudaLaunchAttribute attrs[2];
+    int n = 0;
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = S; attrs[n].val.clusterDim.y = 1; attrs[n].val.clusterDim.z = 1;
+    ++n;
+    if (dependent_launch) {
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n;
+    return deep ? cudaLaunchKernelEx(&cfg, k44_wave_umma_cluster_kernel<7>, tmap, g, d)
+                : cudaLaunchKernelEx(&cfg, k44_wave_umma_cluster_kernel<3>, tmap, g, d);
+}
+
+cudaError_t umma_kernel_setup() {
+    cudaError_t e;
+    if ((e = umma_attr<64, 0>()) != cudaSuccess) return e;
+    if ((e = umma_attr<128, 0>()) != cudaSuccess) return e;
+    if ((e = umma_attr<256, 0>()) != cudaSuccess) return e;
+    if ((e = umma_attr<64, 1>()) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k44_wave_umma_cluster_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smallwave::smem_bytes(3))) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k44_wave_umma_cluster_kernel<7>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smallwave::smem_bytes(7));
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -70,6 +70,16 @@ struct WaveArgs {
     uint32_t *counters = nullptr;         // [tiles], all zero between launches
 };
 
+// Up to four mutually independent small waves launched as one grid (their clusters are numbered consecutively).
+constexpr int kMaxGroupWaves = 4;
+struct WaveGroupArgs {
+    WaveArgs w[kMaxGroupWaves];
+    uint32_t first_cluster[kMaxGroupWaves] = {0, 0, 0, 0};   // first cluster index of each wave
+    uint32_t count = 0;                                       // waves in the group
+    uint32_t splits = 1;                                      // K splits = cluster size, common to the group
+    uint32_t total_clusters = 0;
+};
+
 // tcgen05 operand descriptors are assembled on the host (see k44_exec.cu) and passed in.
 struct UmmaDesc {
     uint64_t a_base = 0, b_base = 0;      // descriptor bits without the start address
@@ -83,6 +93,9 @@ struct UmmaDesc {
 
 cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s);
 cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
+// small waves: one item per CTA, the K splits of a tile form a cluster (k_splits in {1,2,4,8}) and reduce through
+// distributed shared memory; dependent_launch adds the programmatic-dependent-launch attribute
+cudaError_t launch_wave_umma_cluster(const WaveGroupArgs &g, const UmmaDesc &d, const CUtensorMap &tmap, bool dependent_launch, int num_sms, cudaStream_t s);
 cudaError_t umma_kernel_setup();       // opt in to large dynamic shared memory (once per device)
 
 // packer kernels

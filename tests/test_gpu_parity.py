@@ -229,11 +229,15 @@ def test_bad_plan_is_rejected_before_launch():
         NativePlan.from_plan(plan)
 
 
+@pytest.mark.parametrize("cluster", [1, 0])
 @pytest.mark.parametrize("splits", [0, 2, 3, 7, 32])
-def test_split_k_small_waves(splits, monkeypatch):
-    """Waves with fewer 128-neuron tiles than SMs cut their fan-in into K splits whose partial sums meet in an
-    FP32 scratch tile; the scratch must come back zeroed (second run equals the first)."""
+def test_split_k_small_waves(splits, cluster, monkeypatch):
+    """Waves with fewer 128-neuron tiles than SMs cut their fan-in into K splits. Default: the splits of a tile
+    form a thread-block cluster and add their partial sums through distributed shared memory. Fallback
+    (K44B_CLUSTER=0): partial sums meet in an FP32 global scratch tile that must come back zeroed (repeated
+    runs agree)."""
     import torch
+    monkeypatch.setenv("K44B_CLUSTER", str(cluster))
     if splits:
         monkeypatch.setenv("K44B_SPLITS", str(splits))
     plan = synth.dense_chain(seed=110, dims=[2048, 320, 512, 200], columns=64, act=ACT_SILU, weight_std=0.03,
@@ -243,9 +247,13 @@ def test_split_k_small_waves(splits, monkeypatch):
     npn = NativePlan.from_plan(plan, force_path=PATH_UMMA)
     infos = [npn.wave_info(i) for i in range(npn.num_waves)]
     assert all(i.path == PATH_UMMA for i in infos)
-    assert infos[0].k_splits > 1
-    if splits:
-        assert infos[0].k_splits == min(splits, 32) or infos[0].k_splits == -(-32 // -(-32 // splits))
+    if cluster:
+        assert all(i.k_splits in (1, 2, 4, 8) for i in infos)
+        assert infos[0].k_splits == (8 if not splits else min(8, 1 << (min(splits, 32).bit_length() - 1)))
+    else:
+        assert infos[0].k_splits > 1
+        if splits:
+            assert infos[0].k_splits == -(-32 // -(-32 // min(splits, 32)))
     canvas = npn.canvas_tensor()
     xt = torch.from_numpy(x.view(np.int16).reshape(-1)).cuda().view(torch.float16)
     results = []
@@ -259,8 +267,8 @@ def test_split_k_small_waves(splits, monkeypatch):
         assert npn.status() == 0
         results.append(canvas.cpu().numpy().view(np.uint16))
         check(plan, results[-1], want)
-    # FP32 atomics commute only up to rounding: repeated runs agree within the parity tolerance, checked above;
-    # with a single split the result is bit-stable
+    if cluster:      # the on-chip reduction adds the partial sums in a fixed order
+        assert np.array_equal(results[0], results[1]) and np.array_equal(results[0], results[2])
     npn.close()
 
 
@@ -325,3 +333,35 @@ def test_token_shift_short_runs_fall_back():
     plan = shifted_plan(140, runs=16, run_len=8)
     x = synth.random_input(plan, 26, dist="normal")
     check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_FMA), O.run_plan(plan, x))
+
+
+def test_independent_small_waves_share_a_launch():
+    """q/k/v-style waves (same input rows, disjoint output rows) run as one grouped launch; a wave that reads one
+    of them starts a new launch. Results are unchanged."""
+    import torch
+    rng = np.random.default_rng(150)
+    pitch, d_in = 64, 512
+    dims = [("q", 512, 0), ("k", 128, 0), ("v", 128, 0), ("o", 512, 1)]      # (name, rows, source tensor: 0 = x, 1 = q)
+    rows0 = {"x": 0, "q": d_in, "k": d_in + 512, "v": d_in + 640, "o": d_in + 768}
+    waves = []
+    for name, cout, src in dims:
+        src_row = rows0["x"] if src == 0 else rows0["q"]
+        offs = ((src_row + np.arange(d_in)) * pitch).astype(np.uint32)
+        waves.append(Wave(cout=cout, group=128, fan_in=d_in, idx=np.tile(offs, (cout // 128, 1)),
+                          weights=synth.f16_bits(rng.normal(0, 0.05, (cout, d_in))), bias=synth.f16_bits(rng.normal(0, 0.1, cout)),
+                          y_off=rows0[name] * pitch, act=ACT_NONE, name=name))
+    total = d_in + 768 + 512
+    plan = Plan(canvas_elems=total * pitch, pitch=pitch, columns=64, input_off=0, input_c=d_in, output_off=rows0["o"] * pitch,
+                output_c=512, waves=waves)
+    x = synth.random_input(plan, 27)
+    want = O.run_plan(plan, x)
+    npn = NativePlan.from_plan(plan, force_path=PATH_UMMA)
+    canvas = npn.canvas_tensor()
+    xt = torch.from_numpy(x.view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    canvas[: xt.numel()] = xt
+    before = npn.launch_count
+    npn.execute()
+    assert npn.status() == 0
+    assert npn.launch_count - before == 2            # {q, k, v} and {o}
+    check(plan, canvas.cpu().numpy().view(np.uint16), want)
+    npn.close()
