@@ -360,9 +360,9 @@ bool Executor::add_wave(const HostWave &w) {
                 const char *es = std::getenv("K44B_SPLITS");
                 if (es) splits = std::max(1u, std::min((uint32_t)std::atoi(es), a.num_kstages));
                 if (cluster) {
-                    uint32_t s2 = 8;
+                    uint32_t s2 = 8;           // portable cluster size; 16 is accepted when forced but lost to barrier and placement cost
                     while (s2 > 1 && (s2 * tiles > cap || s2 * 2u > a.num_kstages)) s2 >>= 1;   // <= two CTAs per SM
-                    if (es) { s2 = 1; while (s2 * 2u <= std::min(splits, 8u)) s2 <<= 1; }
+                    if (es) { s2 = 1; while (s2 * 2u <= std::min(splits, 16u)) s2 <<= 1; }
                     splits = s2;
                 }
             }

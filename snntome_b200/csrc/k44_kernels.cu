@@ -573,7 +573,7 @@ cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtenso
 namespace smallwave {
 constexpr uint32_t kXBytes = kStageK * 128u;                         // one 64-column block
 constexpr uint32_t kStageBytes = kStageWBytes + kXBytes;             // 24 KiB
-constexpr uint32_t kRecvBytes = 64u * kTileM * 4u;                   // 32 KiB: [src rank][owned row][64 floats]
+constexpr uint32_t kRecvBytes = 36864u;                              // [src rank][group of 4 columns][owned rows + 1 pad][4 floats], largest for 16 splits
 constexpr uint32_t smem_bytes(int stages) { return 1024u + (uint32_t)stages * kStageBytes + kRecvBytes + 256u; }
 constexpr uint32_t kTmemCols = 64u;
 // 3 stages: two CTAs per SM (waves with up to 2 x SMs work items); 7 stages: one CTA per SM with a deep pipeline
@@ -606,7 +606,7 @@ __device__ __forceinline__ void finish_owned_t(const WaveArgs &a, const float *r
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (uint32_t src = 0; src < (uint32_t)S; ++src) {
-            const float4 p = *reinterpret_cast<const float4 *>(recv + ((size_t)(src * rows_owned + row_local) * 64u + col0 + c));
+            const float4 p = *reinterpret_cast<const float4 *>(recv + (((size_t)src * 16u + (col0 + c) / 4u) * (rows_owned + 1u) + row_local) * 4u);
             acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
         }
         v[c] = acc.x; v[c + 1] = acc.y; v[c + 2] = acc.z; v[c + 3] = acc.w;
@@ -617,8 +617,28 @@ __device__ __forceinline__ void finish_owned_t(const WaveArgs &a, const float *r
     const float bias = a.bias ? __half2float(a.bias[j]) : 0.0f;
     const uint64_t o = (uint64_t)oj * a.pitch + (uint64_t)ct * 64u + col0;
     __half *dst = a.canvas + a.y_off + o;
+    if constexpr (ncol == 4u) {  // 16 splits: four values (8 bytes) per thread
+        float r[4] = {0.f, 0.f, 0.f, 0.f};
+        if (a.has_residual) {
+            const uint2 rv = *reinterpret_cast<const uint2 *>(a.canvas + a.res_off + o);
+            const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+            const float2 f0 = __half22float2(rh[0]), f1 = __half22float2(rh[1]);
+            r[0] = f0.x; r[1] = f0.y; r[2] = f1.x; r[3] = f1.y;
+        }
+        uint32_t pk[2];
 #pragma unroll
-    for (uint32_t c = 0; c < ncol; c += 8) {
+        for (int e = 0; e < 2; ++e) {
+            float lo = v[2 * e] + bias, hi = v[2 * e + 1] + bias;
+            if (has_map) { lo += r[2 * e]; hi += r[2 * e + 1]; }
+            lo = act_fast<ACT>(lo); hi = act_fast<ACT>(hi);
+            if (!has_map) { lo += r[2 * e]; hi += r[2 * e + 1]; }
+            const __half2 h2 = __floats2half2_rn(lo, hi);
+            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+        *reinterpret_cast<uint2 *>(dst) = make_uint2(pk[0], pk[1]);
+    } else {
+#pragma unroll
+    for (uint32_t c = 0; c + 8u <= ncol; c += 8) {
         float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         if (a.has_residual) {
             const uint4 rv = *reinterpret_cast<const uint4 *>(a.canvas + a.res_off + o + c);
@@ -637,6 +657,7 @@ __device__ __forceinline__ void finish_owned_t(const WaveArgs &a, const float *r
             pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
         }
         *reinterpret_cast<uint4 *>(dst + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
     }
 }
 
@@ -742,11 +763,13 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         const uint32_t nst = ks1 > ks0 ? ks1 - ks0 : 0u;
         const uint32_t pre = nst < (uint32_t)kStages ? nst : (uint32_t)kStages;
         // (the weights of the first `pre` stages were issued by thread 0 during set-up)
+        // the run table is static too: fetch its first entries before waiting for the previous wave
+        uint32_t cached_base = (ks0 * boxes_per_stage) & ~31u;
+        uint32_t cached = (cached_base + lane < a.boxes_per_group) ? __ldg(rows + cached_base + lane) : 0u;
         if (lane == 0) stamp(2);
         grid_dependency_wait();             // everything below reads rows the previous wave wrote
         fence_proxy_async_global();
         if (lane == 0) stamp(3);
-        uint32_t cached = 0, cached_base = 0xffffffffu;
         bool ok = true;
         uint32_t issued = 0;
         for (uint32_t ks = ks0; ks < ks1 && ok; ++ks, ++issued) {
@@ -824,8 +847,9 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         ptx::tc_fence_after();
         const uint32_t rows_owned = kTileM / S;
         const uint32_t owner = r_in_tile / rows_owned, row_local = r_in_tile % rows_owned;
-        // receive buffer of the owner: [src rank][row_local][64]
-        const uint32_t slot_off = ((rank * rows_owned + row_local) * 64u) * 4u;
+        // receive buffer of the owner: [src rank][group of 4 columns][row_local][4 floats] — the 16 or 32 lanes of a warp
+        // that share an owner write one contiguous run per store instruction
+        const uint32_t slot_off = (rank * 16u * (rows_owned + 1u) + row_local) * 16u;   // +1: padding row against bank conflicts on the read side
         if (S > 1) cluster_wait();          // phase A complete: every CTA of the cluster is running
         if (threadIdx.x == 64u) stamp(9);
         const uint32_t remote = S > 1 ? map_to_rank(recv_smem + slot_off, owner) : 0u;
@@ -842,11 +866,13 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
             if (S > 1) {
 #pragma unroll
                 for (int e = 0; e < 32; e += 4)
-                    st_cluster_v4(remote + (c0 + e) * 4u, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                    st_cluster_v4(remote + ((c0 + e) / 4u) * (rows_owned + 1u) * 16u, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
+                                  __uint_as_float(v[e + 3]));
             } else {
-                float *mine = recv + (size_t)r_in_tile * 64u + c0;
 #pragma unroll
-                for (int e = 0; e < 32; ++e) mine[e] = __uint_as_float(v[e]);
+                for (int e = 0; e < 32; e += 4)
+                    *reinterpret_cast<float4 *>(recv + (((c0 + e) / 4u) * (rows_owned + 1u) + row_local) * 4u) =
+                        make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
             }
         }
     }
@@ -868,7 +894,8 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         case 1: finish_owned<1>(a, recv, t, mt, ct, rank); break;
         case 2: finish_owned<2>(a, recv, t, mt, ct, rank); break;
         case 4: finish_owned<4>(a, recv, t, mt, ct, rank); break;
-        default: finish_owned<8>(a, recv, t, mt, ct, rank); break;
+        case 8: finish_owned<8>(a, recv, t, mt, ct, rank); break;
+        default: finish_owned<16>(a, recv, t, mt, ct, rank); break;
         }
     }
     if (threadIdx.x == 64u) stamp(12);
@@ -881,7 +908,7 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
 
 cudaError_t launch_wave_umma_cluster(const WaveGroupArgs &g, const UmmaDesc &d, const CUtensorMap &tmap, bool dependent_launch, int num_sms, cudaStream_t s) {
     const uint32_t S = g.splits;
-    if (!(S == 1 || S == 2 || S == 4 || S == 8) || g.count == 0 || g.count > (uint32_t)kMaxGroupWaves || g.total_clusters == 0) return cudaErrorInvalidValue;
+    if (!(S == 1 || S == 2 || S == 4 || S == 8 || S == 16) || g.count == 0 || g.count > (uint32_t)kMaxGroupWaves || g.total_clusters == 0) return cudaErrorInvalidValue;
     const uint32_t ctas = g.total_clusters * S;
     const bool deep = false;                              // the 7-stage, one-CTA-per-SM variant lost to cluster placement stalls; kept for tuning
     (void)num_sms;
@@ -902,6 +929,11 @@ cudaError_t launch_wave_umma_cluster(const WaveGroupArgs &g, const UmmaDesc &d, 
     }
     cfg.attrs = attrs;
     cfg.numAttrs = n;
+    if (S > 8) {    // clusters of 16 need an explicit opt-in
+        const cudaError_t e = deep ? cudaFuncSetAttribute(k44_wave_umma_cluster_kernel<7>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1)
+                                   : cudaFuncSetAttribute(k44_wave_umma_cluster_kernel<3>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return e;
+    }
     return deep ? cudaLaunchKernelEx(&cfg, k44_wave_umma_cluster_kernel<7>, tmap, g, d)
                 : cudaLaunchKernelEx(&cfg, k44_wave_umma_cluster_kernel<3>, tmap, g, d);
 }

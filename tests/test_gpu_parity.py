@@ -248,8 +248,8 @@ def test_split_k_small_waves(splits, cluster, monkeypatch):
     infos = [npn.wave_info(i) for i in range(npn.num_waves)]
     assert all(i.path == PATH_UMMA for i in infos)
     if cluster:
-        assert all(i.k_splits in (1, 2, 4, 8) for i in infos)
-        assert infos[0].k_splits == (8 if not splits else min(8, 1 << (min(splits, 32).bit_length() - 1)))
+        assert all(i.k_splits in (1, 2, 4, 8, 16) for i in infos)
+        assert infos[0].k_splits == (8 if not splits else min(16, 1 << (min(splits, 32).bit_length() - 1)))
     else:
         assert infos[0].k_splits > 1
         if splits:
