@@ -1,0 +1,122 @@
+"""Parity at benchmark size and on the benchmark workloads' structure.
+
+* the ultra-sparse plan at its full size (40 M substrate rows, 4 x 1 M neurons, fan-in 4096; about 40 GB on the
+  device): the oracle cannot run all of it, so whole neuron groups are sampled per wave and recomputed by the oracle
+  from the device's own inputs (the rows the group gathers, read back from the canvas) and weights (unpacked from the
+  device's packed copy);
+* a small dense decoder wave chain (same structure as the 1B benchmark: q,k,v / o+residual / gate,up / down+residual
+  per layer, lm_head) replayed as a CUDA graph with grouped launches, against the oracle in full.
+"""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+from oracle import oracle as O
+from snntome_b200 import synth
+from snntome_b200.native import NativePlan, PATH_UMMA
+from snntome_b200.plan import ACT_NONE, ACT_RELU, ACT_SILU, Plan, Wave
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 2e-3, 1e-3
+
+
+def test_ultra_sparse_plan_full_size_sampled_groups():
+    import torch
+    import bench
+    free, _ = torch.cuda.mem_get_info()
+    scale = float(os.environ.get("K44B_TEST_SCALE", "1.0"))
+    if free < 60e9 * scale:
+        pytest.skip("not enough free device memory for the full-size plan")
+    w = bench.workload(scale)
+    plan = bench.build_device_plan(w, 0)
+    from snntome_b200.native import fill_normal_f16
+    canvas = plan.canvas_tensor()
+    fill_normal_f16(canvas[: w["input_rows"] * 64], 5, 1.0)
+    plan.execute()
+    assert plan.status() == 0
+    rng = np.random.default_rng(3)
+    fan_in = w["runs"] * w["run_len"]
+    cv2 = canvas.view(-1, 64)
+    for wi in range(w["waves"]):
+        assert plan.wave_info(wi).path == PATH_UMMA and plan.wave_info(wi).box_rows == 64
+        starts = bench.run_starts_table(wi, w)                          # [groups, runs]
+        wrm = plan.weights_rowmajor(wi)                                   # device, [cout, fan_in] int16
+        groups = rng.choice(starts.shape[0], size=6, replace=False)
+        row0 = w["input_rows"] + wi * w["cout"]
+        for g in groups:
+            rows = (torch.from_numpy(starts[g].astype(np.int64))[:, None] + torch.arange(w["run_len"])[None, :]).reshape(-1).cuda()
+            x = cv2[rows].cpu().numpy().view(np.uint16)                 # [fan_in, 64] gathered rows as the device saw them
+            wg = wrm[g * 128:(g + 1) * 128].cpu().numpy().view(np.uint16)
+            got = cv2[row0 + g * 128: row0 + (g + 1) * 128].cpu().numpy().view(np.uint16)
+            idx = (np.arange(fan_in, dtype=np.uint32) * 64)[None, :]
+            wave = Wave(cout=128, group=128, fan_in=fan_in, idx=idx, weights=wg, bias=None, y_off=fan_in * 64, act=ACT_RELU)
+            mini = Plan(canvas_elems=(fan_in + 128) * 64, pitch=64, columns=64, input_off=0, input_c=fan_in, output_off=fan_in * 64,
+                        output_c=128, waves=[wave])
+            want = O.run_plan(mini, x)[fan_in * 64:]
+            ok, err, k = O.compare(got.reshape(-1), want, RTOL, ATOL)
+            assert ok, f"wave {wi} group {g}: max abs err {err} at {k}"
+        del wrm
+        torch.cuda.empty_cache()
+    plan.close()
+
+
+def mini_decoder(seed=9, hidden=256, kv=64, ffn=768, vocab=1024, layers=2, columns=64):
+    rng = np.random.default_rng(seed)
+    pitch = 64
+    rows, cur = {}, 0
+    for name, n in [("x0", hidden), ("x1", hidden), ("q", hidden), ("k", kv), ("v", kv), ("h", hidden), ("g", ffn), ("u", ffn), ("logits", vocab)]:
+        rows[name] = cur
+        cur += n
+    waves = []
+
+    def add(name, src, dst, cin, cout, act=ACT_NONE, res=None):
+        offs = ((rows[src] + np.arange(cin)) * pitch).astype(np.uint32)
+        g = 128 if cout % 128 == 0 else 64
+        waves.append(Wave(cout=cout, group=g, fan_in=cin, idx=np.tile(offs, (cout // g, 1)), weights=synth.f16_bits(rng.normal(0, 0.03, (cout, cin))),
+                          bias=None, y_off=rows[dst] * pitch, act=act, has_residual=res is not None,
+                          res_off=rows[res] * pitch if res else 0, name=name))
+
+    x_in, x_out = "x0", "x1"
+    for layer in range(layers):
+        add(f"L{layer}.q", x_in, "q", hidden, hidden)
+        add(f"L{layer}.k", x_in, "k", hidden, kv)
+        add(f"L{layer}.v", x_in, "v", hidden, kv)
+        add(f"L{layer}.o", "q", "h", hidden, hidden, res=x_in)
+        add(f"L{layer}.gate", "h", "g", hidden, ffn, act=ACT_SILU)
+        add(f"L{layer}.up", "h", "u", hidden, ffn)
+        add(f"L{layer}.down", "g", x_out, ffn, hidden, res="h")
+        x_in, x_out = x_out, x_in
+    add("lm_head", x_in, "logits", hidden, vocab)
+    return Plan(canvas_elems=cur * pitch, pitch=pitch, columns=columns, input_off=0, input_c=hidden, output_off=rows["logits"] * pitch,
+                output_c=vocab, waves=waves)
+
+
+@pytest.mark.parametrize("group_launches", [1, 0])
+def test_decoder_wave_chain_graph_replay(group_launches, monkeypatch):
+    import torch
+    monkeypatch.setenv("K44B_GROUP", str(group_launches))
+    plan = mini_decoder()
+    x = synth.random_input(plan, 31, dist="normal")
+    want = O.run_plan(plan, x)
+    npn = NativePlan.from_plan(plan, force_path=PATH_UMMA)
+    canvas = npn.canvas_tensor()
+    xt = torch.from_numpy(x.view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    before = npn.launch_count
+    for _ in range(3):
+        canvas[: xt.numel()] = xt                            # the last layer writes its result over the input rows
+        npn.execute_graph()
+    assert npn.status() == 0
+    per_step = (npn.launch_count - before) // 3
+    assert per_step == (9 if group_launches else 15)        # {q,k,v} {o} {gate,up} {down} per layer + lm_head
+    got = canvas.cpu().numpy().view(np.uint16)
+    for w in plan.waves[-8:]:                                 # last layer and lm_head hold their final values
+        a, b = w.y_off, w.y_off + w.cout * plan.pitch
+        ok, err, k = O.compare(got[a:b], want[a:b], RTOL, ATOL)
+        assert ok, (w.name, err, k)
+    npn.close()
