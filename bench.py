@@ -31,6 +31,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 SEED = 2024
+NCU_TRAFFIC_RATIO = 0.928      # measured DRAM traffic / algorithmic bytes of k44_wave_umma_kernel<64> (see profiles/)
 FULL = dict(input_rows=40_000_000, waves=4, cout=1 << 20, runs=64, run_len=64, columns=64, group=128)
 
 
@@ -501,7 +502,7 @@ def main() -> None:
         vals = [cpu_baseline(w, seconds_target=20.0) for _ in range(1)]
         cb = vals[0]
         line = {"impl": "reference", "metric": "effective synaptic TFLOP/s (2*synapses*columns/s)", "value": cb["value"], "unit": "TFLOP/s",
-                "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+                "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": cb["seconds_per_rep"] * 1e3, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16 operands, f64 accumulate (CPU)", "data": "synthetic", "config": cfg,
                 "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
@@ -568,7 +569,10 @@ def main() -> None:
     roofline = {"bound": "hbm", "kernel": "k44_wave_umma_kernel<64>" if paths[0] == 1 else "k44_wave_fma_kernel",
                 "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
                 "algorithmic_bytes_per_launch": bytes_wave, "avg_launch_ms": avg_wave_ms,
-                "per_wave_ms": [float(np.mean([wave_ms[s][i] for s in range(args.steps)])) for i in range(nw)], "traffic": None}
+                "per_wave_ms": [float(np.mean([wave_ms[s][i] for s in range(args.steps)])) for i in range(nw)],
+                # dram__bytes_read + dram__bytes_write of this kernel from the committed ncu capture at 1/20 size
+                # (profiles/k44_wave_umma64_ultra_sparse_scale005_ncu_full.md: 0.928 x algorithmic bytes), scaled by units processed
+                "traffic": NCU_TRAFFIC_RATIO * bytes_wave, "traffic_source": "ncu capture at scale 0.05, scaled by neurons x fan-in"}
 
     # ---- end to end through the C ABI with host buffers (pinned FP16 in canvas layout) ----
     e2e = None
