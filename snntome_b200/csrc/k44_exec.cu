@@ -328,12 +328,28 @@ bool Executor::add_wave(const HostWave &w) {
     }
     // ---- path and tile shape ----
     if (ok) {
-        // Token-shifted runs stay on the FMA kernel: a shift of 1..7 columns would need either an unaligned
-        // shared-memory operand or an accumulator column offset that is not a multiple of the hardware's
-        // alignment, and tcgen05.mma rejects the latter with a misaligned-address fault.
-        if (gp.max_shift > 0) { dw.umma_capable = false; dw.fma_reason = "token-shifted runs"; }
+        // A shift of 1..7 columns can be neither an operand start address nor an accumulator column offset
+        // (tcgen05.mma rejects the latter with a misaligned-address fault).
+        // Token-shifted runs take the aligner kernel: its extra warps realign the shifted rows in registers on the way
+        // into the operand stage. It needs frames that are whole column tiles; otherwise the wave stays on FMA.
+        if (gp.max_shift > 0) {
+            const uint32_t flen = w.frame_len ? w.frame_len : pitch_;
+            bool allow = dw.umma_capable && flen % 64u == 0u;
+            if (const char *e = std::getenv("K44B_SHIFT_UMMA")) allow = allow && std::atoi(e) != 0;
+            if (!allow) { dw.umma_capable = false; dw.fma_reason = flen % 64u ? "token-shifted runs with frames that are not whole column tiles" : "token-shifted runs"; }
+            else dw.use_shift = true;
+        }
         dw.path = (dw.umma_capable && force_path_ != 0) ? PATH_UMMA : PATH_FMA;
-        if (dw.path == PATH_UMMA) {
+        if (dw.path == PATH_UMMA && dw.use_shift) {
+            const uint32_t flen = w.frame_len ? w.frame_len : pitch_;
+            uint32_t n_tile = (tiles64 % 2u == 0u && flen % 128u == 0u && (uint64_t)mtiles * (tiles64 / 2u) >= (uint64_t)num_sms_) ? 128u : 64u;
+            if (const char *e = std::getenv("K44B_N_TILE")) {
+                const uint32_t v = (uint32_t)std::atoi(e);
+                if ((v == 64 || v == 128) && tiles64 % (v / 64u) == 0u && flen % v == 0u) n_tile = v;
+            }
+            a.k_splits = 1; a.kstages_per_split = a.num_kstages;
+            dw.desc = make_umma_desc(n_tile, 0);
+        } else if (dw.path == PATH_UMMA) {
             uint32_t n_tile = 64;
             for (uint32_t cand : {256u, 128u})
                 if (tiles64 % (cand / 64u) == 0u && (uint64_t)mtiles * (tiles64 / (cand / 64u)) >= (uint64_t)num_sms_) { n_tile = cand; break; }
@@ -507,6 +523,8 @@ bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
         g.w[0] = w.args;
         g.total_clusters = ((w.args.cout + kTileM - 1) / kTileM) * w.args.num_col_tiles64;
         e = launch_wave_umma_cluster(g, w.desc, w.tmap, pdl_, num_sms_, stream);
+    } else if (w.path == PATH_UMMA && w.use_shift) {
+        e = launch_wave_umma_shift(w.args, w.desc, num_sms_, stream);
     } else if (w.path == PATH_UMMA) {
         w.args.scratch = d_scratch_;
         w.args.counters = d_counters_;

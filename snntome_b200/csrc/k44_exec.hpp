@@ -35,6 +35,7 @@ struct DeviceWave {
     CUtensorMap tmap;
     int path = PATH_FMA;
     bool use_cluster = false;            // small wave: K splits form a cluster and reduce through shared memory
+    bool use_shift = false;              // token-shifted runs: tensor-core kernel with aligner warps
     bool umma_capable = false;
     std::string fma_reason;
     void *d_weights = nullptr, *d_gather = nullptr, *d_bias = nullptr, *d_map = nullptr, *d_shifts = nullptr;

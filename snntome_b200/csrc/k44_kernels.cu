@@ -15,32 +15,11 @@
 // Every wait on a barrier is bounded in time; on expiry the kernel records a status bit, drains its
 // own copies, frees its tensor memory and returns.
 #include "k44_kernels.cuh"
+#include "k44_epilogue.cuh"
 #include "k44_ptx.cuh"
 
 namespace k44b {
 
-// ---------------------------------------------------------------------------------------------------
-// fused epilogue (semantics of kernels/cuda/kernel44_cuda_pack.cuh:54-58, 69-126; GELU added)
-// ---------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float apply_act(float v, int act) {
-    switch (act) {
-    case 1: return fmaxf(v, 0.0f);
-    case 2: return 1.0f / (1.0f + __expf(-v));
-    case 3: return v / (1.0f + __expf(-v));
-    case 4: return fmaxf(v, 0.1f * v);
-    case 5: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
-    default: return v;
-    }
-}
-
-// residual goes in before the activation when an output-row map is present, after it otherwise
-__device__ __forceinline__ float finish_value(float acc, float bias, float res, int act, bool has_res, bool has_map) {
-    float v = acc + bias;
-    if (has_res && has_map) v += res;
-    v = apply_act(v, act);
-    if (has_res && !has_map) v += res;
-    return v;
-}
 
 // ---------------------------------------------------------------------------------------------------
 // FMA path
@@ -149,111 +128,6 @@ struct UmmaCfg {
     static constexpr uint32_t kSmemBytes = 1024u /*alignment slack*/ + (uint32_t)kStages * kStageBytes + 256u + kOutStageBytes;
 };
 
-__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-// Shared by the direct and the split-K epilogue: 32 accumulator values of one neuron -> FP16 row segment.
-__device__ __forceinline__ void store_row_segment(const WaveArgs &a, const float (&v)[32], float bias, bool has_map, uint64_t elem_off) {
-    uint4 *dst = reinterpret_cast<uint4 *>(a.canvas + a.y_off + elem_off);
-    const uint4 *rsrc = reinterpret_cast<const uint4 *>(a.canvas + a.res_off + elem_off);
-#pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) {
-        float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (a.has_residual) {
-            const uint4 rv = rsrc[q4];
-            const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(rh[e]); r[2 * e] = f.x; r[2 * e + 1] = f.y; }
-        }
-        uint32_t pk[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float lo = finish_value(v[q4 * 8 + 2 * e], bias, r[2 * e], a.act, a.has_residual != 0, has_map);
-            const float hi = finish_value(v[q4 * 8 + 2 * e + 1], bias, r[2 * e + 1], a.act, a.has_residual != 0, has_map);
-            const __half2 h2 = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
-            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
-        }
-        dst[q4] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-    }
-}
-
-// Branch-free activation for the tensor-core epilogue: the activation kind is a template parameter so that the
-// 32 values a thread converts are independent straight-line code (a per-element runtime switch serialises them
-// behind branch latency when only one warp runs per scheduler).
-template <int ACT>
-__device__ __forceinline__ float act_fast(float v) {
-    if (ACT == 1) return fmaxf(v, 0.0f);
-    if (ACT == 2) return __fdividef(1.0f, 1.0f + __expf(-v));
-    if (ACT == 3) return __fdividef(v, 1.0f + __expf(-v));
-    if (ACT == 4) return fmaxf(v, 0.1f * v);
-    if (ACT == 5) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
-    return v;
-}
-
-// Each thread converts its 32 values (one neuron, 32 columns) to FP16 and parks them in a padded shared-memory
-// slot; the warp then writes the 32 rows back as whole 64-byte pieces (8 rows per instruction), so that every
-// global store fills complete 32-byte sectors. Must be called by all 32 lanes of a warp.
-template <int ACT, bool RES, bool MAP>
-__device__ __forceinline__ void stage_and_store_t(const WaveArgs &a, const float (&v)[32], float bias, bool live, uint32_t oj,
-                                                  uint64_t col0, uint8_t *wstage, uint32_t lane) {
-    uint4 *slot = reinterpret_cast<uint4 *>(wstage + lane * 80u);
-    uint32_t pk[16];
-    if (RES) {
-        const uint4 *rsrc = reinterpret_cast<const uint4 *>(a.canvas + a.res_off + (uint64_t)oj * a.pitch + col0);
-        uint4 rv[4];
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) rv[q4] = live ? rsrc[q4] : make_uint4(0, 0, 0, 0);
-        const __half2 *rh = reinterpret_cast<const __half2 *>(rv);
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            const float2 r = __half22float2(rh[e]);
-            float lo = v[2 * e] + bias, hi = v[2 * e + 1] + bias;
-            if (MAP) { lo += r.x; hi += r.y; }
-            lo = act_fast<ACT>(lo); hi = act_fast<ACT>(hi);
-            if (!MAP) { lo += r.x; hi += r.y; }
-            const __half2 h2 = __floats2half2_rn(lo, hi);
-            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
-        }
-    } else {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            const __half2 h2 = __floats2half2_rn(act_fast<ACT>(v[2 * e] + bias), act_fast<ACT>(v[2 * e + 1] + bias));
-            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
-        }
-    }
-#pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) slot[q4] = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-    __syncwarp();
-#pragma unroll
-    for (uint32_t i = 0; i < 4; ++i) {
-        const uint32_t r = 8u * i + (lane >> 2), piece = lane & 3u;
-        const uint32_t oj_r = __shfl_sync(0xffffffffu, oj, r);
-        const int live_r = __shfl_sync(0xffffffffu, live ? 1 : 0, r);
-        const uint4 val = *reinterpret_cast<const uint4 *>(wstage + r * 80u + piece * 16u);
-        if (live_r) *reinterpret_cast<uint4 *>(a.canvas + a.y_off + (uint64_t)oj_r * a.pitch + col0 + piece * 8u) = val;
-    }
-    __syncwarp();
-}
-
-template <int ACT>
-__device__ __forceinline__ void stage_and_store_a(const WaveArgs &a, const float (&v)[32], float bias, bool has_map, bool live, uint32_t oj,
-                                                  uint64_t col0, uint8_t *wstage, uint32_t lane) {
-    if (!a.has_residual) stage_and_store_t<ACT, false, false>(a, v, bias, live, oj, col0, wstage, lane);
-    else if (has_map) stage_and_store_t<ACT, true, true>(a, v, bias, live, oj, col0, wstage, lane);
-    else stage_and_store_t<ACT, true, false>(a, v, bias, live, oj, col0, wstage, lane);
-}
-
-// One uniform branch per 32 values instead of one per value.
-__device__ __forceinline__ void stage_and_store(const WaveArgs &a, const float (&v)[32], float bias, bool has_map, bool live, uint32_t oj,
-                                                uint64_t col0, uint8_t *wstage, uint32_t lane) {
-    switch (a.act) {
-    case 1: stage_and_store_a<1>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
-    case 2: stage_and_store_a<2>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
-    case 3: stage_and_store_a<3>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
-    case 4: stage_and_store_a<4>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
-    case 5: stage_and_store_a<5>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
-    default: stage_and_store_a<0>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
-    }
-}
 
 // Work item = (neuron tile, column tile, K split). With splits == 1 the epilogue writes the canvas directly.
 // With splits > 1 every item adds its partial accumulator into an FP32 scratch tile ([column][neuron] so that

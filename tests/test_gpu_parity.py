@@ -321,10 +321,33 @@ def test_token_shift_plan_general_path(group):
     check(plan, run_gpu(plan, x, PATH_FMA, expect_path=PATH_FMA), O.run_plan(plan, x))
 
 
-def test_token_shift_runs_stay_on_general_path():
-    """Shifted runs are recognised as runs (one table entry per 16 rows, shift in its top bits) but execute on
-    the FMA kernel: tcgen05.mma cannot place its result at an accumulator column offset of 1..7."""
-    plan = shifted_plan(131, runs=8, run_len=16, frames=3, frame_len=256, cout=256)
+@pytest.mark.parametrize("n_tile,frames,frame_len,run_len", [(64, 3, 256, 16), (128, 2, 256, 16), (64, 4, 64, 32), (128, 3, 128, 64), (64, 1, 192, 16)])
+def test_token_shift_runs_on_tensor_cores(n_tile, frames, frame_len, run_len, monkeypatch):
+    """Shifted runs (one table entry per run, shift in its top bits) execute on the tensor-core kernel whose aligner
+    warps shift the rows on their way into the operand stage; frame starts read zero."""
+    monkeypatch.setenv("K44B_N_TILE", str(n_tile))
+    plan = shifted_plan(131 + n_tile + frame_len, runs=128 // run_len, run_len=run_len, frames=frames, frame_len=frame_len, cout=384)
+    x = synth.random_input(plan, 25, dist="normal")
+    want = O.run_plan(plan, x)
+    check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_UMMA), want)
+    check(plan, run_gpu(plan, x, PATH_FMA, expect_path=PATH_FMA), want)
+
+
+def test_token_shift_tensor_path_with_bias_residual_and_many_tiles():
+    """More tiles than SMs (persistent walk over several items per CTA), bias, residual, a partial last neuron tile."""
+    plan = shifted_plan(171, rows_in=512, runs=16, run_len=16, frames=4, frame_len=512, cout=1280 + 64, group=1280 + 64, waves=2, act=ACT_SILU)
+    rng = np.random.default_rng(9)
+    for w in plan.waves:
+        w.bias = synth.f16_bits(rng.normal(0, 0.1, w.cout))
+    w1 = plan.waves[1]
+    w1.has_residual, w1.res_off = True, plan.waves[0].y_off
+    x = synth.random_input(plan, 27, dist="normal")
+    want = O.run_plan(plan, x)
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_UMMA), want)
+
+
+def test_token_shift_frames_that_split_a_tile_fall_back():
+    plan = shifted_plan(133, runs=8, run_len=16, frames=2, frame_len=96, cout=256)
     x = synth.random_input(plan, 25, dist="normal")
     check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_FMA), O.run_plan(plan, x))
 
