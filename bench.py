@@ -465,6 +465,134 @@ def sharded_main(args) -> None:
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------------------
+# fourth workload: receptive-field token shift (tensor-pipe bound)
+# ------------------------------------------------------------------------------------------------------------
+SHIFT = dict(sequences=8, tokens=4096, input_channels=2048, waves=4, cout=8192, runs=32, run_len=16, group=128, max_shift=7)
+
+
+def build_shift_plan(c: dict, device: int):
+    """Token-shift plan built in memory (weights generated on the device); returns the plan and, per wave, the run
+    starts [groups, runs] and shifts [groups, runs] it was built from."""
+    import torch
+    from snntome_b200 import synth
+    from snntome_b200._lib import WaveDesc
+    from snntome_b200.native import NativePlan, fill_normal_f16
+    pitch = c["sequences"] * c["tokens"]
+    fan_in = c["runs"] * c["run_len"]
+    total_rows = c["input_channels"] + c["waves"] * c["cout"]
+    plan = NativePlan.create(total_rows * pitch, pitch, pitch, device=device)
+    scratch = torch.empty((c["cout"], fan_in), dtype=torch.float16, device=f"cuda:{device}")
+    tables = []
+    for wi in range(c["waves"]):
+        fill_normal_f16(scratch, SEED * 1000 + 500 + wi, (1.0 / fan_in) ** 0.5)
+        torch.cuda.synchronize()
+        groups = c["cout"] // c["group"]
+        avail = c["input_channels"] + wi * c["cout"]
+        starts = synth.run_starts(SEED + 1, wi, groups, c["runs"], c["run_len"], avail).astype(np.uint32)
+        shifts = synth.uniform_int(SEED + 2, 2000 + wi, np.arange(groups * c["runs"], dtype=np.uint64), c["max_shift"] + 1).astype(np.uint8)
+        shifts = np.ascontiguousarray(shifts.reshape(groups, c["runs"]))
+        tables.append((starts, shifts))
+        d = WaveDesc()
+        d.cout = d.logical_cout = c["cout"]
+        d.cin = avail
+        d.group, d.fan_in, d.fan_in_raw, d.act, d.has_residual = c["group"], fan_in, fan_in, 5, 0
+        d.y_off = avail * pitch
+        d.run_rows, d.run_len = starts.ctypes.data, c["run_len"]
+        d.shifts, d.frame_len = shifts.ctypes.data, c["tokens"]
+        d.weights, d.weights_on_device = scratch.data_ptr(), 1
+        d.name = f"shift{wi}".encode()
+        plan.add_wave_desc(d)
+    del scratch
+    plan.set_io(0, c["input_channels"], (total_rows - c["cout"]) * pitch, c["cout"], pitch)
+    return plan, tables
+
+
+def shift_main(args) -> None:
+    """8 sequences x 4096 tokens as one row of 32768 columns per channel; 4 waves x 8192 neurons, fan-in 512 = 32 runs of
+    16 channels, every run read 0..7 tokens earlier with zero padding at the start of each sequence; GELU."""
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from snntome_b200.native import fill_normal_f16
+    c = dict(SHIFT)
+    if args.scale != 1.0:
+        c["sequences"] = max(1, int(round(c["sequences"] * args.scale)))
+    plan, _tables = build_shift_plan(c, local_rank)
+    pitch = c["sequences"] * c["tokens"]
+    fan_in = c["runs"] * c["run_len"]
+    canvas = plan.canvas_tensor()
+    fill_normal_f16(canvas[: c["input_channels"] * pitch], SEED + 177 + rank, 1.0)
+    torch.cuda.synchronize()
+    nw = plan.num_waves
+    infos = [plan.wave_info(i) for i in range(nw)]
+    stream = torch.cuda.current_stream()
+    warmup = max(3, args.warmup)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(warmup):
+        plan.execute(stream)
+    assert plan.status() == 0
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(nw + 1)] for _ in range(args.steps)]
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    l0 = plan.launch_count
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for s_ in range(args.steps):
+        ev[s_][0].record(stream)
+        for i in range(nw):
+            plan.execute_wave(i, stream)
+            ev[s_][i + 1].record(stream)
+    t1.record(stream)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches = plan.launch_count - l0
+    assert plan.status() == 0
+    ms = t0.elapsed_time(t1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+    clocks = sampler.stop()
+    per_wave = [float(np.mean([ev[s_][i].elapsed_time(ev[s_][i + 1]) for s_ in range(args.steps)])) for i in range(nw)]
+    flops_wave = 2.0 * c["cout"] * fan_in * pitch
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    kind = "measured (sustained dense bf16)" if peaks else "fallback"
+    achieved = flops_wave / (float(np.mean(per_wave)) * 1e-3) / 1e12
+    if rank == 0:
+        line = {"metric": "effective synaptic TFLOP/s (2*synapses*columns/s)", "value": flops_wave * nw * world / (ms_step * 1e-3) / 1e12,
+                "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+                "config": {"workload": "token-shift receptive fields: sequences x 4096 tokens per GPU, 2048 input channels, 4 waves x 8192 neurons, "
+                                       "fan-in 512 = 32 runs of 16 channels, shift 0..7 tokens per run, groups of 128, GELU",
+                           "sequences_per_gpu": c["sequences"], "columns_per_gpu": pitch, "scale": args.scale,
+                           "l2_policy": "substrate (0.13 - 2.3 GB) exceeds the 126 MB L2; no explicit flush"},
+                "roofline": {"bound": "tensor", "kernel": f"k44_wave_umma_shift_kernel<{infos[0].n_tile}>" if infos[0].path == 1 else "k44_wave_fma_kernel",
+                             "achieved": achieved, "peak": peak, "peak_kind": f"of {kind}", "unit": "TFLOP/s", "frac": achieved / peak,
+                             "flops_per_launch": flops_wave, "per_wave_ms": per_wave, "traffic": None},
+                "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "kernel_paths": [i.path for i in infos], "clocks": clocks}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -472,7 +600,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", type=float, default=float(os.environ.get("K44B_BENCH_SCALE", "1.0")))
-    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "pruned-sharded"])
+    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "pruned-sharded", "token-shift"])
     ap.add_argument("--layers", type=int, default=16, help="decode workload: decoder layers (16 = the 1B shape)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -481,6 +609,8 @@ def main() -> None:
         return decode_main(args)
     if args.workload == "pruned-sharded":
         return sharded_main(args)
+    if args.workload == "token-shift":
+        return shift_main(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -4,6 +4,8 @@
   device): the oracle cannot run all of it, so whole neuron groups are sampled per wave and recomputed by the oracle
   from the device's own inputs (the rows the group gathers, read back from the canvas) and weights (unpacked from the
   device's packed copy);
+* the token-shift plan at its full size (8 sequences x 4096 tokens, 4 waves x 8192 neurons, fan-in 512 as 32 shifted
+  runs of 16 channels): sampled (group, sequence) pairs are recomputed by the oracle from the device's inputs and weights;
 * a small dense decoder wave chain (same structure as the 1B benchmark: q,k,v / o+residual / gate,up / down+residual
   per layer, lm_head) replayed as a CUDA graph with grouped launches, against the oracle in full.
 """
@@ -20,7 +22,7 @@ sys.path.insert(0, str(ROOT))
 from oracle import oracle as O
 from snntome_b200 import synth
 from snntome_b200.native import NativePlan, PATH_UMMA
-from snntome_b200.plan import ACT_NONE, ACT_RELU, ACT_SILU, Plan, Wave
+from snntome_b200.plan import ACT_GELU, ACT_NONE, ACT_RELU, ACT_SILU, Plan, Wave
 
 pytestmark = pytest.mark.gpu
 RTOL, ATOL = 2e-3, 1e-3
@@ -63,6 +65,43 @@ def test_ultra_sparse_plan_full_size_sampled_groups():
             assert ok, f"wave {wi} group {g}: max abs err {err} at {k}"
         del wrm
         torch.cuda.empty_cache()
+    plan.close()
+
+
+def test_token_shift_plan_full_size_sampled_groups():
+    import torch
+    import bench
+    from snntome_b200.native import fill_normal_f16
+    c = dict(bench.SHIFT)
+    plan, tables = bench.build_shift_plan(c, 0)
+    T, pitch = c["tokens"], c["sequences"] * c["tokens"]
+    fan_in = c["runs"] * c["run_len"]
+    canvas = plan.canvas_tensor()
+    fill_normal_f16(canvas[: c["input_channels"] * pitch], 6, 1.0)
+    plan.execute()
+    assert plan.status() == 0
+    rng = np.random.default_rng(4)
+    cv2 = canvas.view(-1, pitch)
+    for wi in range(c["waves"]):
+        info = plan.wave_info(wi)
+        assert info.path == PATH_UMMA and info.n_tile == 128
+        starts, shifts = tables[wi]
+        wrm = plan.weights_rowmajor(wi)
+        row0 = c["input_channels"] + wi * c["cout"]
+        for g, f in zip(rng.choice(starts.shape[0], size=3, replace=False), rng.choice(c["sequences"], size=3, replace=True)):
+            rows = (torch.from_numpy(starts[g].astype(np.int64))[:, None] + torch.arange(c["run_len"])[None, :]).reshape(-1).cuda()
+            x = cv2[rows][:, f * T:(f + 1) * T].contiguous().cpu().numpy().view(np.uint16)     # this sequence's columns of the gathered rows
+            wg = wrm[g * 128:(g + 1) * 128].cpu().numpy().view(np.uint16)
+            got = cv2[row0 + g * 128: row0 + (g + 1) * 128, f * T:(f + 1) * T].contiguous().cpu().numpy().view(np.uint16)
+            idx = (np.arange(fan_in, dtype=np.uint32) * T)[None, :]
+            sh = np.repeat(shifts[g], c["run_len"])[None, :]
+            wave = Wave(cout=128, group=128, fan_in=fan_in, idx=idx, weights=wg, bias=None, y_off=fan_in * T, act=ACT_GELU, shifts=sh, frame_len=T)
+            mini = Plan(canvas_elems=(fan_in + 128) * T, pitch=T, columns=T, input_off=0, input_c=fan_in, output_off=fan_in * T,
+                        output_c=128, waves=[wave])
+            want = O.run_plan(mini, x)[fan_in * T:]
+            ok, err, k = O.compare(got.reshape(-1), want, RTOL, ATOL)
+            assert ok, f"wave {wi} group {g} sequence {f}: max abs err {err} at {k}"
+        del wrm
     plan.close()
 
 
