@@ -524,6 +524,7 @@ def shift_main(args) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     from snntome_b200.native import fill_normal_f16
     c = dict(SHIFT)
+    c["max_shift"] = max(0, min(8, args.max_shift))
     if args.scale != 1.0:
         c["sequences"] = max(1, int(round(c["sequences"] * args.scale)))
     plan, _tables = build_shift_plan(c, local_rank)
@@ -582,9 +583,9 @@ def shift_main(args) -> None:
                 "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
                 "config": {"workload": "token-shift receptive fields: sequences x 4096 tokens per GPU, 2048 input channels, 4 waves x 8192 neurons, "
                                        "fan-in 512 = 32 runs of 16 channels, shift 0..7 tokens per run, groups of 128, GELU",
-                           "sequences_per_gpu": c["sequences"], "columns_per_gpu": pitch, "scale": args.scale,
+                           "sequences_per_gpu": c["sequences"], "columns_per_gpu": pitch, "scale": args.scale, "max_shift": c["max_shift"],
                            "l2_policy": "substrate (0.13 - 2.3 GB) exceeds the 126 MB L2; no explicit flush"},
-                "roofline": {"bound": "tensor", "kernel": f"k44_wave_umma_shift_kernel<{infos[0].n_tile}>" if infos[0].path == 1 else "k44_wave_fma_kernel",
+                "roofline": {"bound": "tensor", "kernel": (f"k44_wave_umma_shift_kernel<{infos[0].n_tile}>" if c["max_shift"] else f"k44_wave_umma_kernel<{infos[0].n_tile}>") if infos[0].path == 1 else "k44_wave_fma_kernel",
                              "achieved": achieved, "peak": peak, "peak_kind": f"of {kind}", "unit": "TFLOP/s", "frac": achieved / peak,
                              "flops_per_launch": flops_wave, "per_wave_ms": per_wave, "traffic": None},
                 "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "kernel_paths": [i.path for i in infos], "clocks": clocks}
@@ -602,6 +603,7 @@ def main() -> None:
     ap.add_argument("--scale", type=float, default=float(os.environ.get("K44B_BENCH_SCALE", "1.0")))
     ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "pruned-sharded", "token-shift"])
     ap.add_argument("--layers", type=int, default=16, help="decode workload: decoder layers (16 = the 1B shape)")
+    ap.add_argument("--max-shift", type=int, default=7, help="token-shift workload: largest token shift drawn per run (0 = unshifted runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()

@@ -91,6 +91,8 @@ int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, in
 /* Development aid: 16 SM-clock timestamps recorded by CTA 0 of the last tcgen05 wave kernel when the
  * library runs with K44B_DEBUG_MODE=16 (all zero otherwise). */
 int k44b_debug_trace(void *plan, long long *out16);
+/* the first `count` (<= 500) 64-bit words of the development trace area */
+int k44b_debug_trace_words(void *plan, long long *out, int count);
 /* Number of kernels this plan has launched so far. */
 uint64_t k44b_launch_count(void *plan);
 /* Unpack wave `wave`'s device weights to row-major [cout][fan_in] FP16 at device pointer d_dst. */

@@ -356,7 +356,12 @@ int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, in
 
 int k44b_debug_trace(void *plan, long long *out16) {
     if (!plan || !out16) return set_error("debug_trace: bad arguments");
-    return P(plan)->exec.read_trace(out16) ? 0 : set_error(P(plan)->exec.err);
+    return P(plan)->exec.read_trace(out16, 16) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_debug_trace_words(void *plan, long long *out, int count) {
+    if (!plan || !out) return set_error("debug_trace_words: bad arguments");
+    return P(plan)->exec.read_trace(out, count) ? 0 : set_error(P(plan)->exec.err);
 }
 
 uint64_t k44b_launch_count(void *plan) { return plan ? P(plan)->exec.launches() : 0; }

@@ -209,14 +209,14 @@ bool Executor::begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t
     pitch_ = pitch; columns_ = columns ? columns : pitch; canvas_elems_ = canvas_elems;
     if (!check(cudaMalloc(&canvas_, canvas_elems * sizeof(__half)), "canvas allocation")) { canvas_ = nullptr; return false; }
     if (!check(cudaMemset(canvas_, 0, canvas_elems * sizeof(__half)), "canvas clear")) return false;
-    if (!check(cudaMalloc(&d_status_, 256), "status allocation")) return false;
-    if (!check(cudaMemset(d_status_, 0, 256), "status clear")) return false;
+    if (!check(cudaMalloc(&d_status_, kStatusBytes), "status allocation")) return false;
+    if (!check(cudaMemset(d_status_, 0, kStatusBytes), "status clear")) return false;
     if (!check(cudaEventCreate(&ev0_), "event") || !check(cudaEventCreate(&ev1_), "event")) return false;
     if (!check(umma_kernel_setup(), "kernel attribute setup")) return false;
     return true;
 }
 
-bool Executor::make_tensor_map(DeviceWave &dw) {
+bool Executor::make_tensor_map(DeviceWave &dw, uint32_t box_cols, bool swizzle128) {
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -230,10 +230,10 @@ bool Executor::make_tensor_map(DeviceWave &dw) {
     }
     const cuuint64_t dims[2] = {pitch_, canvas_elems_ / pitch_};
     const cuuint64_t strides[1] = {(cuuint64_t)pitch_ * 2u};
-    const cuuint32_t box[2] = {64u, dw.args.box_h};
+    const cuuint32_t box[2] = {box_cols, dw.args.box_h};
     const cuuint32_t estr[2] = {1u, 1u};
     const CUresult r = encode(&dw.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, canvas_, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
     return true;
 }
@@ -342,13 +342,17 @@ bool Executor::add_wave(const HostWave &w) {
         dw.path = (dw.umma_capable && force_path_ != 0) ? PATH_UMMA : PATH_FMA;
         if (dw.path == PATH_UMMA && dw.use_shift) {
             const uint32_t flen = w.frame_len ? w.frame_len : pitch_;
-            uint32_t n_tile = (tiles64 % 2u == 0u && flen % 128u == 0u && (uint64_t)mtiles * (tiles64 / 2u) >= (uint64_t)num_sms_) ? 128u : 64u;
+            uint32_t n_tile = 64;
+            for (uint32_t cand : {256u, 128u})
+                if (tiles64 % (cand / 64u) == 0u && flen % cand == 0u && (uint64_t)mtiles * (tiles64 / (cand / 64u)) >= (uint64_t)num_sms_) { n_tile = cand; break; }
             if (const char *e = std::getenv("K44B_N_TILE")) {
                 const uint32_t v = (uint32_t)std::atoi(e);
-                if ((v == 64 || v == 128) && tiles64 % (v / 64u) == 0u && flen % v == 0u) n_tile = v;
+                if ((v == 64 || v == 128 || v == 256) && tiles64 % (v / 64u) == 0u && flen % v == 0u) n_tile = v;
             }
             a.k_splits = 1; a.kstages_per_split = a.num_kstages;
             dw.desc = make_umma_desc(n_tile, 0);
+            if (const char *e = std::getenv("K44B_DEBUG_MODE")) dw.desc.debug = (uint32_t)std::atoi(e);
+            ok = make_tensor_map(dw, std::min(n_tile, 128u) + 8u, false);   // aligned windows of up to 128 columns plus the 8 to their left, as plain rows
         } else if (dw.path == PATH_UMMA) {
             uint32_t n_tile = 64;
             for (uint32_t cand : {256u, 128u})
@@ -389,7 +393,7 @@ bool Executor::add_wave(const HostWave &w) {
             dw.desc.small_wave = small ? 1u : 0u;
             if (const char *e = std::getenv("K44B_DEBUG_MODE")) dw.desc.debug = (uint32_t)std::atoi(e);
             if (a.k_splits > 1 && !cluster) ok = reserve_scratch((size_t)mtiles * tiles64);
-            ok = ok && make_tensor_map(dw);
+            ok = ok && make_tensor_map(dw, 64u, true);
         }
     }
     if (!ok) {
@@ -524,7 +528,7 @@ bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
         g.total_clusters = ((w.args.cout + kTileM - 1) / kTileM) * w.args.num_col_tiles64;
         e = launch_wave_umma_cluster(g, w.desc, w.tmap, pdl_, num_sms_, stream);
     } else if (w.path == PATH_UMMA && w.use_shift) {
-        e = launch_wave_umma_shift(w.args, w.desc, num_sms_, stream);
+        e = launch_wave_umma_shift(w.args, w.desc, w.tmap, num_sms_, stream);
     } else if (w.path == PATH_UMMA) {
         w.args.scratch = d_scratch_;
         w.args.counters = d_counters_;
@@ -608,10 +612,11 @@ bool Executor::read_status(uint32_t *status) {
     return true;
 }
 
-bool Executor::read_trace(long long *out16) {
+bool Executor::read_trace(long long *out, int count) {
     if (!ready()) return fail("executor not initialised");
+    if (count < 0 || (size_t)count * sizeof(long long) + 8 > kStatusBytes) return fail("trace read: count out of range");
     return check(cudaDeviceSynchronize(), "synchronise") &&
-           check(cudaMemcpy(out16, reinterpret_cast<char *>(d_status_) + 8, 16 * sizeof(long long), cudaMemcpyDeviceToHost), "trace read");
+           check(cudaMemcpy(out, reinterpret_cast<char *>(d_status_) + 8, (size_t)count * sizeof(long long), cudaMemcpyDeviceToHost), "trace read");
 }
 
 bool Executor::execute_timed(float *ms) {

@@ -49,6 +49,7 @@ struct DeviceWave {
 
 class Executor {
   public:
+    static constexpr size_t kStatusBytes = 4096;   // status word + development trace area
     ~Executor() { release(); }
     std::string err;
 
@@ -67,7 +68,7 @@ class Executor {
     bool execute_timed(float *ms);                                 // default stream, event-timed, synchronous
     bool infer_f32(const float *h_in, int in_elems, float *h_out, int out_elems, float *gpu_ms);
     bool read_status(uint32_t *status);                            // synchronises the device
-    bool read_trace(long long *out16);                             // development aid: kernel milestone clocks
+    bool read_trace(long long *out, int count);                             // development aid: kernel milestone clocks
     bool weights_to_rowmajor(size_t wave, void *d_dst);            // unpack check: tiled -> [cout][fan_in]
 
     bool ready() const { return canvas_ != nullptr; }
@@ -82,7 +83,7 @@ class Executor {
   private:
     bool fail(const std::string &m) { err = m; return false; }
     bool check(cudaError_t e, const char *what);
-    bool make_tensor_map(DeviceWave &dw);
+    bool make_tensor_map(DeviceWave &dw, uint32_t box_cols, bool swizzle128);
     bool reserve_scratch(size_t tiles);
     bool launch_one(DeviceWave &w, cudaStream_t stream);
     void drop_graph();

@@ -96,8 +96,9 @@ cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtenso
 // small waves: one item per CTA, the K splits of a tile form a cluster (k_splits in {1,2,4,8}) and reduce through
 // distributed shared memory; dependent_launch adds the programmatic-dependent-launch attribute
 cudaError_t launch_wave_umma_cluster(const WaveGroupArgs &g, const UmmaDesc &d, const CUtensorMap &tmap, bool dependent_launch, int num_sms, cudaStream_t s);
-// token-shifted runs (box gather, shifts in the table entries): n_tile 64 or 128, frames must be whole tiles
-cudaError_t launch_wave_umma_shift(const WaveArgs &a, const UmmaDesc &d, int num_sms, cudaStream_t s);
+// token-shifted runs (box gather, shifts in the table entries): n_tile 64 or 128, frames must be whole tiles; the tensor
+// map describes the canvas with boxes of (n_tile + 8) columns x box_h rows and no swizzle
+cudaError_t launch_wave_umma_shift(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
 cudaError_t umma_kernel_setup();       // opt in to large dynamic shared memory (once per device)
 
 // packer kernels

@@ -5,12 +5,13 @@
 // is below the shift. A shift of 1..7 FP16 elements is not a legal start for a tensor copy (16-byte rule) and
 // not a legal operand offset for tcgen05.mma, so the rows are realigned on their way into shared memory:
 //
-//   warp 0      streams the packed weight blocks with bulk copies (as in the unshifted kernel);
-//   warps 6-9   ("aligners", one 16-row run each per stage) load the aligned window [t0 - 8, t0 + N) of their rows
-//               from global memory with 16-byte loads, funnel-shift it by the run's shift in registers and store
-//               the result in the 128-byte-swizzled operand layout; loads for the next stage are issued before
-//               the current one is written, so the global latency hides behind the pipeline;
-//   warp 1      issues tcgen05.mma once the weights have landed and the four aligners have arrived;
+//   warp 0      streams, per 64-synapse step, the packed weight block (bulk copy) and the aligned window
+//               [t0 - 8, t0 + N) of the step's substrate rows (one tensor copy per run, no swizzle) into a ring of
+//               load stages; the ring is deep enough to cover the memory latency;
+//   warps 6-9   ("aligners", 16 rows each per step) read their rows of the window from shared memory, funnel-shift
+//               them by the run's shift in registers and store the result into a second, short ring in the
+//               128-byte-swizzled operand layout;
+//   warp 1      issues tcgen05.mma on (weights of the load stage, operand stage) and releases both;
 //   warps 2-5   epilogue out of double-buffered tensor memory (shared with the unshifted kernel).
 //
 // Tiles are walked column-tile-major: all neuron tiles of one column window run together, so the wave's weights
@@ -26,23 +27,31 @@
 namespace k44b {
 namespace shiftwave {
 
-constexpr int kThreads = 320;
+constexpr int kTabEntries = 128;                    // run-table entries of one item held in shared memory (fan-in up to 2048 with 16-row runs)
 
+// A tile of N_TILE columns is cut into sub-windows of at most 128 columns; each sub-window has its own copy of the
+// 8 columns to its left (a tensor copy is at most 256 elements wide) and its own set of four aligner warps.
 template <int N_TILE>
 struct Cfg {
     static constexpr int kColBlocks = N_TILE / 64;
-    static constexpr uint32_t kXBytes = (uint32_t)kColBlocks * kStageK * 128u;
-    static constexpr uint32_t kStageBytes = kStageWBytes + kXBytes;
-    static constexpr int kStages = N_TILE == 64 ? 8 : 6;
+    static constexpr int kSubCols = N_TILE < 128 ? N_TILE : 128;
+    static constexpr int kSubs = N_TILE / kSubCols;
+    static constexpr int kThreads = 192 + 128 * kSubs;
+    static constexpr uint32_t kXBytes = (uint32_t)kColBlocks * kStageK * 128u;      // operand stage
+    static constexpr uint32_t kRawPitch = (uint32_t)(kSubCols + 8) * 2u;            // bytes per window row (an odd number of 16-byte chunks)
+    static constexpr uint32_t kSubRawBytes = kStageK * kRawPitch;                   // a multiple of 128
+    static constexpr uint32_t kRawBytes = (uint32_t)kSubs * kSubRawBytes;
+    static constexpr int kLoadStages = N_TILE == 64 ? 6 : (N_TILE == 128 ? 5 : 3);  // weights + windows
+    static constexpr int kOpStages = N_TILE == 256 ? 2 : 3;                         // realigned operand
     static constexpr uint32_t kTmemCols = 2u * N_TILE;
     static constexpr uint32_t kOutStageBytes = 128u * 80u;
-    static constexpr uint32_t kSmemBytes = 1024u + (uint32_t)kStages * kStageBytes + 256u + kOutStageBytes;
-    static constexpr int kOutChunks = N_TILE / 16;      // 16-byte chunks one aligner lane produces per row
+    static constexpr uint32_t kSmemBytes = 1024u + (uint32_t)kLoadStages * (kStageWBytes + kRawBytes) + (uint32_t)kOpStages * kXBytes + 256u + kOutStageBytes + 2u * kTabEntries * 4u;
+    static constexpr int kOutChunks = kSubCols / 16;    // 16-byte chunks one aligner lane produces per row
 };
 
-__device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
     uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
     return v;
 }
 __device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
@@ -71,34 +80,42 @@ __device__ __forceinline__ void shift_and_store(const uint4 (&raw)[OC + 1], uint
 }
 
 template <int N_TILE>
-__global__ void __launch_bounds__(kThreads, 1)
-k44_wave_umma_shift_kernel(const WaveArgs a, const UmmaDesc d) {
+__global__ void __launch_bounds__(Cfg<N_TILE>::kThreads, 1)
+k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a, const UmmaDesc d) {
     using C = Cfg<N_TILE>;
-    constexpr int STAGES = C::kStages;
+    constexpr int SL = C::kLoadStages, SB = C::kOpStages;
     constexpr int OC = C::kOutChunks;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
-    const uint32_t w_smem = smem_base;
-    const uint32_t x_smem = smem_base + (uint32_t)STAGES * kStageWBytes;
-    const uint32_t ctl = x_smem + (uint32_t)STAGES * C::kXBytes;
-    const uint32_t full_bar = ctl, empty_bar = ctl + 8u * STAGES;
-    const uint32_t tfull_bar = ctl + 16u * STAGES, tempty_bar = tfull_bar + 16u;
+    const uint32_t w_smem = smem_base;                                        // SL weight blocks
+    const uint32_t x_smem = w_smem + (uint32_t)SL * kStageWBytes;             // SB operand stages (swizzled)
+    const uint32_t raw_smem = x_smem + (uint32_t)SB * C::kXBytes;             // SL windows (plain rows)
+    const uint32_t ctl = raw_smem + (uint32_t)SL * C::kRawBytes;
+    const uint32_t lfull_bar = ctl, lempty_bar = ctl + 8u * SL;               // load ring
+    const uint32_t bfull_bar = ctl + 16u * SL, bempty_bar = bfull_bar + 8u * SB;   // operand ring
+    const uint32_t tfull_bar = bempty_bar + 8u * SB, tempty_bar = tfull_bar + 16u;
     uint8_t *ctl_ptr = smem_raw + (ctl - ptx::smem_addr(smem_raw));
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ctl_ptr + 16 * STAGES + 32);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ctl_ptr + 16 * SL + 16 * SB + 32);
     volatile uint32_t *abort_word = tmem_slot + 1;
     volatile uint32_t *epi_ok = tmem_slot + 4;
     uint8_t *out_stage = ctl_ptr + 256;
+    const uint32_t tab_smem = ctl + 256u + C::kOutStageBytes;                  // two run-table buffers of kTabEntries words
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t tiles_n = a.num_col_tiles64 / C::kColBlocks;
     const uint32_t mtiles = (a.cout + kTileM - 1) / kTileM;
     const uint32_t total_items = mtiles * tiles_n;
     const uint32_t KS = a.num_kstages;
+    const uint32_t boxes_per_stage = kStageK / a.box_h;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            ptx::mbar_init(full_bar + 8u * s, 5);      // weight copy (with its byte count) + four aligner warps
-            ptx::mbar_init(empty_bar + 8u * s, 1);
+        for (int s = 0; s < SL; ++s) {
+            ptx::mbar_init(lfull_bar + 8u * s, 1);       // producer's arrival carrying the byte count
+            ptx::mbar_init(lempty_bar + 8u * s, 1 + 4 * C::kSubs);   // MMA commit (weights) + the aligner warps (windows)
+        }
+        for (int s = 0; s < SB; ++s) {
+            ptx::mbar_init(bfull_bar + 8u * s, 4 * C::kSubs);        // the aligner warps
+            ptx::mbar_init(bempty_bar + 8u * s, 1);      // MMA commit
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(tfull_bar + 8u * b, 1);
@@ -106,6 +123,10 @@ k44_wave_umma_shift_kernel(const WaveArgs a, const UmmaDesc d) {
         }
         *abort_word = 0;
         ptx::fence_mbar_init();
+        if ((d.debug & 16u) && blockIdx.x == 0) {
+            reinterpret_cast<volatile long long *>(a.status + 2)[14] = 0;
+            reinterpret_cast<volatile long long *>(a.status + 2)[15] = 0;
+        }
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_addr(const_cast<uint32_t *>(tmem_slot)), C::kTmemCols);
@@ -115,6 +136,13 @@ k44_wave_umma_shift_kernel(const WaveArgs a, const UmmaDesc d) {
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // development aid (debug bit 16): CTA 0 records SM-clock timestamps / wait totals after the status word
+    const bool trace = (d.debug & 16u) && blockIdx.x == 0;
+    volatile long long *tr = reinterpret_cast<volatile long long *>(a.status + 2);
+    if (trace && threadIdx.x == 0) tr[0] = clock64();
+    // per-step stamps of steps 40..55: slot 16 + 8 * (g - 40) + k; k: 0 producer got the stage, 1 producer issued,
+    // 2 aligner got window and operand stage, 3 aligner arrived, 4 MMA got both, 5 MMA committed
+    auto stamp_step = [&](uint32_t g, int k) { if (trace && g >= 40u && g < 56u) tr[16 + 8 * (g - 40u) + k] = clock64(); };
 
     auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
         const long long t0 = clock64();
@@ -131,65 +159,128 @@ k44_wave_umma_shift_kernel(const WaveArgs a, const UmmaDesc d) {
     const uint32_t my_items = blockIdx.x < total_items ? (total_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
 
     if (warp == 0) {
-        // ---------------- weight producer ----------------
-        if (lane == 0) {
-            const uint64_t pol_w = ptx::policy_evict_last();    // the wave's weights are re-read by every column tile
-            uint32_t issued = 0;
-            bool ok = true;
-            for (uint32_t it = 0; it < my_items && ok; ++it) {
+        // ---------------- producer: weights and substrate windows ----------------
+        // One thread runs the whole issue loop (no warp-wide exchange per step); the run-table entries of an item are
+        // copied into a small shared-memory table by the whole warp one item ahead, with asynchronous 4-byte copies.
+        if (lane == 0) ptx::prefetch_tensormap(&tmap);
+        const uint64_t pol = ptx::policy_evict_last();     // weights and this column window are re-read by other tiles
+        uint32_t issued = 0;
+        bool ok = true;
+        long long pr_wait = 0;
+        const uint32_t per_item = KS * boxes_per_stage;                     // table entries one item consumes
+        const bool use_tab = per_item <= (uint32_t)kTabEntries;
+        auto prefetch_entries = [&](uint32_t it) {
+            uint32_t mt, ct;
+            decode(blockIdx.x + it * gridDim.x, mt, ct);
+            const uint32_t *rows = a.gather + (uint64_t)(mt / a.mtiles_per_group) * a.boxes_per_group;
+            for (uint32_t e = lane; e < per_item; e += 32u)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(tab_smem + ((it & 1u) * kTabEntries + e) * 4u), "l"(rows + e) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        if (use_tab && my_items) prefetch_entries(0u);
+        for (uint32_t it = 0; it < my_items; ++it) {
+            if (use_tab) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncwarp();
+                if (it + 1u < my_items) prefetch_entries(it + 1u);
+            }
+            // lane b issues box b of every step (issuing a tensor copy costs the issuing thread of the order of a hundred
+            // cycles, so the boxes of a step go out as one warp instruction); lane 0 also posts the byte count and the
+            // weight copy. The lanes need no exchange: each reads its own table entry.
+            if (lane < boxes_per_stage * (uint32_t)C::kSubs) {
                 uint32_t mt, ct;
                 decode(blockIdx.x + it * gridDim.x, mt, ct);
                 const uint4 *wsrc = a.w_tiles + (uint64_t)mt * KS * (kStageWBytes / 16u);
+                const uint32_t *rows = a.gather + (uint64_t)(mt / a.mtiles_per_group) * a.boxes_per_group;
+                const uint32_t tab_it = tab_smem + (it & 1u) * (kTabEntries * 4u);
+                const uint32_t pb = lane / (uint32_t)C::kSubs, psub = lane % (uint32_t)C::kSubs;   // this lane's box and sub-window
+                const int32_t x0 = (int32_t)(ct * (uint32_t)N_TILE + psub * (uint32_t)C::kSubCols) - 8;   // columns left of the row start read as zero
                 for (uint32_t ks = 0; ks < KS; ++ks, ++issued) {
-                    const uint32_t stage = issued % STAGES, ph = (issued / STAGES) & 1u;
-                    ok = wait(empty_bar + 8u * stage, ph ^ 1u);
+                    const uint32_t stage = issued % SL, ph = (issued / SL) & 1u;
+                    const uint32_t bi = ks * boxes_per_stage + pb;
+                    uint32_t e;
+                    if (use_tab) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(tab_it + bi * 4u) : "memory");
+                    else e = __ldg(rows + bi);
+                    long long p0 = 0;
+                    if (trace) p0 = clock64();
+                    ok = wait(lempty_bar + 8u * stage, ph ^ 1u);
+                    if (trace) pr_wait += clock64() - p0;
+                    if (lane == 0) stamp_step(issued, 0);
                     if (!ok) break;
-                    ptx::mbar_arrive_expect_tx(full_bar + 8u * stage, kStageWBytes);
-                    ptx::bulk_g2s(w_smem + stage * kStageWBytes, wsrc + (uint64_t)ks * (kStageWBytes / 16u), kStageWBytes,
-                                  full_bar + 8u * stage, pol_w);
+                    const uint32_t wb = (d.debug & 256u) ? 0u : kStageWBytes, rb = (d.debug & 4u) ? 0u : C::kRawBytes;
+                    if (lane == 0) {
+                        if (wb + rb) ptx::mbar_arrive_expect_tx(lfull_bar + 8u * stage, wb + rb);
+                        else ptx::mbar_arrive(lfull_bar + 8u * stage);
+                        if (wb) ptx::bulk_g2s(w_smem + stage * kStageWBytes, wsrc + (uint64_t)ks * (kStageWBytes / 16u), kStageWBytes,
+                                              lfull_bar + 8u * stage, pol);
+                    }
+                    if (rb) ptx::tma_load_2d(raw_smem + stage * C::kRawBytes + psub * C::kSubRawBytes + pb * a.box_h * C::kRawPitch, &tmap, x0, (int32_t)(e & kBoxRowMask),
+                                             lfull_bar + 8u * stage, pol);
+                    if (lane == 0) stamp_step(issued, 1);
                 }
             }
-            if (!ok) {
-                if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PRODUCER);
-                *abort_word = 1u;
-                // the copies still in flight complete on barriers nobody may be waiting on any more: give them time
-                const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0u;
-                for (uint32_t i = first; i < issued; ++i) {
-                    const long long t0 = clock64();
-                    bool done = false;
-                    while (!done && (unsigned long long)(clock64() - t0) < d.wait_cycles)
-                        done = ptx::mbar_try_wait(full_bar + 8u * (i % STAGES), (i / STAGES) & 1u);
-                    if (!done) atomicOr(a.status, (uint32_t)ST_TIMEOUT_DRAIN);
-                }
+            ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+            issued = __shfl_sync(0xffffffffu, issued, 0);
+            if (!ok) break;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (trace && lane == 0) { tr[9] = pr_wait; }
+        if (!ok && lane == 0) {
+            if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PRODUCER);
+            *abort_word = 1u;
+            // wait (bounded) for copies already in flight before this CTA's shared memory goes away
+            const uint32_t first = issued > (uint32_t)SL ? issued - SL : 0u;
+            for (uint32_t i = first; i < issued; ++i) {
+                const long long t0 = clock64();
+                bool done = false;
+                while (!done && (unsigned long long)(clock64() - t0) < d.wait_cycles)
+                    done = ptx::mbar_try_wait(lfull_bar + 8u * (i % SL), (i / SL) & 1u);
+                if (!done) atomicOr(a.status, (uint32_t)ST_TIMEOUT_DRAIN);
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            uint32_t consumed = 0;
+            uint32_t g = 0;
             bool ok = true;
+            long long acc_b = 0, acc_l = 0, acc_t = 0;       // trace: cycles spent waiting for operands / weights / a free accumulator
             for (uint32_t it = 0; it < my_items && ok; ++it) {
                 const uint32_t acc = it & 1u;
+                long long wt0 = 0;
+                if (trace) wt0 = clock64();
                 ok = wait(tempty_bar + 8u * acc, ((it >> 1) & 1u) ^ 1u);
+                if (trace) acc_t += clock64() - wt0;
                 if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * N_TILE;
-                for (uint32_t ks = 0; ks < KS; ++ks, ++consumed) {
-                    const uint32_t stage = consumed % STAGES, ph = (consumed / STAGES) & 1u;
-                    ok = wait(full_bar + 8u * stage, ph);
+                for (uint32_t ks = 0; ks < KS; ++ks, ++g) {
+                    const uint32_t ls = g % SL, lph = (g / SL) & 1u, bs = g % SB, bph = (g / SB) & 1u;
+                    long long w0 = 0;
+                    if (trace) w0 = clock64();
+                    ok = wait(bfull_bar + 8u * bs, bph);                                      // operand realigned
+                    if (trace) { const long long w1 = clock64(); acc_b += w1 - w0; w0 = w1; }
+                    ok = ok && wait(lfull_bar + 8u * ls, lph);                                // weights landed
+                    if (trace) acc_l += clock64() - w0;
+                    stamp_step(g, 4);
                     if (!ok) break;
                     ptx::tc_fence_after();
-                    const uint64_t a0 = d.a_base | (uint64_t)(((w_smem + stage * kStageWBytes) >> 4) & 0x3fffu);
-                    const uint64_t b0 = d.b_base | (uint64_t)(((x_smem + stage * C::kXBytes) >> 4) & 0x3fffu);
+                    const uint64_t a0 = d.a_base | (uint64_t)(((w_smem + ls * kStageWBytes) >> 4) & 0x3fffu);
+                    const uint64_t b0 = d.b_base | (uint64_t)(((x_smem + bs * C::kXBytes) >> 4) & 0x3fffu);
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < kStageK / 16u; ++k4)
-                        ptx::umma_f16(d_tmem, a0 + (uint64_t)(k4 * d.a_k_step), b0 + (uint64_t)(k4 * d.b_k_step), d.idesc,
-                                      (ks != 0u || k4 != 0u) ? 1u : 0u);
-                    ptx::umma_commit(empty_bar + 8u * stage);
+                        if (!(d.debug & 128u) || k4 == 0u)
+                            ptx::umma_f16(d_tmem, a0 + (uint64_t)(k4 * d.a_k_step), b0 + (uint64_t)(k4 * d.b_k_step), d.idesc,
+                                          (ks != 0u || k4 != 0u) ? 1u : 0u);
+                    ptx::umma_commit(lempty_bar + 8u * ls);     // weight block reusable once these MMAs retire
+                    ptx::umma_commit(bempty_bar + 8u * bs);     // operand stage likewise
+                    stamp_step(g, 5);
                 }
                 if (ok) ptx::umma_commit(tfull_bar + 8u * acc);
+                if (trace && it == 0u) tr[1] = clock64();
+                if (trace && it == 9u) tr[3] = clock64();
             }
+            if (trace) { tr[13] = acc_t; tr[14] = acc_b; tr[15] = acc_l; tr[2] = clock64(); }
             if (!ok) {
                 if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_MMA);
                 *abort_word = 1u;
@@ -222,7 +313,7 @@ k44_wave_umma_shift_kernel(const WaveArgs a, const UmmaDesc d) {
                 float f[32];
 #pragma unroll
                 for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
-                stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
+                if (!(d.debug & 8u)) stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
             }
             ptx::tc_fence_before();
             ptx::mbar_arrive(tempty_bar + 8u * acc);
@@ -233,73 +324,85 @@ k44_wave_umma_shift_kernel(const WaveArgs a, const UmmaDesc d) {
         }
     } else {
         // ---------------- aligners ----------------
-        const uint32_t sw = warp - 6u;                      // rows 16*sw .. 16*sw + 15 of every stage
-        const uint32_t r = lane >> 1, half = lane & 1u;
+        const uint32_t sub = (warp - 6u) >> 2, sw = (warp - 6u) & 3u;    // this warp: rows 16*sw .. 16*sw + 15 of sub-window `sub`
+        const uint32_t r = lane & 15u, half = lane >> 4;    // 8 consecutive rows per shared-memory phase: conflict-free both ways
         const uint32_t krow = 16u * sw + r;
-        const uint32_t first_chunk = half * (uint32_t)OC;
+        const uint32_t first_chunk = half * (uint32_t)OC;                // inside the sub-window
+        const uint32_t out_chunk0 = sub * (uint32_t)(C::kSubCols / 8) + first_chunk;   // inside the tile row
         const uint32_t flen = a.frame_len ? a.frame_len : a.pitch;
-        const uint32_t total = my_items * KS;
-
-        uint4 bufA[OC + 1], bufB[OC + 1];
-        uint32_t shA = 0, shB = 0;
-
-        // issue the global loads of flattened step g (item g / KS, stage g % KS)
-        auto load = [&](uint32_t g, uint4 (&buf)[OC + 1], uint32_t &sh) {
-            uint32_t mt, ct;
-            decode(blockIdx.x + (g / KS) * gridDim.x, mt, ct);
-            const uint32_t ks = g % KS;
-            const uint32_t k0 = ks * kStageK + 16u * sw;                   // first synapse of this warp's run
-            const uint32_t *rows = a.gather + (uint64_t)(mt / a.mtiles_per_group) * a.boxes_per_group;
-            const uint32_t e = __ldg(rows + k0 / a.box_h);
-            sh = e >> 28;
-            const uint32_t row = (e & kBoxRowMask) + (k0 % a.box_h) + r;
-            const uint32_t t0 = ct * (uint32_t)N_TILE;
-            const bool frame_start = (t0 % flen) == 0u;                    // the 8 columns left of the tile belong to another frame
-            const __half *src = a.canvas + (uint64_t)row * a.pitch + t0 + first_chunk * 8u;
-#pragma unroll
-            for (int i = 0; i <= OC; ++i) {
-                if (i == 0 && half == 0u && frame_start) buf[0] = make_uint4(0u, 0u, 0u, 0u);
-                else buf[i] = ldg_nc_v4(src + 8 * i - 8);
-            }
-        };
-        // realign and store step g into its pipeline stage, then arrive
-        auto store = [&](uint32_t g, const uint4 (&buf)[OC + 1], uint32_t sh) -> bool {
-            const uint32_t stage = g % STAGES, ph = (g / STAGES) & 1u;
-            uint32_t ok = 1u;
-            if (lane == 0) ok = wait(empty_bar + 8u * stage, ph ^ 1u) ? 1u : 0u;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) return false;
-            const uint32_t dst_row = x_smem + stage * C::kXBytes + krow * 128u;
-            switch (sh) {
-            case 0: shift_and_store<0, OC>(buf, dst_row, first_chunk, krow); break;
-            case 1: shift_and_store<1, OC>(buf, dst_row, first_chunk, krow); break;
-            case 2: shift_and_store<2, OC>(buf, dst_row, first_chunk, krow); break;
-            case 3: shift_and_store<3, OC>(buf, dst_row, first_chunk, krow); break;
-            case 4: shift_and_store<4, OC>(buf, dst_row, first_chunk, krow); break;
-            case 5: shift_and_store<5, OC>(buf, dst_row, first_chunk, krow); break;
-            case 6: shift_and_store<6, OC>(buf, dst_row, first_chunk, krow); break;
-            case 7: shift_and_store<7, OC>(buf, dst_row, first_chunk, krow); break;
-            default: shift_and_store<8, OC>(buf, dst_row, first_chunk, krow); break;
-            }
-            ptx::fence_proxy_async();          // generic-proxy stores -> visible to the tensor core's async proxy
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(full_bar + 8u * stage);
-            return true;
-        };
-
+        uint32_t g = 0;
         bool ok = true;
-        if (total > 0u) load(0u, bufA, shA);
-        for (uint32_t g = 0; g < total && ok; g += 2u) {
-            if (g + 1u < total) load(g + 1u, bufB, shB);
-            ok = store(g, bufA, shA);
-            if (!ok) break;
-            if (g + 2u < total) load(g + 2u, bufA, shA);
-            if (g + 1u < total) ok = store(g + 1u, bufB, shB);
+        long long al_wait = 0, al_t0 = 0, ph_copy = 0, ph_fence = 0, ph_arrive = 0;
+        // table entries (row | shift << 28) of this warp's run in steps 0..31 of an item, one per lane; the next item's
+        // entries are fetched while the current item is processed
+        auto fetch = [&](uint32_t it, uint32_t ks_base) -> uint32_t {
+            uint32_t mt, ct;
+            decode(blockIdx.x + it * gridDim.x, mt, ct);
+            const uint32_t *rows = a.gather + (uint64_t)(mt / a.mtiles_per_group) * a.boxes_per_group;
+            const uint32_t ks = ks_base + lane;
+            return ks < KS ? __ldg(rows + (ks * kStageK + 16u * sw) / a.box_h) : 0u;
+        };
+        uint32_t tab_next = my_items ? fetch(0u, 0u) : 0u;
+        for (uint32_t it = 0; it < my_items && ok; ++it) {
+            uint32_t mt, ct;
+            decode(blockIdx.x + it * gridDim.x, mt, ct);
+            uint32_t tab = tab_next;
+            if (it + 1u < my_items) tab_next = fetch(it + 1u, 0u);
+            const bool frame_start = ((ct * (uint32_t)N_TILE + sub * (uint32_t)C::kSubCols) % flen) == 0u;   // the 8 columns to the left belong to another frame
+            for (uint32_t ks = 0; ks < KS; ++ks, ++g) {
+                if (ks != 0u && (ks & 31u) == 0u) tab = fetch(it, ks);         // fan-in above 2048: fetched on demand
+                const uint32_t ls = g % SL, lph = (g / SL) & 1u, bs = g % SB, bph = (g / SB) & 1u;
+                const uint32_t sh = __shfl_sync(0xffffffffu, tab, ks & 31u) >> 28;
+                uint32_t okw = 1u;
+                if (trace) al_t0 = clock64();
+                if (lane == 0) okw = (wait(lfull_bar + 8u * ls, lph) && wait(bempty_bar + 8u * bs, bph ^ 1u)) ? 1u : 0u;
+                if (trace) al_wait += clock64() - al_t0;
+                ok = __shfl_sync(0xffffffffu, okw, 0) != 0u;
+                if (!ok) break;
+                if (warp == 6u && lane == 0) stamp_step(g, 2);
+                if (d.debug & 64u) {                 // development switch: barrier protocol only
+                    __syncwarp();
+                    if (lane == 0) { ptx::mbar_arrive(bfull_bar + 8u * bs); ptx::mbar_arrive(lempty_bar + 8u * ls); }
+                    if (warp == 6u && lane == 0) stamp_step(g, 3);
+                    continue;
+                }
+                long long c0 = 0;
+                if (trace) c0 = clock64();
+                uint4 buf[OC + 1];
+                const uint32_t src = raw_smem + ls * C::kRawBytes + sub * C::kSubRawBytes + krow * C::kRawPitch + first_chunk * 16u;
+#pragma unroll
+                for (int i = 0; i <= OC; ++i) buf[i] = lds_v4(src + 16u * (uint32_t)i);
+                if (half == 0u && frame_start) buf[0] = make_uint4(0u, 0u, 0u, 0u);
+                const uint32_t dst_row = x_smem + bs * C::kXBytes + krow * 128u;
+                switch (sh) {
+                case 0: shift_and_store<0, OC>(buf, dst_row, out_chunk0, krow); break;
+                case 1: shift_and_store<1, OC>(buf, dst_row, out_chunk0, krow); break;
+                case 2: shift_and_store<2, OC>(buf, dst_row, out_chunk0, krow); break;
+                case 3: shift_and_store<3, OC>(buf, dst_row, out_chunk0, krow); break;
+                case 4: shift_and_store<4, OC>(buf, dst_row, out_chunk0, krow); break;
+                case 5: shift_and_store<5, OC>(buf, dst_row, out_chunk0, krow); break;
+                case 6: shift_and_store<6, OC>(buf, dst_row, out_chunk0, krow); break;
+                case 7: shift_and_store<7, OC>(buf, dst_row, out_chunk0, krow); break;
+                default: shift_and_store<8, OC>(buf, dst_row, out_chunk0, krow); break;
+                }
+                long long c1 = 0, c2 = 0;
+                if (trace) c1 = clock64();
+                ptx::fence_proxy_async();          // generic-proxy stores -> visible to the tensor core's async proxy
+                if (trace) c2 = clock64();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(bfull_bar + 8u * bs);
+                    ptx::mbar_arrive(lempty_bar + 8u * ls);     // this warp's rows of the window are in registers / stored
+                }
+                if (trace) { const long long c3 = clock64(); ph_copy += c1 - c0; ph_fence += c2 - c1; ph_arrive += c3 - c2; }
+                if (warp == 6u && lane == 0) stamp_step(g, 3);
+            }
         }
         if (!ok && lane == 0) {
             if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PRODUCER);
             *abort_word = 1u;
         }
+        if (trace && warp == 6u && lane == 0) { tr[10] = al_wait; tr[12] = clock64(); tr[4] = ph_copy; tr[5] = ph_fence; tr[6] = ph_arrive; }
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -310,7 +413,7 @@ k44_wave_umma_shift_kernel(const WaveArgs a, const UmmaDesc d) {
 }
 
 template <int N_TILE>
-static cudaError_t launch(const WaveArgs &a, const UmmaDesc &d, int num_sms, cudaStream_t s) {
+static cudaError_t launch(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s) {
     using C = Cfg<N_TILE>;
     static bool attr_done[64] = {};
     int dev = 0;
@@ -324,19 +427,21 @@ static cudaError_t launch(const WaveArgs &a, const UmmaDesc &d, int num_sms, cud
     const uint32_t mtiles = (a.cout + kTileM - 1) / kTileM;
     const uint32_t items = mtiles * (a.num_col_tiles64 / (N_TILE / 64u));
     const uint32_t grid = items < (uint32_t)num_sms ? items : (uint32_t)num_sms;
-    k44_wave_umma_shift_kernel<N_TILE><<<grid, kThreads, C::kSmemBytes, s>>>(a, d);
+    k44_wave_umma_shift_kernel<N_TILE><<<grid, C::kThreads, C::kSmemBytes, s>>>(tmap, a, d);
     return cudaGetLastError();
 }
 
 }  // namespace shiftwave
 
-cudaError_t launch_wave_umma_shift(const WaveArgs &a, const UmmaDesc &d, int num_sms, cudaStream_t s) {
+cudaError_t launch_wave_umma_shift(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s) {
     if (a.gather_mode != GATHER_BOX || a.box_h < 16u || (kStageK % a.box_h) != 0u) return cudaErrorInvalidValue;
     const uint32_t flen = a.frame_len ? a.frame_len : a.pitch;
     if (flen % d.n_tile != 0u || a.num_col_tiles64 % (d.n_tile / 64u) != 0u) return cudaErrorInvalidValue;
+    if ((kStageK / a.box_h) * (d.n_tile > 128u ? d.n_tile / 128u : 1u) > 32u) return cudaErrorInvalidValue;   // one producer lane per box
     switch (d.n_tile) {
-    case 64: return shiftwave::launch<64>(a, d, num_sms, s);
-    case 128: return shiftwave::launch<128>(a, d, num_sms, s);
+    case 64: return shiftwave::launch<64>(a, d, tmap, num_sms, s);
+    case 128: return shiftwave::launch<128>(a, d, tmap, num_sms, s);
+    case 256: return shiftwave::launch<256>(a, d, tmap, num_sms, s);
     default: return cudaErrorInvalidValue;
     }
 }

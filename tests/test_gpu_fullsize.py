@@ -84,7 +84,7 @@ def test_token_shift_plan_full_size_sampled_groups():
     cv2 = canvas.view(-1, pitch)
     for wi in range(c["waves"]):
         info = plan.wave_info(wi)
-        assert info.path == PATH_UMMA and info.n_tile == 128
+        assert info.path == PATH_UMMA and info.n_tile == 256
         starts, shifts = tables[wi]
         wrm = plan.weights_rowmajor(wi)
         row0 = c["input_channels"] + wi * c["cout"]

@@ -321,7 +321,8 @@ def test_token_shift_plan_general_path(group):
     check(plan, run_gpu(plan, x, PATH_FMA, expect_path=PATH_FMA), O.run_plan(plan, x))
 
 
-@pytest.mark.parametrize("n_tile,frames,frame_len,run_len", [(64, 3, 256, 16), (128, 2, 256, 16), (64, 4, 64, 32), (128, 3, 128, 64), (64, 1, 192, 16)])
+@pytest.mark.parametrize("n_tile,frames,frame_len,run_len", [(64, 3, 256, 16), (128, 2, 256, 16), (64, 4, 64, 32), (128, 3, 128, 64), (64, 1, 192, 16),
+                                                             (256, 2, 256, 16), (256, 1, 512, 32)])
 def test_token_shift_runs_on_tensor_cores(n_tile, frames, frame_len, run_len, monkeypatch):
     """Shifted runs (one table entry per run, shift in its top bits) execute on the tensor-core kernel whose aligner
     warps shift the rows on their way into the operand stage; frame starts read zero."""
