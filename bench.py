@@ -414,13 +414,33 @@ def sharded_main(args) -> None:
     stream = torch.cuda.current_stream()
     nw = plan.num_waves
 
-    def step():
+    def eager_step():
+        st = torch.cuda.current_stream()
         for i in range(nw):
-            plan.execute_wave(i, stream)
+            plan.execute_wave(i, st)
             y_off, total, blk = waves[i]
             if world > 1 and blk != total:
                 out = canvas[y_off: y_off + total]
                 dist.all_gather_into_tensor(out, out[rank * blk: (rank + 1) * blk])
+
+    # One CUDA graph per step: at one GPU the library's own graph (grouped launches of independent waves); with
+    # sharding the wave launches and the NCCL all-gathers between them are captured together.
+    mode = os.environ.get("K44B_SHARD_GRAPH", "1")
+    graph = None
+    if mode == "1" and world > 1:
+        eager_step()                      # NCCL communicator set-up and lazy initialisation happen outside the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            eager_step()
+
+    def step():
+        if graph is not None:
+            graph.replay()
+        elif world == 1 and mode == "1":
+            plan.execute_graph(stream)
+        else:
+            eager_step()
 
     warmup = max(3, args.warmup)
     sampler = ClockSampler(local_rank); sampler.start()
@@ -456,6 +476,7 @@ def sharded_main(args) -> None:
                 "config": {"workload": "Llama-3-8B shaped wave chain, 90 % of 32-row input clusters removed per 128-neuron group, dense lm_head, "
                                        "batch 256; rows of every wave split over the ranks, per-wave in-place NCCL all-gather",
                            "layers": cfg["layers"], "waves_per_step": nw, "kept_params": kept_params, "lm_head_sharded": lm_sharded,
+                           "launch": "one CUDA graph per step" if mode == "1" else "one launch per wave",
                            "allgather_bytes_received_per_rank_per_step": gather_bytes},
                 "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9, "peak": peak,
                              "peak_kind": f"of {kind}", "unit": "GB/s", "frac": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9 / peak, "traffic": None},

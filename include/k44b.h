@@ -90,6 +90,20 @@ int k44b_status(void *plan, uint32_t *status);
 int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, int out_elems, float *out_gpu_ms);
 /* Development aid: 16 SM-clock timestamps recorded by CTA 0 of the last tcgen05 wave kernel when the
  * library runs with K44B_DEBUG_MODE=16 (all zero otherwise). */
+/* ---- neuron sharding over the GPUs of one box (no counterpart in the reference, which is single-GPU) ----
+ * Every rank holds a plan with its rows of every wave and a full-size canvas. After k44b_plan_set_peers_* the wave
+ * kernels store each output row into the rank's own canvas and into the peers' canvases (peer-mapped memory over
+ * NVLink), and a launch starts reading only when every peer has finished the launches before it (one 32-bit word per
+ * peer, bounded wait: status bit 5 on expiry). All ranks must issue the same sequence of launches. Supported for waves
+ * that run on the tensor-core kernels; plans with FMA-path or token-shifted waves are rejected. world <= 8.
+ *   ipc_handles:    64-byte CUDA IPC handles of this plan's canvas and sync block, to be sent to the other processes
+ *   set_peers_ipc:  `world` handles each (indexed by rank; the own entries are ignored), opened with peer access
+ *   set_peers_raw:  the same with device pointers that are already valid on this GPU (same process)            */
+int k44b_plan_ipc_handles(void *plan, void *canvas_handle64, void *sync_handle64);
+int k44b_plan_set_peers_ipc(void *plan, int rank, int world, const void *canvas_handles, const void *sync_handles);
+int k44b_plan_set_peers_raw(void *plan, int rank, int world, void *const *canvas_ptrs, void *const *sync_ptrs);
+void *k44b_plan_sync_ptr(void *plan);
+
 int k44b_debug_trace(void *plan, long long *out16);
 /* the first `count` (<= 500) 64-bit words of the development trace area */
 int k44b_debug_trace_words(void *plan, long long *out, int count);

@@ -82,6 +82,10 @@ PROTOTYPES = {
     "k44b_infer_f32": (c_int, [c_void_p, _f32p, c_int, _f32p, c_int, _f32p]),
     "k44b_debug_trace": (c_int, [c_void_p, POINTER(ctypes.c_longlong)]),
     "k44b_debug_trace_words": (c_int, [c_void_p, POINTER(ctypes.c_longlong), c_int]),
+    "k44b_plan_ipc_handles": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "k44b_plan_set_peers_ipc": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "k44b_plan_set_peers_raw": (c_int, [c_void_p, c_int, c_int, POINTER(c_void_p), POINTER(c_void_p)]),
+    "k44b_plan_sync_ptr": (c_void_p, [c_void_p]),
     "k44b_launch_count": (c_uint64, [c_void_p]),
     "k44b_wave_weights_rowmajor": (c_int, [c_void_p, c_int, c_void_p]),
     "k44b_wave_forward_static": (c_int, [c_void_p, c_uint64, c_uint32, c_void_p, c_void_p, c_uint32, c_void_p, c_uint32, c_uint32, c_uint32,

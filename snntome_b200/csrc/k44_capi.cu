@@ -359,6 +359,28 @@ int k44b_debug_trace(void *plan, long long *out16) {
     return P(plan)->exec.read_trace(out16, 16) ? 0 : set_error(P(plan)->exec.err);
 }
 
+int k44b_plan_ipc_handles(void *plan, void *canvas_handle64, void *sync_handle64) {
+    if (!plan || !canvas_handle64 || !sync_handle64) return set_error("plan_ipc_handles: bad arguments");
+    return P(plan)->exec.ipc_handles(canvas_handle64, sync_handle64) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_plan_set_peers_ipc(void *plan, int rank, int world, const void *canvas_handles, const void *sync_handles) {
+    if (!plan || !canvas_handles || !sync_handles) return set_error("plan_set_peers_ipc: bad arguments");
+    return P(plan)->exec.set_peers_ipc(rank, world, canvas_handles, sync_handles) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_plan_set_peers_raw(void *plan, int rank, int world, void *const *canvas_ptrs, void *const *sync_ptrs) {
+    if (!plan || !canvas_ptrs || !sync_ptrs) return set_error("plan_set_peers_raw: bad arguments");
+    return P(plan)->exec.set_peers_raw(rank, world, canvas_ptrs, sync_ptrs) ? 0 : set_error(P(plan)->exec.err);
+}
+
+void *k44b_plan_sync_ptr(void *plan) {
+    if (!plan) { set_error("plan_sync_ptr: bad arguments"); return nullptr; }
+    void *p = P(plan)->exec.sync_ptr();
+    if (!p) set_error(P(plan)->exec.err);
+    return p;
+}
+
 int k44b_debug_trace_words(void *plan, long long *out, int count) {
     if (!plan || !out) return set_error("debug_trace_words: bad arguments");
     return P(plan)->exec.read_trace(out, count) ? 0 : set_error(P(plan)->exec.err);

@@ -30,29 +30,42 @@ __device__ __forceinline__ float finish_value(float acc, float bias, float res, 
 
 __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// Shared by the direct and the split-K epilogue: 32 accumulator values of one neuron -> FP16 row segment.
-__device__ __forceinline__ void store_row_segment(const WaveArgs &a, const float (&v)[32], float bias, bool has_map, uint64_t elem_off) {
-    uint4 *dst = reinterpret_cast<uint4 *>(a.canvas + a.y_off + elem_off);
-    const uint4 *rsrc = reinterpret_cast<const uint4 *>(a.canvas + a.res_off + elem_off);
-#pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) {
-        float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (a.has_residual) {
-            const uint4 rv = rsrc[q4];
-            const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(rh[e]); r[2 * e] = f.x; r[2 * e + 1] = f.y; }
-        }
-        uint32_t pk[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float lo = finish_value(v[q4 * 8 + 2 * e], bias, r[2 * e], a.act, a.has_residual != 0, has_map);
-            const float hi = finish_value(v[q4 * 8 + 2 * e + 1], bias, r[2 * e + 1], a.act, a.has_residual != 0, has_map);
-            const __half2 h2 = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
-            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
-        }
-        dst[q4] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+// ---- peer exchange of neuron-sharded plans (see PeerArgs) ------------------------------------------------------
+// 16-byte piece of an output row -> the same element offset of every peer canvas
+__device__ __forceinline__ void store_to_peers(const PeerArgs *p, uint64_t elem_off, const uint4 &val) {
+    const uint32_t n = p->n_peers;
+    for (uint32_t q = 0; q < n; ++q) *reinterpret_cast<uint4 *>(p->canvas[q] + elem_off) = val;
+}
+// One thread per CTA, after the CTA's last store (its storing threads executed __threadfence_system() and met at a
+// barrier): the CTA that arrives last closes the launch and publishes the new launch count to every peer.
+__device__ __forceinline__ void peer_signal_done(const PeerArgs *p, uint32_t ctas_in_launch) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(p->sync + kSyncDone, 1u);
+    if (prev + 1u == ctas_in_launch) {
+        __threadfence();
+        p->sync[kSyncDone] = 0u;
+        const uint32_t epoch = p->sync[kSyncEpoch] + 1u;
+        p->sync[kSyncEpoch] = epoch;
+        __threadfence_system();
+        const uint32_t n = p->n_peers;
+        for (uint32_t q = 0; q < n; ++q) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p->arrive[q]), "r"(epoch) : "memory");
     }
+}
+// One thread, before the launch reads the canvas: every peer must have finished as many launches as this rank has.
+// Bounded: returns false when a peer does not show up within `limit` cycles.
+__device__ __forceinline__ bool peer_wait_ready(const PeerArgs *p, unsigned long long limit) {
+    const uint32_t need = *reinterpret_cast<volatile uint32_t *>(p->sync + kSyncEpoch);
+    const uint32_t n = p->n_peers;
+    const long long t0 = clock64();
+    for (uint32_t q = 0; q < n; ++q) {
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p->sync + q) : "memory");
+            if ((int32_t)(v - need) >= 0) break;
+            if ((unsigned long long)(clock64() - t0) > limit) return false;
+        }
+    }
+    return true;
 }
 
 // Branch-free activation for the tensor-core epilogue: the activation kind is a template parameter so that the
@@ -124,7 +137,11 @@ __device__ __forceinline__ void stage_and_store_t(const WaveArgs &a, const float
         const uint32_t oj_r = __shfl_sync(0xffffffffu, oj, r);
         const int live_r = __shfl_sync(0xffffffffu, live ? 1 : 0, r);
         const uint4 val = *reinterpret_cast<const uint4 *>(wstage + r * 80u + piece * 16u);
-        if (live_r) *reinterpret_cast<uint4 *>(a.canvas + a.y_off + (uint64_t)oj_r * a.pitch + col0 + piece * 8u) = val;
+        if (live_r) {
+            const uint64_t off = a.y_off + (uint64_t)oj_r * a.pitch + col0 + piece * 8u;
+            *reinterpret_cast<uint4 *>(a.canvas + off) = val;
+            if (a.peers) store_to_peers(a.peers, off, val);
+        }
     }
     __syncwarp();
 }

@@ -178,6 +178,10 @@ void Executor::release() {
     cudaFree(d_scratch_); d_scratch_ = nullptr;
     cudaFree(d_counters_); d_counters_ = nullptr;
     scratch_tiles_ = 0;
+    for (void *p : ipc_opened_) cudaIpcCloseMemHandle(p);
+    ipc_opened_.clear();
+    cudaFree(d_sync_); d_sync_ = nullptr;
+    cudaFree(d_peers_); d_peers_ = nullptr;
     cudaFree(canvas_); canvas_ = nullptr;
     cudaFree(d_status_); d_status_ = nullptr;
     cudaFree(d_in_f32_); d_in_f32_ = nullptr;
@@ -258,6 +262,7 @@ bool Executor::add_wave(const HostWave &w) {
     dw.synapses = (uint64_t)w.logical_cout * w.fan_in_raw;
     WaveArgs &a = dw.args;
     a.canvas = canvas_; a.canvas_elems = canvas_elems_; a.status = d_status_;
+    if (d_peers_) return fail("waves cannot be added after the peers were set");
     a.y_off = w.y_off; a.res_off = w.res_off; a.x_base_off = w.x_base_off;
     a.cout = w.cout; a.group = w.group; a.fan_in = w.fan_in;
     a.num_kstages = (w.fan_in + kStageK - 1) / kStageK;
@@ -609,6 +614,69 @@ bool Executor::read_status(uint32_t *status) {
         return false;
     if (status) *status = st;
     if (st) { cudaMemset(d_status_, 0, 4); err = std::string("kernel status: ") + status_string(st); }
+    return true;
+}
+
+// ---- neuron sharding over several GPUs ---------------------------------------------------------------------
+void *Executor::sync_ptr() {
+    if (!ready()) { fail("executor not initialised"); return nullptr; }
+    if (!d_sync_) {
+        if (!check(cudaSetDevice(device_), "cudaSetDevice") || !check(cudaMalloc(&d_sync_, kSyncWords * sizeof(uint32_t)), "sync block allocation") ||
+            !check(cudaMemset(d_sync_, 0, kSyncWords * sizeof(uint32_t)), "sync block clear") || !check(cudaDeviceSynchronize(), "sync block clear"))
+            return nullptr;
+    }
+    return d_sync_;
+}
+
+bool Executor::ipc_handles(void *canvas_handle64, void *sync_handle64) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (!sync_ptr()) return false;
+    cudaIpcMemHandle_t hc, hs;
+    if (!check(cudaIpcGetMemHandle(&hc, canvas_), "canvas IPC handle") || !check(cudaIpcGetMemHandle(&hs, d_sync_), "sync IPC handle")) return false;
+    std::memcpy(canvas_handle64, &hc, 64);
+    std::memcpy(sync_handle64, &hs, 64);
+    return true;
+}
+
+bool Executor::set_peers_ipc(int rank, int world, const void *canvas_handles, const void *sync_handles) {
+    if (world < 2 || world > kMaxPeers + 1 || rank < 0 || rank >= world) return fail("set_peers: bad rank / world size");
+    if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
+    std::vector<void *> cp((size_t)world, nullptr), sp((size_t)world, nullptr);
+    for (int r = 0; r < world; ++r) {
+        if (r == rank) continue;
+        cudaIpcMemHandle_t hc, hs;
+        std::memcpy(&hc, (const char *)canvas_handles + 64 * (size_t)r, 64);
+        std::memcpy(&hs, (const char *)sync_handles + 64 * (size_t)r, 64);
+        if (!check(cudaIpcOpenMemHandle(&cp[r], hc, cudaIpcMemLazyEnablePeerAccess), "open peer canvas")) return false;
+        ipc_opened_.push_back(cp[r]);
+        if (!check(cudaIpcOpenMemHandle(&sp[r], hs, cudaIpcMemLazyEnablePeerAccess), "open peer sync block")) return false;
+        ipc_opened_.push_back(sp[r]);
+    }
+    return set_peers_raw(rank, world, cp.data(), sp.data());
+}
+
+bool Executor::set_peers_raw(int rank, int world, void *const *canvas_ptrs, void *const *sync_ptrs) {
+    if (!ready()) return fail("executor not initialised");
+    if (world < 2 || world > kMaxPeers + 1 || rank < 0 || rank >= world) return fail("set_peers: bad rank / world size");
+    for (const auto &w : waves_)
+        if (w.path != PATH_UMMA || w.use_shift)
+            return fail("set_peers: wave '" + w.name + "' does not run on a tensor-core kernel that stores to peers (" + (w.use_shift ? std::string("token-shifted runs") : w.fma_reason) + ")");
+    if (!sync_ptr()) return false;
+    PeerArgs pa;
+    pa.sync = d_sync_;
+    for (int r = 0; r < world; ++r) {
+        if (r == rank) continue;
+        if (!canvas_ptrs[r] || !sync_ptrs[r]) return fail("set_peers: missing pointer for rank " + std::to_string(r));
+        const uint32_t q = pa.n_peers++;
+        pa.canvas[q] = (__half *)canvas_ptrs[r];
+        // the word of rank `rank` in rank r's block: its position in r's peer list
+        pa.arrive[q] = (uint32_t *)sync_ptrs[r] + (rank < r ? rank : rank - 1);
+    }
+    if (!d_peers_ && !check(cudaMalloc(&d_peers_, sizeof(PeerArgs)), "peer table allocation")) return false;
+    if (!check(cudaMemcpy(d_peers_, &pa, sizeof(PeerArgs), cudaMemcpyHostToDevice), "peer table upload")) return false;
+    for (auto &w : waves_) w.args.peers = d_peers_;
+    groups_valid_ = false;
+    drop_graph();
     return true;
 }
 

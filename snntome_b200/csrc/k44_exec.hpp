@@ -68,6 +68,11 @@ class Executor {
     bool execute_timed(float *ms);                                 // default stream, event-timed, synchronous
     bool infer_f32(const float *h_in, int in_elems, float *h_out, int out_elems, float *gpu_ms);
     bool read_status(uint32_t *status);                            // synchronises the device
+    // Neuron sharding: exchange of wave rows by direct stores into the peers' canvases.
+    bool ipc_handles(void *canvas_handle64, void *sync_handle64);    // handles of this plan's canvas and sync block for the other processes
+    bool set_peers_ipc(int rank, int world, const void *canvas_handles, const void *sync_handles);   // world x 64 bytes each, indexed by rank
+    bool set_peers_raw(int rank, int world, void *const *canvas_ptrs, void *const *sync_ptrs);       // device pointers valid on this GPU, indexed by rank
+    void *sync_ptr();
     bool read_trace(long long *out, int count);                             // development aid: kernel milestone clocks
     bool weights_to_rowmajor(size_t wave, void *d_dst);            // unpack check: tiled -> [cout][fan_in]
 
@@ -106,6 +111,10 @@ class Executor {
     uint64_t launches_ = 0;
     float *d_scratch_ = nullptr;
     uint32_t *d_counters_ = nullptr;
+    // neuron sharding over several GPUs (see PeerArgs)
+    uint32_t *d_sync_ = nullptr;          // kSyncWords words, allocated on first use
+    PeerArgs *d_peers_ = nullptr;
+    std::vector<void *> ipc_opened_;      // peer mappings to close on release
     size_t scratch_tiles_ = 0;
     cudaGraphExec_t graph_exec_ = nullptr;
     bool pdl_ = true;                    // programmatic dependent launch between consecutive small waves

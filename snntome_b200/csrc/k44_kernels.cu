@@ -217,6 +217,15 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         const uint64_t pol_x = ptx::policy_evict_last();    // substrate rows are shared between groups
         uint32_t issued = 0;
         bool ok = true;
+        if (a.peers) {                       // neuron-sharded plan: the peers' rows of the previous launches must have arrived
+            uint32_t okp = 1u;
+            if (lane == 0) {
+                okp = peer_wait_ready(a.peers, d.wait_cycles) ? 1u : 0u;
+                asm volatile("fence.proxy.async.global;" ::: "memory");   // rows written by peers' plain stores -> this thread's tensor copies
+                if (!okp) { atomicOr(a.status, (uint32_t)ST_TIMEOUT_PEER); *abort_word = 1u; }
+            }
+            ok = __shfl_sync(0xffffffffu, okp, 0) != 0u;
+        }
         for (uint32_t item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
             uint32_t tile, ks0, ks1;
             decode(item, tile, ks0, ks1);
@@ -339,8 +348,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                     float f[32];
 #pragma unroll
                     for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
-                    if (d.debug & 32u) { if (live) store_row_segment(a, f, bias, has_map, o + c0); }
-                    else if (!(d.debug & 8u)) stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
+                    if (!(d.debug & 8u)) stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
                 }
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(tempty_bar + 8u * acc);
@@ -380,8 +388,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                             f[e] = __ldcg(p);
                             __stcg(p, 0.0f);
                         }
-                        if (d.debug & 32u) { if (live) store_row_segment(a, f, bias, has_map, o + c0); }
-                        else stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
+                        stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
                     }
                     if (threadIdx.x == 64u) a.counters[tile] = 0u;
                 }
@@ -392,6 +399,11 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         if (!ok && lane == 0) {
             if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_EPILOGUE);
             *abort_word = 1u;
+        }
+        if (a.peers) {                       // this CTA's rows are stored here and on every peer: count it as done
+            __threadfence_system();
+            epilogue_bar_sync();
+            if (threadIdx.x == 64u) peer_signal_done(a.peers, gridDim.x);
         }
     }
     ptx::tc_fence_before();
@@ -510,6 +522,10 @@ __device__ __forceinline__ void finish_owned_t(const WaveArgs &a, const float *r
             pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
         }
         *reinterpret_cast<uint2 *>(dst) = make_uint2(pk[0], pk[1]);
+        if (a.peers) {
+            const uint32_t n = a.peers->n_peers;
+            for (uint32_t q = 0; q < n; ++q) *reinterpret_cast<uint2 *>(a.peers->canvas[q] + a.y_off + o) = make_uint2(pk[0], pk[1]);
+        }
     } else {
 #pragma unroll
     for (uint32_t c = 0; c + 8u <= ncol; c += 8) {
@@ -530,7 +546,9 @@ __device__ __forceinline__ void finish_owned_t(const WaveArgs &a, const float *r
             const __half2 h2 = __floats2half2_rn(lo, hi);
             pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
         }
-        *reinterpret_cast<uint4 *>(dst + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        const uint4 val = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4 *>(dst + c) = val;
+        if (a.peers) store_to_peers(a.peers, a.y_off + o + c, val);
     }
     }
 }
@@ -642,9 +660,17 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         uint32_t cached = (cached_base + lane < a.boxes_per_group) ? __ldg(rows + cached_base + lane) : 0u;
         if (lane == 0) stamp(2);
         grid_dependency_wait();             // everything below reads rows the previous wave wrote
+        bool ok = true;
+        if (a.peers) {                       // ... and, in a neuron-sharded plan, rows the peers stored into this canvas
+            uint32_t okp = 1u;
+            if (lane == 0) {
+                okp = peer_wait_ready(a.peers, d.wait_cycles) ? 1u : 0u;
+                if (!okp) { atomicOr(a.status, (uint32_t)ST_TIMEOUT_PEER); *abort_word = 1u; }
+            }
+            ok = __shfl_sync(0xffffffffu, okp, 0) != 0u;
+        }
         fence_proxy_async_global();
         if (lane == 0) stamp(3);
-        bool ok = true;
         uint32_t issued = 0;
         for (uint32_t ks = ks0; ks < ks1 && ok; ++ks, ++issued) {
             const uint32_t stage = issued % kStages, ph = (issued / kStages) & 1u;
@@ -773,7 +799,9 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         }
     }
     if (threadIdx.x == 64u) stamp(12);
+    if (a.peers && warp >= 2) __threadfence_system();
     __syncthreads();
+    if (a.peers && threadIdx.x == 0) peer_signal_done(a.peers, gridDim.x);
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemCols);

@@ -38,7 +38,23 @@ enum KernelStatus : uint32_t {
     ST_TIMEOUT_EPILOGUE = 1u << 2,
     ST_TIMEOUT_DRAIN = 1u << 3,
     ST_BAD_INDEX = 1u << 4,
+    ST_TIMEOUT_PEER = 1u << 5,
 };
+
+// Neuron sharding over several GPUs: every rank stores the rows it computes into its own canvas and, at the same
+// element offset, into the canvases of its peers (peer-mapped pointers over NVLink), so that each GPU's next wave
+// gathers from a complete canvas in its own HBM. Launch n of a rank may start once every peer has finished its
+// launches 0..n-1: the CTA that finishes a launch last publishes the rank's launch count into one word per peer
+// (`arrive`), and the first thing a launch does with the canvas is a bounded wait for those words.
+constexpr int kMaxPeers = 7;
+struct PeerArgs {
+    __half *canvas[kMaxPeers] = {};       // the peers' canvases
+    uint32_t *arrive[kMaxPeers] = {};     // this rank's word in each peer's sync block
+    uint32_t *sync = nullptr;             // own sync block: [0..6] the peers' launch counts, [8] CTAs done in the running launch, [9] launches completed
+    uint32_t n_peers = 0;
+    uint32_t pad_ = 0;
+};
+constexpr uint32_t kSyncWords = 16, kSyncDone = 8, kSyncEpoch = 9;
 
 struct WaveArgs {
     // tensors
@@ -68,6 +84,7 @@ struct WaveArgs {
     uint32_t k_splits = 1, kstages_per_split = 0;
     float *scratch = nullptr;             // [tiles][N_TILE][128] FP32, all zero between launches
     uint32_t *counters = nullptr;         // [tiles], all zero between launches
+    const PeerArgs *peers = nullptr;      // device memory; null unless the plan is neuron-sharded over several GPUs
 };
 
 // Up to four mutually independent small waves launched as one grid (their clusters are numbered consecutively).

@@ -183,6 +183,39 @@ class NativePlan:
             raise NativeError(f"infer_f16: {last_error()}")
         return float(ms.value)
 
+    # -- neuron sharding over several GPUs: rows go straight into the peers' canvases ------------------------------
+    def ipc_handles(self):
+        """(canvas handle, sync-block handle): two 64-byte CUDA IPC handles for the other ranks' processes."""
+        hc, hs = ctypes.create_string_buffer(64), ctypes.create_string_buffer(64)
+        if self._lib.k44b_plan_ipc_handles(self._ptr, hc, hs) != 0:
+            raise NativeError(f"ipc_handles: {last_error()}")
+        return hc.raw, hs.raw
+
+    def set_peers_ipc(self, rank: int, world: int, canvas_handles, sync_handles) -> None:
+        """`canvas_handles` / `sync_handles`: one 64-byte handle per rank, indexed by rank (own entries ignored)."""
+        hc, hs = b"".join(canvas_handles), b"".join(sync_handles)
+        if len(hc) != 64 * world or len(hs) != 64 * world:
+            raise NativeError("set_peers_ipc: one 64-byte handle per rank is required")
+        if self._lib.k44b_plan_set_peers_ipc(self._ptr, int(rank), int(world), hc, hs) != 0:
+            raise NativeError(f"set_peers_ipc: {last_error()}")
+
+    def set_peers_raw(self, rank: int, world: int, canvas_ptrs, sync_ptrs) -> None:
+        """Device pointers that are already valid on this GPU (plans of the same process), indexed by rank."""
+        arr = ctypes.c_void_p * world
+        if self._lib.k44b_plan_set_peers_raw(self._ptr, int(rank), int(world), arr(*canvas_ptrs), arr(*sync_ptrs)) != 0:
+            raise NativeError(f"set_peers_raw: {last_error()}")
+
+    @property
+    def canvas_ptr(self) -> int:
+        return int(self._lib.k44b_canvas_ptr(self._ptr))
+
+    @property
+    def sync_ptr(self) -> int:
+        p = self._lib.k44b_plan_sync_ptr(self._ptr)
+        if not p:
+            raise NativeError(f"sync_ptr: {last_error()}")
+        return int(p)
+
     def status(self) -> int:
         st = ctypes.c_uint32(0)
         rc = self._lib.k44b_status(self._ptr, ctypes.byref(st))

@@ -103,3 +103,15 @@ class NeuronShardedRunner:
         for i in range(len(self.plan.waves)):
             self.compute(i)
             self.exchange(i)
+
+
+def connect_peers(native_plan, rank: int, world: int) -> None:
+    """Exchange the CUDA IPC handles of every rank's canvas and sync block over the default process group and hand
+    them to the library: from then on the wave kernels store their rows into all canvases and order their launches
+    against the peers' themselves, so a step needs no collective call (and can be one CUDA graph)."""
+    import torch.distributed as dist
+    mine = native_plan.ipc_handles()
+    everyone = [None] * world
+    dist.all_gather_object(everyone, mine)
+    native_plan.set_peers_ipc(rank, world, [h[0] for h in everyone], [h[1] for h in everyone])
+    dist.barrier()          # every rank has its mappings before anybody launches

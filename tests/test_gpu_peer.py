@@ -1,0 +1,76 @@
+"""Neuron sharding with direct stores into the peers' canvases, checked on one GPU: the ranks' plans live on the same
+device, point at each other's canvas and sync block, and their launches are queued strictly in the order
+wave 0 of every rank, wave 1 of every rank, ... on one stream. In that order every launch finds the launch counts it
+waits for already published (nothing ever waits for a launch that is queued behind it), so the addressing, the
+last-CTA election and the counting are exercised without two kernels having to run at the same time."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from snntome_b200 import shard, synth
+from snntome_b200.native import NativeError, NativePlan, PATH_FMA
+from snntome_b200.plan import ACT_RELU, ACT_SILU
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 2e-3, 1e-3
+
+
+def run_sharded_on_one_gpu(plan, x, world, reps=2):
+    import torch
+    plans = [NativePlan.from_plan(shard.shard_plan(plan, r, world), device=0) for r in range(world)]
+    canvases = [p.canvas_tensor() for p in plans]
+    xt = torch.from_numpy(np.ascontiguousarray(x).view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    for c in canvases:
+        c[plan.input_off: plan.input_off + xt.numel()] = xt
+    cps, sps = [p.canvas_ptr for p in plans], [p.sync_ptr for p in plans]
+    for r, p in enumerate(plans):
+        p.set_peers_raw(r, world, cps, sps)
+    for _ in range(reps):
+        for i in range(len(plan.waves)):
+            for p in plans:
+                p.execute_wave(i)
+    out = []
+    for p, c in zip(plans, canvases):
+        assert p.status() == 0
+        out.append(c.cpu().numpy().view(np.uint16))
+    for p in plans:
+        p.close()
+    return out
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_streaming_waves_store_to_every_canvas(world):
+    plan = synth.sparse_plan(seed=91, input_rows=2048, waves=3, cout=1024 * world // 2, runs=8, run_len=32, columns=128, group=128, act=ACT_RELU)
+    x = synth.random_input(plan, 92)
+    want = O.run_plan(plan, x)
+    got = run_sharded_on_one_gpu(plan, x, world)
+    for r in range(world):
+        for w in plan.waves:
+            a, b = w.y_off, w.y_off + w.cout * plan.pitch
+            ok, err, k = O.compare(got[r][a:b], want[a:b], RTOL, ATOL)
+            assert ok, (r, w.name, err, k)
+        assert np.array_equal(got[r], got[0])
+
+
+def test_small_waves_with_residual_store_to_every_canvas():
+    """Dense chain at decode size: every wave runs on the cluster kernel (K splits reduced through distributed shared
+    memory); the second wave adds a residual that a peer produced."""
+    plan = synth.dense_chain(seed=93, dims=[512, 512, 512, 256], columns=64, act=ACT_SILU, weight_std=0.05, residual_from={2: 1})
+    x = synth.random_input(plan, 94, dist="normal")
+    want = O.run_plan(plan, x)
+    got = run_sharded_on_one_gpu(plan, x, 2)
+    for r in range(2):
+        for w in plan.waves:
+            a, b = w.y_off, w.y_off + w.cout * plan.pitch
+            ok, err, k = O.compare(got[r][a:b], want[a:b], RTOL, ATOL)
+            assert ok, (r, w.name, err, k)
+    assert np.array_equal(got[0], got[1])
+
+
+def test_plans_with_general_path_waves_are_rejected():
+    plan = synth.sparse_plan(seed=95, input_rows=512, waves=1, cout=256, runs=8, run_len=32, columns=64, group=128, act=ACT_RELU)
+    p0 = NativePlan.from_plan(shard.shard_plan(plan, 0, 2), device=0, force_path=PATH_FMA)
+    p1 = NativePlan.from_plan(shard.shard_plan(plan, 1, 2), device=0)
+    with pytest.raises(NativeError, match="tensor-core"):
+        p0.set_peers_raw(0, 2, [p0.canvas_ptr, p1.canvas_ptr], [p0.sync_ptr, p1.sync_ptr])
+    p0.close(); p1.close()
