@@ -346,6 +346,7 @@ def sharded_main(args) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     cfg = dict(PRUNED, layers=args.layers if args.layers != 16 else PRUNED["layers"])
     H, F, V, KV, C = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["kv"], cfg["columns"]
+    V = -(-V // (world * 128)) * world * 128      # vocabulary rows padded to whole 128-neuron groups per rank (128256 -> 128512 at 4 and 8 ranks)
     pitch = C
     rows, cur = {}, 0
     for name, n in [("x0", H), ("x1", H), ("q", H), ("k", KV), ("v", KV), ("h", H), ("g", F), ("u", F), ("logits", V)]:
@@ -394,18 +395,8 @@ def sharded_main(args) -> None:
                                                     ("down", "g", x_out, F, H, 0, "h")]:
             add(f"L{layer}.{name}", wi, src, dst, cin, cout, act, res); wi += 1
         x_in, x_out = x_out, x_in
-    # vocab 128256 = 1002 groups of 128: pad the sharded lm_head to a multiple of world*128 rows would change the shape,
-    # so it is split only when it divides evenly; otherwise every rank computes the whole (replicated) lm_head.
-    lm_sharded = (V % (world * 128) == 0)
-    if lm_sharded:
-        add("lm_head", wi, x_in, "logits", H, V, dense=True)
-    else:
-        w_save, r_save = world, rank
-        world_, rank_ = world, rank
-        world, rank = 1, 0
-        scratch = torch.empty(V * H, dtype=torch.float16, device="cuda") if scratch.numel() < V * H else scratch
-        add("lm_head", wi, x_in, "logits", H, V, dense=True)
-        world, rank = world_, rank_
+    add("lm_head", wi, x_in, "logits", H, V, dense=True)
+    lm_sharded = True
     del scratch
     torch.cuda.empty_cache()
     canvas = plan.canvas_tensor()
@@ -423,11 +414,15 @@ def sharded_main(args) -> None:
                 out = canvas[y_off: y_off + total]
                 dist.all_gather_into_tensor(out, out[rank * blk: (rank + 1) * blk])
 
-    # One CUDA graph per step: at one GPU the library's own graph (grouped launches of independent waves); with
-    # sharding the wave launches and the NCCL all-gathers between them are captured together.
-    mode = os.environ.get("K44B_SHARD_GRAPH", "1")
+    # How the ranks exchange rows (K44B_SHARD_MODE):
+    #   peer  (default) the wave kernels store their rows into every canvas themselves (peer-mapped memory) and order
+    #         their launches against the peers' through counter words; a step is one CUDA graph, no collective call;
+    #   nccl  one in-place all-gather per wave after its launch (the plain baseline); nccl-graph: the same, captured.
+    mode = os.environ.get("K44B_SHARD_MODE", "peer")
     graph = None
-    if mode == "1" and world > 1:
+    if world > 1 and mode == "peer":
+        shard.connect_peers(plan, rank, world)
+    elif world > 1 and mode == "nccl-graph":
         eager_step()                      # NCCL communicator set-up and lazy initialisation happen outside the capture
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
@@ -437,7 +432,7 @@ def sharded_main(args) -> None:
     def step():
         if graph is not None:
             graph.replay()
-        elif world == 1 and mode == "1":
+        elif world == 1 or mode == "peer":
             plan.execute_graph(stream)
         else:
             eager_step()
@@ -460,29 +455,50 @@ def sharded_main(args) -> None:
         dist.barrier()
     torch.cuda.synchronize()
     assert plan.status() == 0
+    launches = plan.launch_count - l0
     ms = t0.elapsed_time(t1)
     if world > 1:
         t = torch.tensor([ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
     ms_step = ms / args.steps
     clocks = sampler.stop()
     checksum = float(canvas[rows["logits"] * pitch: rows["logits"] * pitch + 4096].float().abs().sum().item())
+    # per-wave breakdown with one launch per wave (outside the timed region; with peers it includes waiting for them)
+    wave_us = None
+    if world == 1 or mode == "peer":
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(nw + 1)]
+        for _ in range(2):
+            if world > 1:
+                dist.barrier()
+            ev[0].record(stream)
+            for i in range(nw):
+                plan.execute_wave(i, stream)
+                ev[i + 1].record(stream)
+            torch.cuda.synchronize()
+        us = [ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(nw)]
+        wave_us = {"layer0": [round(v, 1) for v in us[:7]], "lm_head": round(us[-1], 1), "sum": round(sum(us), 1)}
     gather_bytes = sum(total * 2 * (world - 1) // world for (_, total, blk) in waves if blk != total)
     if rank == 0:
         peak, kind = measured_peaks()
-        bytes_rank = kept_params * 2.0 / (world if lm_sharded else 1)
+        bytes_rank = kept_params * 2.0 / world
         line = {"metric": "decode tok/s (cluster-pruned 8B wave chain, neuron-sharded, batch 256)", "value": C / (ms_step * 1e-3), "unit": "tok/s",
                 "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
                 "config": {"workload": "Llama-3-8B shaped wave chain, 90 % of 32-row input clusters removed per 128-neuron group, dense lm_head, "
-                                       "batch 256; rows of every wave split over the ranks, per-wave in-place NCCL all-gather",
-                           "layers": cfg["layers"], "waves_per_step": nw, "kept_params": kept_params, "lm_head_sharded": lm_sharded,
-                           "launch": "one CUDA graph per step" if mode == "1" else "one launch per wave",
+                                       "batch 256; rows of every wave split over the ranks, canvas replicated",
+                           "layers": cfg["layers"], "waves_per_step": nw, "kept_params": kept_params, "lm_head_rows": V,
+                           "exchange": ("none (one GPU)" if world == 1 else {"peer": "direct stores into the peers' canvases from the wave kernels, counter-word launch ordering, one CUDA graph per step",
+                                                                        "nccl": "in-place NCCL all-gather after every wave", "nccl-graph": "in-place NCCL all-gather after every wave, captured in one CUDA graph"}[mode]),
                            "allgather_bytes_received_per_rank_per_step": gather_bytes},
                 "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9, "peak": peak,
                              "peak_kind": f"of {kind}", "unit": "GB/s", "frac": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9 / peak, "traffic": None},
-                "cpu_baseline": None, "e2e": None, "gpu_launches": int(plan.launch_count - l0), "checksum": checksum, "clocks": clocks}
-        print(json.dumps(line))
+                "per_wave_us_direct_launch": wave_us,
+                "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "checksum": checksum, "clocks": clocks}
+        print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()                  # no rank frees its canvas while a peer may still store into it
+        graph = None
+        torch.cuda.synchronize()
+        plan.close()
         dist.destroy_process_group()
 
 

@@ -33,13 +33,14 @@ __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 
 // ---- peer exchange of neuron-sharded plans (see PeerArgs) ------------------------------------------------------
 // 16-byte piece of an output row -> the same element offset of every peer canvas
 __device__ __forceinline__ void store_to_peers(const PeerArgs *p, uint64_t elem_off, const uint4 &val) {
-    const uint32_t n = p->n_peers;
+    const uint32_t n = (p->dev_flags & 1u) ? 0u : p->n_peers;
     for (uint32_t q = 0; q < n; ++q) *reinterpret_cast<uint4 *>(p->canvas[q] + elem_off) = val;
 }
-// One thread per CTA, after the CTA's last store (its storing threads executed __threadfence_system() and met at a
-// barrier): the CTA that arrives last closes the launch and publishes the new launch count to every peer.
+// One thread per CTA, after the CTA's last store and a CTA barrier that all storing threads passed: one system-scope
+// fence covers the CTA's stores to the peers (fences are cumulative over what the barrier ordered before them); the
+// CTA that arrives last closes the launch and publishes the new launch count to every peer.
 __device__ __forceinline__ void peer_signal_done(const PeerArgs *p, uint32_t ctas_in_launch) {
-    __threadfence();
+    __threadfence_system();
     const uint32_t prev = atomicAdd(p->sync + kSyncDone, 1u);
     if (prev + 1u == ctas_in_launch) {
         __threadfence();

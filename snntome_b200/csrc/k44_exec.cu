@@ -664,6 +664,7 @@ bool Executor::set_peers_raw(int rank, int world, void *const *canvas_ptrs, void
     if (!sync_ptr()) return false;
     PeerArgs pa;
     pa.sync = d_sync_;
+    if (const char *e = std::getenv("K44B_PEER_DEV")) pa.dev_flags = (uint32_t)std::atoi(e);
     for (int r = 0; r < world; ++r) {
         if (r == rank) continue;
         if (!canvas_ptrs[r] || !sync_ptrs[r]) return fail("set_peers: missing pointer for rank " + std::to_string(r));

@@ -401,8 +401,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
             *abort_word = 1u;
         }
         if (a.peers) {                       // this CTA's rows are stored here and on every peer: count it as done
-            __threadfence_system();
-            epilogue_bar_sync();
+            epilogue_bar_sync();             // the storing threads' writes are ordered before the one fence below (cumulativity)
             if (threadIdx.x == 64u) peer_signal_done(a.peers, gridDim.x);
         }
     }
@@ -523,7 +522,7 @@ __device__ __forceinline__ void finish_owned_t(const WaveArgs &a, const float *r
         }
         *reinterpret_cast<uint2 *>(dst) = make_uint2(pk[0], pk[1]);
         if (a.peers) {
-            const uint32_t n = a.peers->n_peers;
+            const uint32_t n = (a.peers->dev_flags & 1u) ? 0u : a.peers->n_peers;
             for (uint32_t q = 0; q < n; ++q) *reinterpret_cast<uint2 *>(a.peers->canvas[q] + a.y_off + o) = make_uint2(pk[0], pk[1]);
         }
     } else {
@@ -799,8 +798,7 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         }
     }
     if (threadIdx.x == 64u) stamp(12);
-    if (a.peers && warp >= 2) __threadfence_system();
-    __syncthreads();
+    __syncthreads();                         // with peers: orders the storing threads' writes before thread 0's fence
     if (a.peers && threadIdx.x == 0) peer_signal_done(a.peers, gridDim.x);
     if (warp == 1) {
         ptx::tc_fence_after();

@@ -52,7 +52,7 @@ struct PeerArgs {
     uint32_t *arrive[kMaxPeers] = {};     // this rank's word in each peer's sync block
     uint32_t *sync = nullptr;             // own sync block: [0..6] the peers' launch counts, [8] CTAs done in the running launch, [9] launches completed
     uint32_t n_peers = 0;
-    uint32_t pad_ = 0;
+    uint32_t dev_flags = 0;               // development switch: 1 skip the data stores (timing experiments only)
 };
 constexpr uint32_t kSyncWords = 16, kSyncDone = 8, kSyncEpoch = 9;
 
