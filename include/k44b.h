@@ -90,6 +90,25 @@ int k44b_status(void *plan, uint32_t *status);
 int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, int out_elems, float *out_gpu_ms);
 /* Development aid: 16 SM-clock timestamps recorded by CTA 0 of the last tcgen05 wave kernel when the
  * library runs with K44B_DEBUG_MODE=16 (all zero otherwise). */
+/* ---- element-wise / attention commands between waves (the reference's RMSNORM, SWIGLU and ROPE_GQA_ATTN command
+ * types, wavec/k44_plan_types.hpp:603-650, kernels/common/kernel44_valu_pack.cuh:104-248). Offsets are FP16 element
+ * offsets of channel-major tensors in the canvas (multiples of 8); commands run in the order they were added, interleaved
+ * with the waves. gamma_f16 may be null (no scale). Rotary embedding rotates q and k IN PLACE (half-split pairs), then
+ * every column attends causally to the columns of its own sequence (blocks of seq_len columns, seq_len % 32 == 0).
+ * head_dim 64 or 128. add_decode_attn has no counterpart in the reference (which reserves a key / value cache but never
+ * reads it): one new token per column at the position set by k44b_plan_set_decode_pos — q and k are rotated at that
+ * position, k and v are appended to the caches (channel-major [h_kv*head_dim][max_seq][pitch] regions of the canvas) and
+ * the column attends to cache positions 0..pos. The position lives in device memory, so a captured graph can be replayed
+ * for every position. */
+int k44b_plan_add_rmsnorm(void *plan, const char *name, uint64_t src_off, uint64_t dst_off, uint32_t dim, float eps, const uint16_t *gamma_f16);
+int k44b_plan_add_swiglu(void *plan, const char *name, uint64_t gate_off, uint64_t up_off, uint64_t dst_off, uint32_t rows);
+int k44b_plan_add_rope_attn(void *plan, const char *name, uint64_t q_off, uint64_t k_off, uint64_t v_off, uint64_t out_off, uint32_t h_q,
+                            uint32_t h_kv, uint32_t head_dim, float rope_theta, int llama3_scaling, uint32_t seq_len);
+int k44b_plan_add_decode_attn(void *plan, const char *name, uint64_t q_off, uint64_t k_off, uint64_t v_off, uint64_t out_off,
+                              uint64_t kcache_off, uint64_t vcache_off, uint32_t h_q, uint32_t h_kv, uint32_t head_dim, uint32_t max_seq,
+                              float rope_theta, int llama3_scaling);
+int k44b_plan_set_decode_pos(void *plan, int pos, void *stream);
+
 /* ---- neuron sharding over the GPUs of one box (no counterpart in the reference, which is single-GPU) ----
  * Every rank holds a plan with its rows of every wave and a full-size canvas. After k44b_plan_set_peers_* the wave
  * kernels store each output row into the rank's own canvas and into the peers' canvases (peer-mapped memory over

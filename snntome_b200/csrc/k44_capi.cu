@@ -284,6 +284,51 @@ int k44b_plan_add_wave(void *plan, const k44b_wave_desc *wave) {
     return P(plan)->exec.add_wave(w) ? 0 : set_error(P(plan)->exec.err);
 }
 
+int k44b_plan_add_rmsnorm(void *plan, const char *name, uint64_t src_off, uint64_t dst_off, uint32_t dim, float eps, const uint16_t *gamma_f16) {
+    if (!plan || !dim) return set_error("plan_add_rmsnorm: bad arguments");
+    HostWave w;
+    w.kind = AUX_RMSNORM; w.name = name ? name : "rmsnorm"; w.cout = dim; w.src_off = src_off; w.y_off = dst_off; w.eps = eps;
+    if (gamma_f16) w.bias.assign(gamma_f16, gamma_f16 + dim);
+    return P(plan)->exec.add_wave(w) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_plan_add_swiglu(void *plan, const char *name, uint64_t gate_off, uint64_t up_off, uint64_t dst_off, uint32_t rows) {
+    if (!plan || !rows) return set_error("plan_add_swiglu: bad arguments");
+    HostWave w;
+    w.kind = AUX_SWIGLU; w.name = name ? name : "swiglu"; w.cout = rows; w.src_off = gate_off; w.src2_off = up_off; w.y_off = dst_off;
+    return P(plan)->exec.add_wave(w) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_plan_add_rope_attn(void *plan, const char *name, uint64_t q_off, uint64_t k_off, uint64_t v_off, uint64_t out_off, uint32_t h_q,
+                            uint32_t h_kv, uint32_t head_dim, float rope_theta, int llama3_scaling, uint32_t seq_len) {
+    if (!plan) return set_error("plan_add_rope_attn: bad arguments");
+    HostWave w;
+    w.kind = AUX_ROPE_ATTN; w.name = name ? name : "rope_attn"; w.cout = h_q * head_dim;
+    w.src_off = q_off; w.src2_off = k_off; w.src3_off = v_off; w.y_off = out_off;
+    w.h_q = h_q; w.h_kv = h_kv; w.head_dim = head_dim; w.rope_theta = rope_theta; w.llama3_scaling = llama3_scaling != 0; w.seq_len = seq_len;
+    return P(plan)->exec.add_wave(w) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_plan_add_decode_attn(void *plan, const char *name, uint64_t q_off, uint64_t k_off, uint64_t v_off, uint64_t out_off,
+                              uint64_t kcache_off, uint64_t vcache_off, uint32_t h_q, uint32_t h_kv, uint32_t head_dim, uint32_t max_seq,
+                              float rope_theta, int llama3_scaling) {
+    if (!plan) return set_error("plan_add_decode_attn: bad arguments");
+    HostWave w;
+    w.kind = AUX_DECODE_ATTN; w.name = name ? name : "decode_attn"; w.cout = h_q * head_dim;
+    w.src_off = q_off; w.src2_off = k_off; w.src3_off = v_off; w.y_off = out_off; w.kcache_off = kcache_off; w.vcache_off = vcache_off;
+    w.h_q = h_q; w.h_kv = h_kv; w.head_dim = head_dim; w.max_seq = max_seq; w.rope_theta = rope_theta; w.llama3_scaling = llama3_scaling != 0;
+    return P(plan)->exec.add_wave(w) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_plan_set_decode_pos(void *plan, int pos, void *stream) {
+    if (!plan || pos < 0) return set_error("plan_set_decode_pos: bad arguments");
+    int *d = P(plan)->exec.decode_pos_ptr();
+    if (!d) return set_error(P(plan)->exec.err);
+    // a 4-byte asynchronous copy from pageable memory is staged by the runtime before the call returns
+    const cudaError_t e = cudaMemcpyAsync(d, &pos, sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : set_error(std::string("plan_set_decode_pos: ") + cudaGetErrorString(e));
+}
+
 int k44b_plan_set_io(void *plan, uint64_t input_off, uint32_t input_c, uint64_t output_off, uint32_t output_c, uint32_t width) {
     if (!plan) return set_error("null plan");
     Executor &e = P(plan)->exec;

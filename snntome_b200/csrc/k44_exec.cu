@@ -180,6 +180,8 @@ void Executor::release() {
     scratch_tiles_ = 0;
     for (void *p : ipc_opened_) cudaIpcCloseMemHandle(p);
     ipc_opened_.clear();
+    cudaFree(d_pos_); d_pos_ = nullptr;
+    cudaFree(d_decode_partial_); d_decode_partial_ = nullptr; decode_partial_bytes_ = 0;
     cudaFree(d_sync_); d_sync_ = nullptr;
     cudaFree(d_peers_); d_peers_ = nullptr;
     cudaFree(canvas_); canvas_ = nullptr;
@@ -242,7 +244,90 @@ bool Executor::make_tensor_map(DeviceWave &dw, uint32_t box_cols, bool swizzle12
     return true;
 }
 
+int *Executor::decode_pos_ptr() {
+    if (!ready()) { fail("executor not initialised"); return nullptr; }
+    if (!d_pos_) {
+        if (!check(cudaSetDevice(device_), "cudaSetDevice") || !check(cudaMalloc(&d_pos_, sizeof(int)), "position word allocation") ||
+            !check(cudaMemset(d_pos_, 0, sizeof(int)), "position word clear"))
+            return nullptr;
+    }
+    return d_pos_;
+}
+
+// Element-wise / attention step: range-checked here, launched from the same command list as the waves.
+bool Executor::add_aux(const HostWave &w) {
+    if (!ready()) return fail("executor not initialised");
+    if (d_peers_) return fail("commands cannot be added after the peers were set");
+    if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
+    DeviceWave dw;
+    dw.name = w.name; dw.is_aux = true; dw.path = 2;
+    AuxArgs &x = dw.aux;
+    x.kind = w.kind; x.canvas = canvas_; x.pitch = pitch_; x.columns = columns_;
+    x.src_off = w.src_off; x.src2_off = w.src2_off; x.src3_off = w.src3_off; x.dst_off = w.y_off;
+    x.rows = w.cout; x.eps = w.eps;
+    x.h_q = w.h_q; x.h_kv = w.h_kv; x.head_dim = w.head_dim; x.seq_len = w.seq_len ? w.seq_len : pitch_; x.max_seq = w.max_seq;
+    x.llama3 = w.llama3_scaling ? 1u : 0u; x.neg_log_theta = -std::log(w.rope_theta > 0.f ? w.rope_theta : 10000.0f);
+    x.kcache_off = w.kcache_off; x.vcache_off = w.vcache_off;
+    auto inside = [&](uint64_t off, uint64_t rows) { return off % 8u == 0u && off + rows * pitch_ <= canvas_elems_; };
+    uint64_t rlo = ~0ull, rhi = 0;
+    auto reads = [&](uint64_t off, uint64_t rows) { rlo = std::min(rlo, off); rhi = std::max(rhi, off + rows * pitch_); };
+    switch (w.kind) {
+    case AUX_RMSNORM:
+        if (!w.cout || !inside(w.src_off, w.cout) || !inside(w.y_off, w.cout)) return fail("RMSNorm '" + w.name + "' leaves the canvas");
+        if (!w.bias.empty()) {
+            if (w.bias.size() != w.cout) return fail("RMSNorm '" + w.name + "': gamma has the wrong length");
+            if (!check(cudaMalloc(&dw.d_bias, w.bias.size() * 2), "gamma allocation") ||
+                !check(cudaMemcpy(dw.d_bias, w.bias.data(), w.bias.size() * 2, cudaMemcpyHostToDevice), "gamma upload")) return false;
+            x.gamma = (const __half *)dw.d_bias;
+        }
+        reads(w.src_off, w.cout);
+        dw.write_lo = w.y_off; dw.write_hi = w.y_off + (uint64_t)w.cout * pitch_;
+        break;
+    case AUX_SWIGLU:
+        if (!w.cout || !inside(w.src_off, w.cout) || !inside(w.src2_off, w.cout) || !inside(w.y_off, w.cout)) return fail("SwiGLU '" + w.name + "' leaves the canvas");
+        reads(w.src_off, w.cout); reads(w.src2_off, w.cout);
+        dw.write_lo = w.y_off; dw.write_hi = w.y_off + (uint64_t)w.cout * pitch_;
+        break;
+    case AUX_ROPE_ATTN:
+    case AUX_DECODE_ATTN: {
+        if ((w.head_dim != 64u && w.head_dim != 128u) || !w.h_kv || !w.h_q || w.h_q % w.h_kv) return fail("attention '" + w.name + "': head_dim must be 64 or 128 and h_q a multiple of h_kv");
+        const uint64_t rq = (uint64_t)w.h_q * w.head_dim, rk = (uint64_t)w.h_kv * w.head_dim;
+        if (!inside(w.src_off, rq) || !inside(w.src2_off, rk) || !inside(w.src3_off, rk) || !inside(w.y_off, rq)) return fail("attention '" + w.name + "' leaves the canvas");
+        if (w.kind == AUX_ROPE_ATTN) {
+            if (pitch_ % 32u || x.seq_len % 32u) return fail("attention '" + w.name + "': sequences must be multiples of 32 columns");
+        } else {
+            if (!w.max_seq || w.kcache_off % 8u || w.vcache_off % 8u || w.kcache_off + rk * w.max_seq * pitch_ > canvas_elems_ ||
+                w.vcache_off + rk * w.max_seq * pitch_ > canvas_elems_) return fail("attention '" + w.name + "': key / value cache leaves the canvas");
+            if (w.head_dim != 64u || w.h_q / w.h_kv > 8u) return fail("attention '" + w.name + "': the cache kernel supports head_dim 64 and up to 8 query heads per key / value head");
+            if (!(x.pos_ptr = decode_pos_ptr())) return false;
+            const size_t pbytes = (size_t)((w.max_seq + kDecodeChunk - 1u) / kDecodeChunk) * w.h_q * 66u * pitch_ * sizeof(float);
+            if (pbytes > decode_partial_bytes_) {
+                if (!check(cudaDeviceSynchronize(), "synchronise")) return false;
+                cudaFree(d_decode_partial_); d_decode_partial_ = nullptr; decode_partial_bytes_ = 0;
+                if (!check(cudaMalloc(&d_decode_partial_, pbytes), "attention scratch allocation")) return false;
+                decode_partial_bytes_ = pbytes;
+                for (auto &o : waves_) if (o.is_aux && o.aux.kind == AUX_DECODE_ATTN) o.aux.partial = d_decode_partial_;
+            }
+            x.partial = d_decode_partial_;
+            reads(w.kcache_off, rk * w.max_seq); reads(w.vcache_off, rk * w.max_seq);
+        }
+        reads(w.src_off, rq); reads(w.src2_off, rk); reads(w.src3_off, rk);
+        // q and k are rotated in place, the caches are appended to: treat everything touched as written
+        dw.write_lo = std::min({w.y_off, w.src_off, w.src2_off, rlo}); dw.write_hi = std::max({w.y_off + rq * pitch_, rhi});
+        break;
+    }
+    default: return fail("unknown command kind");
+    }
+    dw.read_lo = rlo; dw.read_hi = rhi;
+    dw.groupable = false;
+    waves_.push_back(dw);
+    drop_graph();
+    groups_valid_ = false;
+    return true;
+}
+
 bool Executor::add_wave(const HostWave &w) {
+    if (w.kind != 0) return add_aux(w);
     if (!ready()) return fail("executor not initialised");
     if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
     const uint32_t tiles64 = pitch_ / 64u;
@@ -526,6 +611,10 @@ bool Executor::launch_group(size_t gi, cudaStream_t stream) {
 
 bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
     cudaError_t e;
+    if (w.is_aux) {
+        launches_ += w.aux.kind == AUX_ROPE_ATTN ? 3u : (w.aux.kind == AUX_DECODE_ATTN ? 4u : 1u);
+        return check(launch_aux(w.aux, stream), ("launch of '" + w.name + "'").c_str());
+    }
     if (w.path == PATH_UMMA && w.use_cluster) {
         WaveGroupArgs g;
         g.count = 1; g.splits = w.args.k_splits;

@@ -30,6 +30,8 @@ UmmaDesc make_umma_desc(uint32_t n_tile, int variant);
 
 struct DeviceWave {
     std::string name;
+    bool is_aux = false;                 // element-wise / attention step (k44_valu.cu) instead of a wave
+    AuxArgs aux;
     WaveArgs args;
     UmmaDesc desc;
     CUtensorMap tmap;
@@ -56,6 +58,8 @@ class Executor {
     // force_path: -1 choose per wave, 0 always FMA, 1 tensor cores wherever the gather allows
     bool begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t columns, int force_path);
     bool add_wave(const HostWave &w);
+    bool add_aux(const HostWave &w);                               // HostWave::kind != 0
+    int *decode_pos_ptr();                                         // device word holding the position decode attention works at
     void set_io(uint64_t in_off, uint32_t in_c, uint64_t out_off, uint32_t out_c, uint32_t width);
     bool init(const HostPlan &plan, int device, int force_path);   // begin + add_wave* + set_io
     void release();
@@ -111,6 +115,9 @@ class Executor {
     uint64_t launches_ = 0;
     float *d_scratch_ = nullptr;
     uint32_t *d_counters_ = nullptr;
+    int *d_pos_ = nullptr;                // decode position
+    float *d_decode_partial_ = nullptr;   // per-chunk partial attention results, shared by all decode-attention commands
+    size_t decode_partial_bytes_ = 0;
     // neuron sharding over several GPUs (see PeerArgs)
     uint32_t *d_sync_ = nullptr;          // kSyncWords words, allocated on first use
     PeerArgs *d_peers_ = nullptr;

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
+
 namespace k44b {
 
 // ---- packed ("tiled") weight layout --------------------------------------------------------------
@@ -86,6 +88,24 @@ struct WaveArgs {
     uint32_t *counters = nullptr;         // [tiles], all zero between launches
     const PeerArgs *peers = nullptr;      // device memory; null unless the plan is neuron-sharded over several GPUs
 };
+
+// Element-wise / attention steps between waves (k44_valu.cu)
+enum AuxKind : int { AUX_NONE = 0, AUX_RMSNORM = 1, AUX_SWIGLU = 2, AUX_ROPE_ATTN = 3, AUX_DECODE_ATTN = 4 };
+struct AuxArgs {
+    int kind = AUX_NONE;
+    __half *canvas = nullptr;
+    uint64_t src_off = 0, src2_off = 0, src3_off = 0, dst_off = 0;    // x | gate, up | q, k, v
+    uint64_t kcache_off = 0, vcache_off = 0;                         // decode attention: [h_kv*head_dim][max_seq][pitch]
+    uint32_t rows = 0, pitch = 0, columns = 0;
+    float eps = 1e-5f;
+    const __half *gamma = nullptr;                                   // device, [rows] or null
+    uint32_t h_q = 0, h_kv = 0, head_dim = 0, seq_len = 0, max_seq = 0, llama3 = 0;
+    float neg_log_theta = -9.210340371976184f;
+    const int *pos_ptr = nullptr;                                    // decode: current position, device memory
+    float *partial = nullptr;                                        // decode: per-chunk partial results [chunks][h_q][66][pitch]
+};
+constexpr uint32_t kDecodeChunk = 64;                                // cache positions per partial-attention CTA
+cudaError_t launch_aux(const AuxArgs &a, cudaStream_t s);
 
 // Up to four mutually independent small waves launched as one grid (their clusters are numbered consecutively).
 constexpr int kMaxGroupWaves = 4;

@@ -1,0 +1,336 @@
+// Element-wise and attention steps between the waves of a decoder layer, on the 1-D token layout (channel-major:
+// channel c of a tensor at element offset `off` is canvas[off + c*pitch ...]). All of them are bandwidth- or
+// latency-bound SIMT kernels; none is on the tensor cores.
+//
+//   RMSNorm        y[c][t] = x[c][t] * rsqrt(mean_c x[c][t]^2 + eps) * gamma[c]      (kernels/common/kernel44_valu_pack.cuh:104-134)
+//   SwiGLU product y = gate * up (SiLU is applied by the gate wave's epilogue)          (:135-143)
+//   rotary         pairs (p, p + head_dim/2), angle = position * theta^(-2p/head_dim)  (:65-70, 144-158)
+//   causal GQA     per sequence of `seq_len` columns, streaming softmax                (:159-248)
+//   decode GQA     one new token per column against a key / value cache in the canvas  (no counterpart in the reference)
+//
+// FP16 in and out, FP32 arithmetic, one rounding (to nearest even) at each store, as the reference kernels do.
+#include "k44_kernels.cuh"
+
+namespace k44b {
+
+__device__ __forceinline__ void unpack8(const uint4 &u, float (&f)[8]) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 v = __half22float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 u;
+    __half2 *h = reinterpret_cast<__half2 *>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return u;
+}
+
+// ---- RMSNorm: one CTA per group of 8 columns, 256 threads stride over the channels ----------------------------------
+__global__ void __launch_bounds__(256) k44_valu_rmsnorm_kernel(const AuxArgs a) {
+    __shared__ float part[8][8];
+    const uint32_t col0 = blockIdx.x * 8u, tid = threadIdx.x;
+    const __half *src = a.canvas + a.src_off + col0;
+    __half *dst = a.canvas + a.dst_off + col0;
+    float ss[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (uint32_t c = tid; c < a.rows; c += 256u) {
+        float x[8];
+        unpack8(*reinterpret_cast<const uint4 *>(src + (uint64_t)c * a.pitch), x);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss[k] = fmaf(x[k], x[k], ss[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss[k] += __shfl_xor_sync(0xffffffffu, ss[k], o);
+    }
+    if ((tid & 31u) == 0u) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) part[tid >> 5][k] = ss[k];
+    }
+    __syncthreads();
+    float inv[8];
+    const float inv_d = 1.0f / (float)a.rows;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += part[w][k];
+        inv[k] = rsqrtf(fmaf(tot, inv_d, a.eps));
+    }
+    for (uint32_t c = tid; c < a.rows; c += 256u) {      // second pass: the rows come back from L2
+        float x[8];
+        unpack8(*reinterpret_cast<const uint4 *>(src + (uint64_t)c * a.pitch), x);
+        const float g = a.gamma ? __half2float(a.gamma[c]) : 1.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) x[k] = x[k] * inv[k] * g;
+        *reinterpret_cast<uint4 *>(dst + (uint64_t)c * a.pitch) = pack8(x);
+    }
+}
+
+// ---- SwiGLU product ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k44_valu_swiglu_kernel(const AuxArgs a) {
+    const uint64_t n8 = (uint64_t)a.rows * a.pitch / 8u;
+    const uint4 *g = reinterpret_cast<const uint4 *>(a.canvas + a.src_off);
+    const uint4 *u = reinterpret_cast<const uint4 *>(a.canvas + a.src2_off);
+    uint4 *d = reinterpret_cast<uint4 *>(a.canvas + a.dst_off);
+    for (uint64_t i = (uint64_t)blockIdx.x * 256u + threadIdx.x; i < n8; i += (uint64_t)gridDim.x * 256u) {
+        float x[8], y[8];
+        unpack8(g[i], x);
+        unpack8(u[i], y);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) x[k] *= y[k];
+        d[i] = pack8(x);
+    }
+}
+
+// ---- rotary embedding, in place -------------------------------------------------------------------------------------
+__device__ __forceinline__ float rope_inv_freq(uint32_t p, uint32_t head_dim, float neg_log_theta, bool llama3) {
+    float f = expf((float)(2u * p) * (neg_log_theta / (float)head_dim));
+    if (llama3) {       // Llama-3 long-context frequency scaling
+        const float ratio = 1303.7972938088068f * f;
+        const float smooth = fminf(1.0f, fmaxf(0.0f, (ratio - 1.0f) * 0.3333333432674408f));
+        f = (1.0f - smooth) * (f * 0.03125f) + smooth * f;
+    }
+    return f;
+}
+
+// one thread: one rotation pair of one head, 8 consecutive columns
+__global__ void __launch_bounds__(256) k44_valu_rope_kernel(const AuxArgs a, uint64_t off, uint32_t heads) {
+    const uint32_t half = a.head_dim / 2u, groups = a.pitch / 8u;
+    const uint64_t total = (uint64_t)heads * half * groups;
+    const uint64_t i = (uint64_t)blockIdx.x * 256u + threadIdx.x;
+    if (i >= total) return;
+    const uint32_t cg = (uint32_t)(i % groups);
+    const uint32_t p = (uint32_t)((i / groups) % half), h = (uint32_t)(i / ((uint64_t)groups * half));
+    __half *r0 = a.canvas + off + (uint64_t)(h * a.head_dim + p) * a.pitch + cg * 8u;
+    __half *r1 = r0 + (uint64_t)half * a.pitch;
+    const float f = rope_inv_freq(p, a.head_dim, a.neg_log_theta, a.llama3 != 0u);
+    float x0[8], x1[8];
+    unpack8(*reinterpret_cast<const uint4 *>(r0), x0);
+    unpack8(*reinterpret_cast<const uint4 *>(r1), x1);
+    const int fixed_pos = a.pos_ptr ? *a.pos_ptr : -1;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const uint32_t t = cg * 8u + (uint32_t)k;
+        const float pos = fixed_pos >= 0 ? (float)fixed_pos : (float)(t % a.seq_len);
+        float s, c;
+        sincosf(pos * f, &s, &c);
+        const float y0 = x0[k] * c - x1[k] * s, y1 = x0[k] * s + x1[k] * c;
+        x0[k] = y0; x1[k] = y1;
+    }
+    *reinterpret_cast<uint4 *>(r0) = pack8(x0);
+    *reinterpret_cast<uint4 *>(r1) = pack8(x1);
+}
+
+// ---- causal grouped-query attention ---------------------------------------------------------------------------------
+// CTA = 32 consecutive columns (queries) of one query head; 4 threads per query, each owning HD/4 dimensions.
+// Keys and values are visited in tiles of 32 columns from the start of the query's sequence, staged through shared
+// memory as [column][dimension]; running maximum / sum softmax in FP32.
+template <int HD>
+__global__ void __launch_bounds__(128) k44_valu_causal_attn_kernel(const AuxArgs a) {
+    constexpr int DP = HD / 4;                      // dimensions per thread
+    constexpr int ROW = HD + 8;                     // padded shared row (halves)
+    __shared__ __align__(16) __half sk[32][ROW];
+    __shared__ __align__(16) __half sv[32][ROW];
+    const uint32_t tile = blockIdx.x, hq = blockIdx.y, hkv = hq / (a.h_q / a.h_kv);
+    const uint32_t tid = threadIdx.x, part = tid & 3u, ql = tid >> 2;
+    const uint32_t t0 = tile * 32u, t = t0 + ql;
+    const uint32_t seq0 = (t0 / a.seq_len) * a.seq_len;           // first column of this sequence
+    const float scale = rsqrtf((float)HD);
+    const __half *qh = a.canvas + a.src_off + (uint64_t)hq * HD * a.pitch;
+    const __half *kh = a.canvas + a.src2_off + (uint64_t)hkv * HD * a.pitch;
+    const __half *vh = a.canvas + a.src3_off + (uint64_t)hkv * HD * a.pitch;
+    // stage the query tile (coalesced rows of 32 columns), then keep this thread's slice in registers
+    for (uint32_t e = tid; e < 32u * HD; e += 128u) { const uint32_t d = e >> 5, c = e & 31u; sk[c][d] = qh[(uint64_t)d * a.pitch + t0 + c]; }
+    __syncthreads();
+    float q[DP], acc[DP];
+#pragma unroll
+    for (int d = 0; d < DP; ++d) { q[d] = __half2float(sk[ql][part * DP + d]) * scale; acc[d] = 0.f; }
+    __syncthreads();
+    float m = -65504.0f, l = 0.f;
+    for (uint32_t k0 = seq0; k0 <= t0; k0 += 32u) {
+        for (uint32_t e = tid; e < 32u * HD; e += 128u) {
+            const uint32_t d = e >> 5, c = e & 31u;
+            sk[c][d] = kh[(uint64_t)d * a.pitch + k0 + c];
+            sv[c][d] = vh[(uint64_t)d * a.pitch + k0 + c];
+        }
+        __syncthreads();
+        const uint32_t last = (k0 == t0) ? ql : 31u;              // causal: keys up to the query's own column
+        for (uint32_t u = 0; u <= 31u; ++u) {
+            float dot = 0.f;
+#pragma unroll
+            for (int d = 0; d < DP; ++d) dot = fmaf(q[d], __half2float(sk[u][part * DP + d]), dot);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            if (u <= last) {
+                const float mn = fmaxf(m, dot);
+                const float ep = __expf(m - mn), ec = __expf(dot - mn);
+                l = l * ep + ec;
+#pragma unroll
+                for (int d = 0; d < DP; ++d) acc[d] = acc[d] * ep + ec * __half2float(sv[u][part * DP + d]);
+                m = mn;
+            }
+        }
+        __syncthreads();
+    }
+    const float inv_l = 1.0f / l;
+#pragma unroll
+    for (int d = 0; d < DP; ++d) sk[ql][part * DP + d] = __float2half_rn(acc[d] * inv_l);
+    __syncthreads();
+    __half *oh = a.canvas + a.dst_off + (uint64_t)hq * HD * a.pitch;
+    for (uint32_t e = tid; e < 32u * HD; e += 128u) { const uint32_t d = e >> 5, c = e & 31u; oh[(uint64_t)d * a.pitch + t0 + c] = sk[c][d]; }
+}
+
+// ---- decode attention against a key / value cache ---------------------------------------------------------------------
+// Cache layout (both K and V): channel-major [h_kv*head_dim][max_seq][pitch] FP16, i.e. for a fixed channel and position the
+// columns (sequences) are contiguous. One new token per column at position *pos_ptr.
+
+// rotate k in place at the current position and append k and v to the caches; one thread per (channel pair, 8 columns)
+__global__ void __launch_bounds__(256) k44_valu_rope_k_append_kernel(const AuxArgs a) {
+    const uint32_t half = a.head_dim / 2u, groups = a.pitch / 8u;
+    const uint64_t total = (uint64_t)a.h_kv * half * groups;
+    const uint64_t i = (uint64_t)blockIdx.x * 256u + threadIdx.x;
+    if (i >= total) return;
+    const uint32_t cg = (uint32_t)(i % groups);
+    const uint32_t p = (uint32_t)((i / groups) % half), h = (uint32_t)(i / ((uint64_t)groups * half));
+    const uint32_t c0 = h * a.head_dim + p, c1 = c0 + half;
+    const int pos = *a.pos_ptr;
+    if (pos < 0 || (uint32_t)pos >= a.max_seq) return;
+    __half *k0 = a.canvas + a.src2_off + (uint64_t)c0 * a.pitch + cg * 8u, *k1 = a.canvas + a.src2_off + (uint64_t)c1 * a.pitch + cg * 8u;
+    const float f = rope_inv_freq(p, a.head_dim, a.neg_log_theta, a.llama3 != 0u);
+    float s, c, x0[8], x1[8];
+    sincosf((float)pos * f, &s, &c);
+    unpack8(*reinterpret_cast<const uint4 *>(k0), x0);
+    unpack8(*reinterpret_cast<const uint4 *>(k1), x1);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { const float y0 = x0[k] * c - x1[k] * s, y1 = x0[k] * s + x1[k] * c; x0[k] = y0; x1[k] = y1; }
+    const uint4 r0 = pack8(x0), r1 = pack8(x1);
+    *reinterpret_cast<uint4 *>(k0) = r0;
+    *reinterpret_cast<uint4 *>(k1) = r1;
+    const uint64_t ch_stride = (uint64_t)a.max_seq * a.pitch, at = (uint64_t)pos * a.pitch + cg * 8u;
+    *reinterpret_cast<uint4 *>(a.canvas + a.kcache_off + c0 * ch_stride + at) = r0;
+    *reinterpret_cast<uint4 *>(a.canvas + a.kcache_off + c1 * ch_stride + at) = r1;
+    *reinterpret_cast<uint4 *>(a.canvas + a.vcache_off + c0 * ch_stride + at) = *reinterpret_cast<const uint4 *>(a.canvas + a.src3_off + (uint64_t)c0 * a.pitch + cg * 8u);
+    *reinterpret_cast<uint4 *>(a.canvas + a.vcache_off + c1 * ch_stride + at) = *reinterpret_cast<const uint4 *>(a.canvas + a.src3_off + (uint64_t)c1 * a.pitch + cg * 8u);
+}
+
+// Partial attention of one chunk of kDecChunk cache positions: CTA = (32 columns, one key/value head, one chunk); thread =
+// (column, query head of the group). Key and value rows of 4 positions at a time are staged in shared memory as
+// [position][dimension][column]; every thread keeps its query and its accumulator (64 dimensions) in registers.
+// Output per (chunk, query head): the unnormalised accumulator, the running maximum and the sum, FP32, [..][66][pitch].
+constexpr uint32_t kDecChunk = 64, kDecTP = 4;
+__global__ void __launch_bounds__(256) k44_valu_decode_attn_partial_kernel(const AuxArgs a, float *partial) {
+    constexpr uint32_t HD = 64;
+    __shared__ __align__(16) __half sk[kDecTP][HD][32];
+    __shared__ __align__(16) __half sv[kDecTP][HD][32];
+    const uint32_t cb = blockIdx.x, hkv = blockIdx.y, chunk = blockIdx.z;
+    const uint32_t group = a.h_q / a.h_kv, nthreads = 32u * group;
+    const uint32_t tid = threadIdx.x, b = tid & 31u, hl = tid >> 5, hq = hkv * group + hl;
+    const int pos = *a.pos_ptr;
+    const uint32_t p_begin = chunk * kDecChunk;
+    if (pos < 0 || p_begin > (uint32_t)pos) return;                      // nothing cached in this chunk yet (uniform per CTA)
+    const uint32_t p_end = min(p_begin + kDecChunk, (uint32_t)pos + 1u);
+    const uint32_t col = cb * 32u + b;
+    const float scale = rsqrtf((float)HD);
+    float q[HD], acc[HD];
+    const __half *qh = a.canvas + a.src_off + (uint64_t)hq * HD * a.pitch + col;
+#pragma unroll
+    for (uint32_t d = 0; d < HD; ++d) { q[d] = __half2float(qh[(uint64_t)d * a.pitch]) * scale; acc[d] = 0.f; }
+    float m = -65504.0f, l = 0.f;
+    const uint64_t ch_stride = (uint64_t)a.max_seq * a.pitch;
+    const __half *kc = a.canvas + a.kcache_off + (uint64_t)hkv * HD * ch_stride + cb * 32u;
+    const __half *vc = a.canvas + a.vcache_off + (uint64_t)hkv * HD * ch_stride + cb * 32u;
+    for (uint32_t p0 = p_begin; p0 < p_end; p0 += kDecTP) {
+        // 4 positions x 64 dimensions x 4 pieces of 8 columns = 1024 16-byte pieces per tile
+        for (uint32_t e = tid; e < kDecTP * HD * 4u; e += nthreads) {
+            const uint32_t piece = e & 3u, d = (e >> 2) & (HD - 1u), tp = e >> 8;
+            const uint32_t p = min(p0 + tp, p_end - 1u);
+            const uint64_t off = (uint64_t)d * ch_stride + (uint64_t)p * a.pitch + piece * 8u;
+            *reinterpret_cast<uint4 *>(&sk[tp][d][piece * 8u]) = *reinterpret_cast<const uint4 *>(kc + off);
+            *reinterpret_cast<uint4 *>(&sv[tp][d][piece * 8u]) = *reinterpret_cast<const uint4 *>(vc + off);
+        }
+        __syncthreads();
+        const uint32_t np = min(kDecTP, p_end - p0);
+        for (uint32_t tp = 0; tp < np; ++tp) {
+            float dot = 0.f;
+#pragma unroll
+            for (uint32_t d = 0; d < HD; ++d) dot = fmaf(q[d], __half2float(sk[tp][d][b]), dot);
+            const float mn = fmaxf(m, dot);
+            const float ep = __expf(m - mn), ec = __expf(dot - mn);
+            l = l * ep + ec;
+#pragma unroll
+            for (uint32_t d = 0; d < HD; ++d) acc[d] = fmaf(acc[d], ep, ec * __half2float(sv[tp][d][b]));
+            m = mn;
+        }
+        __syncthreads();
+    }
+    float *out = partial + ((uint64_t)chunk * a.h_q + hq) * (HD + 2u) * a.pitch + col;
+#pragma unroll
+    for (uint32_t d = 0; d < HD; ++d) out[(uint64_t)d * a.pitch] = acc[d];
+    out[(uint64_t)HD * a.pitch] = m;
+    out[(uint64_t)(HD + 1u) * a.pitch] = l;
+}
+
+// combine the chunks: thread = (query head, dimension, column)
+__global__ void __launch_bounds__(256) k44_valu_decode_attn_combine_kernel(const AuxArgs a, const float *partial) {
+    constexpr uint32_t HD = 64;
+    const uint64_t total = (uint64_t)a.h_q * HD * a.pitch;
+    const uint64_t i = (uint64_t)blockIdx.x * 256u + threadIdx.x;
+    if (i >= total) return;
+    const uint32_t col = (uint32_t)(i % a.pitch), d = (uint32_t)((i / a.pitch) % HD), hq = (uint32_t)(i / ((uint64_t)a.pitch * HD));
+    const int pos = *a.pos_ptr;
+    if (pos < 0) return;
+    const uint32_t chunks = (uint32_t)pos / kDecChunk + 1u;
+    float M = -65504.0f;
+    for (uint32_t c = 0; c < chunks; ++c) M = fmaxf(M, partial[(((uint64_t)c * a.h_q + hq) * (HD + 2u) + HD) * a.pitch + col]);
+    float L = 0.f, o = 0.f;
+    for (uint32_t c = 0; c < chunks; ++c) {
+        const float *pc = partial + ((uint64_t)c * a.h_q + hq) * (HD + 2u) * a.pitch + col;
+        const float w = __expf(pc[(uint64_t)HD * a.pitch] - M);
+        L = fmaf(pc[(uint64_t)(HD + 1u) * a.pitch], w, L);
+        o = fmaf(pc[(uint64_t)d * a.pitch], w, o);
+    }
+    a.canvas[a.dst_off + ((uint64_t)hq * HD + d) * a.pitch + col] = __float2half_rn(o / L);
+}
+
+cudaError_t launch_aux(const AuxArgs &a, cudaStream_t s) {
+    switch (a.kind) {
+    case AUX_RMSNORM:
+        if (a.pitch % 8u || a.rows == 0) return cudaErrorInvalidValue;
+        k44_valu_rmsnorm_kernel<<<a.pitch / 8u, 256, 0, s>>>(a);
+        break;
+    case AUX_SWIGLU: {
+        const uint64_t n8 = (uint64_t)a.rows * a.pitch / 8u;
+        const uint32_t grid = (uint32_t)std::min<uint64_t>((n8 + 255u) / 256u, 148u * 16u);
+        k44_valu_swiglu_kernel<<<grid ? grid : 1u, 256, 0, s>>>(a);
+        break;
+    }
+    case AUX_ROPE_ATTN: {
+        if (a.head_dim != 64u && a.head_dim != 128u) return cudaErrorInvalidValue;
+        if (a.pitch % 32u || a.seq_len % 32u || a.h_kv == 0 || a.h_q % a.h_kv) return cudaErrorInvalidValue;
+        const uint32_t groups = a.pitch / 8u, half = a.head_dim / 2u;
+        k44_valu_rope_kernel<<<(uint32_t)(((uint64_t)a.h_q * half * groups + 255u) / 256u), 256, 0, s>>>(a, a.src_off, a.h_q);
+        k44_valu_rope_kernel<<<(uint32_t)(((uint64_t)a.h_kv * half * groups + 255u) / 256u), 256, 0, s>>>(a, a.src2_off, a.h_kv);
+        const dim3 grid((a.columns + 31u) / 32u, a.h_q);
+        if (a.head_dim == 64u) k44_valu_causal_attn_kernel<64><<<grid, 128, 0, s>>>(a);
+        else k44_valu_causal_attn_kernel<128><<<grid, 128, 0, s>>>(a);
+        break;
+    }
+    case AUX_DECODE_ATTN: {
+        // rotary on q at the current position, rotary + cache append for k / v, partial attention per chunk, combine
+        if (a.head_dim != 64u || a.pitch % 32u || !a.pos_ptr || !a.partial || a.h_kv == 0 || a.h_q % a.h_kv || a.h_q / a.h_kv > 8u) return cudaErrorInvalidValue;
+        const uint32_t groups = a.pitch / 8u, half = a.head_dim / 2u;
+        k44_valu_rope_kernel<<<(uint32_t)(((uint64_t)a.h_q * half * groups + 255u) / 256u), 256, 0, s>>>(a, a.src_off, a.h_q);
+        k44_valu_rope_k_append_kernel<<<(uint32_t)(((uint64_t)a.h_kv * half * groups + 255u) / 256u), 256, 0, s>>>(a);
+        const dim3 grid(a.pitch / 32u, a.h_kv, (a.max_seq + kDecChunk - 1u) / kDecChunk);
+        k44_valu_decode_attn_partial_kernel<<<grid, 32u * (a.h_q / a.h_kv), 0, s>>>(a, a.partial);
+        k44_valu_decode_attn_combine_kernel<<<(uint32_t)(((uint64_t)a.h_q * 64u * a.pitch + 255u) / 256u), 256, 0, s>>>(a, a.partial);
+        break;
+    }
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace k44b

@@ -183,6 +183,34 @@ class NativePlan:
             raise NativeError(f"infer_f16: {last_error()}")
         return float(ms.value)
 
+    # -- element-wise / attention commands between waves ----------------------------------------------------------
+    def add_rmsnorm(self, src_off: int, dst_off: int, dim: int, eps: float = 1e-5, gamma_bits=None, name: str = "rmsnorm") -> None:
+        g = None
+        if gamma_bits is not None:
+            g = np.ascontiguousarray(gamma_bits, dtype=np.uint16)
+            g = g.ctypes.data_as(ctypes.POINTER(ctypes.c_uint16))
+        if self._lib.k44b_plan_add_rmsnorm(self._ptr, name.encode(), int(src_off), int(dst_off), int(dim), float(eps), g) != 0:
+            raise NativeError(f"add_rmsnorm: {last_error()}")
+
+    def add_swiglu(self, gate_off: int, up_off: int, dst_off: int, rows: int, name: str = "swiglu") -> None:
+        if self._lib.k44b_plan_add_swiglu(self._ptr, name.encode(), int(gate_off), int(up_off), int(dst_off), int(rows)) != 0:
+            raise NativeError(f"add_swiglu: {last_error()}")
+
+    def add_rope_attn(self, q_off, k_off, v_off, out_off, h_q, h_kv, head_dim, seq_len, theta=10000.0, llama3=False, name="rope_attn") -> None:
+        if self._lib.k44b_plan_add_rope_attn(self._ptr, name.encode(), int(q_off), int(k_off), int(v_off), int(out_off), int(h_q), int(h_kv),
+                                             int(head_dim), float(theta), int(bool(llama3)), int(seq_len)) != 0:
+            raise NativeError(f"add_rope_attn: {last_error()}")
+
+    def add_decode_attn(self, q_off, k_off, v_off, out_off, kcache_off, vcache_off, h_q, h_kv, head_dim, max_seq, theta=10000.0, llama3=False,
+                        name="decode_attn") -> None:
+        if self._lib.k44b_plan_add_decode_attn(self._ptr, name.encode(), int(q_off), int(k_off), int(v_off), int(out_off), int(kcache_off),
+                                               int(vcache_off), int(h_q), int(h_kv), int(head_dim), int(max_seq), float(theta), int(bool(llama3))) != 0:
+            raise NativeError(f"add_decode_attn: {last_error()}")
+
+    def set_decode_pos(self, pos: int, stream=None) -> None:
+        if self._lib.k44b_plan_set_decode_pos(self._ptr, int(pos), ctypes.c_void_p(self._stream_ptr(stream))) != 0:
+            raise NativeError(f"set_decode_pos: {last_error()}")
+
     # -- neuron sharding over several GPUs: rows go straight into the peers' canvases ------------------------------
     def ipc_handles(self):
         """(canvas handle, sync-block handle): two 64-byte CUDA IPC handles for the other ranks' processes."""
