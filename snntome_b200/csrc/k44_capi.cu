@@ -164,13 +164,18 @@ int wavec_add_upconv2x2(void *handle, const char *, const char *, const char *, 
 }
 int wavec_add_maxpool(void *handle, const char *, const char *, const char *, int, int, int) { return unsupported(handle, "max-pool"); }
 int wavec_add_upsample2x(void *handle, const char *, const char *, const char *) { return unsupported(handle, "upsample"); }
-int wavec_add_rmsnorm(void *handle, const char *, const char *, const char *, int, float, const float *, int) {
-    return unsupported(handle, "RMSNorm");
+int wavec_add_rmsnorm(void *handle, const char *name, const char *in, const char *out, int dim, float eps, const float *gamma_f32, int pre_folded) {
+    if (!handle) return set_error("null handle");
+    return H(handle)->graph.add_rmsnorm(name, in, out, dim, eps, gamma_f32, pre_folded) ? 0 : set_error(H(handle)->graph.error);
 }
-int wavec_add_swiglu(void *handle, const char *, const char *, const char *, const char *) { return unsupported(handle, "SwiGLU"); }
-int wavec_add_rope_gqa_attn(void *handle, const char *, const char *, const char *, const char *, const char *, int, int, int,
-                            float, int) {
-    return unsupported(handle, "RoPE / attention");
+int wavec_add_swiglu(void *handle, const char *name, const char *gate, const char *up, const char *out) {
+    if (!handle) return set_error("null handle");
+    return H(handle)->graph.add_swiglu(name, gate, up, out) ? 0 : set_error(H(handle)->graph.error);
+}
+int wavec_add_rope_gqa_attn(void *handle, const char *name, const char *q, const char *k, const char *v, const char *out, int h_q, int h_kv,
+                            int head_dim, float rope_theta, int llama3_scaling) {
+    if (!handle) return set_error("null handle");
+    return H(handle)->graph.add_rope_attn(name, q, k, v, out, h_q, h_kv, head_dim, rope_theta, llama3_scaling) ? 0 : set_error(H(handle)->graph.error);
 }
 
 int wavec_add_split(void *handle, const char *name, const char *in, int n, const char **outs) {

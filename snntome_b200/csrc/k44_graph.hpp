@@ -1,15 +1,18 @@
-// Graph -> wave plan for the part of the reference's front end that the wave path needs:
-// 1-D token graphs made of Input, dense linears (1x1 convolutions, optional residual), and the
-// zero-copy topology nodes Split / Slice / Concat. Everything else of the reference compiler (2-D
-// layouts, pooling, RMSNorm, SwiGLU, RoPE/attention, deconvolution) is not part of this path; those
-// builder calls report failure and leave the graph unchanged.
+// Graph -> wave plan for the part of the reference's front end that 1-D token models need: Input, dense
+// linears (1x1 convolutions, optional residual), the zero-copy topology nodes Split / Slice / Concat, and
+// the element-wise / attention nodes of a decoder layer (RMSNorm with optional folding of its scale into the
+// consuming linears, SwiGLU product, rotary embedding + causal grouped-query attention). The 2-D part of the
+// reference compiler (image layouts, pooling, deconvolution) is not built; those builder calls report failure
+// and leave the graph unchanged.
 //
 // Rules reproduced (not code): batch>1 on a [C,1,1] input becomes the token axis
 // (wavec/k44_wave_compiler.hpp:78-83); padding of rows / fan-in and group-size choice
 // (wavec/k44_plan_types.hpp:157-186); canvas placement by liveness with best-fit reuse, 64-element
 // granularity and a final round-up to 128 (wavec/k44_wave_compiler.hpp:388-593); gather-table and
 // weight ordering of a 1x1 wave with zero-filled padding slots (:746-779); index rebasing when an
-// offset reaches 0x70000000 (:1061-1072); summary JSON keys (:1345-1405).
+// offset reaches 0x70000000 (:1061-1072); summary JSON keys (:1345-1405); RMSNorm scale folding: when every
+// consumer of a normalised tensor is a linear, column c of their weights is multiplied by gamma[c] and the
+// normaliser runs without a scale (:233-301).
 #pragma once
 #include <set>
 
@@ -18,7 +21,7 @@
 namespace k44b {
 
 struct GraphNode {
-    enum Kind { INPUT, LINEAR, SPLIT, SLICE, CONCAT } kind = INPUT;
+    enum Kind { INPUT, LINEAR, SPLIT, SLICE, CONCAT, RMSNORM, SWIGLU, ROPE_ATTN } kind = INPUT;
     std::string name;
     std::vector<std::string> ins, outs;
     std::string residual;
@@ -27,6 +30,11 @@ struct GraphNode {
     int act = ACT_NONE;
     std::vector<uint16_t> w_f16;      // [cout][cin]
     std::vector<uint16_t> bias_f16;   // [cout]
+    // RMSNorm: scale and epsilon; attention: head counts, rotary base
+    std::vector<float> gamma;
+    float eps = 1e-5f, rope_theta = 10000.0f;
+    bool pre_folded = false, llama3_scaling = false, gamma_folded = false;
+    uint32_t h_q = 0, h_kv = 0, head_dim = 0;
 };
 
 class WaveGraph {
@@ -80,6 +88,39 @@ class WaveGraph {
         return true;
     }
 
+    bool add_rmsnorm(const char *name, const char *in, const char *out, int dim, float eps, const float *gamma, int pre_folded) {
+        if (!name || !in || !out || dim <= 0) return fail("add_rmsnorm: bad arguments");
+        GraphNode n;
+        n.kind = GraphNode::RMSNORM; n.name = name; n.ins = {in}; n.outs = {out}; n.cin = n.cout = (uint32_t)dim; n.eps = eps;
+        n.pre_folded = pre_folded != 0;
+        if (gamma && !n.pre_folded) n.gamma.assign(gamma, gamma + dim);
+        nodes.push_back(std::move(n));
+        compiled = false;
+        return true;
+    }
+
+    bool add_swiglu(const char *name, const char *gate, const char *up, const char *out) {
+        if (!name || !gate || !up || !out) return fail("add_swiglu: bad arguments");
+        GraphNode n;
+        n.kind = GraphNode::SWIGLU; n.name = name; n.ins = {gate, up}; n.outs = {out};
+        nodes.push_back(std::move(n));
+        compiled = false;
+        return true;
+    }
+
+    bool add_rope_attn(const char *name, const char *q, const char *k, const char *v, const char *out, int h_q, int h_kv, int head_dim,
+                       float theta, int llama3) {
+        if (!name || !q || !k || !v || !out || h_q <= 0 || h_kv <= 0 || h_q % h_kv) return fail("add_rope_gqa_attn: bad arguments");
+        if (head_dim != 64 && head_dim != 128) return fail("add_rope_gqa_attn: head_dim must be 64 or 128");
+        GraphNode n;
+        n.kind = GraphNode::ROPE_ATTN; n.name = name; n.ins = {q, k, v}; n.outs = {out};
+        n.h_q = (uint32_t)h_q; n.h_kv = (uint32_t)h_kv; n.head_dim = (uint32_t)head_dim; n.rope_theta = theta; n.llama3_scaling = llama3 != 0;
+        n.cout = (uint32_t)(h_q * head_dim);
+        nodes.push_back(std::move(n));
+        compiled = false;
+        return true;
+    }
+
     bool compile() {
         plan = HostPlan();
         compiled = false;
@@ -124,8 +165,51 @@ class WaveGraph {
                 channels[n.outs[0]] = sum;
                 break;
             }
+            case GraphNode::RMSNORM:
+                if (!channels.count(n.ins[0])) return fail("compile: unknown tensor " + n.ins[0]);
+                if (channels[n.ins[0]] != n.cin) return fail("compile: " + n.name + " expects " + std::to_string(n.cin) + " channels");
+                channels[n.outs[0]] = n.cout;
+                break;
+            case GraphNode::SWIGLU:
+                if (!channels.count(n.ins[0]) || !channels.count(n.ins[1])) return fail("compile: unknown tensor at " + n.name);
+                if (channels[n.ins[0]] != channels[n.ins[1]]) return fail("compile: " + n.name + ": gate and up differ in size");
+                n.cin = n.cout = channels[n.ins[0]];
+                channels[n.outs[0]] = n.cout;
+                break;
+            case GraphNode::ROPE_ATTN:
+                for (auto &i : n.ins) if (!channels.count(i)) return fail("compile: unknown tensor " + i);
+                if (channels[n.ins[0]] != n.h_q * n.head_dim || channels[n.ins[1]] != n.h_kv * n.head_dim || channels[n.ins[2]] != n.h_kv * n.head_dim)
+                    return fail("compile: " + n.name + ": q / k / v channel counts do not match the head counts");
+                channels[n.outs[0]] = n.cout;
+                break;
             }
         }
+        // ---- RMSNorm scale folding ------------------------------------------------------------------
+        num_folded = 0;
+        for (size_t s = 0; s < nodes.size(); ++s) {
+            GraphNode &n = nodes[s];
+            if (n.kind != GraphNode::RMSNORM || n.gamma.empty() || n.gamma_folded || !fold_rmsnorm_gamma) continue;
+            bool ok = n.outs[0] != output_tensor;
+            std::vector<size_t> users;
+            for (size_t t = 0; t < nodes.size() && ok; ++t) {
+                if (t == s) continue;
+                const GraphNode &m = nodes[t];
+                if (m.residual == n.outs[0]) ok = false;
+                for (size_t k = 0; k < m.ins.size(); ++k)
+                    if (m.ins[k] == n.outs[0]) { if (m.kind == GraphNode::LINEAR && k == 0) users.push_back(t); else ok = false; }
+            }
+            if (!ok || users.empty()) continue;
+            for (size_t t : users) {
+                GraphNode &m = nodes[t];
+                for (uint32_t j = 0; j < m.cout; ++j)
+                    for (uint32_t c = 0; c < m.cin; ++c) {
+                        uint16_t &w = m.w_f16[(size_t)j * m.cin + c];
+                        w = float_to_half(half_to_float(w) * n.gamma[c]);
+                    }
+            }
+            n.gamma_folded = true;
+        }
+        for (auto &n : nodes) num_folded += (n.kind == GraphNode::RMSNORM && n.gamma_folded) ? 1 : 0;
         if (!channels.count(output_tensor)) {
             // default output = last produced tensor when "out0" was never defined
             output_tensor = nodes.back().outs[0];
@@ -143,7 +227,7 @@ class WaveGraph {
         std::vector<uint32_t> aid_rows;
         for (size_t s = 0; s < nodes.size(); ++s) {
             auto &n = nodes[s];
-            if (n.kind == GraphNode::INPUT || n.kind == GraphNode::LINEAR) {
+            if (produces(n.kind)) {
                 node_aid[s] = (int)aid_rows.size();
                 aid_rows.push_back(n.kind == GraphNode::LINEAR ? pad_cout(n.cout) : n.cout);
                 aliases[n.outs[0]] = {node_aid[s]};
@@ -216,10 +300,11 @@ class WaveGraph {
         std::map<std::string, std::vector<uint64_t>> rows_of;     // tensor -> canvas offset of every channel
         for (size_t s = 0; s < nodes.size(); ++s) {
             auto &n = nodes[s];
-            if (n.kind == GraphNode::INPUT || n.kind == GraphNode::LINEAR) {
+            if (produces(n.kind)) {
                 std::vector<uint64_t> r(n.cout);
                 for (uint32_t c = 0; c < n.cout; ++c) r[c] = aid_at[node_aid[s]] + (uint64_t)c * pitch;
                 if (n.kind == GraphNode::LINEAR && !emit_linear(n, rows_of, aid_at[node_aid[s]])) return false;
+                if (n.kind != GraphNode::LINEAR && n.kind != GraphNode::INPUT && !emit_aux(n, rows_of, aid_at[node_aid[s]])) return false;
                 rows_of[n.outs[0]] = std::move(r);
             } else if (n.kind == GraphNode::SPLIT) {
                 for (auto &o : n.outs) rows_of[o] = rows_of[n.ins[0]];
@@ -247,7 +332,43 @@ class WaveGraph {
     }
 
   private:
+    int num_folded = 0;
     bool fail(const std::string &m) { error = m; return false; }
+    static bool produces(GraphNode::Kind k) {
+        return k == GraphNode::INPUT || k == GraphNode::LINEAR || k == GraphNode::RMSNORM || k == GraphNode::SWIGLU || k == GraphNode::ROPE_ATTN;
+    }
+    // operands of the element-wise / attention kernels must be whole tensors: consecutive rows, `pitch` apart
+    bool contiguous(const std::vector<uint64_t> &rows, uint32_t n) const {
+        if (rows.size() < n) return false;
+        for (uint32_t c = 1; c < n; ++c) if (rows[c] != rows[0] + (uint64_t)c * plan.layout.channel_stride) return false;
+        return true;
+    }
+
+    bool emit_aux(GraphNode &n, std::map<std::string, std::vector<uint64_t>> &rows_of, uint64_t dst) {
+        HostWave w;
+        w.name = n.name; w.y_off = dst; w.cout = w.logical_cout = n.cout; w.cin = n.cin;
+        w.h_out = 1; w.w_out = plan.layout.width;
+        for (auto &i : n.ins)
+            if (!contiguous(rows_of[i], (uint32_t)rows_of[i].size())) return fail("compile: " + n.name + " reads a tensor that is not stored as consecutive rows");
+        w.src_off = rows_of[n.ins[0]][0];
+        switch (n.kind) {
+        case GraphNode::RMSNORM:
+            w.kind = 1; w.eps = n.eps;
+            if (!n.gamma.empty() && !n.gamma_folded) { w.bias.resize(n.cout); for (uint32_t c = 0; c < n.cout; ++c) w.bias[c] = float_to_half(n.gamma[c]); }
+            break;
+        case GraphNode::SWIGLU:
+            w.kind = 2; w.src2_off = rows_of[n.ins[1]][0];
+            break;
+        case GraphNode::ROPE_ATTN:
+            w.kind = 3; w.src2_off = rows_of[n.ins[1]][0]; w.src3_off = rows_of[n.ins[2]][0];
+            w.h_q = n.h_q; w.h_kv = n.h_kv; w.head_dim = n.head_dim; w.rope_theta = n.rope_theta; w.llama3_scaling = n.llama3_scaling;
+            w.seq_len = plan.layout.single_stride;          // one sequence per frame of the 1-D layout
+            break;
+        default: return fail("compile: unexpected node kind");
+        }
+        plan.waves.push_back(std::move(w));
+        return true;
+    }
 
     bool emit_linear(GraphNode &n, std::map<std::string, std::vector<uint64_t>> &rows_of, uint64_t dst) {
         const uint32_t pitch = plan.layout.channel_stride;
@@ -297,30 +418,37 @@ class WaveGraph {
                       "{\n  \"batch_size\": %u,\n  \"num_waves\": %zu,\n  \"num_cmds\": %zu,\n  \"canvas_elems\": %llu,\n"
                       "  \"canvas_bytes\": %llu,\n  \"kv_cache_elems\": 0,\n  \"total_w_bytes\": %llu,\n  \"total_idx_bytes\": %llu,\n"
                       "  \"single_frame_gflops\": %.6g,\n  \"total_gflops\": %.6g,\n  \"single_frame_gsyn\": %.6g,\n  \"total_gsyn\": %.6g,\n"
-                      "  \"num_folded_rmsnorms\": 0,\n  \"num_eliminated_concats\": %d,\n  \"num_eliminated_splits\": %d,\n"
+                      "  \"num_folded_rmsnorms\": %d,\n  \"num_eliminated_concats\": %d,\n  \"num_eliminated_splits\": %d,\n"
                       "  \"num_zero_copy_flattens\": 0,\n  \"input_shape\": [%u, %u, %u],\n  \"output_shape\": [%u, %u, %u],\n"
                       "  \"max_B_per_wave\": %u,\n  \"target_profile\": \"%s\",\n  \"target_num_cus\": %u,\n"
                       "  \"persistent_neurons\": %s,\n  \"reuse_canvas\": %s,\n  \"cmds\": [\n",
-                      plan.batch_size, plan.waves.size(), plan.waves.size(), (unsigned long long)plan.canvas_elems,
+                      plan.batch_size, num_wave_cmds(), plan.waves.size(), (unsigned long long)plan.canvas_elems,
                       (unsigned long long)(plan.canvas_elems * 2ull), (unsigned long long)plan.total_w_bytes,
                       (unsigned long long)plan.total_idx_bytes, plan.single_frame_gflops, plan.total_gflops,
-                      plan.single_frame_gflops * 0.5, plan.total_gflops * 0.5, count(GraphNode::CONCAT),
+                      plan.single_frame_gflops * 0.5, plan.total_gflops * 0.5, num_folded, count(GraphNode::CONCAT),
                       count(GraphNode::SPLIT) + count(GraphNode::SLICE), plan.input_c, plan.input_h, plan.input_w,
                       plan.logical_output_c, plan.output_h, plan.output_w, max_b_per_wave, plan.target.name.c_str(),
                       plan.target.num_units, reuse_canvas ? "false" : "true", reuse_canvas ? "true" : "false");
         summary_json = buf;
         for (size_t i = 0; i < plan.waves.size(); ++i) {
             const HostWave &w = plan.waves[i];
+            static const char *types[] = {"K44_WAVE", "RMSNORM", "SWIGLU", "ROPE_GQA_ATTN", "DECODE_GQA_ATTN"};
             std::snprintf(buf, sizeof buf,
-                          "    {\"idx\": %zu, \"name\": \"%s\", \"type\": \"K44_WAVE\", \"Cin\": %u, \"Cout\": %u, \"logical_Cout\": %u, "
+                          "    {\"idx\": %zu, \"name\": \"%s\", \"type\": \"%s\", \"Cin\": %u, \"Cout\": %u, \"logical_Cout\": %u, "
                           "\"B\": %u, \"B_raw\": %u, \"S\": %u, \"act\": \"%s\", \"has_residual\": %s, \"has_self_read\": false, "
                           "\"subwave\": [0, 1], \"h_out\": %u, \"w_out\": %u, \"src_off\": %llu, \"y_off\": %llu, \"gflops\": %.6g}%s\n",
-                          i, w.name.c_str(), w.cin, w.cout, w.logical_cout, w.fan_in, w.fan_in_raw, w.group, act_name(w.act),
+                          i, w.name.c_str(), types[w.kind >= 0 && w.kind <= 4 ? w.kind : 0], w.cin, w.cout, w.logical_cout, w.fan_in, w.fan_in_raw, w.group, act_name(w.act),
                           w.has_residual ? "true" : "false", w.h_out, w.w_out, (unsigned long long)w.src_off,
                           (unsigned long long)w.y_off, w.gflops, i + 1 < plan.waves.size() ? "," : "");
             summary_json += buf;
         }
         summary_json += "  ]\n}\n";
+    }
+
+    size_t num_wave_cmds() const {
+        size_t c = 0;
+        for (auto &w : plan.waves) c += w.kind == 0;
+        return c;
     }
 
     int count(GraphNode::Kind k) const {

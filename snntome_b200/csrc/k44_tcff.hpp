@@ -72,9 +72,13 @@ inline bool tcff_serialize(const HostPlan &plan, const char *prefix, bool includ
                            std::vector<uint8_t> &out_bytes, std::string &err) {
     using namespace tcff;
     const char *pfx = (prefix && prefix[0]) ? prefix : "K44Model";
-    const uint32_t nw = (uint32_t)plan.waves.size();
+    // only waves have pages; element-wise / attention commands carry no tensors worth storing (an RMSNorm scale that
+    // was not folded into the next waves stays with the graph)
+    std::vector<const HostWave *> ws;
+    for (const auto &w : plan.waves) if (w.kind == 0) ws.push_back(&w);
+    const uint32_t nw = (uint32_t)ws.size();
     uint64_t need = 4096;
-    for (const auto &w : plan.waves) need += (uint64_t)w.cout * w.fan_in * 2 + w.idx.size() * 4 + w.cout * 2 + 4096;
+    for (const HostWave *w : ws) need += (uint64_t)w->cout * w->fan_in * 2 + w->idx.size() * 4 + w->cout * 2 + 4096;
     if (need >= 0xffffffffull) { err = "plan too large for a TCFFv1.0 file (32-bit offsets)"; return false; }
     Out o;
     o.b.reserve((size_t)need);
@@ -85,7 +89,7 @@ inline bool tcff_serialize(const HostPlan &plan, const char *prefix, bool includ
     o.align(ALIGN);
     size_t link = 4;
     for (uint32_t wi = 0; wi < nw; ++wi) {
-        const HostWave &w = plan.waves[wi];
+        const HostWave &w = *ws[wi];
         if (w.w_wmma.size() != (size_t)w.cout * w.fan_in) { err = "wave " + w.name + " has no host weights"; return false; }
         const uint32_t start = o.pos();
         const uint32_t w_off = o.pos(), w_bytes = (uint32_t)(w.w_wmma.size() * 2);
@@ -223,10 +227,12 @@ inline bool tcff_load_into(HostPlan &plan, const char *path, std::string &err) {
     std::vector<uint8_t> buf;
     TcffView view;
     if (!tcff::slurp(path, buf, err) || !tcff_parse(buf, view, err)) return false;
-    if (view.waves.size() < plan.waves.size()) { err = "file has fewer wave pages than the plan"; return false; }
+    std::vector<HostWave *> ws;
+    for (auto &w : plan.waves) if (w.kind == 0) ws.push_back(&w);
+    if (view.waves.size() < ws.size()) { err = "file has fewer wave pages than the plan"; return false; }
     const bool take_idx = plan.batch_size == 1u && plan.canvas_elems * 2ull == (uint64_t)view.canvas_bytes;
-    for (size_t i = 0; i < plan.waves.size(); ++i) {
-        HostWave &w = plan.waves[i];
+    for (size_t i = 0; i < ws.size(); ++i) {
+        HostWave &w = *ws[i];
         const auto &a = view.waves[i].aux;
         const size_t want_w = (size_t)w.cout * w.fan_in * 2;
         w.w_wmma.assign(std::max(want_w, (size_t)a[1]) / 2, 0);

@@ -154,7 +154,9 @@ def test_unsupported_nodes_are_refused():
         g.add_input("img", 3, 32, 32)
     g.add_input("x", 64, 1, 1, is_1d=True)
     with pytest.raises(WaveError, match="not part of the wave path"):
-        g.add_rmsnorm("n", "x", "y", 64, np.ones(64))
+        g.add_maxpool("p", "x", "y")
+    with pytest.raises(WaveError, match="head_dim"):
+        g.add_rope_gqa_attn("a", "x", "x", "x", "y", 2, 1, 32)
     with pytest.raises(WaveError):
         g.add_conv2d("c", "x", "y", 64, 64, 3, 3, np.zeros((64, 64, 3, 3)), pad=1)
     with pytest.raises(WaveError):
