@@ -187,10 +187,13 @@ def cpu_baseline(w: dict, seconds_target: float = 15.0, threads: int | None = No
 DECODER = dict(hidden=2048, layers=16, heads=32, kv_heads=8, head_dim=64, ffn=8192, vocab=128256, columns=64)
 
 
-def build_decoder_plan(cfg: dict, device: int, seed: int = 7):
-    """Every linear of the decoder is one wave whose neurons gather the full input width (one run). Only the
-    wave chain is built: attention, RMSNorm, RoPE and the SwiGLU product are not waves, so `o` reads the q rows
-    and `down` reads the gate rows as stand-ins of the same shape. Weights N(0, 0.01^2) generated on the device."""
+def build_decoder_plan(cfg: dict, device: int, seed: int = 7, full: bool = False, ctx: int = 512):
+    """Every linear of the decoder is one wave whose neurons gather the full input width (one run). Weights
+    N(0, 0.01^2) generated on the device. With full=False only the wave chain is built (`o` reads the q rows and
+    `down` the gate rows as stand-ins of the same shape); with full=True the element-wise and attention commands
+    sit between the waves as in the model: RMSNorm (scale 1, folded) before q/k/v and before the MLP, rotary
+    embedding + attention of the new token against a key / value cache of `ctx` positions per sequence (filled
+    with N(0,1), the new token written at the last position), SwiGLU product, final RMSNorm."""
     import torch
     from snntome_b200._lib import WaveDesc
     from snntome_b200.native import NativePlan, fill_normal_f16
@@ -199,7 +202,10 @@ def build_decoder_plan(cfg: dict, device: int, seed: int = 7):
     pitch = 64
     rows = {}
     cur = 0
-    for name, n in [("x0", H), ("x1", H), ("q", H), ("k", KV), ("v", KV), ("h", H), ("g", F), ("u", F), ("logits", V)]:
+    names = [("x0", H), ("x1", H), ("q", H), ("k", KV), ("v", KV), ("h", H), ("g", F), ("u", F), ("logits", V)]
+    if full:
+        names += [("n", H), ("att", H), ("f", F)] + [(f"{c}cache{l}", KV * ctx) for l in range(cfg["layers"]) for c in "kv"]
+    for name, n in names:
         rows[name] = cur
         cur += n
     plan = NativePlan.create(cur * pitch, pitch, cfg["columns"], device=device)
@@ -229,16 +235,36 @@ def build_decoder_plan(cfg: dict, device: int, seed: int = 7):
         params += cout * cin
 
     x_in, x_out = "x0", "x1"
+    off = lambda name: rows[name] * pitch
     for layer in range(cfg["layers"]):
-        add(f"L{layer}.q", x_in, "q", H, H)
-        add(f"L{layer}.k", x_in, "k", H, KV)
-        add(f"L{layer}.v", x_in, "v", H, KV)
-        add(f"L{layer}.o", "q", "h", H, H, res=x_in)
-        add(f"L{layer}.gate", "h", "g", H, F, act=3)
-        add(f"L{layer}.up", "h", "u", H, F)
-        add(f"L{layer}.down", "g", x_out, F, H, res="h")
+        if full:
+            plan.add_rmsnorm(off(x_in), off("n"), H, 1e-5, None, name=f"L{layer}.norm1")
+        src = "n" if full else x_in
+        add(f"L{layer}.q", src, "q", H, H)
+        add(f"L{layer}.k", src, "k", H, KV)
+        add(f"L{layer}.v", src, "v", H, KV)
+        if full:
+            plan.add_decode_attn(off("q"), off("k"), off("v"), off("att"), off(f"kcache{layer}"), off(f"vcache{layer}"), cfg["heads"],
+                                 cfg["kv_heads"], cfg["head_dim"], ctx, 500000.0, True, name=f"L{layer}.attn")
+        add(f"L{layer}.o", "att" if full else "q", "h", H, H, res=x_in)
+        if full:
+            plan.add_rmsnorm(off("h"), off("n"), H, 1e-5, None, name=f"L{layer}.norm2")
+        src = "n" if full else "h"
+        add(f"L{layer}.gate", src, "g", H, F, act=3)
+        add(f"L{layer}.up", src, "u", H, F)
+        if full:
+            plan.add_swiglu(off("g"), off("u"), off("f"), F, name=f"L{layer}.swiglu")
+        add(f"L{layer}.down", "f" if full else "g", x_out, F, H, res="h")
         x_in, x_out = x_out, x_in
-    add("lm_head", x_in, "logits", H, V)
+    if full:
+        plan.add_rmsnorm(off(x_in), off("n"), H, 1e-5, None, name="final_norm")
+    add("lm_head", "n" if full else x_in, "logits", H, V)
+    if full:
+        canvas = plan.canvas_tensor()
+        c0 = off("kcache0")
+        fill_normal_f16(canvas[c0: c0 + 2 * cfg["layers"] * KV * ctx * pitch], seed * 31 + 5, 1.0)
+        plan.set_decode_pos(ctx - 1)
+        torch.cuda.synchronize()
     del scratch
     torch.cuda.empty_cache()
     plan.set_io(0, H, rows["logits"] * pitch, V, cfg["columns"])
@@ -258,8 +284,10 @@ def decode_main(args) -> None:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     cfg = dict(DECODER, layers=args.layers)
+    full = args.workload == "decode-full"
+    ctx = 512
     from snntome_b200.native import fill_normal_f16
-    plan, params, rows = build_decoder_plan(cfg, local_rank)
+    plan, params, rows = build_decoder_plan(cfg, local_rank, full=full, ctx=ctx)
     canvas = plan.canvas_tensor()
     fill_normal_f16(canvas[: cfg["hidden"] * 64], 99 + rank, 1.0)
     torch.cuda.synchronize()
@@ -303,22 +331,25 @@ def decode_main(args) -> None:
     wave_us = [ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(nw)]
     clocks = sampler.stop()
     peak, kind = measured_peaks()
-    bytes_step = params * 2.0
+    kv_bytes = 2.0 * cfg["layers"] * cfg["kv_heads"] * cfg["head_dim"] * ctx * 64 * 2 if full else 0.0      # K and V of every layer, read once
+    bytes_step = params * 2.0 + kv_bytes
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
     infos = [plan.wave_info(i) for i in range(nw)]
     if rank == 0:
-        line = {"metric": "decode tok/s (wave chain of a 1B dense decoder, batch 64 per GPU)", "value": cfg["columns"] * world / (ms_step * 1e-3),
+        line = {"metric": ("decode tok/s (1B dense decoder, whole layer stack with attention over a 512-position cache, batch 64 per GPU)" if full else
+                           "decode tok/s (wave chain of a 1B dense decoder, batch 64 per GPU)"), "value": cfg["columns"] * world / (ms_step * 1e-3),
                 "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
                 "config": {"workload": "dense decoder as waves: hidden 2048, 32/8 heads x 64, FFN 8192, vocab 128256, one wave per linear, "
-                                       "64 columns per GPU; wave chain only (no attention / norm / rope kernels)",
-                           "layers": cfg["layers"], "waves_per_step": nw, "params": params, "launch": "one CUDA graph per step",
+                                       "64 columns per GPU; " + ("RMSNorm, rotary + attention against a key/value cache of 512 positions per sequence, SwiGLU product between the waves"
+                                                                 if full else "wave chain only (no attention / norm / rope kernels)"),
+                           "layers": cfg["layers"], "commands_per_step": nw, "params": params, "kv_cache_bytes_read_per_step": kv_bytes, "launch": "one CUDA graph per step",
                            "l2_policy": "2.47 GB of weights per step exceed the 126 MB L2; no explicit flush"},
                 "roofline": {"bound": "hbm", "kernel": "whole step (k44_wave_umma_kernel<64> small-wave and streaming variants)", "achieved": achieved,
                              "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s", "frac": achieved / peak, "algorithmic_bytes_per_step": bytes_step,
                              "traffic": None},
-                "per_wave_us_direct_launch": {"layer0": wave_us[:7], "lm_head": wave_us[-1], "sum": sum(wave_us)},
-                "k_splits": {"layer0": [i.k_splits for i in infos[:7]], "lm_head": infos[-1].k_splits},
+                "per_wave_us_direct_launch": {"layer0": wave_us[:12 if full else 7], "lm_head": wave_us[-1], "sum": sum(wave_us)},
+                "k_splits": {"layer0": [i.k_splits for i in infos[:12 if full else 7]], "lm_head": infos[-1].k_splits},
                 "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks}
         print(json.dumps(line))
     if dist is not None:
@@ -638,13 +669,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", type=float, default=float(os.environ.get("K44B_BENCH_SCALE", "1.0")))
-    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "pruned-sharded", "token-shift"])
+    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "decode-full", "pruned-sharded", "token-shift"])
     ap.add_argument("--layers", type=int, default=16, help="decode workload: decoder layers (16 = the 1B shape)")
     ap.add_argument("--max-shift", type=int, default=7, help="token-shift workload: largest token shift drawn per run (0 = unshifted runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
-    if args.workload == "decode":
+    if args.workload in ("decode", "decode-full"):
         return decode_main(args)
     if args.workload == "pruned-sharded":
         return sharded_main(args)

@@ -97,7 +97,8 @@ int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, in
  * every column attends causally to the columns of its own sequence (blocks of seq_len columns, seq_len % 32 == 0).
  * head_dim 64 or 128. add_decode_attn has no counterpart in the reference (which reserves a key / value cache but never
  * reads it): one new token per column at the position set by k44b_plan_set_decode_pos — q and k are rotated at that
- * position, k and v are appended to the caches (channel-major [h_kv*head_dim][max_seq][pitch] regions of the canvas) and
+ * position, k and v are appended to the caches ([h_kv][max_seq][pitch][head_dim] regions of the canvas: the head_dim values of
+ * one head, position and column are contiguous) and
  * the column attends to cache positions 0..pos. The position lives in device memory, so a captured graph can be replayed
  * for every position. */
 int k44b_plan_add_rmsnorm(void *plan, const char *name, uint64_t src_off, uint64_t dst_off, uint32_t dim, float eps, const uint16_t *gamma_f16);

@@ -99,17 +99,20 @@ def causal_attention(canvas, q_off, k_off, v_off, out_off, h_q, h_kv, head_dim, 
 def decode_attention(canvas, q_off, k_off, v_off, out_off, kc_off, vc_off, h_q, h_kv, head_dim, pitch, max_seq, pos,
                      theta=10000.0, llama3=False):
     """One new token per column at position `pos`: rotary on q and k at that position, k and v appended to the
-    caches (channel-major [h_kv*head_dim][max_seq][pitch]), attention over cache positions 0..pos."""
+    caches ([h_kv][max_seq][pitch][head_dim]: one head, position and column is one contiguous row), attention over
+    cache positions 0..pos."""
     rope(canvas, q_off, h_q, head_dim, pitch, 1, theta, llama3, positions=np.full(pitch, pos))
     rope(canvas, k_off, h_kv, head_dim, pitch, 1, theta, llama3, positions=np.full(pitch, pos))
     ckv = h_kv * head_dim
-    kc = canvas[kc_off: kc_off + ckv * max_seq * pitch].reshape(ckv, max_seq, pitch)
-    vc = canvas[vc_off: vc_off + ckv * max_seq * pitch].reshape(ckv, max_seq, pitch)
-    kc[:, pos, :] = canvas[k_off: k_off + ckv * pitch].reshape(ckv, pitch)
-    vc[:, pos, :] = canvas[v_off: v_off + ckv * pitch].reshape(ckv, pitch)
+    n = h_kv * max_seq * pitch * head_dim
+    kc = canvas[kc_off: kc_off + n].reshape(h_kv, max_seq, pitch, head_dim)
+    vc = canvas[vc_off: vc_off + n].reshape(h_kv, max_seq, pitch, head_dim)
+    kc[:, pos] = canvas[k_off: k_off + ckv * pitch].reshape(h_kv, head_dim, pitch).transpose(0, 2, 1)
+    vc[:, pos] = canvas[v_off: v_off + ckv * pitch].reshape(h_kv, head_dim, pitch).transpose(0, 2, 1)
     q = _rows(canvas, q_off, h_q * head_dim, pitch).astype(np.float64)
-    K = kc[:, :pos + 1, :].view(np.float16).astype(np.float64)           # [ckv, pos+1, pitch]
-    V = vc[:, :pos + 1, :].view(np.float16).astype(np.float64)
+    # [h_kv, positions, pitch, hd] -> [h_kv*hd, positions, pitch]
+    K = kc[:, :pos + 1].view(np.float16).astype(np.float64).transpose(0, 3, 1, 2).reshape(ckv, pos + 1, pitch)
+    V = vc[:, :pos + 1].view(np.float16).astype(np.float64).transpose(0, 3, 1, 2).reshape(ckv, pos + 1, pitch)
     out = np.zeros((h_q * head_dim, pitch))
     grp = h_q // h_kv
     scale = 1.0 / np.sqrt(head_dim)

@@ -298,9 +298,9 @@ bool Executor::add_aux(const HostWave &w) {
         } else {
             if (!w.max_seq || w.kcache_off % 8u || w.vcache_off % 8u || w.kcache_off + rk * w.max_seq * pitch_ > canvas_elems_ ||
                 w.vcache_off + rk * w.max_seq * pitch_ > canvas_elems_) return fail("attention '" + w.name + "': key / value cache leaves the canvas");
-            if (w.head_dim != 64u || w.h_q / w.h_kv > 8u) return fail("attention '" + w.name + "': the cache kernel supports head_dim 64 and up to 8 query heads per key / value head");
+            { const uint32_t grp = w.h_q / w.h_kv; if (w.head_dim != 64u || !(grp == 1u || grp == 2u || grp == 4u || grp == 8u)) return fail("attention '" + w.name + "': the cache kernel supports head_dim 64 and 1, 2, 4 or 8 query heads per key / value head"); }
             if (!(x.pos_ptr = decode_pos_ptr())) return false;
-            const size_t pbytes = (size_t)((w.max_seq + kDecodeChunk - 1u) / kDecodeChunk) * w.h_q * 66u * pitch_ * sizeof(float);
+            const size_t pbytes = (size_t)((w.max_seq + kDecodeChunk - 1u) / kDecodeChunk) * w.h_q * kDecodeRow * pitch_ * sizeof(float);
             if (pbytes > decode_partial_bytes_) {
                 if (!check(cudaDeviceSynchronize(), "synchronise")) return false;
                 cudaFree(d_decode_partial_); d_decode_partial_ = nullptr; decode_partial_bytes_ = 0;
@@ -612,7 +612,7 @@ bool Executor::launch_group(size_t gi, cudaStream_t stream) {
 bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
     cudaError_t e;
     if (w.is_aux) {
-        launches_ += w.aux.kind == AUX_ROPE_ATTN ? 3u : (w.aux.kind == AUX_DECODE_ATTN ? 4u : 1u);
+        launches_ += w.aux.kind == AUX_ROPE_ATTN ? 3u : (w.aux.kind == AUX_DECODE_ATTN ? 3u : 1u);
         return check(launch_aux(w.aux, stream), ("launch of '" + w.name + "'").c_str());
     }
     if (w.path == PATH_UMMA && w.use_cluster) {

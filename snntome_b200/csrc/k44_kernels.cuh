@@ -95,16 +95,17 @@ struct AuxArgs {
     int kind = AUX_NONE;
     __half *canvas = nullptr;
     uint64_t src_off = 0, src2_off = 0, src3_off = 0, dst_off = 0;    // x | gate, up | q, k, v
-    uint64_t kcache_off = 0, vcache_off = 0;                         // decode attention: [h_kv*head_dim][max_seq][pitch]
+    uint64_t kcache_off = 0, vcache_off = 0;                         // decode attention: [h_kv][max_seq][pitch][head_dim]
     uint32_t rows = 0, pitch = 0, columns = 0;
     float eps = 1e-5f;
     const __half *gamma = nullptr;                                   // device, [rows] or null
     uint32_t h_q = 0, h_kv = 0, head_dim = 0, seq_len = 0, max_seq = 0, llama3 = 0;
     float neg_log_theta = -9.210340371976184f;
     const int *pos_ptr = nullptr;                                    // decode: current position, device memory
-    float *partial = nullptr;                                        // decode: per-chunk partial results [chunks][h_q][66][pitch]
+    float *partial = nullptr;                                        // decode: per-chunk partial results [chunks][h_q][pitch][kDecodeRow]
 };
-constexpr uint32_t kDecodeChunk = 64;                                // cache positions per partial-attention CTA
+constexpr uint32_t kDecodeChunk = 32;
+constexpr uint32_t kDecodeRow = 68;                                  // floats per partial result: 64 values, maximum, sum, 2 pad (16-byte aligned rows)                                // cache positions per partial-attention CTA
 cudaError_t launch_aux(const AuxArgs &a, cudaStream_t s);
 
 // Up to four mutually independent small waves launched as one grid (their clusters are numbered consecutively).

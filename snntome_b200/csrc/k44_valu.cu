@@ -183,115 +183,136 @@ __global__ void __launch_bounds__(128) k44_valu_causal_attn_kernel(const AuxArgs
 }
 
 // ---- decode attention against a key / value cache ---------------------------------------------------------------------
-// Cache layout (both K and V): channel-major [h_kv*head_dim][max_seq][pitch] FP16, i.e. for a fixed channel and position the
-// columns (sequences) are contiguous. One new token per column at position *pos_ptr.
+// Cache layout (both K and V): [h_kv][max_seq][pitch][head_dim] FP16 — the head_dim values of one (head, position, column)
+// are contiguous (128 bytes for head_dim 64), so the thread that owns a column reads its key / value row with 16-byte
+// loads straight from global memory; no staging, no barrier. One new token per column at position *pos_ptr.
 
-// rotate k in place at the current position and append k and v to the caches; one thread per (channel pair, 8 columns)
-__global__ void __launch_bounds__(256) k44_valu_rope_k_append_kernel(const AuxArgs a) {
-    const uint32_t half = a.head_dim / 2u, groups = a.pitch / 8u;
-    const uint64_t total = (uint64_t)a.h_kv * half * groups;
+// Rotate q and k in place at the current position and append k and v to the caches: one thread per (head, rotation
+// pair, column); the first h_q heads are the query heads, the rest the key heads.
+__global__ void __launch_bounds__(256) k44_valu_decode_rope_append_kernel(const AuxArgs a) {
+    const uint32_t half = a.head_dim / 2u;
+    const uint64_t total = (uint64_t)(a.h_q + a.h_kv) * half * a.pitch;
     const uint64_t i = (uint64_t)blockIdx.x * 256u + threadIdx.x;
     if (i >= total) return;
-    const uint32_t cg = (uint32_t)(i % groups);
-    const uint32_t p = (uint32_t)((i / groups) % half), h = (uint32_t)(i / ((uint64_t)groups * half));
-    const uint32_t c0 = h * a.head_dim + p, c1 = c0 + half;
+    const uint32_t col = (uint32_t)(i % a.pitch);
+    const uint32_t p = (uint32_t)((i / a.pitch) % half);
+    uint32_t h = (uint32_t)(i / ((uint64_t)a.pitch * half));
     const int pos = *a.pos_ptr;
     if (pos < 0 || (uint32_t)pos >= a.max_seq) return;
-    __half *k0 = a.canvas + a.src2_off + (uint64_t)c0 * a.pitch + cg * 8u, *k1 = a.canvas + a.src2_off + (uint64_t)c1 * a.pitch + cg * 8u;
-    const float f = rope_inv_freq(p, a.head_dim, a.neg_log_theta, a.llama3 != 0u);
-    float s, c, x0[8], x1[8];
-    sincosf((float)pos * f, &s, &c);
-    unpack8(*reinterpret_cast<const uint4 *>(k0), x0);
-    unpack8(*reinterpret_cast<const uint4 *>(k1), x1);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { const float y0 = x0[k] * c - x1[k] * s, y1 = x0[k] * s + x1[k] * c; x0[k] = y0; x1[k] = y1; }
-    const uint4 r0 = pack8(x0), r1 = pack8(x1);
-    *reinterpret_cast<uint4 *>(k0) = r0;
-    *reinterpret_cast<uint4 *>(k1) = r1;
-    const uint64_t ch_stride = (uint64_t)a.max_seq * a.pitch, at = (uint64_t)pos * a.pitch + cg * 8u;
-    *reinterpret_cast<uint4 *>(a.canvas + a.kcache_off + c0 * ch_stride + at) = r0;
-    *reinterpret_cast<uint4 *>(a.canvas + a.kcache_off + c1 * ch_stride + at) = r1;
-    *reinterpret_cast<uint4 *>(a.canvas + a.vcache_off + c0 * ch_stride + at) = *reinterpret_cast<const uint4 *>(a.canvas + a.src3_off + (uint64_t)c0 * a.pitch + cg * 8u);
-    *reinterpret_cast<uint4 *>(a.canvas + a.vcache_off + c1 * ch_stride + at) = *reinterpret_cast<const uint4 *>(a.canvas + a.src3_off + (uint64_t)c1 * a.pitch + cg * 8u);
+    const bool is_q = h < a.h_q;
+    if (!is_q) h -= a.h_q;
+    const uint32_t c0 = h * a.head_dim + p, c1 = c0 + half;
+    const uint64_t base = is_q ? a.src_off : a.src2_off;
+    __half *r0 = a.canvas + base + (uint64_t)c0 * a.pitch + col, *r1 = a.canvas + base + (uint64_t)c1 * a.pitch + col;
+    float s, c;
+    sincosf((float)pos * rope_inv_freq(p, a.head_dim, a.neg_log_theta, a.llama3 != 0u), &s, &c);
+    const float x0 = __half2float(*r0), x1 = __half2float(*r1);
+    const __half y0 = __float2half_rn(x0 * c - x1 * s), y1 = __float2half_rn(x0 * s + x1 * c);
+    *r0 = y0; *r1 = y1;
+    if (is_q) return;
+    const uint64_t row = (((uint64_t)h * a.max_seq + (uint32_t)pos) * a.pitch + col) * a.head_dim;
+    a.canvas[a.kcache_off + row + p] = y0;
+    a.canvas[a.kcache_off + row + p + half] = y1;
+    a.canvas[a.vcache_off + row + p] = a.canvas[a.src3_off + (uint64_t)c0 * a.pitch + col];
+    a.canvas[a.vcache_off + row + p + half] = a.canvas[a.src3_off + (uint64_t)c1 * a.pitch + col];
 }
 
-// Partial attention of one chunk of kDecChunk cache positions: CTA = (32 columns, one key/value head, one chunk); thread =
-// (column, query head of the group). Key and value rows of 4 positions at a time are staged in shared memory as
-// [position][dimension][column]; every thread keeps its query and its accumulator (64 dimensions) in registers.
-// Output per (chunk, query head): the unnormalised accumulator, the running maximum and the sum, FP32, [..][66][pitch].
-constexpr uint32_t kDecChunk = 64, kDecTP = 4;
-__global__ void __launch_bounds__(256) k44_valu_decode_attn_partial_kernel(const AuxArgs a, float *partial) {
-    constexpr uint32_t HD = 64;
-    __shared__ __align__(16) __half sk[kDecTP][HD][32];
-    __shared__ __align__(16) __half sv[kDecTP][HD][32];
+// Partial attention of one chunk of kDecodeChunk cache positions. CTA = 128 threads = 16 columns of one key/value head and
+// one chunk; 8 lanes share a column, each owning 8 of the 64 dimensions, so that one warp instruction reads the key (or
+// value) rows of 4 columns as 512 contiguous bytes. Every lane serves all query heads of the group (the key / value row is
+// loaded once for them); dot products are reduced over the 8 lanes by shuffles. Four positions are in flight per lane.
+// Output per (chunk, query head, column): 64 unnormalised accumulator values, the running maximum and the sum, FP32,
+// [chunk][h_q][pitch][kDecodeRow] (rows of 68 floats: 16-byte aligned for the vector accesses).
+template <int G>
+__global__ void __launch_bounds__(128) k44_valu_decode_attn_partial_kernel(const AuxArgs a, float *partial) {
+    constexpr uint32_t HD = 64, UNROLL = 4;
     const uint32_t cb = blockIdx.x, hkv = blockIdx.y, chunk = blockIdx.z;
-    const uint32_t group = a.h_q / a.h_kv, nthreads = 32u * group;
-    const uint32_t tid = threadIdx.x, b = tid & 31u, hl = tid >> 5, hq = hkv * group + hl;
+    const uint32_t tid = threadIdx.x, j = tid & 7u, col = cb * 16u + (tid >> 3);
     const int pos = *a.pos_ptr;
-    const uint32_t p_begin = chunk * kDecChunk;
+    const uint32_t p_begin = chunk * kDecodeChunk;
     if (pos < 0 || p_begin > (uint32_t)pos) return;                      // nothing cached in this chunk yet (uniform per CTA)
-    const uint32_t p_end = min(p_begin + kDecChunk, (uint32_t)pos + 1u);
-    const uint32_t col = cb * 32u + b;
+    const uint32_t p_end = min(p_begin + kDecodeChunk, (uint32_t)pos + 1u);
     const float scale = rsqrtf((float)HD);
-    float q[HD], acc[HD];
-    const __half *qh = a.canvas + a.src_off + (uint64_t)hq * HD * a.pitch + col;
+    float q[G][8], acc[G][8], m[G], l[G];
 #pragma unroll
-    for (uint32_t d = 0; d < HD; ++d) { q[d] = __half2float(qh[(uint64_t)d * a.pitch]) * scale; acc[d] = 0.f; }
-    float m = -65504.0f, l = 0.f;
-    const uint64_t ch_stride = (uint64_t)a.max_seq * a.pitch;
-    const __half *kc = a.canvas + a.kcache_off + (uint64_t)hkv * HD * ch_stride + cb * 32u;
-    const __half *vc = a.canvas + a.vcache_off + (uint64_t)hkv * HD * ch_stride + cb * 32u;
-    for (uint32_t p0 = p_begin; p0 < p_end; p0 += kDecTP) {
-        // 4 positions x 64 dimensions x 4 pieces of 8 columns = 1024 16-byte pieces per tile
-        for (uint32_t e = tid; e < kDecTP * HD * 4u; e += nthreads) {
-            const uint32_t piece = e & 3u, d = (e >> 2) & (HD - 1u), tp = e >> 8;
-            const uint32_t p = min(p0 + tp, p_end - 1u);
-            const uint64_t off = (uint64_t)d * ch_stride + (uint64_t)p * a.pitch + piece * 8u;
-            *reinterpret_cast<uint4 *>(&sk[tp][d][piece * 8u]) = *reinterpret_cast<const uint4 *>(kc + off);
-            *reinterpret_cast<uint4 *>(&sv[tp][d][piece * 8u]) = *reinterpret_cast<const uint4 *>(vc + off);
-        }
-        __syncthreads();
-        const uint32_t np = min(kDecTP, p_end - p0);
-        for (uint32_t tp = 0; tp < np; ++tp) {
-            float dot = 0.f;
+    for (int g = 0; g < G; ++g) {
+        const __half *qh = a.canvas + a.src_off + ((uint64_t)(hkv * G + g) * HD + j * 8u) * a.pitch + col;
 #pragma unroll
-            for (uint32_t d = 0; d < HD; ++d) dot = fmaf(q[d], __half2float(sk[tp][d][b]), dot);
-            const float mn = fmaxf(m, dot);
-            const float ep = __expf(m - mn), ec = __expf(dot - mn);
-            l = l * ep + ec;
-#pragma unroll
-            for (uint32_t d = 0; d < HD; ++d) acc[d] = fmaf(acc[d], ep, ec * __half2float(sv[tp][d][b]));
-            m = mn;
-        }
-        __syncthreads();
+        for (int e = 0; e < 8; ++e) { q[g][e] = __half2float(qh[(uint64_t)e * a.pitch]) * scale; acc[g][e] = 0.f; }
+        m[g] = -65504.0f; l[g] = 0.f;
     }
-    float *out = partial + ((uint64_t)chunk * a.h_q + hq) * (HD + 2u) * a.pitch + col;
+    const uint64_t row_step = (uint64_t)a.pitch * HD / 8u;                // in 16-byte units
+    const uint64_t row0 = (((uint64_t)hkv * a.max_seq + p_begin) * a.pitch + col) * HD / 8u + j;
+    const uint4 *kr = reinterpret_cast<const uint4 *>(a.canvas + a.kcache_off) + row0;
+    const uint4 *vr = reinterpret_cast<const uint4 *>(a.canvas + a.vcache_off) + row0;
+    for (uint32_t p = p_begin; p < p_end; p += UNROLL) {
+        uint4 kv[UNROLL], vv[UNROLL];
 #pragma unroll
-    for (uint32_t d = 0; d < HD; ++d) out[(uint64_t)d * a.pitch] = acc[d];
-    out[(uint64_t)HD * a.pitch] = m;
-    out[(uint64_t)(HD + 1u) * a.pitch] = l;
+        for (uint32_t u = 0; u < UNROLL; ++u) {
+            const uint64_t o = (uint64_t)min(u, p_end - 1u - p) * row_step;          // past the end: re-read the last row (ignored below)
+            kv[u] = __ldg(kr + o);
+            vv[u] = __ldg(vr + o);
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < UNROLL; ++u) {
+            if (p + u >= p_end) break;
+            float kf[8], vf[8];
+            unpack8(kv[u], kf);
+            unpack8(vv[u], vf);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float dot = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) dot = fmaf(q[g][e], kf[e], dot);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+                const float mn = fmaxf(m[g], dot);
+                const float ep = __expf(m[g] - mn), ec = __expf(dot - mn);
+                l[g] = l[g] * ep + ec;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(acc[g][e], ep, ec * vf[e]);
+                m[g] = mn;
+            }
+        }
+        kr += UNROLL * row_step; vr += UNROLL * row_step;
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float *out = partial + (((uint64_t)chunk * a.h_q + hkv * G + g) * a.pitch + col) * kDecodeRow;
+        *reinterpret_cast<float4 *>(out + j * 8u) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        *reinterpret_cast<float4 *>(out + j * 8u + 4u) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+        if (j == 0u) { out[HD] = m[g]; out[HD + 1u] = l[g]; }
+    }
 }
 
-// combine the chunks: thread = (query head, dimension, column)
+// combine the chunks: 8 lanes per (query head, column), 8 dimensions each
 __global__ void __launch_bounds__(256) k44_valu_decode_attn_combine_kernel(const AuxArgs a, const float *partial) {
     constexpr uint32_t HD = 64;
-    const uint64_t total = (uint64_t)a.h_q * HD * a.pitch;
+    const uint64_t total = (uint64_t)a.h_q * a.pitch * 8u;
     const uint64_t i = (uint64_t)blockIdx.x * 256u + threadIdx.x;
     if (i >= total) return;
-    const uint32_t col = (uint32_t)(i % a.pitch), d = (uint32_t)((i / a.pitch) % HD), hq = (uint32_t)(i / ((uint64_t)a.pitch * HD));
+    const uint32_t j = (uint32_t)(i & 7u), col = (uint32_t)((i >> 3) % a.pitch), hq = (uint32_t)((i >> 3) / a.pitch);
     const int pos = *a.pos_ptr;
     if (pos < 0) return;
-    const uint32_t chunks = (uint32_t)pos / kDecChunk + 1u;
+    const uint32_t chunks = (uint32_t)pos / kDecodeChunk + 1u;
+    const uint64_t stride = (uint64_t)a.h_q * a.pitch * kDecodeRow;
+    const float *pc = partial + ((uint64_t)hq * a.pitch + col) * kDecodeRow;
     float M = -65504.0f;
-    for (uint32_t c = 0; c < chunks; ++c) M = fmaxf(M, partial[(((uint64_t)c * a.h_q + hq) * (HD + 2u) + HD) * a.pitch + col]);
-    float L = 0.f, o = 0.f;
+    for (uint32_t c = 0; c < chunks; ++c) M = fmaxf(M, pc[c * stride + HD]);
+    float L = 0.f, o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (uint32_t c = 0; c < chunks; ++c) {
-        const float *pc = partial + ((uint64_t)c * a.h_q + hq) * (HD + 2u) * a.pitch + col;
-        const float w = __expf(pc[(uint64_t)HD * a.pitch] - M);
-        L = fmaf(pc[(uint64_t)(HD + 1u) * a.pitch], w, L);
-        o = fmaf(pc[(uint64_t)d * a.pitch], w, o);
+        const float *r = pc + c * stride;
+        const float w = __expf(r[HD] - M);
+        L = fmaf(r[HD + 1u], w, L);
+        const float4 x = *reinterpret_cast<const float4 *>(r + j * 8u), y = *reinterpret_cast<const float4 *>(r + j * 8u + 4u);
+        o[0] = fmaf(x.x, w, o[0]); o[1] = fmaf(x.y, w, o[1]); o[2] = fmaf(x.z, w, o[2]); o[3] = fmaf(x.w, w, o[3]);
+        o[4] = fmaf(y.x, w, o[4]); o[5] = fmaf(y.y, w, o[5]); o[6] = fmaf(y.z, w, o[6]); o[7] = fmaf(y.w, w, o[7]);
     }
-    a.canvas[a.dst_off + ((uint64_t)hq * HD + d) * a.pitch + col] = __float2half_rn(o / L);
+    const float inv = 1.0f / L;
+    __half *dst = a.canvas + a.dst_off + ((uint64_t)hq * HD + j * 8u) * a.pitch + col;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dst[(uint64_t)e * a.pitch] = __float2half_rn(o[e] * inv);
 }
 
 cudaError_t launch_aux(const AuxArgs &a, cudaStream_t s) {
@@ -318,14 +339,18 @@ cudaError_t launch_aux(const AuxArgs &a, cudaStream_t s) {
         break;
     }
     case AUX_DECODE_ATTN: {
-        // rotary on q at the current position, rotary + cache append for k / v, partial attention per chunk, combine
-        if (a.head_dim != 64u || a.pitch % 32u || !a.pos_ptr || !a.partial || a.h_kv == 0 || a.h_q % a.h_kv || a.h_q / a.h_kv > 8u) return cudaErrorInvalidValue;
-        const uint32_t groups = a.pitch / 8u, half = a.head_dim / 2u;
-        k44_valu_rope_kernel<<<(uint32_t)(((uint64_t)a.h_q * half * groups + 255u) / 256u), 256, 0, s>>>(a, a.src_off, a.h_q);
-        k44_valu_rope_k_append_kernel<<<(uint32_t)(((uint64_t)a.h_kv * half * groups + 255u) / 256u), 256, 0, s>>>(a);
-        const dim3 grid(a.pitch / 32u, a.h_kv, (a.max_seq + kDecChunk - 1u) / kDecChunk);
-        k44_valu_decode_attn_partial_kernel<<<grid, 32u * (a.h_q / a.h_kv), 0, s>>>(a, a.partial);
-        k44_valu_decode_attn_combine_kernel<<<(uint32_t)(((uint64_t)a.h_q * 64u * a.pitch + 255u) / 256u), 256, 0, s>>>(a, a.partial);
+        // rotary on q and k at the current position + cache append of k / v, partial attention per chunk, combine
+        if (a.head_dim != 64u || a.pitch % 32u || !a.pos_ptr || !a.partial || a.h_kv == 0 || a.h_q % a.h_kv) return cudaErrorInvalidValue;
+        k44_valu_decode_rope_append_kernel<<<(uint32_t)(((uint64_t)(a.h_q + a.h_kv) * (a.head_dim / 2u) * a.pitch + 255u) / 256u), 256, 0, s>>>(a);
+        const dim3 grid(a.pitch / 16u, a.h_kv, (a.max_seq + kDecodeChunk - 1u) / kDecodeChunk);
+        switch (a.h_q / a.h_kv) {
+        case 1: k44_valu_decode_attn_partial_kernel<1><<<grid, 128, 0, s>>>(a, a.partial); break;
+        case 2: k44_valu_decode_attn_partial_kernel<2><<<grid, 128, 0, s>>>(a, a.partial); break;
+        case 4: k44_valu_decode_attn_partial_kernel<4><<<grid, 128, 0, s>>>(a, a.partial); break;
+        case 8: k44_valu_decode_attn_partial_kernel<8><<<grid, 128, 0, s>>>(a, a.partial); break;
+        default: return cudaErrorInvalidValue;
+        }
+        k44_valu_decode_attn_combine_kernel<<<(uint32_t)(((uint64_t)a.h_q * a.pitch * 8u + 255u) / 256u), 256, 0, s>>>(a, a.partial);
         break;
     }
     default: return cudaErrorInvalidValue;
