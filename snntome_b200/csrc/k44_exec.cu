@@ -613,7 +613,7 @@ bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
     cudaError_t e;
     if (w.is_aux) {
         launches_ += w.aux.kind == AUX_ROPE_ATTN ? 3u : (w.aux.kind == AUX_DECODE_ATTN ? 3u : 1u);
-        return check(launch_aux(w.aux, stream), ("launch of '" + w.name + "'").c_str());
+        return check(launch_aux(w.aux, pdl_, stream), ("launch of '" + w.name + "'").c_str());
     }
     if (w.path == PATH_UMMA && w.use_cluster) {
         WaveGroupArgs g;

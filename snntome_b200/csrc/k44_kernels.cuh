@@ -106,7 +106,7 @@ struct AuxArgs {
 };
 constexpr uint32_t kDecodeChunk = 32;
 constexpr uint32_t kDecodeRow = 68;                                  // floats per partial result: 64 values, maximum, sum, 2 pad (16-byte aligned rows)                                // cache positions per partial-attention CTA
-cudaError_t launch_aux(const AuxArgs &a, cudaStream_t s);
+cudaError_t launch_aux(const AuxArgs &a, bool dependent_launch, cudaStream_t s);
 
 // Up to four mutually independent small waves launched as one grid (their clusters are numbered consecutively).
 constexpr int kMaxGroupWaves = 4;

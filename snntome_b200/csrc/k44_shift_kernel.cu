@@ -123,10 +123,6 @@ k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveA
         }
         *abort_word = 0;
         ptx::fence_mbar_init();
-        if ((d.debug & 16u) && blockIdx.x == 0) {
-            reinterpret_cast<volatile long long *>(a.status + 2)[14] = 0;
-            reinterpret_cast<volatile long long *>(a.status + 2)[15] = 0;
-        }
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_addr(const_cast<uint32_t *>(tmem_slot)), C::kTmemCols);
@@ -136,14 +132,6 @@ k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveA
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // development aid (debug bit 16): CTA 0 records SM-clock timestamps / wait totals after the status word
-    const bool trace = (d.debug & 16u) && blockIdx.x == 0;
-    volatile long long *tr = reinterpret_cast<volatile long long *>(a.status + 2);
-    if (trace && threadIdx.x == 0) tr[0] = clock64();
-    // per-step stamps of steps 40..55: slot 16 + 8 * (g - 40) + k; k: 0 producer got the stage, 1 producer issued,
-    // 2 aligner got window and operand stage, 3 aligner arrived, 4 MMA got both, 5 MMA committed
-    auto stamp_step = [&](uint32_t g, int k) { if (trace && g >= 40u && g < 56u) tr[16 + 8 * (g - 40u) + k] = clock64(); };
-
     auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
         const long long t0 = clock64();
         for (uint32_t it = 0;; ++it) {
@@ -166,7 +154,6 @@ k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveA
         const uint64_t pol = ptx::policy_evict_last();     // weights and this column window are re-read by other tiles
         uint32_t issued = 0;
         bool ok = true;
-        long long pr_wait = 0;
         const uint32_t per_item = KS * boxes_per_stage;                     // table entries one item consumes
         const bool use_tab = per_item <= (uint32_t)kTabEntries;
         auto prefetch_entries = [&](uint32_t it) {
@@ -201,22 +188,15 @@ k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveA
                     uint32_t e;
                     if (use_tab) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(tab_it + bi * 4u) : "memory");
                     else e = __ldg(rows + bi);
-                    long long p0 = 0;
-                    if (trace) p0 = clock64();
                     ok = wait(lempty_bar + 8u * stage, ph ^ 1u);
-                    if (trace) pr_wait += clock64() - p0;
-                    if (lane == 0) stamp_step(issued, 0);
                     if (!ok) break;
-                    const uint32_t wb = (d.debug & 256u) ? 0u : kStageWBytes, rb = (d.debug & 4u) ? 0u : C::kRawBytes;
                     if (lane == 0) {
-                        if (wb + rb) ptx::mbar_arrive_expect_tx(lfull_bar + 8u * stage, wb + rb);
-                        else ptx::mbar_arrive(lfull_bar + 8u * stage);
-                        if (wb) ptx::bulk_g2s(w_smem + stage * kStageWBytes, wsrc + (uint64_t)ks * (kStageWBytes / 16u), kStageWBytes,
-                                              lfull_bar + 8u * stage, pol);
+                        ptx::mbar_arrive_expect_tx(lfull_bar + 8u * stage, kStageWBytes + C::kRawBytes);
+                        ptx::bulk_g2s(w_smem + stage * kStageWBytes, wsrc + (uint64_t)ks * (kStageWBytes / 16u), kStageWBytes,
+                                      lfull_bar + 8u * stage, pol);
                     }
-                    if (rb) ptx::tma_load_2d(raw_smem + stage * C::kRawBytes + psub * C::kSubRawBytes + pb * a.box_h * C::kRawPitch, &tmap, x0, (int32_t)(e & kBoxRowMask),
+                    ptx::tma_load_2d(raw_smem + stage * C::kRawBytes + psub * C::kSubRawBytes + pb * a.box_h * C::kRawPitch, &tmap, x0, (int32_t)(e & kBoxRowMask),
                                              lfull_bar + 8u * stage, pol);
-                    if (lane == 0) stamp_step(issued, 1);
                 }
             }
             ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
@@ -224,7 +204,6 @@ k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveA
             if (!ok) break;
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        if (trace && lane == 0) { tr[9] = pr_wait; }
         if (!ok && lane == 0) {
             if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PRODUCER);
             *abort_word = 1u;
@@ -244,43 +223,29 @@ k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveA
         if (lane == 0) {
             uint32_t g = 0;
             bool ok = true;
-            long long acc_b = 0, acc_l = 0, acc_t = 0;       // trace: cycles spent waiting for operands / weights / a free accumulator
             for (uint32_t it = 0; it < my_items && ok; ++it) {
                 const uint32_t acc = it & 1u;
-                long long wt0 = 0;
-                if (trace) wt0 = clock64();
                 ok = wait(tempty_bar + 8u * acc, ((it >> 1) & 1u) ^ 1u);
-                if (trace) acc_t += clock64() - wt0;
                 if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * N_TILE;
                 for (uint32_t ks = 0; ks < KS; ++ks, ++g) {
                     const uint32_t ls = g % SL, lph = (g / SL) & 1u, bs = g % SB, bph = (g / SB) & 1u;
-                    long long w0 = 0;
-                    if (trace) w0 = clock64();
                     ok = wait(bfull_bar + 8u * bs, bph);                                      // operand realigned
-                    if (trace) { const long long w1 = clock64(); acc_b += w1 - w0; w0 = w1; }
                     ok = ok && wait(lfull_bar + 8u * ls, lph);                                // weights landed
-                    if (trace) acc_l += clock64() - w0;
-                    stamp_step(g, 4);
                     if (!ok) break;
                     ptx::tc_fence_after();
                     const uint64_t a0 = d.a_base | (uint64_t)(((w_smem + ls * kStageWBytes) >> 4) & 0x3fffu);
                     const uint64_t b0 = d.b_base | (uint64_t)(((x_smem + bs * C::kXBytes) >> 4) & 0x3fffu);
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < kStageK / 16u; ++k4)
-                        if (!(d.debug & 128u) || k4 == 0u)
-                            ptx::umma_f16(d_tmem, a0 + (uint64_t)(k4 * d.a_k_step), b0 + (uint64_t)(k4 * d.b_k_step), d.idesc,
-                                          (ks != 0u || k4 != 0u) ? 1u : 0u);
+                        ptx::umma_f16(d_tmem, a0 + (uint64_t)(k4 * d.a_k_step), b0 + (uint64_t)(k4 * d.b_k_step), d.idesc,
+                                      (ks != 0u || k4 != 0u) ? 1u : 0u);
                     ptx::umma_commit(lempty_bar + 8u * ls);     // weight block reusable once these MMAs retire
                     ptx::umma_commit(bempty_bar + 8u * bs);     // operand stage likewise
-                    stamp_step(g, 5);
                 }
                 if (ok) ptx::umma_commit(tfull_bar + 8u * acc);
-                if (trace && it == 0u) tr[1] = clock64();
-                if (trace && it == 9u) tr[3] = clock64();
             }
-            if (trace) { tr[13] = acc_t; tr[14] = acc_b; tr[15] = acc_l; tr[2] = clock64(); }
             if (!ok) {
                 if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_MMA);
                 *abort_word = 1u;
@@ -313,7 +278,7 @@ k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveA
                 float f[32];
 #pragma unroll
                 for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
-                if (!(d.debug & 8u)) stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
+                stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
             }
             ptx::tc_fence_before();
             ptx::mbar_arrive(tempty_bar + 8u * acc);
@@ -332,7 +297,6 @@ k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveA
         const uint32_t flen = a.frame_len ? a.frame_len : a.pitch;
         uint32_t g = 0;
         bool ok = true;
-        long long al_wait = 0, al_t0 = 0, ph_copy = 0, ph_fence = 0, ph_arrive = 0;
         // table entries (row | shift << 28) of this warp's run in steps 0..31 of an item, one per lane; the next item's
         // entries are fetched while the current item is processed
         auto fetch = [&](uint32_t it, uint32_t ks_base) -> uint32_t {
@@ -354,20 +318,9 @@ k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveA
                 const uint32_t ls = g % SL, lph = (g / SL) & 1u, bs = g % SB, bph = (g / SB) & 1u;
                 const uint32_t sh = __shfl_sync(0xffffffffu, tab, ks & 31u) >> 28;
                 uint32_t okw = 1u;
-                if (trace) al_t0 = clock64();
                 if (lane == 0) okw = (wait(lfull_bar + 8u * ls, lph) && wait(bempty_bar + 8u * bs, bph ^ 1u)) ? 1u : 0u;
-                if (trace) al_wait += clock64() - al_t0;
                 ok = __shfl_sync(0xffffffffu, okw, 0) != 0u;
                 if (!ok) break;
-                if (warp == 6u && lane == 0) stamp_step(g, 2);
-                if (d.debug & 64u) {                 // development switch: barrier protocol only
-                    __syncwarp();
-                    if (lane == 0) { ptx::mbar_arrive(bfull_bar + 8u * bs); ptx::mbar_arrive(lempty_bar + 8u * ls); }
-                    if (warp == 6u && lane == 0) stamp_step(g, 3);
-                    continue;
-                }
-                long long c0 = 0;
-                if (trace) c0 = clock64();
                 uint4 buf[OC + 1];
                 const uint32_t src = raw_smem + ls * C::kRawBytes + sub * C::kSubRawBytes + krow * C::kRawPitch + first_chunk * 16u;
 #pragma unroll
@@ -385,24 +338,18 @@ k44_wave_umma_shift_kernel(const __grid_constant__ CUtensorMap tmap, const WaveA
                 case 7: shift_and_store<7, OC>(buf, dst_row, out_chunk0, krow); break;
                 default: shift_and_store<8, OC>(buf, dst_row, out_chunk0, krow); break;
                 }
-                long long c1 = 0, c2 = 0;
-                if (trace) c1 = clock64();
                 ptx::fence_proxy_async();          // generic-proxy stores -> visible to the tensor core's async proxy
-                if (trace) c2 = clock64();
                 __syncwarp();
                 if (lane == 0) {
                     ptx::mbar_arrive(bfull_bar + 8u * bs);
                     ptx::mbar_arrive(lempty_bar + 8u * ls);     // this warp's rows of the window are in registers / stored
                 }
-                if (trace) { const long long c3 = clock64(); ph_copy += c1 - c0; ph_fence += c2 - c1; ph_arrive += c3 - c2; }
-                if (warp == 6u && lane == 0) stamp_step(g, 3);
             }
         }
         if (!ok && lane == 0) {
             if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PRODUCER);
             *abort_word = 1u;
         }
-        if (trace && warp == 6u && lane == 0) { tr[10] = al_wait; tr[12] = clock64(); tr[4] = ph_copy; tr[5] = ph_fence; tr[6] = ph_arrive; }
     }
     ptx::tc_fence_before();
     __syncthreads();

@@ -13,6 +13,24 @@
 
 namespace k44b {
 
+// Every kernel here may be launched with programmatic stream serialisation: it lets the next kernel start its own set-up
+// at once and waits itself for the previous kernel's results before touching memory.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, bool pdl, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ void unpack8(const uint4 &u, float (&f)[8]) {
     const __half2 *h = reinterpret_cast<const __half2 *>(&u);
 #pragma unroll
@@ -26,18 +44,39 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return u;
 }
 
-// ---- RMSNorm: one CTA per group of 8 columns, 256 threads stride over the channels ----------------------------------
-__global__ void __launch_bounds__(256) k44_valu_rmsnorm_kernel(const AuxArgs a) {
-    __shared__ float part[8][8];
+// ---- RMSNorm: one CTA of 1024 threads per group of 8 columns ------------------------------------------------------------
+// Thread t owns channels t, t + 1024, ...; with at most R of them per thread the 16-byte pieces stay in registers between
+// the sum of squares and the scaling, so the tensor is read once and all loads of a thread are in flight together (a decode
+// step has only 8 such CTAs, so latency, not bandwidth, is what counts). Larger tensors take the two-pass loop (R = 0).
+template <int R>
+__global__ void __launch_bounds__(1024) k44_valu_rmsnorm_kernel(const AuxArgs a) {
+    pdl_enter();
+    __shared__ float part[32][8];
     const uint32_t col0 = blockIdx.x * 8u, tid = threadIdx.x;
     const __half *src = a.canvas + a.src_off + col0;
     __half *dst = a.canvas + a.dst_off + col0;
     float ss[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (uint32_t c = tid; c < a.rows; c += 256u) {
-        float x[8];
-        unpack8(*reinterpret_cast<const uint4 *>(src + (uint64_t)c * a.pitch), x);
+    uint4 keep[R > 0 ? R : 1];
+    if (R > 0) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) ss[k] = fmaf(x[k], x[k], ss[k]);
+        for (int r = 0; r < R; ++r) {
+            const uint32_t c = tid + 1024u * (uint32_t)r;
+            keep[r] = c < a.rows ? *reinterpret_cast<const uint4 *>(src + (uint64_t)c * a.pitch) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float x[8];
+            unpack8(keep[r], x);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss[k] = fmaf(x[k], x[k], ss[k]);
+        }
+    } else {
+        for (uint32_t c = tid; c < a.rows; c += 1024u) {
+            float x[8];
+            unpack8(*reinterpret_cast<const uint4 *>(src + (uint64_t)c * a.pitch), x);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss[k] = fmaf(x[k], x[k], ss[k]);
+        }
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -55,21 +94,36 @@ __global__ void __launch_bounds__(256) k44_valu_rmsnorm_kernel(const AuxArgs a) 
     for (int k = 0; k < 8; ++k) {
         float tot = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) tot += part[w][k];
+        for (int w = 0; w < 32; ++w) tot += part[w][k];
         inv[k] = rsqrtf(fmaf(tot, inv_d, a.eps));
     }
-    for (uint32_t c = tid; c < a.rows; c += 256u) {      // second pass: the rows come back from L2
-        float x[8];
-        unpack8(*reinterpret_cast<const uint4 *>(src + (uint64_t)c * a.pitch), x);
-        const float g = a.gamma ? __half2float(a.gamma[c]) : 1.0f;
+    if (R > 0) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) x[k] = x[k] * inv[k] * g;
-        *reinterpret_cast<uint4 *>(dst + (uint64_t)c * a.pitch) = pack8(x);
+        for (int r = 0; r < R; ++r) {
+            const uint32_t c = tid + 1024u * (uint32_t)r;
+            if (c >= a.rows) break;
+            float x[8];
+            unpack8(keep[r], x);
+            const float g = a.gamma ? __half2float(a.gamma[c]) : 1.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) x[k] = x[k] * inv[k] * g;
+            *reinterpret_cast<uint4 *>(dst + (uint64_t)c * a.pitch) = pack8(x);
+        }
+    } else {
+        for (uint32_t c = tid; c < a.rows; c += 1024u) {      // second pass: the rows come back from L2
+            float x[8];
+            unpack8(*reinterpret_cast<const uint4 *>(src + (uint64_t)c * a.pitch), x);
+            const float g = a.gamma ? __half2float(a.gamma[c]) : 1.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) x[k] = x[k] * inv[k] * g;
+            *reinterpret_cast<uint4 *>(dst + (uint64_t)c * a.pitch) = pack8(x);
+        }
     }
 }
 
 // ---- SwiGLU product ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k44_valu_swiglu_kernel(const AuxArgs a) {
+    pdl_enter();
     const uint64_t n8 = (uint64_t)a.rows * a.pitch / 8u;
     const uint4 *g = reinterpret_cast<const uint4 *>(a.canvas + a.src_off);
     const uint4 *u = reinterpret_cast<const uint4 *>(a.canvas + a.src2_off);
@@ -97,6 +151,7 @@ __device__ __forceinline__ float rope_inv_freq(uint32_t p, uint32_t head_dim, fl
 
 // one thread: one rotation pair of one head, 8 consecutive columns
 __global__ void __launch_bounds__(256) k44_valu_rope_kernel(const AuxArgs a, uint64_t off, uint32_t heads) {
+    pdl_enter();
     const uint32_t half = a.head_dim / 2u, groups = a.pitch / 8u;
     const uint64_t total = (uint64_t)heads * half * groups;
     const uint64_t i = (uint64_t)blockIdx.x * 256u + threadIdx.x;
@@ -129,6 +184,7 @@ __global__ void __launch_bounds__(256) k44_valu_rope_kernel(const AuxArgs a, uin
 // memory as [column][dimension]; running maximum / sum softmax in FP32.
 template <int HD>
 __global__ void __launch_bounds__(128) k44_valu_causal_attn_kernel(const AuxArgs a) {
+    pdl_enter();
     constexpr int DP = HD / 4;                      // dimensions per thread
     constexpr int ROW = HD + 8;                     // padded shared row (halves)
     __shared__ __align__(16) __half sk[32][ROW];
@@ -190,6 +246,7 @@ __global__ void __launch_bounds__(128) k44_valu_causal_attn_kernel(const AuxArgs
 // Rotate q and k in place at the current position and append k and v to the caches: one thread per (head, rotation
 // pair, column); the first h_q heads are the query heads, the rest the key heads.
 __global__ void __launch_bounds__(256) k44_valu_decode_rope_append_kernel(const AuxArgs a) {
+    pdl_enter();
     const uint32_t half = a.head_dim / 2u;
     const uint64_t total = (uint64_t)(a.h_q + a.h_kv) * half * a.pitch;
     const uint64_t i = (uint64_t)blockIdx.x * 256u + threadIdx.x;
@@ -225,6 +282,7 @@ __global__ void __launch_bounds__(256) k44_valu_decode_rope_append_kernel(const 
 // [chunk][h_q][pitch][kDecodeRow] (rows of 68 floats: 16-byte aligned for the vector accesses).
 template <int G>
 __global__ void __launch_bounds__(128) k44_valu_decode_attn_partial_kernel(const AuxArgs a, float *partial) {
+    pdl_enter();
     constexpr uint32_t HD = 64, UNROLL = 4;
     const uint32_t cb = blockIdx.x, hkv = blockIdx.y, chunk = blockIdx.z;
     const uint32_t tid = threadIdx.x, j = tid & 7u, col = cb * 16u + (tid >> 3);
@@ -288,6 +346,7 @@ __global__ void __launch_bounds__(128) k44_valu_decode_attn_partial_kernel(const
 
 // combine the chunks: 8 lanes per (query head, column), 8 dimensions each
 __global__ void __launch_bounds__(256) k44_valu_decode_attn_combine_kernel(const AuxArgs a, const float *partial) {
+    pdl_enter();
     constexpr uint32_t HD = 64;
     const uint64_t total = (uint64_t)a.h_q * a.pitch * 8u;
     const uint64_t i = (uint64_t)blockIdx.x * 256u + threadIdx.x;
@@ -315,47 +374,54 @@ __global__ void __launch_bounds__(256) k44_valu_decode_attn_combine_kernel(const
     for (int e = 0; e < 8; ++e) dst[(uint64_t)e * a.pitch] = __float2half_rn(o[e] * inv);
 }
 
-cudaError_t launch_aux(const AuxArgs &a, cudaStream_t s) {
+cudaError_t launch_aux(const AuxArgs &a, bool pdl, cudaStream_t s) {
+    cudaError_t e = cudaSuccess;
     switch (a.kind) {
-    case AUX_RMSNORM:
+    case AUX_RMSNORM: {
         if (a.pitch % 8u || a.rows == 0) return cudaErrorInvalidValue;
-        k44_valu_rmsnorm_kernel<<<a.pitch / 8u, 256, 0, s>>>(a);
+        const dim3 grid(a.pitch / 8u), block(1024);
+        if (a.rows <= 2048u) e = launch_k(k44_valu_rmsnorm_kernel<2>, grid, block, pdl, s, a);
+        else if (a.rows <= 4096u) e = launch_k(k44_valu_rmsnorm_kernel<4>, grid, block, pdl, s, a);
+        else e = launch_k(k44_valu_rmsnorm_kernel<0>, grid, block, pdl, s, a);
         break;
+    }
     case AUX_SWIGLU: {
         const uint64_t n8 = (uint64_t)a.rows * a.pitch / 8u;
         const uint32_t grid = (uint32_t)std::min<uint64_t>((n8 + 255u) / 256u, 148u * 16u);
-        k44_valu_swiglu_kernel<<<grid ? grid : 1u, 256, 0, s>>>(a);
+        e = launch_k(k44_valu_swiglu_kernel, dim3(grid ? grid : 1u), dim3(256), pdl, s, a);
         break;
     }
     case AUX_ROPE_ATTN: {
         if (a.head_dim != 64u && a.head_dim != 128u) return cudaErrorInvalidValue;
         if (a.pitch % 32u || a.seq_len % 32u || a.h_kv == 0 || a.h_q % a.h_kv) return cudaErrorInvalidValue;
         const uint32_t groups = a.pitch / 8u, half = a.head_dim / 2u;
-        k44_valu_rope_kernel<<<(uint32_t)(((uint64_t)a.h_q * half * groups + 255u) / 256u), 256, 0, s>>>(a, a.src_off, a.h_q);
-        k44_valu_rope_kernel<<<(uint32_t)(((uint64_t)a.h_kv * half * groups + 255u) / 256u), 256, 0, s>>>(a, a.src2_off, a.h_kv);
+        e = launch_k(k44_valu_rope_kernel, dim3((uint32_t)(((uint64_t)a.h_q * half * groups + 255u) / 256u)), dim3(256), pdl, s, a, a.src_off, a.h_q);
+        if (e == cudaSuccess) e = launch_k(k44_valu_rope_kernel, dim3((uint32_t)(((uint64_t)a.h_kv * half * groups + 255u) / 256u)), dim3(256), pdl, s, a, a.src2_off, a.h_kv);
         const dim3 grid((a.columns + 31u) / 32u, a.h_q);
-        if (a.head_dim == 64u) k44_valu_causal_attn_kernel<64><<<grid, 128, 0, s>>>(a);
-        else k44_valu_causal_attn_kernel<128><<<grid, 128, 0, s>>>(a);
+        if (e == cudaSuccess) e = a.head_dim == 64u ? launch_k(k44_valu_causal_attn_kernel<64>, grid, dim3(128), pdl, s, a)
+                                                    : launch_k(k44_valu_causal_attn_kernel<128>, grid, dim3(128), pdl, s, a);
         break;
     }
     case AUX_DECODE_ATTN: {
         // rotary on q and k at the current position + cache append of k / v, partial attention per chunk, combine
         if (a.head_dim != 64u || a.pitch % 32u || !a.pos_ptr || !a.partial || a.h_kv == 0 || a.h_q % a.h_kv) return cudaErrorInvalidValue;
-        k44_valu_decode_rope_append_kernel<<<(uint32_t)(((uint64_t)(a.h_q + a.h_kv) * (a.head_dim / 2u) * a.pitch + 255u) / 256u), 256, 0, s>>>(a);
+        e = launch_k(k44_valu_decode_rope_append_kernel, dim3((uint32_t)(((uint64_t)(a.h_q + a.h_kv) * (a.head_dim / 2u) * a.pitch + 255u) / 256u)), dim3(256), pdl, s, a);
         const dim3 grid(a.pitch / 16u, a.h_kv, (a.max_seq + kDecodeChunk - 1u) / kDecodeChunk);
+        if (e != cudaSuccess) break;
         switch (a.h_q / a.h_kv) {
-        case 1: k44_valu_decode_attn_partial_kernel<1><<<grid, 128, 0, s>>>(a, a.partial); break;
-        case 2: k44_valu_decode_attn_partial_kernel<2><<<grid, 128, 0, s>>>(a, a.partial); break;
-        case 4: k44_valu_decode_attn_partial_kernel<4><<<grid, 128, 0, s>>>(a, a.partial); break;
-        case 8: k44_valu_decode_attn_partial_kernel<8><<<grid, 128, 0, s>>>(a, a.partial); break;
+        case 1: e = launch_k(k44_valu_decode_attn_partial_kernel<1>, grid, dim3(128), pdl, s, a, a.partial); break;
+        case 2: e = launch_k(k44_valu_decode_attn_partial_kernel<2>, grid, dim3(128), pdl, s, a, a.partial); break;
+        case 4: e = launch_k(k44_valu_decode_attn_partial_kernel<4>, grid, dim3(128), pdl, s, a, a.partial); break;
+        case 8: e = launch_k(k44_valu_decode_attn_partial_kernel<8>, grid, dim3(128), pdl, s, a, a.partial); break;
         default: return cudaErrorInvalidValue;
         }
-        k44_valu_decode_attn_combine_kernel<<<(uint32_t)(((uint64_t)a.h_q * a.pitch * 8u + 255u) / 256u), 256, 0, s>>>(a, a.partial);
+        if (e == cudaSuccess)
+            e = launch_k(k44_valu_decode_attn_combine_kernel, dim3((uint32_t)(((uint64_t)a.h_q * a.pitch * 8u + 255u) / 256u)), dim3(256), pdl, s, a, (const float *)a.partial);
         break;
     }
     default: return cudaErrorInvalidValue;
     }
-    return cudaGetLastError();
+    return e;
 }
 
 }  // namespace k44b
