@@ -52,6 +52,7 @@ template <int R>
 __global__ void __launch_bounds__(1024) k44_valu_rmsnorm_kernel(const AuxArgs a) {
     pdl_enter();
     __shared__ float part[32][8];
+    __shared__ float inv_s[8];
     const uint32_t col0 = blockIdx.x * 8u, tid = threadIdx.x;
     const __half *src = a.canvas + a.src_off + col0;
     __half *dst = a.canvas + a.dst_off + col0;
@@ -88,15 +89,20 @@ __global__ void __launch_bounds__(1024) k44_valu_rmsnorm_kernel(const AuxArgs a)
         for (int k = 0; k < 8; ++k) part[tid >> 5][k] = ss[k];
     }
     __syncthreads();
-    float inv[8];
-    const float inv_d = 1.0f / (float)a.rows;
+    if (tid < 32u) {                                   // one warp folds the 32 per-warp sums and publishes 1/rms per column
+        const float inv_d = 1.0f / (float)a.rows;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        float tot = 0.f;
+        for (int k = 0; k < 8; ++k) {
+            float tot = part[tid][k];
 #pragma unroll
-        for (int w = 0; w < 32; ++w) tot += part[w][k];
-        inv[k] = rsqrtf(fmaf(tot, inv_d, a.eps));
+            for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+            if (tid == 0u) inv_s[k] = rsqrtf(fmaf(tot, inv_d, a.eps));
+        }
     }
+    __syncthreads();
+    float inv[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) inv[k] = inv_s[k];
     if (R > 0) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -301,16 +307,22 @@ __global__ void __launch_bounds__(128) k44_valu_decode_attn_partial_kernel(const
     }
     const uint64_t row_step = (uint64_t)a.pitch * HD / 8u;                // in 16-byte units
     const uint64_t row0 = (((uint64_t)hkv * a.max_seq + p_begin) * a.pitch + col) * HD / 8u + j;
-    const uint4 *kr = reinterpret_cast<const uint4 *>(a.canvas + a.kcache_off) + row0;
-    const uint4 *vr = reinterpret_cast<const uint4 *>(a.canvas + a.vcache_off) + row0;
-    for (uint32_t p = p_begin; p < p_end; p += UNROLL) {
-        uint4 kv[UNROLL], vv[UNROLL];
+    const uint4 *const kr = reinterpret_cast<const uint4 *>(a.canvas + a.kcache_off) + row0;
+    const uint4 *const vr = reinterpret_cast<const uint4 *>(a.canvas + a.vcache_off) + row0;
+    // the rows of the next batch of positions are requested before the current batch is consumed
+    uint4 kv[UNROLL], vv[UNROLL], kn[UNROLL], vn[UNROLL];
+    auto fetch = [&](uint32_t p, uint4 (&kd)[UNROLL], uint4 (&vd)[UNROLL]) {
 #pragma unroll
         for (uint32_t u = 0; u < UNROLL; ++u) {
-            const uint64_t o = (uint64_t)min(u, p_end - 1u - p) * row_step;          // past the end: re-read the last row (ignored below)
-            kv[u] = __ldg(kr + o);
-            vv[u] = __ldg(vr + o);
+            const uint32_t pp = min(p + u, p_end - 1u);                  // past the end: re-read the last row (ignored below)
+            const uint64_t o = (uint64_t)(pp - p_begin) * row_step;
+            kd[u] = __ldg(kr + o);
+            vd[u] = __ldg(vr + o);
         }
+    };
+    fetch(p_begin, kv, vv);
+    for (uint32_t p = p_begin; p < p_end; p += UNROLL) {
+        if (p + UNROLL < p_end) fetch(p + UNROLL, kn, vn);
 #pragma unroll
         for (uint32_t u = 0; u < UNROLL; ++u) {
             if (p + u >= p_end) break;
@@ -333,7 +345,8 @@ __global__ void __launch_bounds__(128) k44_valu_decode_attn_partial_kernel(const
                 m[g] = mn;
             }
         }
-        kr += UNROLL * row_step; vr += UNROLL * row_step;
+#pragma unroll
+        for (uint32_t u = 0; u < UNROLL; ++u) { kv[u] = kn[u]; vv[u] = vn[u]; }
     }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -357,16 +370,34 @@ __global__ void __launch_bounds__(256) k44_valu_decode_attn_combine_kernel(const
     const uint32_t chunks = (uint32_t)pos / kDecodeChunk + 1u;
     const uint64_t stride = (uint64_t)a.h_q * a.pitch * kDecodeRow;
     const float *pc = partial + ((uint64_t)hq * a.pitch + col) * kDecodeRow;
+    // all loads of a batch of 8 chunks are issued before any is used (the chunks are far apart in memory)
     float M = -65504.0f;
-    for (uint32_t c = 0; c < chunks; ++c) M = fmaxf(M, pc[c * stride + HD]);
+    for (uint32_t c0 = 0; c0 < chunks; c0 += 8u) {
+        float mv[8];
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) mv[u] = pc[(uint64_t)min(c0 + u, chunks - 1u) * stride + HD];
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) M = fmaxf(M, mv[u]);
+    }
     float L = 0.f, o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (uint32_t c = 0; c < chunks; ++c) {
-        const float *r = pc + c * stride;
-        const float w = __expf(r[HD] - M);
-        L = fmaf(r[HD + 1u], w, L);
-        const float4 x = *reinterpret_cast<const float4 *>(r + j * 8u), y = *reinterpret_cast<const float4 *>(r + j * 8u + 4u);
-        o[0] = fmaf(x.x, w, o[0]); o[1] = fmaf(x.y, w, o[1]); o[2] = fmaf(x.z, w, o[2]); o[3] = fmaf(x.w, w, o[3]);
-        o[4] = fmaf(y.x, w, o[4]); o[5] = fmaf(y.y, w, o[5]); o[6] = fmaf(y.z, w, o[6]); o[7] = fmaf(y.w, w, o[7]);
+    for (uint32_t c0 = 0; c0 < chunks; c0 += 8u) {
+        float mv[8], lv[8];
+        float4 x[8], y[8];
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) {
+            const float *r = pc + (uint64_t)min(c0 + u, chunks - 1u) * stride;
+            mv[u] = r[HD]; lv[u] = r[HD + 1u];
+            x[u] = *reinterpret_cast<const float4 *>(r + j * 8u);
+            y[u] = *reinterpret_cast<const float4 *>(r + j * 8u + 4u);
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) {
+            if (c0 + u >= chunks) break;
+            const float w = __expf(mv[u] - M);
+            L = fmaf(lv[u], w, L);
+            o[0] = fmaf(x[u].x, w, o[0]); o[1] = fmaf(x[u].y, w, o[1]); o[2] = fmaf(x[u].z, w, o[2]); o[3] = fmaf(x[u].w, w, o[3]);
+            o[4] = fmaf(y[u].x, w, o[4]); o[5] = fmaf(y[u].y, w, o[5]); o[6] = fmaf(y[u].z, w, o[6]); o[7] = fmaf(y[u].w, w, o[7]);
+        }
     }
     const float inv = 1.0f / L;
     __half *dst = a.canvas + a.dst_off + ((uint64_t)hq * HD + j * 8u) * a.pitch + col;
