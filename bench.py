@@ -662,6 +662,41 @@ def shift_main(args) -> None:
         dist.destroy_process_group()
 
 
+def tiny_main(args) -> None:
+    """The tiny correctness plan (2 waves x 1024 neurons, fan-in 256 as 16 runs of 16 rows, 32 columns): launch-latency
+    bound, reported as microseconds per wave of a replayed CUDA graph."""
+    import torch
+    from snntome_b200 import synth
+    from snntome_b200.native import NativePlan
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    plan = synth.config0(group=128)
+    npn = NativePlan.from_plan(plan, device=torch.cuda.current_device())
+    x = synth.random_input(plan, 11)
+    canvas = npn.canvas_tensor()
+    canvas[plan.input_off: plan.input_off + x.size] = torch.from_numpy(x.view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    stream = torch.cuda.current_stream()
+    reps = max(200, args.steps)
+    for _ in range(20):
+        npn.execute_graph(stream)
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0.record(stream)
+    for _ in range(reps):
+        npn.execute_graph(stream)
+    t1.record(stream)
+    torch.cuda.synchronize()
+    assert npn.status() == 0
+    us_step = t0.elapsed_time(t1) * 1e3 / reps
+    nw = npn.num_waves
+    print(json.dumps({"metric": "microseconds per wave (tiny correctness plan, CUDA graph replay)", "value": us_step / nw, "unit": "us/wave",
+                      "n_gpus": 1, "steps": reps, "warmup": 20, "ms_per_step": us_step / 1e3, "higher_is_better": False, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+                      "config": {"workload": "tiny plan: 4096 input rows, 2 waves x 1024 neurons, fan-in 256 = 16 runs of 16 rows, groups of 128, ReLU, 32 columns",
+                                 "l2_policy": "0.7 MB per wave: L2-resident, launch-latency bound by construction"},
+                      "kernel_paths": [npn.wave_info(i).path for i in range(nw)], "k_splits": [npn.wave_info(i).k_splits for i in range(nw)],
+                      "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": int(npn.launch_count)}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -669,7 +704,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", type=float, default=float(os.environ.get("K44B_BENCH_SCALE", "1.0")))
-    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "decode-full", "pruned-sharded", "token-shift"])
+    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "decode-full", "pruned-sharded", "token-shift", "tiny"])
     ap.add_argument("--layers", type=int, default=16, help="decode workload: decoder layers (16 = the 1B shape)")
     ap.add_argument("--max-shift", type=int, default=7, help="token-shift workload: largest token shift drawn per run (0 = unshifted runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -681,6 +716,8 @@ def main() -> None:
         return sharded_main(args)
     if args.workload == "token-shift":
         return shift_main(args)
+    if args.workload == "tiny":
+        return tiny_main(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
