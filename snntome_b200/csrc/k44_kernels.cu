@@ -245,21 +245,22 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
-                // one TMA box per run, issued right after its table lookup (the whole warp fetches 32 entries at a time;
-                // an entry is row | token shift << 28, the shift is only used by the FMA kernel)
-                for (uint32_t b = 0; b < boxes_per_stage; ++b) {
-                    const uint32_t bi = ks * boxes_per_stage + b;
-                    if ((bi & ~31u) != cached_base) {
-                        cached_base = bi & ~31u;
+                // One TMA box per (run, 64-column block). The whole warp fetches 32 table entries at a time (an entry is
+                // row | token shift << 28; the shift is only used by other kernels). Issuing a tensor copy costs its thread
+                // of the order of a hundred cycles, so when a step has several boxes they go out from different lanes in one
+                // warp instruction; a step with a single box (runs of 64 rows, 64-column tiles) is issued by lane 0 as before.
+                const uint32_t per_stage = boxes_per_stage * (uint32_t)Cfg::kColBlocks;     // at most 8 x 4
+                {
+                    const uint32_t bi0 = ks * boxes_per_stage;
+                    if ((bi0 & ~31u) != cached_base) {       // the boxes of one step never straddle a group of 32 entries
+                        cached_base = bi0 & ~31u;
                         cached = (cached_base + lane < a.boxes_per_group) ? __ldg(rows + cached_base + lane) : 0u;
                     }
-                    const uint32_t row = __shfl_sync(0xffffffffu, cached, bi & 31u) & kBoxRowMask;
-                    if (lane == 0 && !(d.debug & 4u)) {
-#pragma unroll
-                        for (int cb = 0; cb < Cfg::kColBlocks; ++cb)
-                            ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + (uint32_t)cb * (kStageK * 128u) + b * a.box_h * 128u, &tmap,
-                                             (int32_t)(ct * N_TILE + cb * 64), (int32_t)row, full_bar + 8u * stage, pol_x);
-                    }
+                    const uint32_t b = lane / (uint32_t)Cfg::kColBlocks, cb = lane % (uint32_t)Cfg::kColBlocks;
+                    const uint32_t row = __shfl_sync(0xffffffffu, cached, (bi0 + b) & 31u) & kBoxRowMask;
+                    if (lane < per_stage && !(d.debug & 4u))
+                        ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + cb * (kStageK * 128u) + b * a.box_h * 128u, &tmap,
+                                         (int32_t)(ct * N_TILE + cb * 64u), (int32_t)row, full_bar + 8u * stage, pol_x);
                 }
                 if (issued == 0 && lane == 0) stamp(2);
                 ++issued;
