@@ -236,6 +236,10 @@ def build_decoder_plan(cfg: dict, device: int, seed: int = 7, full: bool = False
 
     x_in, x_out = "x0", "x1"
     off = lambda name: rows[name] * pitch
+    if full:        # token ids in: embedding rows gathered into the first activation tensor
+        plan.embedding_table = torch.empty(V * H, dtype=torch.float16, device=f"cuda:{device}")
+        fill_normal_f16(plan.embedding_table, seed * 17 + 3, 1.0)
+        plan.add_embedding(plan.embedding_table.data_ptr(), V, H, off("x0"))
     for layer in range(cfg["layers"]):
         if full:
             plan.add_rmsnorm(off(x_in), off("n"), H, 1e-5, None, name=f"L{layer}.norm1")
@@ -260,6 +264,7 @@ def build_decoder_plan(cfg: dict, device: int, seed: int = 7, full: bool = False
         plan.add_rmsnorm(off(x_in), off("n"), H, 1e-5, None, name="final_norm")
     add("lm_head", "n" if full else x_in, "logits", H, V)
     if full:
+        plan.add_argmax(off("logits"), V)                 # greedy next token per sequence, read back by the host
         canvas = plan.canvas_tensor()
         c0 = off("kcache0")
         fill_normal_f16(canvas[c0: c0 + 2 * cfg["layers"] * KV * ctx * pitch], seed * 31 + 5, 1.0)
@@ -329,6 +334,31 @@ def decode_main(args) -> None:
             ev[i + 1].record(stream)
     torch.cuda.synchronize()
     wave_us = [ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(nw)]
+    # end to end through the public API: token ids host -> device, one graph replay, next token ids device -> host
+    e2e = None
+    if full:
+        toks = np.random.default_rng(5).integers(0, cfg["vocab"], size=cfg["columns"]).astype(np.int32)
+        e_steps = max(5, min(args.steps, 20))
+        plan.set_tokens(toks, stream); plan.execute_graph(stream); toks = plan.next_tokens(cfg["columns"], stream)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        w0 = time.perf_counter()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(e_steps):
+            plan.set_tokens(toks, stream)
+            plan.execute_graph(stream)
+            toks = plan.next_tokens(cfg["columns"], stream)        # synchronises: the host holds the ids before the next step
+        e1.record(stream)
+        torch.cuda.synchronize()
+        e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - w0) * 1e3)
+        if dist is not None:
+            t = torch.tensor([e_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); e_ms = float(t.item())
+        e2e = {"value": cfg["columns"] * world / (e_ms / e_steps * 1e-3), "unit": "tok/s", "ms_per_step": e_ms / e_steps, "steps": e_steps,
+               "h2d_bytes_per_step": 4 * cfg["columns"], "d2h_bytes_per_step": 4 * cfg["columns"],
+               "api": "k44b_plan_set_tokens + k44b_execute_graph + k44b_plan_get_next_tokens (greedy, one token per sequence and step)",
+               "checksum": int(toks.astype(np.int64).sum())}
     clocks = sampler.stop()
     peak, kind = measured_peaks()
     kv_bytes = 2.0 * cfg["layers"] * cfg["kv_heads"] * cfg["head_dim"] * ctx * 64 * 2 if full else 0.0      # K and V of every layer, read once
@@ -350,7 +380,7 @@ def decode_main(args) -> None:
                              "traffic": None},
                 "per_wave_us_direct_launch": {"layer0": wave_us[:12 if full else 7], "lm_head": wave_us[-1], "sum": sum(wave_us)},
                 "k_splits": {"layer0": [i.k_splits for i in infos[:12 if full else 7]], "lm_head": infos[-1].k_splits},
-                "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks}
+                "cpu_baseline": None, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks}
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

@@ -109,6 +109,16 @@ int k44b_plan_add_decode_attn(void *plan, const char *name, uint64_t q_off, uint
                               uint64_t kcache_off, uint64_t vcache_off, uint32_t h_q, uint32_t h_kv, uint32_t head_dim, uint32_t max_seq,
                               float rope_theta, int llama3_scaling);
 int k44b_plan_set_decode_pos(void *plan, int pos, void *stream);
+/* Token I/O on the device (no counterpart in the reference, whose boundary is host F32 tensors): an embedding gather —
+ * column b of the destination becomes row tokens[b] of an FP16 table [vocab][dim] that the caller keeps in device memory —
+ * and a greedy arg-max over the rows of a tensor per column (lowest row wins ties). With advance != 0 the arg-max also
+ * stores its result as the next step's tokens and moves the decode position on by one (saturating at max_seq - 1), so a
+ * captured graph generates token after token without the host. set_tokens / get_next_tokens copy `n` 32-bit ids
+ * (get_next_tokens synchronises the stream). */
+int k44b_plan_add_embedding(void *plan, const char *name, const void *d_table_f16, uint32_t vocab, uint32_t dim, uint64_t dst_off);
+int k44b_plan_add_argmax(void *plan, const char *name, uint64_t src_off, uint32_t rows, int advance, uint32_t max_seq);
+int k44b_plan_set_tokens(void *plan, const int32_t *h_tokens, uint32_t n, void *stream);
+int k44b_plan_get_next_tokens(void *plan, int32_t *h_tokens, uint32_t n, void *stream);
 
 /* ---- neuron sharding over the GPUs of one box (no counterpart in the reference, which is single-GPU) ----
  * Every rank holds a plan with its rows of every wave and a full-size canvas. After k44b_plan_set_peers_* the wave

@@ -88,6 +88,10 @@ PROTOTYPES = {
     "k44b_plan_add_decode_attn": (c_int, [c_void_p, c_char_p, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_uint32, c_uint32, c_uint32,
                                            c_uint32, c_float, c_int]),
     "k44b_plan_set_decode_pos": (c_int, [c_void_p, c_int, c_void_p]),
+    "k44b_plan_add_embedding": (c_int, [c_void_p, c_char_p, c_void_p, c_uint32, c_uint32, c_uint64]),
+    "k44b_plan_add_argmax": (c_int, [c_void_p, c_char_p, c_uint64, c_uint32, c_int, c_uint32]),
+    "k44b_plan_set_tokens": (c_int, [c_void_p, POINTER(ctypes.c_int32), c_uint32, c_void_p]),
+    "k44b_plan_get_next_tokens": (c_int, [c_void_p, POINTER(ctypes.c_int32), c_uint32, c_void_p]),
     "k44b_plan_ipc_handles": (c_int, [c_void_p, c_void_p, c_void_p]),
     "k44b_plan_set_peers_ipc": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "k44b_plan_set_peers_raw": (c_int, [c_void_p, c_int, c_int, POINTER(c_void_p), POINTER(c_void_p)]),

@@ -325,6 +325,41 @@ int k44b_plan_add_decode_attn(void *plan, const char *name, uint64_t q_off, uint
     return P(plan)->exec.add_wave(w) ? 0 : set_error(P(plan)->exec.err);
 }
 
+int k44b_plan_add_embedding(void *plan, const char *name, const void *d_table_f16, uint32_t vocab, uint32_t dim, uint64_t dst_off) {
+    if (!plan || !d_table_f16 || !vocab || !dim) return set_error("plan_add_embedding: bad arguments");
+    HostWave w;
+    w.kind = AUX_EMBED; w.name = name ? name : "embedding"; w.cout = dim; w.y_off = dst_off; w.dev_table = d_table_f16; w.vocab = vocab;
+    return P(plan)->exec.add_wave(w) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_plan_add_argmax(void *plan, const char *name, uint64_t src_off, uint32_t rows, int advance, uint32_t max_seq) {
+    if (!plan || !rows) return set_error("plan_add_argmax: bad arguments");
+    HostWave w;
+    w.kind = AUX_ARGMAX; w.name = name ? name : "argmax"; w.cout = rows; w.src_off = src_off; w.advance = advance != 0; w.max_seq = max_seq;
+    return P(plan)->exec.add_wave(w) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_plan_set_tokens(void *plan, const int32_t *h_tokens, uint32_t n, void *stream) {
+    if (!plan || !h_tokens) return set_error("plan_set_tokens: bad arguments");
+    Executor &e = P(plan)->exec;
+    int *d = e.tokens_ptr();
+    if (!d) return set_error(e.err);
+    if (n > e.pitch()) return set_error("plan_set_tokens: more tokens than columns");
+    const cudaError_t r = cudaMemcpyAsync(d, h_tokens, (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice, (cudaStream_t)stream);
+    return r == cudaSuccess ? 0 : set_error(std::string("plan_set_tokens: ") + cudaGetErrorString(r));
+}
+
+int k44b_plan_get_next_tokens(void *plan, int32_t *h_tokens, uint32_t n, void *stream) {
+    if (!plan || !h_tokens) return set_error("plan_get_next_tokens: bad arguments");
+    Executor &e = P(plan)->exec;
+    int *d = e.next_tokens_ptr();
+    if (!d) return set_error(e.err);
+    if (n > e.pitch()) return set_error("plan_get_next_tokens: more tokens than columns");
+    cudaError_t r = cudaMemcpyAsync(h_tokens, d, (size_t)n * sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (r == cudaSuccess) r = cudaStreamSynchronize((cudaStream_t)stream);
+    return r == cudaSuccess ? 0 : set_error(std::string("plan_get_next_tokens: ") + cudaGetErrorString(r));
+}
+
 int k44b_plan_set_decode_pos(void *plan, int pos, void *stream) {
     if (!plan || pos < 0) return set_error("plan_set_decode_pos: bad arguments");
     int *d = P(plan)->exec.decode_pos_ptr();

@@ -181,6 +181,9 @@ void Executor::release() {
     for (void *p : ipc_opened_) cudaIpcCloseMemHandle(p);
     ipc_opened_.clear();
     cudaFree(d_pos_); d_pos_ = nullptr;
+    cudaFree(d_tokens_); d_tokens_ = nullptr;
+    cudaFree(d_next_tokens_); d_next_tokens_ = nullptr;
+    cudaFree(d_argmax_); d_argmax_ = nullptr; argmax_words_ = 0;
     cudaFree(d_decode_partial_); d_decode_partial_ = nullptr; decode_partial_bytes_ = 0;
     cudaFree(d_sync_); d_sync_ = nullptr;
     cudaFree(d_peers_); d_peers_ = nullptr;
@@ -254,6 +257,26 @@ int *Executor::decode_pos_ptr() {
     return d_pos_;
 }
 
+static int *alloc_words(int device, uint32_t n, std::string &err) {
+    int *p = nullptr;
+    if (cudaSetDevice(device) != cudaSuccess || cudaMalloc(&p, (size_t)n * sizeof(int)) != cudaSuccess || cudaMemset(p, 0, (size_t)n * sizeof(int)) != cudaSuccess) {
+        err = "token buffer allocation failed";
+        cudaFree(p);
+        return nullptr;
+    }
+    return p;
+}
+int *Executor::tokens_ptr() {
+    if (!ready()) { fail("executor not initialised"); return nullptr; }
+    if (!d_tokens_) d_tokens_ = alloc_words(device_, pitch_, err);
+    return d_tokens_;
+}
+int *Executor::next_tokens_ptr() {
+    if (!ready()) { fail("executor not initialised"); return nullptr; }
+    if (!d_next_tokens_) d_next_tokens_ = alloc_words(device_, pitch_, err);
+    return d_next_tokens_;
+}
+
 // Element-wise / attention step: range-checked here, launched from the same command list as the waves.
 bool Executor::add_aux(const HostWave &w) {
     if (!ready()) return fail("executor not initialised");
@@ -314,6 +337,31 @@ bool Executor::add_aux(const HostWave &w) {
         reads(w.src_off, rq); reads(w.src2_off, rk); reads(w.src3_off, rk);
         // q and k are rotated in place, the caches are appended to: treat everything touched as written
         dw.write_lo = std::min({w.y_off, w.src_off, w.src2_off, rlo}); dw.write_hi = std::max({w.y_off + rq * pitch_, rhi});
+        break;
+    }
+    case AUX_EMBED:
+        if (!w.cout || w.cout % 8u || !w.dev_table || !w.vocab || !inside(w.y_off, w.cout)) return fail("embedding '" + w.name + "': bad table or destination");
+        x.table = (const __half *)w.dev_table; x.vocab = w.vocab;
+        if (!(x.tokens = tokens_ptr())) return false;
+        rlo = 0; rhi = 0;
+        dw.write_lo = w.y_off; dw.write_hi = w.y_off + (uint64_t)w.cout * pitch_;
+        break;
+    case AUX_ARGMAX: {
+        if (!w.cout || pitch_ % 64u || !inside(w.src_off, w.cout)) return fail("arg-max '" + w.name + "' leaves the canvas");
+        x.advance = w.advance ? 1u : 0u; x.max_seq = w.max_seq;
+        if (!(x.next_tokens = next_tokens_ptr()) || !(x.tokens = tokens_ptr())) return false;
+        if (w.advance && !(x.pos_rw = decode_pos_ptr())) return false;
+        const size_t words = (size_t)((w.cout + kArgmaxChunk - 1u) / kArgmaxChunk) * pitch_;
+        if (words > argmax_words_) {
+            if (!check(cudaDeviceSynchronize(), "synchronise")) return false;
+            cudaFree(d_argmax_); d_argmax_ = nullptr; argmax_words_ = 0;
+            if (!check(cudaMalloc(&d_argmax_, words * sizeof(unsigned long long)), "arg-max scratch allocation")) return false;
+            argmax_words_ = words;
+            for (auto &o : waves_) if (o.is_aux && o.aux.kind == AUX_ARGMAX) o.aux.argmax_scratch = d_argmax_;
+        }
+        x.argmax_scratch = d_argmax_;
+        reads(w.src_off, w.cout);
+        dw.write_lo = 0; dw.write_hi = 0;
         break;
     }
     default: return fail("unknown command kind");
@@ -612,7 +660,7 @@ bool Executor::launch_group(size_t gi, cudaStream_t stream) {
 bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
     cudaError_t e;
     if (w.is_aux) {
-        launches_ += w.aux.kind == AUX_ROPE_ATTN ? 3u : (w.aux.kind == AUX_DECODE_ATTN ? 3u : 1u);
+        launches_ += (w.aux.kind == AUX_ROPE_ATTN || w.aux.kind == AUX_DECODE_ATTN) ? 3u : (w.aux.kind == AUX_ARGMAX ? 2u : 1u);
         return check(launch_aux(w.aux, pdl_, stream), ("launch of '" + w.name + "'").c_str());
     }
     if (w.path == PATH_UMMA && w.use_cluster) {

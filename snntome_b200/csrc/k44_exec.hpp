@@ -59,6 +59,8 @@ class Executor {
     bool begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t columns, int force_path);
     bool add_wave(const HostWave &w);
     bool add_aux(const HostWave &w);                               // HostWave::kind != 0
+    int *tokens_ptr();                                             // device int32 [pitch]: token id per column (embedding gather input)
+    int *next_tokens_ptr();                                        // device int32 [pitch]: result of the last arg-max command
     int *decode_pos_ptr();                                         // device word holding the position decode attention works at
     void set_io(uint64_t in_off, uint32_t in_c, uint64_t out_off, uint32_t out_c, uint32_t width);
     bool init(const HostPlan &plan, int device, int force_path);   // begin + add_wave* + set_io
@@ -116,6 +118,9 @@ class Executor {
     float *d_scratch_ = nullptr;
     uint32_t *d_counters_ = nullptr;
     int *d_pos_ = nullptr;                // decode position
+    int *d_tokens_ = nullptr, *d_next_tokens_ = nullptr;
+    unsigned long long *d_argmax_ = nullptr;
+    size_t argmax_words_ = 0;
     float *d_decode_partial_ = nullptr;   // per-chunk partial attention results, shared by all decode-attention commands
     size_t decode_partial_bytes_ = 0;
     // neuron sharding over several GPUs (see PeerArgs)

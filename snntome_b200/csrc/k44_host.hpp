@@ -192,7 +192,11 @@ struct HostWave {
     // Commands that are not waves (K44ExecCmd types RMSNORM / SWIGLU / ROPE_GQA_ATTN of the reference,
     // wavec/k44_plan_types.hpp:603-650): kind != 0, `cout` = channels of the main operand, `bias` = gamma (RMSNorm),
     // src_off / src2_off / src3_off = x | gate, up | q, k, v, y_off = destination.
-    int kind = 0;                      // 0 wave, 1 RMSNorm, 2 SwiGLU product, 3 rotary + causal attention, 4 decode attention (cache)
+    int kind = 0;                      // 0 wave, 1 RMSNorm, 2 SwiGLU product, 3 rotary + causal attention, 4 decode attention (cache),
+                                       // 5 embedding gather (table in device memory), 6 arg-max over rows (greedy sampling)
+    const void *dev_table = nullptr;   // kind 5: FP16 [vocab][cout] row-major, device memory, owned by the caller
+    uint32_t vocab = 0;
+    bool advance = false;              // kind 6: feed the result back as the next tokens and advance the decode position
     uint64_t src2_off = 0, src3_off = 0, kcache_off = 0, vcache_off = 0;
     float eps = 1e-5f, rope_theta = 10000.0f;
     uint32_t h_q = 0, h_kv = 0, head_dim = 0, seq_len = 0, max_seq = 0;

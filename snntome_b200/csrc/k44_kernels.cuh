@@ -90,7 +90,7 @@ struct WaveArgs {
 };
 
 // Element-wise / attention steps between waves (k44_valu.cu)
-enum AuxKind : int { AUX_NONE = 0, AUX_RMSNORM = 1, AUX_SWIGLU = 2, AUX_ROPE_ATTN = 3, AUX_DECODE_ATTN = 4 };
+enum AuxKind : int { AUX_NONE = 0, AUX_RMSNORM = 1, AUX_SWIGLU = 2, AUX_ROPE_ATTN = 3, AUX_DECODE_ATTN = 4, AUX_EMBED = 5, AUX_ARGMAX = 6 };
 struct AuxArgs {
     int kind = AUX_NONE;
     __half *canvas = nullptr;
@@ -103,7 +103,15 @@ struct AuxArgs {
     float neg_log_theta = -9.210340371976184f;
     const int *pos_ptr = nullptr;                                    // decode: current position, device memory
     float *partial = nullptr;                                        // decode: per-chunk partial results [chunks][h_q][pitch][kDecodeRow]
+    // token I/O: embedding gather (table FP16 [vocab][rows] row-major in device memory, one token id per column) and
+    // greedy arg-max over the rows of a tensor (lowest row wins ties); `advance` also feeds the result back as the next
+    // step's tokens and moves the decode position on by one (saturating at max_seq - 1)
+    const __half *table = nullptr;
+    uint32_t vocab = 0, advance = 0;
+    int *tokens = nullptr, *next_tokens = nullptr, *pos_rw = nullptr;
+    unsigned long long *argmax_scratch = nullptr;                    // [row chunks][pitch] packed (value key, row)
 };
+constexpr uint32_t kArgmaxChunk = 256;                               // rows per arg-max CTA
 constexpr uint32_t kDecodeChunk = 32;
 constexpr uint32_t kDecodeRow = 68;                                  // floats per partial result: 64 values, maximum, sum, 2 pad (16-byte aligned rows)                                // cache positions per partial-attention CTA
 cudaError_t launch_aux(const AuxArgs &a, bool dependent_launch, cudaStream_t s);

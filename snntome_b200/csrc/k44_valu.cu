@@ -404,6 +404,77 @@ __global__ void __launch_bounds__(256) k44_valu_decode_attn_combine_kernel(const
 #pragma unroll
     for (int e = 0; e < 8; ++e) dst[(uint64_t)e * a.pitch] = __float2half_rn(o[e] * inv);
 }
+// ---- token I/O ---------------------------------------------------------------------------------------------------------
+// Embedding gather: column b of the destination tensor becomes row tokens[b] of the table. One thread per (8 channels,
+// column): one 16-byte load from the table row, eight 2-byte stores (consecutive lanes = consecutive columns).
+__global__ void __launch_bounds__(256) k44_valu_embed_kernel(const AuxArgs a) {
+    pdl_enter();
+    const uint32_t chunks = a.rows / 8u;
+    const uint64_t i = (uint64_t)blockIdx.x * 256u + threadIdx.x;
+    if (i >= (uint64_t)chunks * a.pitch) return;
+    const uint32_t col = (uint32_t)(i % a.pitch), c8 = (uint32_t)(i / a.pitch);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (col < a.columns) {
+        const int tok = a.tokens[col];
+        if (tok >= 0 && (uint32_t)tok < a.vocab) v = *reinterpret_cast<const uint4 *>(a.table + (uint64_t)tok * a.rows + c8 * 8u);
+    }
+    const __half *h = reinterpret_cast<const __half *>(&v);
+    __half *dst = a.canvas + a.dst_off + (uint64_t)c8 * 8u * a.pitch + col;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dst[(uint64_t)e * a.pitch] = h[e];
+}
+
+// Arg-max over the rows of a tensor, per column. FP16 values are mapped to integer keys that sort like the numbers; a key
+// and the complement of its row are packed into 64 bits so that one max() picks the largest value and, among equals, the
+// lowest row. NaN sorts below everything.
+__device__ __forceinline__ unsigned long long argmax_pack(__half v, uint32_t row) {
+    const uint16_t u = __half_as_ushort(v);
+    uint32_t key = (u & 0x8000u) ? (uint32_t)(0x7fffu - (u & 0x7fffu)) : (uint32_t)(0x8000u + u);
+    if ((u & 0x7fffu) > 0x7c00u) key = 0u;
+    return ((unsigned long long)key << 32) | (unsigned long long)(0xffffffffu - row);
+}
+
+// stage 1: CTA = kArgmaxChunk rows x 64 columns; 4 threads per column take every fourth row
+__global__ void __launch_bounds__(256) k44_valu_argmax_partial_kernel(const AuxArgs a) {
+    pdl_enter();
+    __shared__ unsigned long long best_s[4][64];
+    const uint32_t col = blockIdx.x * 64u + (threadIdx.x & 63u), ph = threadIdx.x >> 6;
+    const uint32_t r0 = blockIdx.y * kArgmaxChunk, r1 = min(a.rows, r0 + kArgmaxChunk);
+    unsigned long long best = 0ull;
+    const __half *src = a.canvas + a.src_off + col;
+    for (uint32_t r = r0 + ph; r < r1; r += 4u) best = max(best, argmax_pack(src[(uint64_t)r * a.pitch], r));
+    best_s[ph][threadIdx.x & 63u] = best;
+    __syncthreads();
+    if (ph == 0u) {
+        const uint32_t c = threadIdx.x & 63u;
+        best = max(max(best_s[0][c], best_s[1][c]), max(best_s[2][c], best_s[3][c]));
+        a.argmax_scratch[(uint64_t)blockIdx.y * a.pitch + col] = best;
+    }
+}
+
+// stage 2: one thread per column folds the chunks, writes the winning row and optionally feeds it back
+__global__ void __launch_bounds__(256) k44_valu_argmax_final_kernel(const AuxArgs a) {
+    pdl_enter();
+    const uint32_t col = blockIdx.x * 256u + threadIdx.x;
+    const uint32_t chunks = (a.rows + kArgmaxChunk - 1u) / kArgmaxChunk;
+    if (col < a.pitch) {
+        unsigned long long best = 0ull;
+        for (uint32_t c0 = 0; c0 < chunks; c0 += 8u) {
+            unsigned long long v[8];
+#pragma unroll
+            for (uint32_t u = 0; u < 8u; ++u) v[u] = a.argmax_scratch[(uint64_t)min(c0 + u, chunks - 1u) * a.pitch + col];
+#pragma unroll
+            for (uint32_t u = 0; u < 8u; ++u) best = max(best, v[u]);
+        }
+        const int row = (int)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
+        a.next_tokens[col] = row;
+        if (a.advance && col < a.columns) a.tokens[col] = row;
+    }
+    if (a.advance && col == 0u && a.pos_rw) {
+        const int p = *a.pos_rw;
+        *a.pos_rw = (a.max_seq && p + 1 >= (int)a.max_seq) ? (int)a.max_seq - 1 : p + 1;
+    }
+}
 
 cudaError_t launch_aux(const AuxArgs &a, bool pdl, cudaStream_t s) {
     cudaError_t e = cudaSuccess;
@@ -448,6 +519,16 @@ cudaError_t launch_aux(const AuxArgs &a, bool pdl, cudaStream_t s) {
         }
         if (e == cudaSuccess)
             e = launch_k(k44_valu_decode_attn_combine_kernel, dim3((uint32_t)(((uint64_t)a.h_q * a.pitch * 8u + 255u) / 256u)), dim3(256), pdl, s, a, (const float *)a.partial);
+        break;
+    }
+    case AUX_EMBED:
+        if (a.rows % 8u || !a.table || !a.tokens) return cudaErrorInvalidValue;
+        e = launch_k(k44_valu_embed_kernel, dim3((uint32_t)(((uint64_t)(a.rows / 8u) * a.pitch + 255u) / 256u)), dim3(256), pdl, s, a);
+        break;
+    case AUX_ARGMAX: {
+        if (a.pitch % 64u || !a.argmax_scratch || !a.next_tokens || a.rows == 0) return cudaErrorInvalidValue;
+        e = launch_k(k44_valu_argmax_partial_kernel, dim3(a.pitch / 64u, (a.rows + kArgmaxChunk - 1u) / kArgmaxChunk), dim3(256), pdl, s, a);
+        if (e == cudaSuccess) e = launch_k(k44_valu_argmax_final_kernel, dim3((a.pitch + 255u) / 256u), dim3(256), pdl, s, a);
         break;
     }
     default: return cudaErrorInvalidValue;

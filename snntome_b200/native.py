@@ -207,6 +207,26 @@ class NativePlan:
                                                int(vcache_off), int(h_q), int(h_kv), int(head_dim), int(max_seq), float(theta), int(bool(llama3))) != 0:
             raise NativeError(f"add_decode_attn: {last_error()}")
 
+    def add_embedding(self, table_dev_ptr: int, vocab: int, dim: int, dst_off: int, name: str = "embedding") -> None:
+        """`table_dev_ptr`: FP16 [vocab][dim] row-major in device memory; the caller keeps it alive."""
+        if self._lib.k44b_plan_add_embedding(self._ptr, name.encode(), ctypes.c_void_p(int(table_dev_ptr)), int(vocab), int(dim), int(dst_off)) != 0:
+            raise NativeError(f"add_embedding: {last_error()}")
+
+    def add_argmax(self, src_off: int, rows: int, advance: bool = False, max_seq: int = 0, name: str = "argmax") -> None:
+        if self._lib.k44b_plan_add_argmax(self._ptr, name.encode(), int(src_off), int(rows), int(bool(advance)), int(max_seq)) != 0:
+            raise NativeError(f"add_argmax: {last_error()}")
+
+    def set_tokens(self, tokens, stream=None) -> None:
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        if self._lib.k44b_plan_set_tokens(self._ptr, t.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), int(t.size), ctypes.c_void_p(self._stream_ptr(stream))) != 0:
+            raise NativeError(f"set_tokens: {last_error()}")
+
+    def next_tokens(self, n: int, stream=None) -> np.ndarray:
+        out = np.empty(int(n), dtype=np.int32)
+        if self._lib.k44b_plan_get_next_tokens(self._ptr, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), int(n), ctypes.c_void_p(self._stream_ptr(stream))) != 0:
+            raise NativeError(f"next_tokens: {last_error()}")
+        return out
+
     def set_decode_pos(self, pos: int, stream=None) -> None:
         if self._lib.k44b_plan_set_decode_pos(self._ptr, int(pos), ctypes.c_void_p(self._stream_ptr(stream))) != 0:
             raise NativeError(f"set_decode_pos: {last_error()}")

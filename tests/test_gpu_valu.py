@@ -104,3 +104,62 @@ def test_decode_attention_with_cache(h_q, h_kv, max_seq, steps):
         close(got[o_off:kc_off], canvas[o_off:kc_off], f"decode attention at position {pos}")
         close(got[kc_off:], canvas[kc_off:], f"caches after position {pos}")
     npn.close()
+
+
+def test_embedding_gather_and_argmax_are_exact():
+    import torch
+    vocab, dim, pitch, cols, rows = 1000, 256, 64, 50, 3000
+    rng = np.random.default_rng(21)
+    table = f16(rng.normal(0, 1, (vocab, dim)))
+    tokens = rng.integers(0, vocab, size=cols).astype(np.int32)
+    logits = (rng.integers(-40, 40, size=(rows, pitch)) / 8.0).astype(np.float16)          # coarse values: plenty of ties
+    logits[rows - 1, 7] = np.float16(np.nan)
+    canvas = np.zeros((dim + rows) * pitch, dtype=np.uint16)
+    canvas[dim * pitch:] = logits.view(np.uint16).reshape(-1)
+    d_table = torch.from_numpy(table.view(np.int16)).cuda()
+    npn, c = run(lambda p: (p.add_embedding(d_table.data_ptr(), vocab, dim, 0), p.add_argmax(dim * pitch, rows)), canvas, pitch, cols)
+    npn.set_tokens(tokens)
+    npn.execute_graph()
+    assert npn.status() == 0
+    got = c.cpu().numpy().view(np.uint16)[: dim * pitch].reshape(dim, pitch)
+    assert np.array_equal(got[:, :cols], table[tokens].T)
+    assert not got[:, cols:].any()
+    want = np.argmax(np.where(np.isnan(logits), -np.inf, logits.astype(np.float32)), axis=0)   # first maximum wins
+    assert np.array_equal(npn.next_tokens(pitch), want.astype(np.int32))
+    npn.close()
+
+
+def test_greedy_loop_feeds_tokens_back_on_the_device():
+    """embedding -> dense wave (logits) -> arg-max with feedback, replayed as one graph: every step's token must be a
+    maximiser of the logits the oracle computes from the previous token (within the wave tolerance), and the decode
+    position advances and saturates."""
+    import torch
+    from snntome_b200 import synth
+    from snntome_b200.plan import Plan, Wave
+    vocab, dim, pitch, cols = 512, 128, 64, 64
+    rng = np.random.default_rng(22)
+    table = f16(rng.normal(0, 1, (vocab, dim)))
+    w = f16(rng.normal(0, 0.3, (vocab, dim)))
+    offs = (np.arange(dim, dtype=np.uint32) * pitch)[None, :].repeat(vocab // 128, axis=0)
+    wave = Wave(cout=vocab, group=128, fan_in=dim, idx=offs, weights=w, bias=None, y_off=dim * pitch, act=0, name="lm_head")
+    plan = Plan(canvas_elems=(dim + vocab) * pitch, pitch=pitch, columns=cols, input_off=0, input_c=dim, output_off=dim * pitch, output_c=vocab, waves=[wave])
+    d_table = torch.from_numpy(table.view(np.int16)).cuda()
+    npn = NativePlan.create(plan.canvas_elems, pitch, cols, device=0)
+    npn.add_embedding(d_table.data_ptr(), vocab, dim, 0)
+    npn.add_wave(wave)
+    npn.add_argmax(dim * pitch, vocab, advance=True, max_seq=3)
+    tokens = rng.integers(0, vocab, size=cols).astype(np.int32)
+    npn.set_tokens(tokens)
+    npn.set_decode_pos(0)
+    for step in range(4):
+        npn.execute_graph()
+        nxt = npn.next_tokens(cols)
+        assert npn.status() == 0
+        canvas = np.zeros(plan.canvas_elems, dtype=np.uint16)
+        canvas[: dim * pitch].reshape(dim, pitch)[:, :cols] = table[tokens].T
+        O.wave_forward(canvas, wave, plan)
+        logits = canvas[dim * pitch:].view(np.float16).reshape(vocab, pitch)[:, :cols].astype(np.float32)
+        chosen = logits[nxt, np.arange(cols)]
+        assert np.all(chosen >= logits.max(axis=0) - (ATOL + RTOL * np.abs(logits.max(axis=0)))), f"step {step}"
+        tokens = nxt                                      # what the device fed back
+    npn.close()
