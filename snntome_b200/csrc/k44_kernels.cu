@@ -8,9 +8,14 @@
 //      warps 2-5 epilogue: tcgen05.ld -> bias -> activation -> residual -> FP16 RTE -> canvas rows.
 //    Replaces the roles of the reference's three mma.sync kernels and its tcgen05 prototype
 //    (kernels/cuda/kernel44_cuda_pack.cuh:242-286, 370-391, 438-623) for run-structured gathers.
+//  * k44_wave_umma_cluster_kernel — small waves (fewer tiles than SMs): the K splits of a tile form a thread-block
+//    cluster and reduce through distributed shared memory; written for programmatic dependent launch and for
+//    grouped launches of independent waves.
 //  * k44_wave_fma_kernel — general FP32-FMA path (any gather table, any element alignment, any group
 //    size); also the cross-check for the tensor-core path.
 //  * packer / conversion kernels.
+//  (Token-shifted runs: k44_shift_kernel.cu. Element-wise and attention steps: k44_valu.cu. Epilogue and the peer
+//  exchange of neuron-sharded plans: k44_epilogue.cuh.)
 //
 // Every wait on a barrier is bounded in time; on expiry the kernel records a status bit, drains its
 // own copies, frees its tensor memory and returns.
