@@ -8,6 +8,7 @@ namespace k44b {
 const char *status_string(uint32_t st) {
     if (st == 0) return "ok";
     if (st & ST_BAD_INDEX) return "gather offset outside the canvas";
+    if (st & ST_TIMEOUT_PEER) return "timed out waiting for a peer GPU's rows";
     if (st & ST_TIMEOUT_DRAIN) return "timed out draining in-flight copies";
     if (st & ST_TIMEOUT_PRODUCER) return "producer timed out waiting for a free stage";
     if (st & ST_TIMEOUT_MMA) return "MMA issuer timed out waiting for operands";
@@ -156,6 +157,10 @@ UmmaDesc make_umma_desc(uint32_t n_tile, int variant) {
     // (bit 16 = 1), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
     d.idesc = (1u << 4) | (1u << 16) | ((n_tile >> 3) << 17) | ((kTileM >> 4) << 24);
     d.wait_cycles = 4000000000ull;     // about two seconds at boost clock
+    if (const char *e = std::getenv("K44B_WAIT_MS")) {     // bound of every in-kernel wait, in milliseconds at ~2 GHz
+        const long ms = std::atol(e);
+        if (ms > 0 && ms <= 60000) d.wait_cycles = (unsigned long long)ms * 2000000ull;
+    }
     return d;
 }
 

@@ -74,3 +74,45 @@ def test_plans_with_general_path_waves_are_rejected():
     with pytest.raises(NativeError, match="tensor-core"):
         p0.set_peers_raw(0, 2, [p0.canvas_ptr, p1.canvas_ptr], [p0.sync_ptr, p1.sync_ptr])
     p0.close(); p1.close()
+
+
+def test_missing_peer_ends_the_wait_with_a_status_bit(monkeypatch):
+    """A rank whose peer never shows up: its second launch waits for the peer's first launch count, the bounded wait
+    (shortened to 200 ms here) runs out, the kernel records status bit 5 and returns, and the context stays usable —
+    a plan executed afterwards on the same GPU still matches the oracle. Nothing faults or hangs: the flag is simply
+    never written."""
+    import torch
+    monkeypatch.setenv("K44B_WAIT_MS", "200")
+    plan = synth.sparse_plan(seed=97, input_rows=1024, waves=2, cout=512, runs=8, run_len=32, columns=64, group=128, act=ACT_RELU)
+    x = synth.random_input(plan, 98)
+    p0 = NativePlan.from_plan(shard.shard_plan(plan, 0, 2), device=0)
+    p1 = NativePlan.from_plan(shard.shard_plan(plan, 1, 2), device=0)      # never executes
+    cps, sps = [p0.canvas_ptr, p1.canvas_ptr], [p0.sync_ptr, p1.sync_ptr]
+    p0.set_peers_raw(0, 2, cps, sps)
+    p1.set_peers_raw(1, 2, cps, sps)
+    xt = torch.from_numpy(np.ascontiguousarray(x).view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    p0.canvas_tensor()[plan.input_off: plan.input_off + xt.numel()] = xt
+    p0.execute_wave(0)                    # needs nothing from the peer
+    torch.cuda.synchronize()
+    assert p0.status() == 0
+    p0.execute_wave(1)                    # needs the peer's launch 0, which never comes
+    torch.cuda.synchronize()
+    with pytest.raises(NativeError) as ei:
+        p0.status()
+    assert "0x20" in str(ei.value) or "peer" in str(ei.value).lower()
+    p0.close(); p1.close()
+    monkeypatch.delenv("K44B_WAIT_MS")
+    small = synth.config0(group=128)                                       # the context is still healthy
+    xs = synth.random_input(small, 11)
+    npn = NativePlan.from_plan(small, device=0)
+    c = npn.canvas_tensor()
+    c[small.input_off: small.input_off + xs.size] = torch.from_numpy(xs.view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    npn.execute()
+    assert npn.status() == 0
+    want = O.run_plan(small, xs)
+    got = c.cpu().numpy().view(np.uint16)
+    for w in small.waves:
+        a, b = w.y_off, w.y_off + w.cout * small.pitch
+        ok, err, k = O.compare(got[a:b], want[a:b], RTOL, ATOL)
+        assert ok, (w.name, err, k)
+    npn.close()
