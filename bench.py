@@ -171,7 +171,7 @@ def cpu_baseline(w: dict, seconds_target: float = 15.0, threads: int | None = No
     while True:
         O.wave_forward(canvas, wave, plan)
         reps += 1
-        if time.perf_counter() - t0 > seconds_target / 2 or reps >= 8:
+        if time.perf_counter() - t0 > seconds_target / 2 or reps >= 400:
             break
     dt = (time.perf_counter() - t0) / reps
     flops = 2.0 * cout * fan_in * 64
