@@ -736,6 +736,7 @@ def main() -> None:
     ap.add_argument("--scale", type=float, default=float(os.environ.get("K44B_BENCH_SCALE", "1.0")))
     ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "decode-full", "pruned-sharded", "token-shift", "tiny"])
     ap.add_argument("--layers", type=int, default=16, help="decode workload: decoder layers (16 = the 1B shape)")
+    ap.add_argument("--columns", type=int, default=64, help="ultra-sparse workload: valid columns (batch) per GPU, 1..64")
     ap.add_argument("--max-shift", type=int, default=7, help="token-shift workload: largest token shift drawn per run (0 = unshifted runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -752,6 +753,7 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     w = workload(args.scale)
+    w["columns"] = max(1, min(64, args.columns))
     warmup = max(3, args.warmup)
     cfg = {"workload": "ultra-sparse plan: 40M-row FP16 substrate, 4 waves x 1M neurons, fan-in 4096 as 64 runs of 64 rows, "
                        "groups of 128, ReLU, 64 columns per GPU",

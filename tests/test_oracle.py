@@ -207,3 +207,93 @@ def test_token_shift_oracle_twins_agree_and_pad_causally():
         want = np.float16(0.5 * acc * (1 + __import__("math").erf(acc * 0.7071067811865476)))
         got = a[wave.y_off + 5 * pitch + col: wave.y_off + 5 * pitch + col + 1].view(np.float16)[0]
         assert abs(float(got) - float(want)) <= 1e-3 + 2e-3 * abs(float(want))
+
+
+# ---- element-wise / attention oracle (oracle/valu.py) against independent loops ---------------------------------------
+def _f16(a):
+    return np.asarray(a, dtype=np.float32).astype(np.float16).view(np.uint16)
+
+
+def test_valu_oracle_rmsnorm_swiglu_against_direct_formulas():
+    from oracle import valu as V
+    rng = np.random.default_rng(1)
+    dim, pitch = 48, 16
+    canvas = np.zeros(4 * dim * pitch, dtype=np.uint16)
+    canvas[: 2 * dim * pitch] = _f16(rng.normal(0, 1, 2 * dim * pitch))
+    gamma = _f16(1 + 0.2 * rng.normal(size=dim))
+    x = canvas[: dim * pitch].view(np.float16).astype(np.float64).reshape(dim, pitch)
+    u = canvas[dim * pitch: 2 * dim * pitch].view(np.float16).astype(np.float64).reshape(dim, pitch)
+    V.rmsnorm(canvas, 0, 2 * dim * pitch, dim, pitch, 1e-5, gamma)
+    V.swiglu(canvas, 0, dim * pitch, 3 * dim * pitch, dim, pitch)
+    g = gamma.view(np.float16).astype(np.float64)
+    want_n = np.empty((dim, pitch))
+    for t in range(pitch):
+        ms = sum(x[c, t] ** 2 for c in range(dim)) / dim
+        for c in range(dim):
+            want_n[c, t] = x[c, t] / np.sqrt(ms + 1e-5) * g[c]
+    got_n = canvas[2 * dim * pitch: 3 * dim * pitch].view(np.float16).astype(np.float64).reshape(dim, pitch)
+    assert np.allclose(got_n, want_n, rtol=1e-3, atol=1e-4)
+    got_s = canvas[3 * dim * pitch:].view(np.float16).astype(np.float64).reshape(dim, pitch)
+    assert np.allclose(got_s, x * u, rtol=1e-3, atol=1e-4)
+
+
+def test_valu_oracle_rope_and_attention_against_direct_loops():
+    from oracle import valu as V
+    rng = np.random.default_rng(2)
+    h_q, h_kv, hd, seq, frames = 4, 2, 8, 6, 2
+    pitch = seq * frames
+    rq, rk = h_q * hd, h_kv * hd
+    canvas = np.zeros((2 * rq + 2 * rk) * pitch, dtype=np.uint16)
+    canvas[: (rq + 2 * rk) * pitch] = _f16(rng.normal(0, 1, (rq + 2 * rk) * pitch))
+    q_off, k_off, v_off, o_off = 0, rq * pitch, (rq + rk) * pitch, (rq + 2 * rk) * pitch
+    q0 = canvas[q_off:k_off].view(np.float16).astype(np.float64).reshape(rq, pitch)
+    V.rope(canvas, q_off, h_q, hd, pitch, seq, 10000.0, False)
+    V.rope(canvas, k_off, h_kv, hd, pitch, seq, 10000.0, False)
+    q = canvas[q_off:k_off].view(np.float16).astype(np.float64).reshape(rq, pitch)
+    k = canvas[k_off:v_off].view(np.float16).astype(np.float64).reshape(rk, pitch)
+    v = canvas[v_off:o_off].view(np.float16).astype(np.float64).reshape(rk, pitch)
+    # rotary: pair (p, p + hd/2), angle = position * theta^(-2p/hd), position restarts in every sequence
+    for h in range(h_q):
+        for p in range(hd // 2):
+            for t in range(pitch):
+                ang = (t % seq) * 10000.0 ** (-2.0 * p / hd)
+                a, b = q0[h * hd + p, t], q0[h * hd + p + hd // 2, t]
+                assert abs(q[h * hd + p, t] - (a * np.cos(ang) - b * np.sin(ang))) < 2e-3
+                assert abs(q[h * hd + p + hd // 2, t] - (a * np.sin(ang) + b * np.cos(ang))) < 2e-3
+    V.causal_attention(canvas, q_off, k_off, v_off, o_off, h_q, h_kv, hd, pitch, seq)
+    out = canvas[o_off:].view(np.float16).astype(np.float64).reshape(rq, pitch)
+    for h in range(h_q):
+        kv = h // (h_q // h_kv)
+        for t in range(pitch):
+            s0 = (t // seq) * seq
+            sc = np.array([q[h * hd:(h + 1) * hd, t] @ k[kv * hd:(kv + 1) * hd, u] / np.sqrt(hd) for u in range(s0, t + 1)])
+            p = np.exp(sc - sc.max()); p /= p.sum()
+            want = sum(p[i] * v[kv * hd:(kv + 1) * hd, s0 + i] for i in range(len(p)))
+            assert np.allclose(out[h * hd:(h + 1) * hd, t], want, rtol=2e-3, atol=1e-3)
+
+
+def test_valu_oracle_decode_attention_equals_causal_attention_on_the_last_token():
+    """Appending tokens one by one through the cache must reproduce, for the newest token, what causal attention over
+    the whole sequence computes (same rotary positions)."""
+    from oracle import valu as V
+    rng = np.random.default_rng(3)
+    h_q, h_kv, hd, T, pitch = 4, 2, 8, 5, 8
+    rq, rk = h_q * hd, h_kv * hd
+    toks = _f16(rng.normal(0, 1, (T, rq + 2 * rk, pitch)))           # per step: q, k, v rows for `pitch` sequences
+    # decode path
+    sizes = [rq, rk, rk, rq, rk * T, rk * T]
+    offs = [int(x) for x in np.cumsum([0] + sizes) * pitch]
+    dec = np.zeros(offs[-1], dtype=np.uint16)
+    for pos in range(T):
+        dec[: offs[3]] = toks[pos].reshape(-1)
+        V.decode_attention(dec, offs[0], offs[1], offs[2], offs[3], offs[4], offs[5], h_q, h_kv, hd, pitch, T, pos)
+    got = dec[offs[3]: offs[4]].view(np.float16).astype(np.float64).reshape(rq, pitch)
+    # the same history as one sequence per column: prefill layout [channels][T] for every column separately
+    for b in range(pitch):
+        pre = np.zeros((2 * rq + 2 * rk) * T, dtype=np.uint16)
+        pre[: (rq + 2 * rk) * T] = np.ascontiguousarray(toks[:, :, b].T).reshape(-1)
+        V.rope(pre, 0, h_q, hd, T, T)
+        V.rope(pre, rq * T, h_kv, hd, T, T)
+        V.causal_attention(pre, 0, rq * T, (rq + rk) * T, (rq + 2 * rk) * T, h_q, h_kv, hd, T, T)
+        want = pre[(rq + 2 * rk) * T:].view(np.float16).astype(np.float64).reshape(rq, T)[:, T - 1]
+        assert np.allclose(got[:, b], want, rtol=3e-3, atol=2e-3)
