@@ -103,7 +103,7 @@ __device__ __forceinline__ float act_fast(float v) {
 // global store fills complete 32-byte sectors. Must be called by all 32 lanes of a warp.
 template <int ACT, bool RES, bool MAP>
 __device__ __forceinline__ void stage_and_store_t(const WaveArgs &a, const float (&v)[32], float bias, bool live, uint32_t oj,
-                                                  uint64_t col0, uint8_t *wstage, uint32_t lane, uint32_t pieces) {
+                                                  uint64_t col0, uint8_t *wstage, uint32_t lane) {
     uint4 *slot = reinterpret_cast<uint4 *>(wstage + lane * 80u);
     uint32_t pk[16];
     if (RES) {
@@ -138,7 +138,7 @@ __device__ __forceinline__ void stage_and_store_t(const WaveArgs &a, const float
         const uint32_t oj_r = __shfl_sync(0xffffffffu, oj, r);
         const int live_r = __shfl_sync(0xffffffffu, live ? 1 : 0, r);
         const uint4 val = *reinterpret_cast<const uint4 *>(wstage + r * 80u + piece * 16u);
-        if (live_r && piece < pieces) {
+        if (live_r) {
             const uint64_t off = a.y_off + (uint64_t)oj_r * a.pitch + col0 + piece * 8u;
             *reinterpret_cast<uint4 *>(a.canvas + off) = val;
             if (a.peers) store_to_peers(a.peers, off, val);
@@ -149,23 +149,22 @@ __device__ __forceinline__ void stage_and_store_t(const WaveArgs &a, const float
 
 template <int ACT>
 __device__ __forceinline__ void stage_and_store_a(const WaveArgs &a, const float (&v)[32], float bias, bool has_map, bool live, uint32_t oj,
-                                                  uint64_t col0, uint8_t *wstage, uint32_t lane, uint32_t pieces) {
-    if (!a.has_residual) stage_and_store_t<ACT, false, false>(a, v, bias, live, oj, col0, wstage, lane, pieces);
-    else if (has_map) stage_and_store_t<ACT, true, true>(a, v, bias, live, oj, col0, wstage, lane, pieces);
-    else stage_and_store_t<ACT, true, false>(a, v, bias, live, oj, col0, wstage, lane, pieces);
+                                                  uint64_t col0, uint8_t *wstage, uint32_t lane) {
+    if (!a.has_residual) stage_and_store_t<ACT, false, false>(a, v, bias, live, oj, col0, wstage, lane);
+    else if (has_map) stage_and_store_t<ACT, true, true>(a, v, bias, live, oj, col0, wstage, lane);
+    else stage_and_store_t<ACT, true, false>(a, v, bias, live, oj, col0, wstage, lane);
 }
 
-// One uniform branch per 32 values instead of one per value. `pieces`: how many 8-column pieces of the 32 values are
-// stored (4; 2 for the 16-column tile, whose upper 16 values are padding).
+// One uniform branch per 32 values instead of one per value.
 __device__ __forceinline__ void stage_and_store(const WaveArgs &a, const float (&v)[32], float bias, bool has_map, bool live, uint32_t oj,
-                                                uint64_t col0, uint8_t *wstage, uint32_t lane, uint32_t pieces = 4u) {
+                                                uint64_t col0, uint8_t *wstage, uint32_t lane) {
     switch (a.act) {
-    case 1: stage_and_store_a<1>(a, v, bias, has_map, live, oj, col0, wstage, lane, pieces); break;
-    case 2: stage_and_store_a<2>(a, v, bias, has_map, live, oj, col0, wstage, lane, pieces); break;
-    case 3: stage_and_store_a<3>(a, v, bias, has_map, live, oj, col0, wstage, lane, pieces); break;
-    case 4: stage_and_store_a<4>(a, v, bias, has_map, live, oj, col0, wstage, lane, pieces); break;
-    case 5: stage_and_store_a<5>(a, v, bias, has_map, live, oj, col0, wstage, lane, pieces); break;
-    default: stage_and_store_a<0>(a, v, bias, has_map, live, oj, col0, wstage, lane, pieces); break;
+    case 1: stage_and_store_a<1>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    case 2: stage_and_store_a<2>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    case 3: stage_and_store_a<3>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    case 4: stage_and_store_a<4>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    case 5: stage_and_store_a<5>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
+    default: stage_and_store_a<0>(a, v, bias, has_map, live, oj, col0, wstage, lane); break;
     }
 }
 

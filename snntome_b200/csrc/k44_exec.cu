@@ -153,12 +153,6 @@ UmmaDesc make_umma_desc(uint32_t n_tile, int variant) {
     // (leading dimension = N). A K=16 step moves 16 rows = 2048 bytes.
     d.b_base = (variant == 1) ? smem_desc_bits(1024, kStageK * 128u, 2) : smem_desc_bits(kStageK * 128u, 1024, 2);
     d.b_k_step = 2048 >> 4;
-    if (n_tile == 16) {
-        // 16-column tile: each synapse row is 32 bytes, 32-byte swizzle (layout type 6): 8-row groups 256 bytes apart, a
-        // K=16 step moves 16 rows = 512 bytes; a single 16-column block, so the leading-dimension offset is unused
-        d.b_base = (variant == 1) ? smem_desc_bits(256, 16, 6) : smem_desc_bits(16, 256, 6);
-        d.b_k_step = 512 >> 4;
-    }
     // instruction descriptor: FP32 accumulate (bit 4), A/B FP16 (0), A K-major (bit 15 = 0), B MN-major
     // (bit 16 = 1), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
     d.idesc = (1u << 4) | (1u << 16) | ((n_tile >> 3) << 17) | ((kTileM >> 4) << 24);
@@ -236,7 +230,7 @@ bool Executor::begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t
     return true;
 }
 
-bool Executor::make_tensor_map(DeviceWave &dw, uint32_t box_cols, int swizzle_bytes) {
+bool Executor::make_tensor_map(DeviceWave &dw, uint32_t box_cols, bool swizzle128) {
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -253,7 +247,7 @@ bool Executor::make_tensor_map(DeviceWave &dw, uint32_t box_cols, int swizzle_by
     const cuuint32_t box[2] = {box_cols, dw.args.box_h};
     const cuuint32_t estr[2] = {1u, 1u};
     const CUresult r = encode(&dw.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, canvas_, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
     return true;
 }
@@ -501,7 +495,7 @@ bool Executor::add_wave(const HostWave &w) {
             a.k_splits = 1; a.kstages_per_split = a.num_kstages;
             dw.desc = make_umma_desc(n_tile, 0);
             if (const char *e = std::getenv("K44B_DEBUG_MODE")) dw.desc.debug = (uint32_t)std::atoi(e);
-            ok = make_tensor_map(dw, std::min(n_tile, 128u) + 8u, 0);   // aligned windows of up to 128 columns plus the 8 to their left, as plain rows
+            ok = make_tensor_map(dw, std::min(n_tile, 128u) + 8u, false);   // aligned windows of up to 128 columns plus the 8 to their left, as plain rows
         } else if (dw.path == PATH_UMMA) {
             uint32_t n_tile = 64;
             for (uint32_t cand : {256u, 128u})
@@ -510,9 +504,6 @@ bool Executor::add_wave(const HostWave &w) {
                 const uint32_t v = (uint32_t)std::atoi(e);
                 if ((v == 64 || v == 128 || v == 256) && tiles64 % (v / 64u) == 0u) n_tile = v;
             }
-            // at most 16 valid columns (small batch): a 16-column tile reads 32 bytes of every gathered row instead of 128
-            bool narrow = columns_ <= 16u && tiles64 == 1u;
-            if (const char *e = std::getenv("K44B_NARROW")) narrow = narrow && std::atoi(e) != 0;
             int variant = 0;
             if (const char *e = std::getenv("K44B_UMMA_VARIANT")) variant = std::atoi(e);
             // Small waves (fewer tiles than SMs): 64-column tiles, two CTAs per SM, and the fan-in cut into
@@ -538,7 +529,6 @@ bool Executor::add_wave(const HostWave &w) {
                     splits = s2;
                 }
             }
-            if (!small && narrow) n_tile = 16;
             a.kstages_per_split = (a.num_kstages + splits - 1) / splits;
             a.k_splits = cluster ? splits : (a.num_kstages + a.kstages_per_split - 1) / a.kstages_per_split;
             dw.use_cluster = cluster;
@@ -546,7 +536,7 @@ bool Executor::add_wave(const HostWave &w) {
             dw.desc.small_wave = small ? 1u : 0u;
             if (const char *e = std::getenv("K44B_DEBUG_MODE")) dw.desc.debug = (uint32_t)std::atoi(e);
             if (a.k_splits > 1 && !cluster) ok = reserve_scratch((size_t)mtiles * tiles64);
-            ok = ok && make_tensor_map(dw, n_tile == 16u ? 16u : 64u, n_tile == 16u ? 32 : 128);
+            ok = ok && make_tensor_map(dw, 64u, true);
         }
     }
     if (!ok) {

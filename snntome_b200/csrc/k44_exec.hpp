@@ -94,7 +94,7 @@ class Executor {
   private:
     bool fail(const std::string &m) { err = m; return false; }
     bool check(cudaError_t e, const char *what);
-    bool make_tensor_map(DeviceWave &dw, uint32_t box_cols, int swizzle_bytes);   // 128, 32 or 0 (none)
+    bool make_tensor_map(DeviceWave &dw, uint32_t box_cols, bool swizzle128);
     bool reserve_scratch(size_t tiles);
     bool launch_one(DeviceWave &w, cudaStream_t stream);
     void drop_graph();

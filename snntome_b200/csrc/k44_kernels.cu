@@ -123,14 +123,12 @@ constexpr int kUmmaThreads = 192;
 // STAGES_SEL == 1: 4 stages, two CTAs per SM (small waves: more CTAs in flight, split-K).
 template <int N_TILE, int STAGES_SEL>
 struct UmmaCfg {
-    static constexpr int kColBlocks = N_TILE < 64 ? 1 : N_TILE / 64;                  // 64-column blocks per tile
-    static constexpr uint32_t kRowBytes = N_TILE < 64 ? (uint32_t)N_TILE * 2u : 128u; // bytes of one substrate row inside a block
-    static constexpr uint32_t kBlockBytes = kStageK * kRowBytes;                      // 8 KiB per 64 columns, 2 KiB for the 16-column tile
-    static constexpr uint32_t kXBytes = (uint32_t)kColBlocks * kBlockBytes;
+    static constexpr int kColBlocks = N_TILE / 64;                                    // 64-column blocks per tile
+    static constexpr uint32_t kXBytes = (uint32_t)kColBlocks * kStageK * 128u;        // 8 KiB per 64 columns
     static constexpr uint32_t kStageBytes = kStageWBytes + kXBytes;
-    static constexpr int kStages = STAGES_SEL == 1 ? 4 : (N_TILE == 16 ? 10 : ((N_TILE == 64) ? 8 : (N_TILE == 128 ? 6 : 4)));
+    static constexpr int kStages = STAGES_SEL == 1 ? 4 : ((N_TILE == 64) ? 8 : (N_TILE == 128 ? 6 : 4));
     static constexpr int kCtasPerSm = STAGES_SEL == 1 ? 2 : 1;
-    static constexpr uint32_t kTmemCols = N_TILE < 32 ? 32u : 2u * N_TILE;            // two accumulators; 32 columns is the smallest allocation
+    static constexpr uint32_t kTmemCols = 2u * N_TILE;
     static constexpr uint32_t kOutStageBytes = 128u * 80u;                           // epilogue staging: 128 rows x (64 + 16 pad) bytes
     static constexpr uint32_t kSmemBytes = 1024u /*alignment slack*/ + (uint32_t)kStages * kStageBytes + 256u + kOutStageBytes;
 };
@@ -266,7 +264,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                     const uint32_t b = lane / (uint32_t)Cfg::kColBlocks, cb = lane % (uint32_t)Cfg::kColBlocks;
                     const uint32_t row = __shfl_sync(0xffffffffu, cached, (bi0 + b) & 31u) & kBoxRowMask;
                     if (lane < per_stage && !(d.debug & 4u))
-                        ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + cb * Cfg::kBlockBytes + b * a.box_h * Cfg::kRowBytes, &tmap,
+                        ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + cb * (kStageK * 128u) + b * a.box_h * 128u, &tmap,
                                          (int32_t)(ct * N_TILE + cb * 64u), (int32_t)row, full_bar + 8u * stage, pol_x);
                 }
                 if (issued == 0 && lane == 0) stamp(2);
@@ -350,22 +348,13 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
             if (splits == 1u) {
 #pragma unroll 1
                 for (uint32_t c0 = 0; c0 < (uint32_t)N_TILE; c0 += 32u) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * N_TILE + c0, v);
+                    ptx::tmem_ld_wait();
                     float f[32];
-                    if constexpr (N_TILE == 16) {            // 16 accumulator columns; the upper half of the 32 values is padding
-                        uint32_t v[16];
-                        ptx::tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + acc * N_TILE, v);
-                        ptx::tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) { f[e] = __uint_as_float(v[e]); f[16 + e] = 0.0f; }
-                    } else {
-                        uint32_t v[32];
-                        ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * N_TILE + c0, v);
-                        ptx::tmem_ld_wait();
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
-                    }
-                    if (!(d.debug & 8u))
-                        stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane, N_TILE == 16 ? 2u : 4u);
+                    for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
+                    if (!(d.debug & 8u)) stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
                 }
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(tempty_bar + 8u * acc);
@@ -442,7 +431,7 @@ template <int N_TILE, int SEL>
 static cudaError_t umma_launch(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s) {
     using Cfg = UmmaCfg<N_TILE, SEL>;
     const uint32_t mtiles = (a.cout + kTileM - 1) / kTileM;
-    const uint32_t items = mtiles * (a.num_col_tiles64 / (uint32_t)Cfg::kColBlocks) * a.k_splits;
+    const uint32_t items = mtiles * (a.num_col_tiles64 / (N_TILE / 64u)) * a.k_splits;
     const uint32_t cap = (uint32_t)num_sms * Cfg::kCtasPerSm;
     const uint32_t grid = items < cap ? items : cap;
     k44_wave_umma_kernel<N_TILE, SEL><<<grid, kUmmaThreads, Cfg::kSmemBytes, s>>>(tmap, a, d);
@@ -454,7 +443,6 @@ cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtenso
     if (a.k_splits > 1 && (!a.scratch || !a.counters)) return cudaErrorInvalidValue;
     if (d.small_wave) return d.n_tile == 64 ? umma_launch<64, 1>(a, d, tmap, num_sms, s) : cudaErrorInvalidValue;
     switch (d.n_tile) {
-    case 16: return (a.k_splits == 1 && a.num_col_tiles64 == 1) ? umma_launch<16, 0>(a, d, tmap, num_sms, s) : cudaErrorInvalidValue;
     case 64: return umma_launch<64, 0>(a, d, tmap, num_sms, s);
     case 128: return umma_launch<128, 0>(a, d, tmap, num_sms, s);
     case 256: return umma_launch<256, 0>(a, d, tmap, num_sms, s);
@@ -858,7 +846,6 @@ cudaError_t launch_wave_umma_cluster(const WaveGroupArgs &g, const UmmaDesc &d, 
 
 cudaError_t umma_kernel_setup() {
     cudaError_t e;
-    if ((e = umma_attr<16, 0>()) != cudaSuccess) return e;
     if ((e = umma_attr<64, 0>()) != cudaSuccess) return e;
     if ((e = umma_attr<128, 0>()) != cudaSuccess) return e;
     if ((e = umma_attr<256, 0>()) != cudaSuccess) return e;

@@ -389,24 +389,3 @@ def test_independent_small_waves_share_a_launch():
     assert npn.launch_count - before == 2            # {q, k, v} and {o}
     check(plan, canvas.cpu().numpy().view(np.uint16), want)
     npn.close()
-
-
-@pytest.mark.parametrize("columns,run_len,act", [(8, 64, ACT_RELU), (16, 16, ACT_SILU), (1, 32, ACT_NONE)])
-def test_small_batch_uses_the_16_column_tile(columns, run_len, act):
-    """At most 16 valid columns and enough neuron tiles to fill the GPU: the streaming kernel runs with a 16-column tile
-    (32-byte rows, 32-byte swizzle, N = 16 MMAs) and writes columns 0..15 of every row; the rest of the row is padding
-    and is left alone."""
-    plan = synth.sparse_plan(seed=400 + columns, input_rows=4096, waves=2, cout=19200, runs=256 // run_len, run_len=run_len,
-                             columns=columns, group=128, act=act)
-    x = synth.random_input(plan, 41, dist="normal")
-    want = O.run_plan(plan, x)
-    npn = NativePlan.from_plan(plan, device=0, force_path=PATH_UMMA)
-    assert all(npn.wave_info(i).n_tile == 16 for i in range(npn.num_waves))
-    npn.close()
-    got = run_gpu(plan, x, PATH_UMMA, expect_path=PATH_UMMA)
-    for w in plan.waves:
-        a, b = w.y_off, w.y_off + w.cout * plan.pitch
-        g16 = got[a:b].reshape(w.cout, plan.pitch)[:, :16].reshape(-1)
-        w16 = want[a:b].reshape(w.cout, plan.pitch)[:, :16].reshape(-1)
-        ok, err, k = O.compare(g16, w16, RTOL, ATOL)
-        assert ok, f"wave {w.name}: max abs err {err} at {k} (row {k // 16}, col {k % 16})"
