@@ -835,13 +835,14 @@ def main() -> None:
     avg_wave_ms = float(np.mean(wave_ms))
     peak, peak_kind = measured_peaks()
     achieved = bytes_wave / (avg_wave_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "k44_wave_umma_kernel<64>" if paths[0] == 1 else "k44_wave_fma_kernel",
+    roofline = {"bound": "hbm", "kernel": f"k44_wave_umma_kernel<{plan.wave_info(0).n_tile}>" if paths[0] == 1 else "k44_wave_fma_kernel",
                 "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
                 "algorithmic_bytes_per_launch": bytes_wave, "avg_launch_ms": avg_wave_ms,
                 "per_wave_ms": [float(np.mean([wave_ms[s][i] for s in range(args.steps)])) for i in range(nw)],
                 # dram__bytes_read + dram__bytes_write of this kernel from the committed ncu capture at 1/20 size
                 # (profiles/k44_wave_umma64_ultra_sparse_scale005_ncu_full.md: 0.928 x algorithmic bytes), scaled by units processed
-                "traffic": NCU_TRAFFIC_RATIO * bytes_wave, "traffic_source": "ncu capture at scale 0.05, scaled by neurons x fan-in"}
+                "traffic": NCU_TRAFFIC_RATIO * bytes_wave if w["columns"] == 64 else None,
+                "traffic_source": "ncu capture at scale 0.05, scaled by neurons x fan-in" if w["columns"] == 64 else None}
 
     # ---- end to end through the C ABI with host buffers (pinned FP16 in canvas layout) ----
     e2e = None
