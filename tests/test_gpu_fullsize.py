@@ -105,6 +105,48 @@ def test_token_shift_plan_full_size_sampled_groups():
     plan.close()
 
 
+def test_dense_decoder_chain_full_size_sampled_rows():
+    """The 113-wave chain of the 1B decoder at its benchmark size (2.47 GB of weights generated on the device): after one
+    graph replay the last layer's tensors and the logits are still in the canvas, so sampled 128-row groups of its seven
+    waves and of the lm_head are recomputed by the oracle from the device's own inputs and unpacked weights."""
+    import torch
+    import bench
+    from snntome_b200.native import fill_normal_f16
+    cfg = dict(bench.DECODER)
+    plan, params, rows = bench.build_decoder_plan(cfg, 0)
+    H, F, V, KV = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["kv_heads"] * cfg["head_dim"]
+    canvas = plan.canvas_tensor()
+    fill_normal_f16(canvas[: H * 64], 99, 1.0)
+    plan.execute_graph()
+    assert plan.status() == 0
+    cv2 = canvas.view(-1, 64)
+    rng = np.random.default_rng(8)
+    nw = plan.num_waves
+    last = nw - 8                                            # first wave of layer 15; it reads x1 and writes x0
+    # (wave index, source tensor, destination tensor, fan-in, rows, activation, residual tensor)
+    checks = [(last + 0, "x1", "q", H, H, ACT_NONE, None), (last + 1, "x1", "k", H, KV, ACT_NONE, None), (last + 2, "x1", "v", H, KV, ACT_NONE, None),
+              (last + 3, "q", "h", H, H, ACT_NONE, "x1"), (last + 4, "h", "g", H, F, ACT_SILU, None), (last + 5, "h", "u", H, F, ACT_NONE, None),
+              (last + 6, "g", "x0", F, H, ACT_NONE, "h"), (nw - 1, "x0", "logits", H, V, ACT_NONE, None)]
+    for wi, src, dst, cin, cout, act, res in checks:
+        wrm = plan.weights_rowmajor(wi)
+        x = cv2[rows[src]: rows[src] + cin].cpu().numpy().view(np.uint16)
+        for g in rng.choice(cout // 128, size=2, replace=False):
+            wg = wrm[g * 128:(g + 1) * 128].cpu().numpy().view(np.uint16)
+            got = cv2[rows[dst] + g * 128: rows[dst] + (g + 1) * 128].cpu().numpy().view(np.uint16)
+            idx = (np.arange(cin, dtype=np.uint32) * 64)[None, :]
+            extra = 128 if res else 0
+            wave = Wave(cout=128, group=128, fan_in=cin, idx=idx, weights=wg, bias=None, y_off=(cin + extra) * 64, act=act,
+                        has_residual=res is not None, res_off=cin * 64)
+            mini = Plan(canvas_elems=(cin + extra + 128) * 64, pitch=64, columns=64, input_off=0, input_c=cin + extra, output_off=(cin + extra) * 64,
+                        output_c=128, waves=[wave])
+            xin = x if not res else np.concatenate([x, cv2[rows[res] + g * 128: rows[res] + (g + 1) * 128].cpu().numpy().view(np.uint16)])
+            want = O.run_plan(mini, xin)[(cin + extra) * 64:]
+            ok, err, k = O.compare(got.reshape(-1), want, RTOL, ATOL)
+            assert ok, f"wave {wi} ({dst}) group {g}: max abs err {err} at {k}"
+        del wrm
+    plan.close()
+
+
 def mini_decoder(seed=9, hidden=256, kv=64, ffn=768, vocab=1024, layers=2, columns=64):
     rng = np.random.default_rng(seed)
     pitch = 64
