@@ -95,3 +95,74 @@ def test_decoder_layer_matches_float64_model(fold, tmp_path):
     err = float(np.max(np.abs(y - want)))
     cos = float(np.dot(y.ravel(), want.ravel()) / (np.linalg.norm(y) * np.linalg.norm(want)))
     assert err < 2e-2 and cos > 0.9999, (err, cos)
+
+
+@pytest.mark.gpu
+def test_mini_decoder_step_with_cache_matches_oracle():
+    """The decode-full benchmark plan at a small size (2 layers, hidden 256, 4/2 heads x 64, FFN 512, vocabulary 1024, a
+    cache of 64 positions): embedding gather, RMSNorm, q/k/v waves, rotary + attention against the cache, o wave with
+    residual, RMSNorm, gated MLP with SwiGLU product, final norm, lm_head, arg-max — one CUDA graph, replayed at two
+    positions — against the oracle replaying the same command list on a copy of the device's canvas, weights and table."""
+    import sys
+    from pathlib import Path
+    import torch
+    sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+    import bench
+    from oracle import oracle as O
+    from oracle import valu as V
+    from snntome_b200.plan import Plan, Wave
+    cfg = dict(hidden=256, layers=2, heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1024, columns=64)
+    ctx, pitch = 64, 64
+    plan, params, rows = bench.build_decoder_plan(cfg, 0, full=True, ctx=ctx)
+    H, F, Vv, KV = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["kv_heads"] * cfg["head_dim"]
+    off = lambda n: rows[n] * pitch
+    canvas_t = plan.canvas_tensor()
+    n_cmd = plan.num_waves
+    wave_ids = [i for i in range(n_cmd) if plan.wave_info(i).path != 2]
+    assert len(wave_ids) == 7 * cfg["layers"] + 1
+    weights = [plan.weights_rowmajor(i).cpu().numpy().view(np.uint16) for i in wave_ids]
+    table = plan.embedding_table.cpu().numpy().view(np.uint16).reshape(Vv, H)
+    rng = np.random.default_rng(12)
+    for pos in (ctx - 1, 17):
+        tokens = rng.integers(0, Vv, size=64).astype(np.int32)
+        ref = canvas_t.cpu().numpy().view(np.uint16).copy()            # caches and leftovers exactly as the device has them
+        plan.set_tokens(tokens)
+        plan.set_decode_pos(pos)
+        plan.execute_graph()
+        got_tokens = plan.next_tokens(64)
+        assert plan.status() == 0
+        got = canvas_t.cpu().numpy().view(np.uint16)
+
+        def wave(k, src, dst, cin, cout, act=0, res=None):
+            idx = ((rows[src] + np.arange(cin, dtype=np.uint32)) * pitch)[None, :].repeat(cout // 128, axis=0)
+            w = Wave(cout=cout, group=128, fan_in=cin, idx=idx, weights=weights[k], bias=None, y_off=off(dst), act=act,
+                     has_residual=res is not None, res_off=off(res) if res else 0)
+            O.wave_forward(ref, w, Plan(canvas_elems=ref.size, pitch=pitch, columns=64, input_off=0, input_c=1, output_off=0, output_c=1, waves=[w]))
+
+        ref[off("x0"): off("x0") + H * pitch].reshape(H, pitch)[:] = table[tokens].T
+        x_in, x_out, k = "x0", "x1", 0
+        for layer in range(cfg["layers"]):
+            V.rmsnorm(ref, off(x_in), off("n"), H, pitch, 1e-5)
+            wave(k, "n", "q", H, H); wave(k + 1, "n", "k", H, KV); wave(k + 2, "n", "v", H, KV)
+            V.decode_attention(ref, off("q"), off("k"), off("v"), off("att"), off(f"kcache{layer}"), off(f"vcache{layer}"), cfg["heads"], cfg["kv_heads"],
+                               cfg["head_dim"], pitch, ctx, pos, 500000.0, True)
+            wave(k + 3, "att", "h", H, H, res=x_in)
+            V.rmsnorm(ref, off("h"), off("n"), H, pitch, 1e-5)
+            wave(k + 4, "n", "g", H, F, act=3); wave(k + 5, "n", "u", H, F)
+            V.swiglu(ref, off("g"), off("u"), off("f"), F, pitch)
+            wave(k + 6, "f", x_out, F, H, res="h")
+            x_in, x_out, k = x_out, x_in, k + 7
+        V.rmsnorm(ref, off(x_in), off("n"), H, pitch, 1e-5)
+        wave(k, "n", "logits", H, Vv)
+        a, b = off("logits"), off("logits") + Vv * pitch
+        # two layers of FP16 intermediates: compare the logits with a tolerance scaled to their spread, then the tokens
+        lg, lw = got[a:b].view(np.float16).astype(np.float32), ref[a:b].view(np.float16).astype(np.float32)
+        assert np.max(np.abs(lg - lw)) < 5e-3 * max(1.0, float(np.abs(lw).max())), float(np.max(np.abs(lg - lw)))
+        lw2 = lw.reshape(Vv, pitch)
+        chosen = lw2[got_tokens, np.arange(64)]
+        assert np.all(chosen >= lw2.max(axis=0) - 1e-2 * np.maximum(1.0, np.abs(lw2.max(axis=0))))
+        for layer in range(cfg["layers"]):                        # the caches received the same new rows
+            ok, err, kk = O.compare(got[off(f"kcache{layer}"): off(f"kcache{layer}") + 2 * KV * ctx * pitch],
+                                    ref[off(f"kcache{layer}"): off(f"kcache{layer}") + 2 * KV * ctx * pitch], 4e-3, 2e-3)
+            assert ok, (layer, err, kk)
+    plan.close()
