@@ -76,7 +76,7 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
         : "memory");
 }
 
-// 2-D tiled tensor copy global -> shared (no multicast). x is the innermost coordinate and must be
+// 2-D tiled tensor copy global -> shared, to this CTA only. x is the innermost coordinate and must be
 // a multiple of 8 FP16 elements.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int32_t x, int32_t y, uint32_t bar,
                                             uint64_t policy) {
