@@ -47,7 +47,7 @@ typedef struct k44b_wave_desc {
 
 typedef struct k44b_wave_info_t {
     uint32_t cout, group, fan_in, box_rows;   /* box_rows: rows fetched per TMA box, 0 on the index path */
-    int32_t path;                             /* 0 FMA kernel, 1 tcgen05 kernel */
+    int32_t path;                             /* 0 FP32-FMA kernel, 1 tcgen05 kernels, 2 element-wise / attention command, 3 general kernel on mma.sync */
     uint32_t n_tile;                          /* columns per tile on the tcgen05 path */
     uint32_t k_splits;                        /* K splits per tile (partial sums meet in FP32 scratch) */
     uint64_t synapses;                        /* logical_cout * fan_in_raw */
@@ -125,7 +125,7 @@ int k44b_plan_get_next_tokens(void *plan, int32_t *h_tokens, uint32_t n, void *s
  * kernels store each output row into the rank's own canvas and into the peers' canvases (peer-mapped memory over
  * NVLink), and a launch starts reading only when every peer has finished the launches before it (one 32-bit word per
  * peer, bounded wait: status bit 5 on expiry). All ranks must issue the same sequence of launches. Supported for waves
- * that run on the tensor-core kernels; plans with FMA-path or token-shifted waves are rejected. world <= 8.
+ * that run on the tcgen05 kernels; plans with general-path or token-shifted waves are rejected. world <= 8.
  *   ipc_handles:    64-byte CUDA IPC handles of this plan's canvas and sync block, to be sent to the other processes
  *   set_peers_ipc:  `world` handles each (indexed by rank; the own entries are ignored), opened with peer access
  *   set_peers_raw:  the same with device pointers that are already valid on this GPU (same process)            */

@@ -288,7 +288,7 @@ bool Executor::add_aux(const HostWave &w) {
     if (d_peers_) return fail("commands cannot be added after the peers were set");
     if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
     DeviceWave dw;
-    dw.name = w.name; dw.is_aux = true; dw.path = 2;
+    dw.name = w.name; dw.is_aux = true; dw.path = PATH_AUX;
     AuxArgs &x = dw.aux;
     x.kind = w.kind; x.canvas = canvas_; x.pitch = pitch_; x.columns = columns_;
     x.src_off = w.src_off; x.src2_off = w.src2_off; x.src3_off = w.src3_off; x.dst_off = w.y_off;
@@ -482,7 +482,9 @@ bool Executor::add_wave(const HostWave &w) {
             if (!allow) { dw.umma_capable = false; dw.fma_reason = flen % 64u ? "token-shifted runs with frames that are not whole column tiles" : "token-shifted runs"; }
             else dw.use_shift = true;
         }
-        dw.path = (dw.umma_capable && force_path_ != 0) ? PATH_UMMA : PATH_FMA;
+        // waves the tcgen05 kernels cannot take run on the warp-level tensor path; the FP32-FMA kernel only when asked for
+        dw.path = force_path_ == 0 ? PATH_FMA : (dw.umma_capable ? PATH_UMMA : PATH_MMA);
+        if (const char *e = std::getenv("K44B_GENERAL_MMA")) if (dw.path == PATH_MMA && std::atoi(e) == 0) dw.path = PATH_FMA;
         if (dw.path == PATH_UMMA && dw.use_shift) {
             const uint32_t flen = w.frame_len ? w.frame_len : pitch_;
             uint32_t n_tile = 64;
@@ -680,6 +682,8 @@ bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
         w.args.scratch = d_scratch_;
         w.args.counters = d_counters_;
         e = launch_wave_umma(w.args, w.desc, w.tmap, num_sms_, stream);
+    } else if (w.path == PATH_MMA) {
+        e = launch_wave_mma(w.args, stream);
     } else {
         e = launch_wave_fma(w.args, stream);
     }

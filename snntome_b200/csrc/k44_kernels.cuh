@@ -30,7 +30,7 @@ enum GatherMode : int {
 };
 constexpr uint32_t kBoxRowMask = 0x0fffffffu;   // canvas row of a box entry; the top 4 bits carry its token shift (0..8)
 
-enum WavePath : int { PATH_FMA = 0, PATH_UMMA = 1 };
+enum WavePath : int { PATH_FMA = 0, PATH_UMMA = 1, PATH_AUX = 2, PATH_MMA = 3 };   // FP32 FMA | tcgen05 | element-wise command | mma.sync
 
 // Status word written by kernels instead of trapping or hanging.
 enum KernelStatus : uint32_t {
@@ -138,6 +138,7 @@ struct UmmaDesc {
 };
 
 cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s);
+cudaError_t launch_wave_mma(const WaveArgs &a, cudaStream_t s);       // general path on mma.sync (k44_mma_kernel.cu)
 cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
 // small waves: one item per CTA, the K splits of a tile form a cluster (k_splits in {1,2,4,8}) and reduce through
 // distributed shared memory; dependent_launch adds the programmatic-dependent-launch attribute

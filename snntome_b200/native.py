@@ -11,6 +11,7 @@ from ._lib import WaveDesc, WaveInfo, get_lib, last_error
 from .plan import Plan, Wave
 
 PATH_AUTO, PATH_FMA, PATH_UMMA = -1, 0, 1
+PATH_AUX, PATH_MMA = 2, 3        # reported by wave_info: element-wise command | general wave kernel on mma.sync
 
 
 class NativeError(RuntimeError):

@@ -9,7 +9,7 @@ import pytest
 
 from oracle import oracle as O
 from snntome_b200 import native, synth
-from snntome_b200.native import PATH_AUTO, PATH_FMA, PATH_UMMA, NativePlan
+from snntome_b200.native import PATH_AUTO, PATH_FMA, PATH_MMA, PATH_UMMA, NativePlan
 from snntome_b200.plan import ACT_GELU, ACT_LEAKY_RELU, ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, Plan, Wave
 
 pytestmark = pytest.mark.gpu
@@ -52,10 +52,10 @@ def test_config0_tensor_core_path():
     check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_UMMA), O.run_plan(plan, x))
 
 
-def test_config0_group16_falls_back_to_fma_automatically():
+def test_config0_group16_takes_the_general_tensor_path_automatically():
     plan = synth.config0(group=16)
     x = synth.random_input(plan, 12)
-    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_FMA), O.run_plan(plan, x))
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_MMA), O.run_plan(plan, x))
 
 
 def test_ultra_sparse_rule_scaled_down():
@@ -129,7 +129,7 @@ def test_token_shift_offsets_use_general_path():
     plan = Plan(canvas_elems=(rows_in + cout) * pitch, pitch=pitch, columns=200, input_off=0, input_c=rows_in,
                 output_off=rows_in * pitch, output_c=cout, waves=[wave])
     x = synth.random_input(plan, 19)
-    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_FMA), O.run_plan(plan, x))
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_MMA), O.run_plan(plan, x))
 
 
 def test_minimum_size_wave():
@@ -350,13 +350,13 @@ def test_token_shift_tensor_path_with_bias_residual_and_many_tiles():
 def test_token_shift_frames_that_split_a_tile_fall_back():
     plan = shifted_plan(133, runs=8, run_len=16, frames=2, frame_len=96, cout=256)
     x = synth.random_input(plan, 25, dist="normal")
-    check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_FMA), O.run_plan(plan, x))
+    check(plan, run_gpu(plan, x, PATH_UMMA, expect_path=PATH_MMA), O.run_plan(plan, x))
 
 
 def test_token_shift_short_runs_fall_back():
     plan = shifted_plan(140, runs=16, run_len=8)
     x = synth.random_input(plan, 26, dist="normal")
-    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_FMA), O.run_plan(plan, x))
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_MMA), O.run_plan(plan, x))
 
 
 def test_independent_small_waves_share_a_launch():
@@ -389,3 +389,30 @@ def test_independent_small_waves_share_a_launch():
     assert npn.launch_count - before == 2            # {q, k, v} and {o}
     check(plan, canvas.cpu().numpy().view(np.uint16), want)
     npn.close()
+
+
+
+@pytest.mark.parametrize("group", [16, 32, 64])
+@pytest.mark.parametrize("act", [ACT_RELU, ACT_GELU])
+def test_small_groups_on_the_general_tensor_path(group, act):
+    """Groups of 16 / 32 / 64 neurons with their own gather lists (runs and scattered rows): too small for a tcgen05 tile,
+    so the wave runs on the mma.sync kernel; the FP32-FMA kernel must agree with it."""
+    plan = synth.sparse_plan(seed=500 + group, input_rows=2048, waves=2, cout=192, runs=12, run_len=16, columns=100, group=group, act=act)
+    rng = np.random.default_rng(group)
+    w1 = plan.waves[1]
+    w1.idx = (rng.integers(0, 2048 + 192, size=w1.idx.shape) * plan.pitch).astype(np.uint32)      # scattered single rows
+    x = synth.random_input(plan, 51, dist="normal")
+    want = O.run_plan(plan, x)
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_MMA), want)
+    check(plan, run_gpu(plan, x, PATH_FMA, expect_path=PATH_FMA), want)
+
+
+def test_general_tensor_path_with_row_map_residual_and_partial_block():
+    plan = synth.dense_chain(seed=61, dims=[96, 80, 80], columns=64, act=ACT_SILU, weight_std=0.1, residual_from={2: 1}, group=16)
+    plan.waves[1].cout_map = np.random.default_rng(6).permutation(plan.waves[1].cout).astype(np.uint16)
+    for w in plan.waves:                                   # distinct lists per group: rotate the synapse order
+        w.idx = np.stack([np.roll(w.idx[g], g) for g in range(w.idx.shape[0])])
+        w.weights = np.stack([np.roll(w.weights[j], j // w.group) for j in range(w.cout)])
+        w.fan_in_raw = w.fan_in                            # the zero-weight padding slots moved with the roll
+    x = synth.random_input(plan, 52, dist="normal")
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_MMA), O.run_plan(plan, x))
