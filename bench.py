@@ -683,7 +683,7 @@ def shift_main(args) -> None:
                                        "fan-in 512 = 32 runs of 16 channels, shift 0..7 tokens per run, groups of 128, GELU",
                            "sequences_per_gpu": c["sequences"], "columns_per_gpu": pitch, "scale": args.scale, "max_shift": c["max_shift"],
                            "l2_policy": "substrate (0.13 - 2.3 GB) exceeds the 126 MB L2; no explicit flush"},
-                "roofline": {"bound": "tensor", "kernel": (f"k44_wave_umma_shift_kernel<{infos[0].n_tile}>" if c["max_shift"] else f"k44_wave_umma_kernel<{infos[0].n_tile}>") if infos[0].path == 1 else "k44_wave_fma_kernel",
+                "roofline": {"bound": "tensor", "kernel": (f"k44_wave_umma_shift_kernel<{infos[0].n_tile}>" if c["max_shift"] else f"k44_wave_umma_kernel<{infos[0].n_tile}>") if infos[0].path == 1 else ("k44_wave_mma_kernel" if infos[0].path == 3 else "k44_wave_fma_kernel"),
                              "achieved": achieved, "peak": peak, "peak_kind": f"of {kind}", "unit": "TFLOP/s", "frac": achieved / peak,
                              "flops_per_launch": flops_wave, "per_wave_ms": per_wave, "traffic": None},
                 "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "kernel_paths": [i.path for i in infos], "clocks": clocks}
@@ -737,6 +737,8 @@ def main() -> None:
     ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "decode-full", "pruned-sharded", "token-shift", "tiny"])
     ap.add_argument("--layers", type=int, default=16, help="decode workload: decoder layers (16 = the 1B shape)")
     ap.add_argument("--columns", type=int, default=64, help="ultra-sparse workload: valid columns (batch) per GPU, 1..64")
+    ap.add_argument("--group", type=int, default=128, choices=[16, 32, 64, 128],
+                    help="ultra-sparse workload: neurons sharing one gather list (below 128: the general mma.sync kernel)")
     ap.add_argument("--max-shift", type=int, default=7, help="token-shift workload: largest token shift drawn per run (0 = unshifted runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -754,9 +756,10 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     w = workload(args.scale)
     w["columns"] = max(1, min(64, args.columns))
+    w["group"] = args.group
     warmup = max(3, args.warmup)
     cfg = {"workload": "ultra-sparse plan: 40M-row FP16 substrate, 4 waves x 1M neurons, fan-in 4096 as 64 runs of 64 rows, "
-                       "groups of 128, ReLU, 64 columns per GPU",
+                       f"groups of {args.group}, ReLU, 64 columns per GPU",
            "input_rows": w["input_rows"], "neurons_per_wave": w["cout"], "waves": w["waves"], "fan_in": w["runs"] * w["run_len"],
            "run_len": w["run_len"], "group": w["group"], "columns_per_gpu": w["columns"], "global_columns": w["columns"] * world,
            "parallelism": f"column replicas x{world} (plan replicated, no collective)",
@@ -835,7 +838,7 @@ def main() -> None:
     avg_wave_ms = float(np.mean(wave_ms))
     peak, peak_kind = measured_peaks()
     achieved = bytes_wave / (avg_wave_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": f"k44_wave_umma_kernel<{plan.wave_info(0).n_tile}>" if paths[0] == 1 else "k44_wave_fma_kernel",
+    roofline = {"bound": "hbm", "kernel": f"k44_wave_umma_kernel<{plan.wave_info(0).n_tile}>" if paths[0] == 1 else ("k44_wave_mma_kernel" if paths[0] == 3 else "k44_wave_fma_kernel"),
                 "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
                 "algorithmic_bytes_per_launch": bytes_wave, "avg_launch_ms": avg_wave_ms,
                 "per_wave_ms": [float(np.mean([wave_ms[s][i] for s in range(args.steps)])) for i in range(nw)],

@@ -526,7 +526,7 @@ int k44b_analyze_gather(const k44b_wave_desc *wave, uint32_t pitch, uint64_t can
     } else return set_error("analyze_gather: no gather table");
     const GatherPlan gp = analyze_gather(w, pitch, canvas_elems);
     if (out_count) *out_count = gp.box_rows.size();
-    if (!gp.box_ok) { g_last_error = gp.why_not; return 0; }
+    if (!gp.box_ok || gp.small_group) { g_last_error = gp.why_not; return 0; }     // not usable by the tcgen05 kernels
     if (out_box_rows) std::memcpy(out_box_rows, gp.box_rows.data(), std::min<uint64_t>(capacity, gp.box_rows.size()) * 4);
     return (int)gp.box_h;
 }

@@ -75,7 +75,7 @@ GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_ele
     }
     if (!(w.group % kTileM == 0u || groups == 1u)) {
         gp.why_not = "group size is not a multiple of 128 neurons";
-        return gp;
+        gp.small_group = true;            // the run table below still serves the general kernels
     }
     struct Run { uint32_t row, len, shift; };
     std::vector<std::vector<Run>> runs(groups);
@@ -116,7 +116,7 @@ GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_ele
     const uint32_t tail = (kStageK - w.fan_in % kStageK) % kStageK;
     while (h >= 8 && tail % h) h >>= 1;
     if (h < 8) { gp.why_not = "runs are not made of whole 8-row blocks"; return gp; }
-    if (gp.max_shift > 0 && h < 16) { gp.why_not = "shifted runs must be made of whole 16-row blocks"; return gp; }
+    if (gp.max_shift > 0 && h < 16 && !gp.small_group) { gp.why_not = "shifted runs must be made of whole 16-row blocks"; return gp; }
     if (gp.max_shift > 8) { gp.why_not = "token shifts above 8 columns"; return gp; }
     if (total_rows > kBoxRowMask) { gp.why_not = "canvas has more than 2^28 rows"; return gp; }
     gp.box_h = h;
@@ -226,7 +226,7 @@ bool Executor::begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t
     if (!check(cudaMalloc(&d_status_, kStatusBytes), "status allocation")) return false;
     if (!check(cudaMemset(d_status_, 0, kStatusBytes), "status clear")) return false;
     if (!check(cudaEventCreate(&ev0_), "event") || !check(cudaEventCreate(&ev1_), "event")) return false;
-    if (!check(umma_kernel_setup(), "kernel attribute setup")) return false;
+    if (!check(umma_kernel_setup(), "kernel attribute setup") || !check(mma_kernel_setup(), "kernel attribute setup")) return false;
     return true;
 }
 
@@ -430,7 +430,17 @@ bool Executor::add_wave(const HostWave &w) {
     // ---- gather tables ----
     GatherPlan gp;
     if (ok) gp = analyze_gather(w, pitch_, canvas_elems_);
-    if (ok && gp.box_ok) {
+    if (ok && gp.box_ok && gp.small_group) {
+        // runs of whole boxes, but groups below 128 neurons: the general kernels read the run table as it is
+        const size_t bytes = gp.box_rows.size() * 4;
+        ok = check(cudaMalloc(&dw.d_gather, bytes), "run table allocation") &&
+             check(cudaMemcpy(dw.d_gather, gp.box_rows.data(), bytes, cudaMemcpyHostToDevice), "run table upload");
+        a.gather = (const uint32_t *)dw.d_gather;
+        a.gather_mode = GATHER_BOX;
+        a.box_h = gp.box_h; a.boxes_per_group = gp.boxes_per_group;
+        a.x_base_off = 0;                 // box rows are absolute canvas rows
+        dw.fma_reason = gp.why_not;
+    } else if (ok && gp.box_ok) {
         const size_t bytes = gp.box_rows.size() * 4;
         ok = check(cudaMalloc(&dw.d_gather, bytes), "run table allocation") &&
              check(cudaMemcpy(dw.d_gather, gp.box_rows.data(), bytes, cudaMemcpyHostToDevice), "run table upload");

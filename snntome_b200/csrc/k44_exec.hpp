@@ -15,6 +15,7 @@ namespace k44b {
 // Gather description derived from a wave's index table (or given directly as runs).
 struct GatherPlan {
     bool box_ok = false;                 // every run is made of whole boxes of `box_h` rows
+    bool small_group = false;            // groups of 16 / 32 / 64 neurons: boxes are usable, but only by the general kernels
     bool shared_by_all = false;          // all groups had the same list: the table holds it once
     uint32_t box_h = 0;                  // 8, 16, 32 or 64
     uint32_t boxes_per_group = 0;        // == 64/box_h * ceil(fan_in/64)

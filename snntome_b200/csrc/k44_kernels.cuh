@@ -146,6 +146,7 @@ cudaError_t launch_wave_umma_cluster(const WaveGroupArgs &g, const UmmaDesc &d, 
 // token-shifted runs (box gather, shifts in the table entries): n_tile 64 or 128, frames must be whole tiles; the tensor
 // map describes the canvas with boxes of (n_tile + 8) columns x box_h rows and no swizzle
 cudaError_t launch_wave_umma_shift(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
+cudaError_t mma_kernel_setup();        // same for the mma.sync kernel
 cudaError_t umma_kernel_setup();       // opt in to large dynamic shared memory (once per device)
 
 // packer kernels

@@ -5,17 +5,24 @@
 // stays as the arithmetic cross-check.
 //
 // CTA = 128 threads = MT x 16 neurons of one group (MT = 1, 2 or 4) x one 64-column tile; warp w owns columns
-// 16w .. 16w+15. Per 64-synapse stage the gathered rows go to shared memory as [synapse][column] — with 16-byte loads
-// where an offset is 16-byte aligned and unshifted, 2-byte loads with the causal mask otherwise — and the weight block
-// as [neuron][synapse]; A fragments come from ldmatrix, B fragments from ldmatrix.trans (the tile is column-contiguous),
-// FP32 accumulators in registers. Nothing here waits on anything.
+// 16w .. 16w+15. A ring of kStages stages of 64 synapses is filled with cp.async: the gathered rows as [synapse][column]
+// (row pitch 72 halves, so the 8 rows of an ldmatrix fall into distinct banks) and the weight rows exactly as the tiled
+// format stores them (128-byte rows, 16-byte chunk c at position c ^ (row & 7): conflict-free for ldmatrix as it is).
+// Gather-table entries travel two stages ahead of their rows in a small ring of their own. Rows whose offset is not
+// 16-byte aligned, or that carry a token shift, are fetched with 2-byte loads and the causal mask by the same thread
+// that would have issued the copy. A fragments come from ldmatrix, B fragments from ldmatrix.trans, FP32 accumulators in
+// registers. Nothing here waits on another CTA.
 #include "k44_kernels.cuh"
 #include "k44_epilogue.cuh"
 
 namespace k44b {
 namespace mmawave {
 
-constexpr uint32_t kPitch = 72;         // halves per shared-memory row (64 + 8: ldmatrix rows fall into distinct banks)
+constexpr uint32_t kPitch = 72;         // halves per gathered row in shared memory
+constexpr uint32_t kStages = 3;
+constexpr uint32_t kXBytesStage = kStageK * kPitch * 2u;
+constexpr uint32_t kTabRing = 2u * (kStages - 1u) + 1u;   // table entries run up to 2 (kStages - 1) stages ahead of the stage being consumed
+constexpr uint32_t smem_bytes(uint32_t mt) { return kStages * (kXBytesStage + mt * 16u * 128u) + kTabRing * kStageK * 4u; }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -28,13 +35,72 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src) { asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Eight columns of a gathered row whose start is not 16-byte aligned or that carries a token shift are cut out of the two
+// aligned 16-byte vectors around them (funnel shift); columns whose position inside their frame is below the shift read
+// zero.
+// `elem` is the canvas element of the unshifted first column, `cif0` that column's position inside its frame.
+__device__ __forceinline__ bool unaligned_in_range(uint64_t canvas_elems, uint64_t elem, uint32_t sh) {
+    return elem >= sh && ((elem - sh) & ~7ull) + 16u <= canvas_elems;
+}
+__device__ __forceinline__ uint4 finish_unaligned(const uint4 &v0, const uint4 &v1, uint32_t m, uint32_t sh, uint32_t cif0, uint32_t flen) {
+    const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    const uint32_t bits = (m & 1u) * 16u;
+    uint32_t out[4];
+    switch (m >> 1) {
+    case 0:
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = __funnelshift_r(w[i], w[i + 1], bits);
+        break;
+    case 1:
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = __funnelshift_r(w[i + 1], w[i + 2], bits);
+        break;
+    case 2:
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = __funnelshift_r(w[i + 2], w[i + 3], bits);
+        break;
+    default:
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = __funnelshift_r(w[i + 3], w[i + 4], bits);
+        break;
+    }
+    if (sh != 0u && !(cif0 >= sh && cif0 + 7u < flen)) {       // some of the eight columns sit left of their frame's column `sh`
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const uint32_t cif = (cif0 + (uint32_t)c) % flen;
+            if (cif < sh) out[c >> 1] &= (c & 1) ? 0x0000ffffu : 0xffff0000u;
+        }
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+// the same at the very edge of the canvas, element by element
+__device__ __forceinline__ uint4 fetch_piece_edge(const __half *canvas, uint64_t canvas_elems, uint64_t elem, uint32_t sh, uint32_t cif0, uint32_t flen) {
+    __half h[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const uint32_t cif = (cif0 + (uint32_t)c) % flen;
+        const uint64_t e = elem + (uint64_t)c;
+        h[c] = (cif >= sh && e >= sh && e - sh < canvas_elems) ? canvas[e - sh] : __float2half(0.0f);
+    }
+    return *reinterpret_cast<const uint4 *>(h);
+}
 
 template <int MT>
 __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a) {
-    __shared__ __align__(16) __half xs[kStageK][kPitch];
-    __shared__ __align__(16) __half ws[MT * 16][kPitch];
-    __shared__ uint64_t offs[kStageK];
-    __shared__ uint32_t shs[kStageK];
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr uint32_t kWBytesStage = MT * 16u * 128u;
+    constexpr uint32_t D = kStages - 1u;                    // stages in flight ahead of the one being consumed
+    const uint32_t xs = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t ws = xs + kStages * kXBytesStage;
+    const uint32_t tabs = ws + kStages * kWBytesStage;
+    uint8_t *const xs_gen = smem;
+    const uint32_t *const tab_gen = reinterpret_cast<const uint32_t *>(smem + kStages * (kXBytesStage + kWBytesStage));
 
     const uint32_t tile = blockIdx.x;                       // 64-column tile
     const uint32_t j0 = blockIdx.y * (MT * 16u);            // first neuron of this CTA
@@ -44,6 +110,10 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a) {
     const uint64_t x_limit = a.canvas_elems - a.x_base_off - (uint64_t)tile * 64u;       // exclusive bound for off + 64
     const uint32_t flen = a.frame_len ? a.frame_len : a.pitch;
     const uint32_t tile_in_frame = (tile * 64u) % flen;
+    const uint32_t nk = a.num_kstages;
+    const bool box = a.gather_mode == GATHER_BOX;
+    const uint32_t *table = a.gather + (uint64_t)g * (box ? a.boxes_per_group : a.fan_in);
+    const uint4 *wrow0 = a.w_tiles + ((uint64_t)(j0 >> 7) * nk * 128u + (j0 & 127u)) * 8u;   // + ks * 1024 vectors per stage
 
     float acc[MT][2][4];
 #pragma unroll
@@ -54,70 +124,87 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a) {
             for (int e = 0; e < 4; ++e) acc[m][n][e] = 0.f;
     bool bad = false;
 
-    for (uint32_t ks = 0; ks < a.num_kstages; ++ks) {
-        if (tid < kStageK) {
-            const uint32_t s = ks * kStageK + tid;
-            uint64_t off = 0;
-            uint32_t sh = 0;
-            if (s < a.fan_in) {
-                if (a.gather_mode == GATHER_IDX) {
-                    off = a.gather[(uint64_t)g * a.fan_in + s];
-                    if (a.shifts) sh = a.shifts[(uint64_t)g * a.fan_in + s];
-                } else {
-                    const uint32_t e = a.gather[(uint64_t)g * a.boxes_per_group + s / a.box_h];
-                    off = (uint64_t)((e & kBoxRowMask) + s % a.box_h) * a.pitch;
-                    sh = e >> 28;
-                }
-            }
-            if (off + 64u > x_limit) { off = 0; bad = true; }   // record and skip instead of faulting
-            offs[tid] = off;
-            shs[tid] = sh;
+    // table entry of synapse tid of stage ks (clamped to the last real synapse: its weight is zero past fan_in)
+    const uint32_t piece = tid & 7u;
+    const uint32_t cif0 = (tile_in_frame + piece * 8u) % flen;
+    const uint32_t box_mask = a.box_h - 1u, box_shift = 31u - (uint32_t)__clz((int)(a.box_h | 1u));   // box heights are powers of two
+    auto issue_table = [&](uint32_t ks) {
+        if (tid < kStageK && ks < nk) {
+            const uint32_t s = min(ks * kStageK + tid, a.fan_in - 1u);
+            cp_async_4(tabs + ((ks % kTabRing) * kStageK + tid) * 4u, table + (box ? s >> box_shift : s));
         }
-        // weights: MT*16 rows x 8 vectors of 8 synapses
-        for (uint32_t v = tid; v < MT * 16u * 8u; v += 128u) {
-            const uint32_t r = v >> 3, k8 = v & 7u;
-            uint4 wv = make_uint4(0u, 0u, 0u, 0u);
-            if (j0 + r < a.cout) wv = a.w_tiles[tiled_vec_index(j0 + r, ks * 8u + k8, a.num_kstages)];
-            *reinterpret_cast<uint4 *>(&ws[r][k8 * 8u]) = wv;
-        }
-        __syncthreads();
-        // substrate rows: 64 synapses x 8 pieces of 8 columns
-        for (uint32_t v = tid; v < kStageK * 8u; v += 128u) {
-            const uint32_t k = v >> 3, piece = v & 7u;
-            const uint64_t off = offs[k];
-            const uint32_t sh = shs[k];
-            const __half *src = xbase + off + piece * 8u;
-            uint4 val;
-            if (sh == 0u && ((a.x_base_off + off) & 7u) == 0u) {
-                val = *reinterpret_cast<const uint4 *>(src);
-            } else {
-                __half h[8];
+    };
+    auto issue_data = [&](uint32_t ks) {
+        if (ks >= nk) return;
+        const uint32_t st = ks % kStages;
+        // weights: MT*16 rows of 128 bytes, contiguous in the tiled format
+        const uint4 *wsrc = wrow0 + (uint64_t)ks * 1024u;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const uint32_t cif = (tile_in_frame + piece * 8u + (uint32_t)e) % flen;        // column inside its frame
-                    h[e] = cif >= sh ? src[(int)e - (int)sh] : __float2half(0.0f);
+        for (uint32_t v = tid; v < MT * 128u; v += 128u) cp_async_16(ws + st * kWBytesStage + v * 16u, wsrc + v);
+        // gathered rows: 64 synapses x 8 pieces of 8 columns
+#pragma unroll
+        for (uint32_t i = 0; i < 4u; ++i) {
+            const uint32_t k = (tid >> 3) + 16u * i;
+            const uint32_t s = min(ks * kStageK + k, a.fan_in - 1u);
+            const uint32_t e = tab_gen[(ks % kTabRing) * kStageK + k];
+            uint64_t off;
+            uint32_t sh;
+            if (box) { off = (uint64_t)((e & kBoxRowMask) + (s & box_mask)) * a.pitch; sh = e >> 28; }
+            else { off = e; sh = a.shifts ? a.shifts[(uint64_t)g * a.fan_in + s] : 0u; }
+            if (off + 64u > x_limit) { off = 0; bad = true; }   // record and skip instead of faulting
+            const uint32_t dst_off = st * kXBytesStage + (k * kPitch + piece * 8u) * 2u;
+            if (sh == 0u && ((a.x_base_off + off) & 7u) == 0u) {
+                cp_async_16(xs + dst_off, xbase + off + piece * 8u);
+            } else {
+                const uint64_t elem = a.x_base_off + (uint64_t)tile * 64u + off + piece * 8u;
+                uint4 val;
+                if (unaligned_in_range(a.canvas_elems, elem, sh)) {
+                    const uint64_t first = elem - sh, lo = first & ~7ull;
+                    const uint32_t m = (uint32_t)(first - lo);
+                    const uint4 v0 = *reinterpret_cast<const uint4 *>(a.canvas + lo);
+                    const uint4 v1 = m ? *reinterpret_cast<const uint4 *>(a.canvas + lo + 8u) : v0;
+                    val = finish_unaligned(v0, v1, m, sh, cif0, flen);
+                } else {
+                    val = fetch_piece_edge(a.canvas, a.canvas_elems, elem, sh, cif0, flen);
                 }
-                val = *reinterpret_cast<const uint4 *>(h);
+                *reinterpret_cast<uint4 *>(xs_gen + dst_off) = val;
             }
-            *reinterpret_cast<uint4 *>(&xs[k][piece * 8u]) = val;
         }
-        __syncthreads();
+    };
+
+    // prologue: table entries of the first 2D stages, then the rows of the first D stages
+    for (uint32_t ks = 0; ks < 2u * D; ++ks) issue_table(ks);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    for (uint32_t ks = 0; ks < D; ++ks) { issue_data(ks); cp_async_commit(); }
+
+    for (uint32_t ks = 0; ks < nk; ++ks) {
+        cp_async_wait<D - 1>();             // rows of stage ks (and the table entries of stage ks + D) have landed
+        __syncthreads();                    // ... for every thread; and everyone is done with the stage refilled below
+        issue_data(ks + D);
+        issue_table(ks + 2u * D);
+        cp_async_commit();
+        const uint32_t st = ks % kStages;
+        const uint32_t xs_st = xs + st * kXBytesStage, ws_st = ws + st * kWBytesStage;
 #pragma unroll
         for (uint32_t k16 = 0; k16 < kStageK / 16u; ++k16) {
             uint32_t bfrag[2][2];
 #pragma unroll
             for (int n = 0; n < 2; ++n)
-                ldmatrix_x2_trans(bfrag[n], (uint32_t)__cvta_generic_to_shared(&xs[k16 * 16u + (lane & 15u)][warp * 16u + (uint32_t)n * 8u]));
+                ldmatrix_x2_trans(bfrag[n], xs_st + ((k16 * 16u + (lane & 15u)) * kPitch + warp * 16u + (uint32_t)n * 8u) * 2u);
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 uint32_t afrag[4];
-                ldmatrix_x4(afrag, (uint32_t)__cvta_generic_to_shared(&ws[m * 16 + (lane & 15u)][k16 * 16u + (lane >> 4) * 8u]));
+                const uint32_t r = (uint32_t)m * 16u + (lane & 15u);
+                // the tile's swizzle uses the row inside the 128-row tile; j0 is a multiple of 16, so (j0 + r) & 7 == r & 7
+                ldmatrix_x4(afrag, ws_st + r * 128u + (((k16 * 2u + (lane >> 4)) ^ (r & 7u)) << 4));
 #pragma unroll
                 for (int n = 0; n < 2; ++n) mma_16816(acc[m][n], afrag, bfrag[n]);
             }
         }
-        __syncthreads();
     }
+    cp_async_wait<0>();
     if (bad) atomicOr(a.status, (uint32_t)ST_BAD_INDEX);
 
     // epilogue: accumulator (m, n): rows lane/4 and lane/4 + 8 of the 16-row block, columns (lane%4)*2 + {0,1} of the 8-column block
@@ -153,11 +240,18 @@ cudaError_t launch_wave_mma(const WaveArgs &a, cudaStream_t s) {
     const uint32_t rows = a.group % 64u == 0u ? 64u : (a.group % 32u == 0u ? 32u : 16u);
     const dim3 grid(a.num_col_tiles64, (a.cout + rows - 1u) / rows);
     switch (rows) {
-    case 64: mmawave::k44_wave_mma_kernel<4><<<grid, 128, 0, s>>>(a); break;
-    case 32: mmawave::k44_wave_mma_kernel<2><<<grid, 128, 0, s>>>(a); break;
-    default: mmawave::k44_wave_mma_kernel<1><<<grid, 128, 0, s>>>(a); break;
+    case 64: mmawave::k44_wave_mma_kernel<4><<<grid, 128, mmawave::smem_bytes(4), s>>>(a); break;
+    case 32: mmawave::k44_wave_mma_kernel<2><<<grid, 128, mmawave::smem_bytes(2), s>>>(a); break;
+    default: mmawave::k44_wave_mma_kernel<1><<<grid, 128, mmawave::smem_bytes(1), s>>>(a); break;
     }
     return cudaGetLastError();
+}
+
+cudaError_t mma_kernel_setup() {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(mmawave::k44_wave_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mmawave::smem_bytes(4))) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(mmawave::k44_wave_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mmawave::smem_bytes(2))) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(mmawave::k44_wave_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mmawave::smem_bytes(1));
 }
 
 }  // namespace k44b

@@ -319,6 +319,18 @@ def test_token_shift_plan_general_path(group):
     plan = shifted_plan(120, group=group)
     x = synth.random_input(plan, 24, dist="normal")
     check(plan, run_gpu(plan, x, PATH_FMA, expect_path=PATH_FMA), O.run_plan(plan, x))
+    if group < 128:     # shifted runs of a small group: run table + funnel-shifted fetches on the mma.sync kernel
+        check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_MMA), O.run_plan(plan, x))
+
+
+@pytest.mark.parametrize("group,frames,frame_len", [(32, 2, 96), (64, 8, 40), (16, 3, 256)])
+def test_token_shift_small_groups_and_odd_frames_on_the_general_tensor_path(group, frames, frame_len):
+    plan = shifted_plan(150 + group, runs=8, run_len=16, frames=frames, frame_len=frame_len, cout=192, group=group)
+    x = synth.random_input(plan, 27, dist="normal")
+    want = O.run_plan(plan, x)
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_MMA), want)
+    check(plan, run_gpu(plan, x, PATH_FMA, expect_path=PATH_FMA), want)
+
 
 
 @pytest.mark.parametrize("n_tile,frames,frame_len,run_len", [(64, 3, 256, 16), (128, 2, 256, 16), (64, 4, 64, 32), (128, 3, 128, 64), (64, 1, 192, 16),
