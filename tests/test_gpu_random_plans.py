@@ -1,0 +1,60 @@
+"""GPU parity on seeded random plans: group size, run length (down to scattered single rows), fan-in tails, column
+counts, activations, bias, residuals, row maps and token shifts are drawn per case; the executor picks its own kernel
+for every wave (tcgen05, tcgen05 with aligners, small-wave clusters, mma.sync) and must match the CPU oracle within
+rtol 2e-3 / atol 1e-3. The FP32-FMA kernel runs the same plans as a second witness."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from snntome_b200 import synth
+from snntome_b200.native import PATH_AUTO, PATH_FMA
+from snntome_b200.plan import ACT_GELU, ACT_LEAKY_RELU, ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU
+
+from test_gpu_parity import check, run_gpu
+
+pytestmark = pytest.mark.gpu
+ACTS = [ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, ACT_LEAKY_RELU, ACT_GELU]
+
+
+def draw_plan(seed: int):
+    rng = np.random.default_rng(9000 + seed)
+    group = int(rng.choice([16, 32, 64, 128, 256]))
+    cout = group * int(rng.integers(1, 4 if group >= 128 else 7))
+    run_len = int(rng.choice([1, 8, 16, 32, 64]))
+    fan_in = int(rng.choice([64, 96, 128, 160, 256, 320]))
+    while fan_in % run_len:
+        fan_in += 32
+    columns = int(rng.choice([1, 7, 33, 64, 100, 128, 200]))
+    waves = int(rng.integers(2, 4))
+    plan = synth.sparse_plan(seed=seed, input_rows=int(rng.choice([512, 1024])), waves=waves, cout=cout, runs=fan_in // run_len,
+                             run_len=run_len, columns=columns, group=group, act=int(rng.choice(ACTS)),
+                             bias_scale=0.05 if rng.random() < 0.7 else 0.0)
+    notes = [f"group {group}", f"cout {cout}", f"run_len {run_len}", f"fan_in {fan_in}", f"columns {columns}", f"waves {waves}"]
+    for wi, w in enumerate(plan.waves):
+        w.act = int(rng.choice(ACTS))
+        if wi > 0 and rng.random() < 0.4:                          # residual: the previous wave's rows
+            w.has_residual, w.res_off = True, plan.waves[wi - 1].y_off
+            notes.append(f"residual@{wi}")
+        if rng.random() < 0.25:
+            w.cout_map = rng.permutation(cout).astype(np.uint16)
+            notes.append(f"row map@{wi}")
+        if run_len >= 8 and rng.random() < 0.35:                   # token shifts per run, causal zero padding per frame
+            frames = [f for f in (plan.pitch, plan.pitch // 2, 64, 32, 24) if f and plan.pitch % f == 0]
+            w.frame_len = int(rng.choice(frames))
+            per_run = rng.integers(0, 8, size=(cout // group, fan_in // run_len)).astype(np.uint8)
+            w.shifts = np.repeat(per_run, run_len, axis=1)
+            notes.append(f"shifts@{wi} frame {w.frame_len}")
+    return plan, ", ".join(notes)
+
+
+@pytest.mark.parametrize("seed", range(60))
+def test_random_plan_matches_the_oracle(seed):
+    plan, notes = draw_plan(seed)
+    x = synth.random_input(plan, 300 + seed, dist="normal")
+    want = O.run_plan(plan, x)
+    try:
+        check(plan, run_gpu(plan, x, PATH_AUTO), want)
+        if seed % 3 == 0:
+            check(plan, run_gpu(plan, x, PATH_FMA), want)
+    except AssertionError as e:
+        raise AssertionError(f"{notes}: {e}") from None
