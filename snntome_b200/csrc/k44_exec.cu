@@ -693,7 +693,7 @@ bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
         w.args.counters = d_counters_;
         e = launch_wave_umma(w.args, w.desc, w.tmap, num_sms_, stream);
     } else if (w.path == PATH_MMA) {
-        e = launch_wave_mma(w.args, stream);
+        e = launch_wave_mma(w.args, make_umma_desc(64, 0).wait_cycles, stream);
     } else {
         e = launch_wave_fma(w.args, stream);
     }
@@ -815,8 +815,9 @@ bool Executor::set_peers_raw(int rank, int world, void *const *canvas_ptrs, void
     if (!ready()) return fail("executor not initialised");
     if (world < 2 || world > kMaxPeers + 1 || rank < 0 || rank >= world) return fail("set_peers: bad rank / world size");
     for (const auto &w : waves_)
-        if (w.path != PATH_UMMA || w.use_shift)
-            return fail("set_peers: wave '" + w.name + "' does not run on a tensor-core kernel that stores to peers (" + (w.use_shift ? std::string("token-shifted runs") : w.fma_reason) + ")");
+        if ((w.path != PATH_UMMA && w.path != PATH_MMA) || w.use_shift)
+            return fail("set_peers: '" + w.name + "' does not run on a kernel that stores to peers (" +
+                        (w.use_shift ? std::string("token-shifted runs") : w.is_aux ? std::string("element-wise command") : std::string("FP32-FMA kernel")) + ")");
     if (!sync_ptr()) return false;
     PeerArgs pa;
     pa.sync = d_sync_;

@@ -138,7 +138,7 @@ struct UmmaDesc {
 };
 
 cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s);
-cudaError_t launch_wave_mma(const WaveArgs &a, cudaStream_t s);       // general path on mma.sync (k44_mma_kernel.cu)
+cudaError_t launch_wave_mma(const WaveArgs &a, unsigned long long wait_cycles, cudaStream_t s);   // general path on mma.sync (k44_mma_kernel.cu); wait_cycles bounds the peer wait
 cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
 // small waves: one item per CTA, the K splits of a tile form a cluster (k_splits in {1,2,4,8}) and reduce through
 // distributed shared memory; dependent_launch adds the programmatic-dependent-launch attribute

@@ -11,7 +11,9 @@
 // Gather-table entries travel two stages ahead of their rows in a small ring of their own. Rows whose offset is not
 // 16-byte aligned, or that carry a token shift, are fetched with 2-byte loads and the causal mask by the same thread
 // that would have issued the copy. A fragments come from ldmatrix, B fragments from ldmatrix.trans, FP32 accumulators in
-// registers. Nothing here waits on another CTA.
+// registers. Nothing here waits on another CTA; in a neuron-sharded plan one thread waits (bounded) for the peer GPUs' previous
+// launches before the first gather, every output pair is also stored into the peers' canvases, and the CTA that finishes
+// last publishes the launch count (same protocol as the tcgen05 kernels).
 #include "k44_kernels.cuh"
 #include "k44_epilogue.cuh"
 
@@ -92,7 +94,7 @@ __device__ __forceinline__ uint4 fetch_piece_edge(const __half *canvas, uint64_t
 }
 
 template <int MT>
-__global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a) {
+__global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, const unsigned long long wait_cycles) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t kWBytesStage = MT * 16u * 128u;
     constexpr uint32_t D = kStages - 1u;                    // stages in flight ahead of the one being consumed
@@ -172,6 +174,16 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a) {
         }
     };
 
+    // neuron-sharded plans: the rows this launch gathers were stored into this canvas by the peers' previous launches
+    if (a.peers) {
+        __shared__ uint32_t peer_ok;
+        if (tid == 0) {
+            peer_ok = peer_wait_ready(a.peers, wait_cycles) ? 1u : 0u;
+            if (!peer_ok) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PEER);
+        }
+        __syncthreads();
+    }
+
     // prologue: table entries of the first 2D stages, then the rows of the first D stages
     for (uint32_t ks = 0; ks < 2u * D; ++ks) issue_table(ks);
     cp_async_commit();
@@ -227,22 +239,31 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a) {
                 }
                 const float v0 = finish_value(acc[m][n][hrow * 2 + 0], b, r0, a.act, a.has_residual != 0, has_map);
                 const float v1 = finish_value(acc[m][n][hrow * 2 + 1], b, r1, a.act, a.has_residual != 0, has_map);
-                *reinterpret_cast<__half2 *>(a.canvas + a.y_off + o) = __floats2half2_rn(v0, v1);
+                const __half2 out = __floats2half2_rn(v0, v1);
+                *reinterpret_cast<__half2 *>(a.canvas + a.y_off + o) = out;
+                if (a.peers) {
+                    const uint32_t n = (a.peers->dev_flags & 1u) ? 0u : a.peers->n_peers;
+                    for (uint32_t q = 0; q < n; ++q) *reinterpret_cast<__half2 *>(a.peers->canvas[q] + a.y_off + o) = out;
+                }
             }
         }
+    if (a.peers) {
+        __syncthreads();                    // orders every thread's peer stores before thread 0's system-scope fence
+        if (tid == 0) peer_signal_done(a.peers, gridDim.x * gridDim.y);
+    }
 }
 
 }  // namespace mmawave
 
-cudaError_t launch_wave_mma(const WaveArgs &a, cudaStream_t s) {
+cudaError_t launch_wave_mma(const WaveArgs &a, unsigned long long wait_cycles, cudaStream_t s) {
     if (a.group % 16u) return cudaErrorInvalidValue;
     // the CTA's neurons must share one gather list: 64, 32 or 16 of them, whichever divides the group
     const uint32_t rows = a.group % 64u == 0u ? 64u : (a.group % 32u == 0u ? 32u : 16u);
     const dim3 grid(a.num_col_tiles64, (a.cout + rows - 1u) / rows);
     switch (rows) {
-    case 64: mmawave::k44_wave_mma_kernel<4><<<grid, 128, mmawave::smem_bytes(4), s>>>(a); break;
-    case 32: mmawave::k44_wave_mma_kernel<2><<<grid, 128, mmawave::smem_bytes(2), s>>>(a); break;
-    default: mmawave::k44_wave_mma_kernel<1><<<grid, 128, mmawave::smem_bytes(1), s>>>(a); break;
+    case 64: mmawave::k44_wave_mma_kernel<4><<<grid, 128, mmawave::smem_bytes(4), s>>>(a, wait_cycles); break;
+    case 32: mmawave::k44_wave_mma_kernel<2><<<grid, 128, mmawave::smem_bytes(2), s>>>(a, wait_cycles); break;
+    default: mmawave::k44_wave_mma_kernel<1><<<grid, 128, mmawave::smem_bytes(1), s>>>(a, wait_cycles); break;
     }
     return cudaGetLastError();
 }

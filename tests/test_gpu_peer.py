@@ -67,11 +67,30 @@ def test_small_waves_with_residual_store_to_every_canvas():
     assert np.array_equal(got[0], got[1])
 
 
-def test_plans_with_general_path_waves_are_rejected():
+@pytest.mark.parametrize("world,group", [(2, 32), (4, 16), (2, 64)])
+def test_small_group_waves_store_to_every_canvas(world, group):
+    """Groups of 16 / 32 / 64 neurons run on the mma.sync kernel, which speaks the same protocol: bounded wait for the peers'
+    launch counts, every output pair stored into every canvas, launch count published by the last CTA. The last wave gathers
+    scattered single rows (index table instead of a run table)."""
+    plan = synth.sparse_plan(seed=99 + group, input_rows=1024, waves=3, cout=64 * world, runs=8, run_len=16, columns=100, group=group, act=ACT_SILU)
+    rng = np.random.default_rng(group)
+    plan.waves[2].idx = (rng.integers(0, 1024 + 2 * 64 * world, size=plan.waves[2].idx.shape) * plan.pitch).astype(np.uint32)
+    x = synth.random_input(plan, 96, dist="normal")
+    want = O.run_plan(plan, x)
+    got = run_sharded_on_one_gpu(plan, x, world)
+    for r in range(world):
+        for w in plan.waves:
+            a, b = w.y_off, w.y_off + w.cout * plan.pitch
+            ok, err, k = O.compare(got[r][a:b], want[a:b], RTOL, ATOL)
+            assert ok, (r, w.name, err, k)
+        assert np.array_equal(got[r], got[0])
+
+
+def test_plans_with_fma_path_waves_are_rejected():
     plan = synth.sparse_plan(seed=95, input_rows=512, waves=1, cout=256, runs=8, run_len=32, columns=64, group=128, act=ACT_RELU)
     p0 = NativePlan.from_plan(shard.shard_plan(plan, 0, 2), device=0, force_path=PATH_FMA)
     p1 = NativePlan.from_plan(shard.shard_plan(plan, 1, 2), device=0)
-    with pytest.raises(NativeError, match="tensor-core"):
+    with pytest.raises(NativeError, match="stores to peers"):
         p0.set_peers_raw(0, 2, [p0.canvas_ptr, p1.canvas_ptr], [p0.sync_ptr, p1.sync_ptr])
     p0.close(); p1.close()
 
