@@ -20,8 +20,8 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _plan():
-    return synth.sparse_plan(seed=81, input_rows=2048, waves=3, cout=1024, runs=8, run_len=32, columns=128, group=128, act=ACT_RELU)
+def _plan(group=128):
+    return synth.sparse_plan(seed=81, input_rows=2048, waves=3, cout=1024, runs=8, run_len=32, columns=128, group=group, act=ACT_RELU)
 
 
 def _worker(rank, world, port, out_dir):
@@ -66,7 +66,7 @@ def test_two_gpu_neuron_sharding_matches_oracle(tmp_path):
     assert np.array_equal(np.load(tmp_path / "canvas0.npy"), np.load(tmp_path / "canvas1.npy"))
 
 
-def _worker_fused(rank, world, port, out_dir):
+def _worker_fused(rank, world, port, out_dir, group):
     import torch
     import torch.distributed as dist
     from snntome_b200.native import NativePlan
@@ -76,7 +76,7 @@ def _worker_fused(rank, world, port, out_dir):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        plan = _plan()
+        plan = _plan(group)
         x = synth.random_input(plan, 82)
         npn = NativePlan.from_plan(shard.shard_plan(plan, rank, world), device=rank)
         canvas = npn.canvas_tensor()
@@ -96,13 +96,15 @@ def _worker_fused(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-def test_two_gpu_peer_stores_match_oracle(tmp_path):
+@pytest.mark.parametrize("group", [128, 32])
+def test_two_gpu_peer_stores_match_oracle(tmp_path, group):
+    """group 128: tcgen05 kernels; group 32: the mma.sync kernel — both store their rows into the peer's canvas themselves."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_worker_fused, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    plan = _plan()
+    mp.spawn(_worker_fused, args=(2, _free_port(), str(tmp_path), group), nprocs=2, join=True)
+    plan = _plan(group)
     want = O.run_plan(plan, synth.random_input(plan, 82))
     for r in range(2):
         got = np.load(tmp_path / f"fused{r}.npy")
