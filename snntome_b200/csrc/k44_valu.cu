@@ -326,29 +326,6 @@ __global__ void __launch_bounds__(128, MINB) k44_valu_decode_attn_partial_kernel
     fetch(p_begin, kv, vv);
     for (uint32_t p = p_begin; p < p_end; p += UNROLL) {
         if (p + UNROLL < p_end) fetch(p + UNROLL, kn, vn);
-        if constexpr (UNROLL == 2u) {
-            // two positions share one rescale of the running state: three exponentials and three FMAs per value instead of four
-            float k0[8], k1[8], v0[8], v1[8];
-            unpack8(kv[0], k0); unpack8(kv[1], k1);
-            unpack8(vv[0], v0); unpack8(vv[1], v1);
-            const bool second = p + 1u < p_end;
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float d0 = 0.f, d1 = 0.f;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) { d0 = fmaf(q[g][e], k0[e], d0); d1 = fmaf(q[g][e], k1[e], d1); }
-                d0 += __shfl_xor_sync(0xffffffffu, d0, 1); d1 += __shfl_xor_sync(0xffffffffu, d1, 1);
-                d0 += __shfl_xor_sync(0xffffffffu, d0, 2); d1 += __shfl_xor_sync(0xffffffffu, d1, 2);
-                d0 += __shfl_xor_sync(0xffffffffu, d0, 4); d1 += __shfl_xor_sync(0xffffffffu, d1, 4);
-                if (!second) d1 = -1.0e30f;                          // no second position: weight exp(-inf) = 0
-                const float mn = fmaxf(m[g], fmaxf(d0, d1));
-                const float ep = __expf(m[g] - mn), e0 = __expf(d0 - mn), e1 = __expf(d1 - mn);
-                l[g] = fmaf(l[g], ep, e0 + e1);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(acc[g][e], ep, fmaf(e0, v0[e], e1 * v1[e]));
-                m[g] = mn;
-            }
-        } else {
 #pragma unroll
         for (uint32_t u = 0; u < UNROLL; ++u) {
             if (p + u >= p_end) break;
@@ -370,7 +347,6 @@ __global__ void __launch_bounds__(128, MINB) k44_valu_decode_attn_partial_kernel
                 for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(acc[g][e], ep, ec * vf[e]);
                 m[g] = mn;
             }
-        }
         }
 #pragma unroll
         for (uint32_t u = 0; u < UNROLL; ++u) { kv[u] = kn[u]; vv[u] = vn[u]; }
