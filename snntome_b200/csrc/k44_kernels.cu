@@ -41,8 +41,8 @@ __global__ void __launch_bounds__(256) k44_wave_fma_kernel(const WaveArgs a) {
     __shared__ uint64_t offs[kStageK];
     __shared__ uint32_t shs[kStageK];
 
-    const uint32_t tile = blockIdx.x;                     // 64-column tile
-    const uint32_t j0 = blockIdx.y * kFmaRows;            // first neuron
+    const uint32_t tile = blockIdx.x % a.num_col_tiles64;                 // 64-column tile (one-dimensional grid: y stops at 65535 blocks)
+    const uint32_t j0 = (blockIdx.x / a.num_col_tiles64) * kFmaRows;      // first neuron
     const uint32_t g = j0 / a.group;
     const uint32_t tid = threadIdx.x, c = tid & 63u, q = tid >> 6;
     const __half *xbase = a.canvas + a.x_base_off + (uint64_t)tile * 64u;
@@ -109,7 +109,9 @@ __global__ void __launch_bounds__(256) k44_wave_fma_kernel(const WaveArgs a) {
 }
 
 cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s) {
-    dim3 grid(a.num_col_tiles64, (a.cout + kFmaRows - 1) / kFmaRows);
+    const uint64_t blocks = (uint64_t)a.num_col_tiles64 * ((a.cout + kFmaRows - 1) / kFmaRows);
+    if (blocks == 0 || blocks > 0x7fffffffull) return cudaErrorInvalidValue;
+    dim3 grid((uint32_t)blocks);
     k44_wave_fma_kernel<<<grid, 256, 0, s>>>(a);
     return cudaGetLastError();
 }

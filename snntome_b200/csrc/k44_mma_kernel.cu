@@ -104,8 +104,10 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
     uint8_t *const xs_gen = smem;
     const uint32_t *const tab_gen = reinterpret_cast<const uint32_t *>(smem + kStages * (kXBytesStage + kWBytesStage));
 
-    const uint32_t tile = blockIdx.x;                       // 64-column tile
-    const uint32_t j0 = blockIdx.y * (MT * 16u);            // first neuron of this CTA
+    // one-dimensional grid (the y extent of a grid stops at 65535 blocks: too few for a million neurons in blocks of 16);
+    // column tiles of one neuron block are neighbours, so they find the block's weights in L2
+    const uint32_t tile = blockIdx.x % a.num_col_tiles64;                   // 64-column tile
+    const uint32_t j0 = (blockIdx.x / a.num_col_tiles64) * (MT * 16u);      // first neuron of this CTA
     const uint32_t g = j0 / a.group;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const __half *xbase = a.canvas + a.x_base_off + (uint64_t)tile * 64u;
@@ -249,7 +251,7 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
         }
     if (a.peers) {
         __syncthreads();                    // orders every thread's peer stores before thread 0's system-scope fence
-        if (tid == 0) peer_signal_done(a.peers, gridDim.x * gridDim.y);
+        if (tid == 0) peer_signal_done(a.peers, gridDim.x);
     }
 }
 
@@ -259,7 +261,9 @@ cudaError_t launch_wave_mma(const WaveArgs &a, unsigned long long wait_cycles, c
     if (a.group % 16u) return cudaErrorInvalidValue;
     // the CTA's neurons must share one gather list: 64, 32 or 16 of them, whichever divides the group
     const uint32_t rows = a.group % 64u == 0u ? 64u : (a.group % 32u == 0u ? 32u : 16u);
-    const dim3 grid(a.num_col_tiles64, (a.cout + rows - 1u) / rows);
+    const uint64_t blocks = (uint64_t)a.num_col_tiles64 * ((a.cout + rows - 1u) / rows);
+    if (blocks == 0 || blocks > 0x7fffffffull) return cudaErrorInvalidValue;
+    const dim3 grid((uint32_t)blocks);
     switch (rows) {
     case 64: mmawave::k44_wave_mma_kernel<4><<<grid, 128, mmawave::smem_bytes(4), s>>>(a, wait_cycles); break;
     case 32: mmawave::k44_wave_mma_kernel<2><<<grid, 128, mmawave::smem_bytes(2), s>>>(a, wait_cycles); break;

@@ -201,3 +201,45 @@ def test_decoder_wave_chain_graph_replay(group_launches, monkeypatch):
         ok, err, k = O.compare(got[a:b], want[a:b], RTOL, ATOL)
         assert ok, (w.name, err, k)
     npn.close()
+
+
+@pytest.mark.parametrize("path_name", ["auto", "fma"])
+def test_more_than_65535_neuron_blocks_of_a_small_group(path_name):
+    """A million neurons in groups of 16 (the full-size plan's neuron count): 65,538 neuron blocks per column tile, more than
+    the y extent of a grid allows, so the general kernels index a one-dimensional grid. Sampled groups against the oracle,
+    the last (partial-range) blocks included."""
+    import torch
+    from snntome_b200.native import PATH_AUTO, PATH_FMA, PATH_MMA
+    from snntome_b200.plan import expand_runs
+    force = PATH_AUTO if path_name == "auto" else PATH_FMA
+    rng = np.random.default_rng(77)
+    group, fan_in, pitch, rows_in = 16, 64, 64, 4096
+    cout = 65536 * 16 + 32
+    groups = cout // group
+    starts = (rng.integers(0, rows_in // 16, size=(groups, 4)) * 16).astype(np.int64)          # four runs of 16 rows per group
+    idx = expand_runs(starts, 16, pitch)
+    wts = synth.f16_bits(rng.normal(0, 0.125, size=(cout, fan_in)).astype(np.float32))
+    wave = Wave(cout=cout, group=group, fan_in=fan_in, idx=idx, weights=wts, bias=None, y_off=rows_in * pitch, act=ACT_RELU, name="wide")
+    plan = Plan(canvas_elems=(rows_in + cout) * pitch, pitch=pitch, columns=pitch, input_off=0, input_c=rows_in,
+                output_off=rows_in * pitch, output_c=cout, waves=[wave])
+    x = synth.random_input(plan, 78, dist="normal")
+    npn = NativePlan.from_plan(plan, device=0, force_path=force)
+    assert npn.wave_info(0).path == (PATH_MMA if path_name == "auto" else PATH_FMA)
+    canvas = npn.canvas_tensor()
+    canvas[: x.size] = torch.from_numpy(x.view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    npn.execute()
+    assert npn.status() == 0
+    got = canvas.cpu().numpy().view(np.uint16)
+    npn.close()
+    picks = np.concatenate([rng.integers(0, groups, size=48), [0, 4095, 4096, groups - 3, groups - 2, groups - 1]])
+    xin = x.reshape(rows_in, pitch)
+    for g in picks:
+        g = int(g)
+        sub = Wave(cout=group, group=group, fan_in=fan_in, idx=idx[g:g + 1].copy(), weights=wts[g * group:(g + 1) * group].copy(), bias=None,
+                   y_off=rows_in * pitch, act=ACT_RELU, name="sample")
+        sp = Plan(canvas_elems=(rows_in + group) * pitch, pitch=pitch, columns=pitch, input_off=0, input_c=rows_in,
+                  output_off=rows_in * pitch, output_c=group, waves=[sub])
+        want = O.run_plan(sp, xin)[rows_in * pitch:]
+        a = (rows_in + g * group) * pitch
+        ok, err, k = O.compare(got[a:a + group * pitch], want, RTOL, ATOL)
+        assert ok, (g, err, k)
