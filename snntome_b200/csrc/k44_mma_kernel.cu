@@ -9,8 +9,8 @@
 // (row pitch 72 halves, so the 8 rows of an ldmatrix fall into distinct banks) and the weight rows exactly as the tiled
 // format stores them (128-byte rows, 16-byte chunk c at position c ^ (row & 7): conflict-free for ldmatrix as it is).
 // Gather-table entries travel two stages ahead of their rows in a small ring of their own. Rows whose offset is not
-// 16-byte aligned, or that carry a token shift, are fetched with 2-byte loads and the causal mask by the same thread
-// that would have issued the copy. A fragments come from ldmatrix, B fragments from ldmatrix.trans, FP32 accumulators in
+// 16-byte aligned, or that carry a token shift, are cut out of the two aligned 16-byte vectors around them (funnel shift,
+// causal mask in registers) by the same thread that would have issued the copy. A fragments come from ldmatrix, B fragments from ldmatrix.trans, FP32 accumulators in
 // registers. Nothing here waits on another CTA; in a neuron-sharded plan one thread waits (bounded) for the peer GPUs' previous
 // launches before the first gather, every output pair is also stored into the peers' canvases, and the CTA that finishes
 // last publishes the launch count (same protocol as the tcgen05 kernels).
