@@ -5,7 +5,7 @@
 // stays as the arithmetic cross-check.
 //
 // CTA = 128 threads = MT x 16 neurons of one group (MT = 1, 2 or 4) x one 64-column tile; warp w owns columns
-// 16w .. 16w+15. A ring of kStages stages of 64 synapses is filled with cp.async: the gathered rows as [synapse][column]
+// 16w .. 16w+15. A ring of kStages (two) stages of 64 synapses is filled with cp.async: the gathered rows as [synapse][column]
 // (row pitch 72 halves, so the 8 rows of an ldmatrix fall into distinct banks) and the weight rows exactly as the tiled
 // format stores them (128-byte rows, 16-byte chunk c at position c ^ (row & 7): conflict-free for ldmatrix as it is).
 // Gather-table entries travel two stages ahead of their rows in a small ring of their own. Rows whose offset is not
@@ -21,7 +21,7 @@ namespace k44b {
 namespace mmawave {
 
 constexpr uint32_t kPitch = 72;         // halves per gathered row in shared memory
-constexpr uint32_t kStages = 3;
+constexpr uint32_t kStages = 2;
 constexpr uint32_t kXBytesStage = kStageK * kPitch * 2u;
 constexpr uint32_t kTabRing = 2u * (kStages - 1u) + 1u;   // table entries run up to 2 (kStages - 1) stages ahead of the stage being consumed
 constexpr uint32_t smem_bytes(uint32_t mt) { return kStages * (kXBytesStage + mt * 16u * 128u) + kTabRing * kStageK * 4u; }
