@@ -125,7 +125,8 @@ int k44b_plan_get_next_tokens(void *plan, int32_t *h_tokens, uint32_t n, void *s
  * kernels store each output row into the rank's own canvas and into the peers' canvases (peer-mapped memory over
  * NVLink), and a launch starts reading only when every peer has finished the launches before it (one 32-bit word per
  * peer, bounded wait: status bit 5 on expiry). All ranks must issue the same sequence of launches. Supported for waves
- * that run on the tcgen05 kernels; plans with general-path or token-shifted waves are rejected. world <= 8.
+ * that run on the tcgen05 kernels or on the mma.sync kernel (small neuron groups); plans with token-shifted waves,
+ * element-wise commands or waves forced onto the FP32-FMA kernel are rejected. world <= 8.
  *   ipc_handles:    64-byte CUDA IPC handles of this plan's canvas and sync block, to be sent to the other processes
  *   set_peers_ipc:  `world` handles each (indexed by rank; the own entries are ignored), opened with peer access
  *   set_peers_raw:  the same with device pointers that are already valid on this GPU (same process)            */
