@@ -5,7 +5,7 @@
 // stays as the arithmetic cross-check.
 //
 // CTA = 128 threads = MT x 16 neurons of one group (MT = 1, 2 or 4) x one 64-column tile; warp w owns columns
-// 16w .. 16w+15. A ring of kStages (two) stages of 64 synapses is filled with cp.async: the gathered rows as [synapse][column]
+// 16w .. 16w+15 (64 rows: the four warps form a 2 x 2 grid of 32 x 32 blocks). A ring of kStages (two) stages of 64 synapses is filled with cp.async: the gathered rows as [synapse][column]
 // (row pitch 72 halves, so the 8 rows of an ldmatrix fall into distinct banks) and the weight rows exactly as the tiled
 // format stores them (128-byte rows, 16-byte chunk c at position c ^ (row & 7): conflict-free for ldmatrix as it is).
 // Gather-table entries travel two stages ahead of their rows in a small ring of their own. Rows whose offset is not
@@ -29,8 +29,8 @@ constexpr uint32_t smem_bytes(uint32_t mt) { return kStages * (kXBytesStage + mt
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
-__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -119,11 +119,16 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
     const uint32_t *table = a.gather + (uint64_t)g * (box ? a.boxes_per_group : a.fan_in);
     const uint4 *wrow0 = a.w_tiles + ((uint64_t)(j0 >> 7) * nk * 128u + (j0 & 127u)) * 8u;   // + ks * 1024 vectors per stage
 
-    float acc[MT][2][4];
+    // warp grid: 2 x 2 warps for 64 rows (each warp: two 16-row blocks x 32 columns), 1 x 4 for 16 / 32 rows (all rows x 16
+    // columns per warp; measured: 2 x 2 gains 2 % at 64 rows and loses 8 % at 32). The B fragments of two neighbouring
+    // 8-column blocks come from one ldmatrix.x4.trans and are reused by the warp's MW row blocks.
+    constexpr uint32_t WR = MT >= 4 ? 2u : 1u, WC = 4u / WR, MW = MT / WR, NW = 8u / WC;
+    const uint32_t wr = warp / WC, wc = warp % WC;
+    float acc[MW][NW][4];
 #pragma unroll
-    for (int m = 0; m < MT; ++m)
+    for (int m = 0; m < (int)MW; ++m)
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
+        for (int n = 0; n < (int)NW; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[m][n][e] = 0.f;
     bool bad = false;
@@ -203,18 +208,23 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
         const uint32_t xs_st = xs + st * kXBytesStage, ws_st = ws + st * kWBytesStage;
 #pragma unroll
         for (uint32_t k16 = 0; k16 < kStageK / 16u; ++k16) {
-            uint32_t bfrag[2][2];
+            uint32_t bfrag[NW][2];
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
-                ldmatrix_x2_trans(bfrag[n], xs_st + ((k16 * 16u + (lane & 15u)) * kPitch + warp * 16u + (uint32_t)n * 8u) * 2u);
+            for (int n2 = 0; n2 < (int)NW / 2; ++n2) {
+                // four 8 x 8 blocks: synapses 0-7 / 8-15 of this K step x two neighbouring 8-column blocks
+                uint32_t t4[4];
+                ldmatrix_x4_trans(t4, xs_st + ((k16 * 16u + (lane & 15u)) * kPitch + wc * (NW * 8u) + (uint32_t)n2 * 16u + (lane >> 4) * 8u) * 2u);
+                bfrag[2 * n2][0] = t4[0]; bfrag[2 * n2][1] = t4[1];
+                bfrag[2 * n2 + 1][0] = t4[2]; bfrag[2 * n2 + 1][1] = t4[3];
+            }
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
+            for (int m = 0; m < (int)MW; ++m) {
                 uint32_t afrag[4];
-                const uint32_t r = (uint32_t)m * 16u + (lane & 15u);
+                const uint32_t r = (wr * MW + (uint32_t)m) * 16u + (lane & 15u);
                 // the tile's swizzle uses the row inside the 128-row tile; j0 is a multiple of 16, so (j0 + r) & 7 == r & 7
                 ldmatrix_x4(afrag, ws_st + r * 128u + (((k16 * 2u + (lane >> 4)) ^ (r & 7u)) << 4));
 #pragma unroll
-                for (int n = 0; n < 2; ++n) mma_16816(acc[m][n], afrag, bfrag[n]);
+                for (int n = 0; n < (int)NW; ++n) mma_16816(acc[m][n], afrag, bfrag[n]);
             }
         }
     }
@@ -224,16 +234,16 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
     // epilogue: accumulator (m, n): rows lane/4 and lane/4 + 8 of the 16-row block, columns (lane%4)*2 + {0,1} of the 8-column block
     const bool has_map = a.cout_map != nullptr;
 #pragma unroll
-    for (int m = 0; m < MT; ++m)
+    for (int m = 0; m < (int)MW; ++m)
 #pragma unroll
         for (int hrow = 0; hrow < 2; ++hrow) {
-            const uint32_t j = j0 + (uint32_t)m * 16u + (lane >> 2) + (uint32_t)hrow * 8u;
+            const uint32_t j = j0 + (wr * MW + (uint32_t)m) * 16u + (lane >> 2) + (uint32_t)hrow * 8u;
             if (j >= a.cout) continue;
             const uint32_t oj = has_map ? a.cout_map[j] : j;
             const float b = a.bias ? __half2float(a.bias[j]) : 0.0f;
 #pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const uint64_t o = (uint64_t)oj * a.pitch + (uint64_t)tile * 64u + warp * 16u + (uint32_t)n * 8u + (lane & 3u) * 2u;
+            for (int n = 0; n < (int)NW; ++n) {
+                const uint64_t o = (uint64_t)oj * a.pitch + (uint64_t)tile * 64u + wc * (NW * 8u) + (uint32_t)n * 8u + (lane & 3u) * 2u;
                 float r0 = 0.f, r1 = 0.f;
                 if (a.has_residual) {
                     const float2 rr = __half22float2(*reinterpret_cast<const __half2 *>(a.canvas + a.res_off + o));
