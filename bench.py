@@ -65,6 +65,60 @@ def measured_peaks() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
+def host_threads() -> int:
+    """CPU threads this process may use. (torch.distributed.run exports OMP_NUM_THREADS=1 to its children; the CPU arm sets
+    its own thread count from this instead.)"""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        return max(1, os.cpu_count() or 1)
+
+
+def gpu_numa_cpus(device: int) -> list[int]:
+    """CPUs of the NUMA node the GPU hangs off (from sysfs), restricted to the CPUs this process may use; empty if unknown."""
+    try:
+        import torch
+        props = torch.cuda.get_device_properties(device)
+        if hasattr(props, "pci_bus_id"):
+            addr = f"{getattr(props, 'pci_domain_id', 0):04x}:{props.pci_bus_id:02x}:{getattr(props, 'pci_device_id', 0):02x}.0"
+        else:       # older bindings: ask the driver tool (the index is the visible-device ordinal only without a device mask)
+            out = subprocess.run(["nvidia-smi", "--query-gpu=pci.bus_id", "--format=csv,noheader", "-i", str(device)],
+                                 capture_output=True, text=True, timeout=10).stdout.strip().lower()
+            addr = out[-12:]                            # "00000000:1b:00.0" -> "0000:1b:00.0"
+        node = int(Path(f"/sys/bus/pci/devices/{addr}/numa_node").read_text().strip())
+        if node < 0:
+            return []
+        cpus: list[int] = []
+        for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+            a, _, b = part.partition("-")
+            cpus += list(range(int(a), int(b or a) + 1))
+        allowed = os.sched_getaffinity(0)
+        return [c for c in cpus if c in allowed]
+    except Exception:
+        return []
+
+
+def pinned_near_gpu(n_elems: int, device: int):
+    """Pinned FP16 host buffer whose pages are first touched by a thread running on the GPU's own NUMA node, so that with
+    several ranks per host the uploads do not all cross the socket interconnect. Returns (tensor, node cpus used or None)."""
+    import torch
+    cpus = gpu_numa_cpus(device)
+    before = None
+    if cpus:
+        try:
+            before = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, cpus)
+        except OSError:
+            before = None
+    try:
+        t = torch.empty(n_elems, dtype=torch.float16).pin_memory()
+        t.zero_()
+    finally:
+        if before is not None:
+            os.sched_setaffinity(0, before)
+    return t, (len(cpus) if before is not None else None)
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -150,8 +204,7 @@ def cpu_baseline(w: dict, seconds_target: float = 15.0, threads: int | None = No
     from snntome_b200 import synth
     from snntome_b200.plan import Plan, Wave, expand_runs
     L = O.lib()
-    if threads:
-        L.k44o_set_num_threads(threads)
+    L.k44o_set_num_threads(threads or host_threads())
     cores = L.k44o_num_threads()
     fan_in = w["runs"] * w["run_len"]
     rows = 1 << 20                                   # 128 MiB substrate sample (far beyond the CPU caches)
@@ -276,6 +329,64 @@ def build_decoder_plan(cfg: dict, device: int, seed: int = 7, full: bool = False
     return plan, params, rows
 
 
+def reference_call_e2e(device: int, steps: int = 5, layers: int | None = None, tokens: int = 64) -> dict:
+    """End to end through the reference's own execution call, `wavec_gpu_infer_f32` (wavec/k44_wave_executor.cu:972-986): a
+    decoder of the 1B shape built with the reference's graph-builder calls the way its LLM example does (RMSNorm, q/k/v/o,
+    rotary + causal grouped-query attention, gated MLP, residuals, final norm, lm_head), one sequence of 64 tokens, dense
+    host FP32 [2048][1][64] in and [128256][1][64] out per call, blocking. The ultra-sparse plan itself cannot go through this
+    call: its input tensor has 2.56e9 elements and the call's `int in_elems` stops at 2^31 - 1. Weights: one random FP16
+    block per distinct shape, reused by every layer (the call's cost does not depend on the values)."""
+    import torch
+    from snntome_b200.wavec import WaveGraph
+    cfg = dict(DECODER, layers=layers or DECODER["layers"])
+    H, F, V, HQ, HKV, HD = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+    rng = np.random.default_rng(31)
+    blk = lambda o, i: (rng.standard_normal((o, i), dtype=np.float32) * 0.02).astype(np.float16)
+    wq, wkv, wgu, wd, wlm = blk(H, H), blk(HKV * HD, H), blk(F, H), blk(H, F), blk(V, H)
+    ones = np.ones(H, dtype=np.float32)
+    t_build = time.perf_counter()
+    g = WaveGraph(max_B_per_wave=F, default_S=64, fold_rmsnorm_gamma=True, reuse_canvas=True)
+    g.add_input("x0", c=H, h=1, w=tokens, is_1d=True)
+    x = "x0"
+    for l in range(cfg["layers"]):
+        g.add_rmsnorm(f"L{l}.n1", x, f"L{l}.a", H, ones, eps=1e-5)
+        g.add_linear(f"L{l}.q", f"L{l}.a", f"L{l}.qv", H, H, wq, act="none")
+        g.add_linear(f"L{l}.k", f"L{l}.a", f"L{l}.kv", H, HKV * HD, wkv, act="none")
+        g.add_linear(f"L{l}.v", f"L{l}.a", f"L{l}.vv", H, HKV * HD, wkv, act="none")
+        g.add_rope_gqa_attn(f"L{l}.att", f"L{l}.qv", f"L{l}.kv", f"L{l}.vv", f"L{l}.ao", HQ, HKV, HD, rope_theta=500000.0, llama3_scaling=True)
+        g.add_linear(f"L{l}.o", f"L{l}.ao", f"L{l}.h", H, H, wq, act="none", res_blob=x)
+        g.add_rmsnorm(f"L{l}.n2", f"L{l}.h", f"L{l}.b", H, ones, eps=1e-5)
+        g.add_linear(f"L{l}.gate", f"L{l}.b", f"L{l}.g", H, F, wgu, act="silu")
+        g.add_linear(f"L{l}.up", f"L{l}.b", f"L{l}.u", H, F, wgu, act="none")
+        g.add_swiglu(f"L{l}.sw", f"L{l}.g", f"L{l}.u", f"L{l}.f", F)
+        g.add_linear(f"L{l}.down", f"L{l}.f", f"L{l}.x", F, H, wd, act="none", res_blob=f"L{l}.h")
+        x = f"L{l}.x"
+    g.add_rmsnorm("final_norm", x, "xn", H, ones, eps=1e-5)
+    g.add_linear("lm_head", "xn", "logits", H, V, wlm, act="none")
+    g.set_output("logits")
+    plan = g.compile()
+    plan.init_gpu(device=device)
+    build_s = time.perf_counter() - t_build
+    xin = (rng.standard_normal((H, 1, tokens)) * 0.5).astype(np.float32)
+    out, _ = plan.infer_f32(xin)                       # warm-up (also allocates the staging buffers)
+    torch.cuda.synchronize()
+    gpu_ms = []
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        out, ms = plan.infer_f32(xin)
+        gpu_ms.append(ms)
+    wall_ms = (time.perf_counter() - t0) * 1e3 / steps
+    summ = plan.summary
+    res = {"api": "wavec_gpu_infer_f32 (dense host FP32 in and out, blocking; graph built with wavec_add_* and wavec_compile)",
+           "workload": f"1B-shape decoder, {cfg['layers']} layers + final norm + lm_head, one sequence of {tokens} tokens "
+                       f"({summ.get('num_waves')} waves, {summ.get('num_cmds')} commands)",
+           "value": tokens / (wall_ms * 1e-3), "unit": "tok/s", "ms_per_call": wall_ms, "gpu_ms_waves_only": float(np.mean(gpu_ms)),
+           "steps": steps, "h2d_bytes_per_step": int(xin.nbytes), "d2h_bytes_per_step": int(out.nbytes),
+           "build_and_upload_s": build_s, "finite": bool(np.isfinite(out).all()), "checksum": float(np.abs(out[:64]).sum())}
+    plan.release_gpu()
+    return res
+
+
 def decode_main(args) -> None:
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -392,20 +503,18 @@ def decode_main(args) -> None:
 PRUNED = dict(hidden=4096, layers=32, kv=1024, ffn=14336, vocab=128256, columns=256, cluster=32, keep=0.10)
 
 
-def sharded_main(args) -> None:
+def sharded_measure(layers: int, steps: int, warmup: int, rank: int, local_rank: int, world: int, breakdown: bool = True) -> dict:
     """Llama-3-8B shaped wave chain; every 128-neuron group keeps 10 % of its 32-row input clusters (uniform,
     seeded); the lm_head stays dense. Rank r owns rows [r*cout/n, (r+1)*cout/n) of every wave and only their
-    weights; after each wave the rows are all-gathered in place on the replicated canvas (NCCL over NVLink)."""
+    weights; the rows of every wave reach all replicas of the canvas (see K44B_SHARD_MODE below). The default process
+    group must already exist when world > 1. Every rank returns the same result line (a dict); a kernel status other
+    than zero on any rank is reported in it as "error" instead of raised, so that all ranks keep taking the same path."""
     import torch
     import torch.distributed as dist
     from snntome_b200 import shard, synth
     from snntome_b200._lib import WaveDesc
     from snntome_b200.native import NativePlan, fill_normal_f16
-    rank = int(os.environ.get("RANK", "0")); local_rank = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    cfg = dict(PRUNED, layers=args.layers if args.layers != 16 else PRUNED["layers"])
+    cfg = dict(PRUNED, layers=layers)
     H, F, V, KV, C = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["kv"], cfg["columns"]
     V = -(-V // (world * 128)) * world * 128      # vocabulary rows padded to whole 128-neuron groups per rank (128256 -> 128512 at 4 and 8 ranks)
     pitch = C
@@ -441,6 +550,7 @@ def sharded_main(args) -> None:
         d.cin, d.group, d.fan_in, d.fan_in_raw, d.act = cin, 128, fan_in, fan_in, act
         d.has_residual = 1 if res else 0
         d.y_off = (rows[dst] + r0) * pitch
+        d.src_off = rows[src] * pitch
         d.res_off = (rows[res] + r0) * pitch if res else 0
         d.run_rows, d.run_len = starts.ctypes.data, run_len
         d.weights, d.weights_on_device = wv.data_ptr(), 1
@@ -457,7 +567,6 @@ def sharded_main(args) -> None:
             add(f"L{layer}.{name}", wi, src, dst, cin, cout, act, res); wi += 1
         x_in, x_out = x_out, x_in
     add("lm_head", wi, x_in, "logits", H, V, dense=True)
-    lm_sharded = True
     del scratch
     torch.cuda.empty_cache()
     canvas = plan.canvas_tensor()
@@ -498,34 +607,44 @@ def sharded_main(args) -> None:
         else:
             eager_step()
 
-    warmup = max(3, args.warmup)
+    def all_status() -> int:              # the kernels' status word, worst over the ranks (every rank calls this at the same points)
+        st = plan.status_code()
+        if world > 1:
+            t = torch.tensor([st], device="cuda", dtype=torch.int32)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            st = int(t.item())
+        return st
+
+    warmup = max(3, warmup)
     sampler = ClockSampler(local_rank); sampler.start()
     for _ in range(warmup):
         step()
-    assert plan.status() == 0
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
-    l0 = plan.launch_count
-    t0.record(stream)
-    for _ in range(args.steps):
-        step()
-    t1.record(stream)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    assert plan.status() == 0
-    launches = plan.launch_count - l0
-    ms = t0.elapsed_time(t1)
-    if world > 1:
-        t = torch.tensor([ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
-    ms_step = ms / args.steps
+    status = all_status()
+    ms_step, launches = float("nan"), 0
+    if status == 0:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        l0 = plan.launch_count
+        t0.record(stream)
+        for _ in range(steps):
+            step()
+        t1.record(stream)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        status = all_status()
+        launches = plan.launch_count - l0
+        ms = t0.elapsed_time(t1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+        ms_step = ms / steps
     clocks = sampler.stop()
     checksum = float(canvas[rows["logits"] * pitch: rows["logits"] * pitch + 4096].float().abs().sum().item())
     # per-wave breakdown with one launch per wave (outside the timed region; with peers it includes waiting for them)
     wave_us = None
-    if world == 1 or mode == "peer":
+    if breakdown and status == 0 and (world == 1 or mode == "peer"):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(nw + 1)]
         for _ in range(2):
             if world > 1:
@@ -537,29 +656,45 @@ def sharded_main(args) -> None:
             torch.cuda.synchronize()
         us = [ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(nw)]
         wave_us = {"layer0": [round(v, 1) for v in us[:7]], "lm_head": round(us[-1], 1), "sum": round(sum(us), 1)}
+        status = all_status()
     gather_bytes = sum(total * 2 * (world - 1) // world for (_, total, blk) in waves if blk != total)
-    if rank == 0:
-        peak, kind = measured_peaks()
-        bytes_rank = kept_params * 2.0 / world
-        line = {"metric": "decode tok/s (cluster-pruned 8B wave chain, neuron-sharded, batch 256)", "value": C / (ms_step * 1e-3), "unit": "tok/s",
-                "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
-                "config": {"workload": "Llama-3-8B shaped wave chain, 90 % of 32-row input clusters removed per 128-neuron group, dense lm_head, "
-                                       "batch 256; rows of every wave split over the ranks, canvas replicated",
-                           "layers": cfg["layers"], "waves_per_step": nw, "kept_params": kept_params, "lm_head_rows": V,
-                           "exchange": ("none (one GPU)" if world == 1 else {"peer": "direct stores into the peers' canvases from the wave kernels, counter-word launch ordering, one CUDA graph per step",
-                                                                        "nccl": "in-place NCCL all-gather after every wave", "nccl-graph": "in-place NCCL all-gather after every wave, captured in one CUDA graph"}[mode]),
-                           "allgather_bytes_received_per_rank_per_step": gather_bytes},
-                "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9, "peak": peak,
-                             "peak_kind": f"of {kind}", "unit": "GB/s", "frac": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9 / peak, "traffic": None},
-                "per_wave_us_direct_launch": wave_us,
-                "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "checksum": checksum, "clocks": clocks}
-        print(json.dumps(line), flush=True)
+    peak, kind = measured_peaks()
+    line = {"metric": "decode tok/s (cluster-pruned 8B wave chain, neuron-sharded, batch 256)", "value": C / (ms_step * 1e-3), "unit": "tok/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "Llama-3-8B shaped wave chain, 90 % of 32-row input clusters removed per 128-neuron group, dense lm_head, "
+                                   "batch 256; rows of every wave split over the ranks, canvas replicated",
+                       "layers": cfg["layers"], "waves_per_step": nw, "kept_params": kept_params, "lm_head_rows": V,
+                       "exchange": ("none (one GPU)" if world == 1 else {"peer": "direct stores into the peers' canvases from the wave kernels, counter-word launch ordering, one CUDA graph per step",
+                                                                    "nccl": "in-place NCCL all-gather after every wave", "nccl-graph": "in-place NCCL all-gather after every wave, captured in one CUDA graph"}[mode]),
+                       "exchange_mode": "none" if world == 1 else mode,
+                       "bytes_received_per_rank_per_step": gather_bytes,
+                       "nvlink_time_bound_ms": gather_bytes / 770e9 * 1e3},
+            "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9, "peak": peak,
+                         "peak_kind": f"of {kind}", "unit": "GB/s", "frac": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9 / peak, "traffic": None},
+            "per_wave_us_direct_launch": wave_us,
+            "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "checksum": checksum, "clocks": clocks}
+    if status != 0:
+        line["error"] = f"kernel status {status:#x} on at least one rank"
     if world > 1:
         dist.barrier()                  # no rank frees its canvas while a peer may still store into it
         graph = None
         torch.cuda.synchronize()
-        plan.close()
+    plan.close()
+    return line
+
+
+def sharded_main(args) -> None:
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0")); local_rank = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    line = sharded_measure(args.layers if args.layers != 16 else PRUNED["layers"], args.steps, args.warmup, rank, local_rank, world)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
         dist.destroy_process_group()
 
 
@@ -742,6 +877,7 @@ def main() -> None:
     ap.add_argument("--max-shift", type=int, default=7, help="token-shift workload: largest token shift drawn per run (0 = unshifted runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true", help="with several GPUs: skip the neuron-sharded sub-measurement")
     args = ap.parse_args()
     if args.workload in ("decode", "decode-full"):
         return decode_main(args)
@@ -758,8 +894,8 @@ def main() -> None:
     w["columns"] = max(1, min(64, args.columns))
     w["group"] = args.group
     warmup = max(3, args.warmup)
-    cfg = {"workload": "ultra-sparse plan: 40M-row FP16 substrate, 4 waves x 1M neurons, fan-in 4096 as 64 runs of 64 rows, "
-                       f"groups of {args.group}, ReLU, 64 columns per GPU",
+    cfg = {"workload": f"ultra-sparse plan: {w['input_rows'] / 1e6:g}M-row FP16 substrate, {w['waves']} waves x {w['cout']} neurons, fan-in "
+                       f"{w['runs'] * w['run_len']} as {w['runs']} runs of {w['run_len']} rows, groups of {w['group']}, ReLU, {w['columns']} columns per GPU",
            "input_rows": w["input_rows"], "neurons_per_wave": w["cout"], "waves": w["waves"], "fan_in": w["runs"] * w["run_len"],
            "run_len": w["run_len"], "group": w["group"], "columns_per_gpu": w["columns"], "global_columns": w["columns"] * world,
            "parallelism": f"column replicas x{world} (plan replicated, no collective)",
@@ -771,8 +907,7 @@ def main() -> None:
         if rank != 0:
             return
         steps = max(1, min(args.steps, 3))
-        vals = [cpu_baseline(w, seconds_target=20.0) for _ in range(1)]
-        cb = vals[0]
+        cb = cpu_baseline(w, seconds_target=20.0, threads=host_threads())     # all host threads, whatever OMP_NUM_THREADS says
         line = {"impl": "reference", "metric": "effective synaptic TFLOP/s (2*synapses*columns/s)", "value": cb["value"], "unit": "TFLOP/s",
                 "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": cb["seconds_per_rep"] * 1e3, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16 operands, f64 accumulate (CPU)", "data": "synthetic", "config": cfg,
@@ -842,20 +977,35 @@ def main() -> None:
                 "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
                 "algorithmic_bytes_per_launch": bytes_wave, "avg_launch_ms": avg_wave_ms,
                 "per_wave_ms": [float(np.mean([wave_ms[s][i] for s in range(args.steps)])) for i in range(nw)],
-                # dram__bytes_read + dram__bytes_write of this kernel from the committed ncu capture at 1/20 size
-                # (profiles/k44_wave_umma64_ultra_sparse_scale005_ncu_full.md: 0.928 x algorithmic bytes), scaled by units processed
-                "traffic": NCU_TRAFFIC_RATIO * bytes_wave if w["columns"] == 64 else None,
-                "traffic_source": "ncu capture at scale 0.05, scaled by neurons x fan-in" if w["columns"] == 64 else None}
+                # dram__bytes_read + dram__bytes_write per launch of this kernel: not measured in this run. The figure is the
+                # ratio (DRAM bytes / algorithmic bytes = 0.928) of an ncu capture of the same kernel on the same plan at 1/20
+                # size, times this run's algorithmic bytes; at 1/20 size part of the 256 MB substrate stays in L2, so at full
+                # size the true figure is nearer the algorithmic bytes.
+                "traffic": NCU_TRAFFIC_RATIO * bytes_wave if (w["columns"] == 64 and w["group"] == 128) else None,
+                "traffic_kind": "scaled: ncu capture at 1/20 size (ratio 0.928 of algorithmic bytes) x this run's algorithmic bytes"
+                                if (w["columns"] == 64 and w["group"] == 128) else None}
 
     # ---- end to end through the C ABI with host buffers (pinned FP16 in canvas layout) ----
     e2e = None
     if not args.no_e2e:
         out_rows = w["cout"]
-        h_in = torch.empty(in_elems, dtype=torch.float16).pin_memory()
+        h_in, numa_cpus = pinned_near_gpu(in_elems, local_rank)
         h_in.copy_(canvas[:in_elems])
-        h_out = torch.empty(out_rows * 64, dtype=torch.float16).pin_memory()
+        h_out, _ = pinned_near_gpu(out_rows * 64, local_rank)
         e_steps = max(2, min(args.steps, 5))
         plan.infer_f16(h_in.data_ptr(), h_out.data_ptr(), stream)      # warm-up
+        # the bound the host side sets: the same upload alone, all ranks at once (host memory and PCIe are shared by the ranks)
+        barrier()
+        c0 = torch.cuda.Event(enable_timing=True); c1 = torch.cuda.Event(enable_timing=True)
+        c0.record(stream)
+        canvas[:in_elems].copy_(h_in, non_blocking=True)
+        c1.record(stream)
+        barrier()
+        copy_ms = c0.elapsed_time(c1)
+        if dist is not None:
+            t = torch.tensor([copy_ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            copy_ms = float(t.item())
         barrier()
         t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
         t0.record(stream)
@@ -871,6 +1021,9 @@ def main() -> None:
         e2e = {"value": flops_step * world / (e_ms / e_steps * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e_ms / e_steps,
                "steps": e_steps, "h2d_bytes_per_step": in_elems * 2, "d2h_bytes_per_step": out_rows * 64 * 2,
                "api": "k44b_infer_f16 (host FP16 rows in, last wave's rows out, pinned memory)",
+               "host_copy_bound": {"upload_ms_alone_max_over_ranks": copy_ms, "upload_gbs_per_rank": in_elems * 2 / (copy_ms * 1e-3) / 1e9,
+                                   "bound_ms_per_step": copy_ms + ms_per_step, "frac_of_bound": (copy_ms + ms_per_step) / (e_ms / e_steps),
+                                   "pinned_on_gpu_numa_node": numa_cpus is not None},
                "checksum": float(h_out[: 64 * 1024].float().abs().sum().item())}
         del h_in, h_out
 
@@ -878,12 +1031,38 @@ def main() -> None:
     cb = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cb = cpu_baseline(w)
+    plan.close()
+    del canvas
+    torch.cuda.empty_cache()
+    # the reference's own execution call (wavec_gpu_infer_f32: dense host FP32 in and out) on a workload whose tensors fit its
+    # `int` element counts; one GPU only
+    ref_call = None
+    if rank == 0 and world == 1 and not args.no_e2e and args.scale == 1.0:
+        try:
+            ref_call = reference_call_e2e(local_rank, steps=max(3, min(args.steps, 10)))
+        except Exception as exc:      # reported, never fatal for the main line
+            ref_call = {"error": f"{type(exc).__name__}: {exc}"}
+    # neuron sharding (rows of every wave split over the ranks, rows exchanged by the wave kernels): strong scaling of one
+    # batch, reported beside the column-replica result whenever there is more than one GPU
+    sharded = None
+    if world > 1 and not args.no_sharded:
+        try:
+            sh = sharded_measure(PRUNED["layers"], steps=10, warmup=3, rank=rank, local_rank=local_rank, world=world, breakdown=False)
+            sharded = {k: sh[k] for k in ("metric", "value", "unit", "ms_per_step", "scaling", "steps", "gpu_launches", "checksum") if k in sh}
+            sharded.update({"exchange_mode": sh["config"]["exchange_mode"], "exchange": sh["config"]["exchange"],
+                            "bytes_received_per_rank_per_step": sh["config"]["bytes_received_per_rank_per_step"],
+                            "nvlink_time_bound_ms": sh["config"]["nvlink_time_bound_ms"], "workload": sh["config"]["workload"],
+                            "waves_per_step": sh["config"]["waves_per_step"]})
+            if "error" in sh:
+                sharded["error"] = sh["error"]
+        except Exception as exc:
+            sharded = {"error": f"{type(exc).__name__}: {exc}"}
     if rank == 0:
         line = {"metric": "effective synaptic TFLOP/s (2*synapses*columns/s)", "value": value, "unit": "TFLOP/s", "n_gpus": world,
                 "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic", "config": cfg,
                 "hbm_gbs_algorithmic": bytes_wave * nw * world / (ms_per_step * 1e-3) / 1e9, "roofline": roofline, "cpu_baseline": cb,
-                "e2e": e2e, "gpu_launches": int(launches), "kernel_paths": paths, "clocks": clocks}
+                "e2e": e2e, "e2e_reference_call": ref_call, "sharded": sharded, "gpu_launches": int(launches), "kernel_paths": paths, "clocks": clocks}
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

@@ -24,7 +24,7 @@ typedef struct k44b_wave_desc {
     uint32_t group;           /* neurons sharing one gather list (K44ExecCmd::cluster_size) */
     uint32_t fan_in;          /* padded synapses per neuron, multiple of 8 (K44ExecCmd::B) */
     uint32_t fan_in_raw;      /* slots >= fan_in_raw must carry zero weights (K44ExecCmd::B_raw) */
-    int32_t act;              /* 0 none, 1 relu, 2 sigmoid, 3 silu, 4 leaky-relu(0.1), 5 gelu(erf) */
+    int32_t act;              /* 0 none, 1 relu, 2 sigmoid, 3 silu, 4 leaky-relu(0.1), 5 gelu (erf form; the tensor-core kernels use a fit within 2.6e-5 of it) */
     uint32_t has_residual;
     uint64_t y_off;           /* canvas element offset of output row 0 */
     uint64_t src_off;         /* informational */
@@ -88,8 +88,6 @@ int k44b_infer_f16(void *plan, const uint16_t *h_in, uint16_t *h_out, float *out
 int k44b_status(void *plan, uint32_t *status);
 /* Same contract as wavec_gpu_infer_f32 for a native plan. */
 int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, int out_elems, float *out_gpu_ms);
-/* Development aid: 16 SM-clock timestamps recorded by CTA 0 of the last tcgen05 wave kernel when the
- * library runs with K44B_DEBUG_MODE=16 (all zero otherwise). */
 /* ---- element-wise / attention commands between waves (the reference's RMSNORM, SWIGLU and ROPE_GQA_ATTN command
  * types, wavec/k44_plan_types.hpp:603-650, kernels/common/kernel44_valu_pack.cuh:104-248). Offsets are FP16 element
  * offsets of channel-major tensors in the canvas (multiples of 8); commands run in the order they were added, interleaved
@@ -135,9 +133,6 @@ int k44b_plan_set_peers_ipc(void *plan, int rank, int world, const void *canvas_
 int k44b_plan_set_peers_raw(void *plan, int rank, int world, void *const *canvas_ptrs, void *const *sync_ptrs);
 void *k44b_plan_sync_ptr(void *plan);
 
-int k44b_debug_trace(void *plan, long long *out16);
-/* the first `count` (<= 500) 64-bit words of the development trace area */
-int k44b_debug_trace_words(void *plan, long long *out, int count);
 /* Number of kernels this plan has launched so far. */
 uint64_t k44b_launch_count(void *plan);
 /* Unpack wave `wave`'s device weights to row-major [cout][fan_in] FP16 at device pointer d_dst. */
@@ -161,10 +156,11 @@ int k44b_wave_weights_rowmajor(void *plan, int wave, void *d_dst);
  *   k_splits         1..ceil(fan_in/64): how many CTAs share one output tile's fan-in
  *
  * Limits: (cout/128 rounded up) * (pitch/64) <= K44B_STATIC_MAX_TILES, otherwise the call fails with a message
- * naming the limit; no residual and no row map. The first call on a device resolves the array's address and
- * sets kernel attributes: make that call outside any stream capture. Every call uses the same array and
- * clears the part it needs first, so two calls that overlap on one GPU (different streams or threads) race.
- * The call queues its work on `stream` and returns after the wave has finished and its status was checked.
+ * naming the limit; no residual and no row map; the rows the wave gathers must not overlap the rows it writes.
+ * The first call on a device resolves the array's address and sets kernel attributes. Every call queues its work
+ * on `stream`, then waits for the stream and reads the kernel's status word back, so no call may be made while
+ * `stream` is being captured (such a call is refused with a message). Every call uses the same array and clears
+ * the part it needs first, so two calls that overlap on one GPU (different streams or threads) race.
  * Returns 0, or -1 with a message copied to `err` (if given). Calls no cudaMalloc / cudaFree. */
 #define K44B_STATIC_MAX_TILES 64
 int k44b_wave_forward_static(void *d_canvas, uint64_t canvas_elems, uint32_t pitch, const void *d_weights_tiled,

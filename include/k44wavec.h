@@ -5,9 +5,12 @@
  * loads this library unchanged. Differences, all on the safe side:
  *   - a GPU runtime error never terminates the process (the reference calls exit(), :54-62): the
  *     call returns -1 and k44b_last_error() (k44b.h) holds the reason;
- *   - only 1-D token graphs made of Input / linear / split / slice / concat nodes compile; every other
- *     builder call returns -1 and leaves the graph unchanged;
- *   - activation value 5 selects exact (erf) GELU in addition to the reference's 0-4.
+ *   - 1-D token graphs compile: Input / linear (1x1 convolution) / split / slice / concat / RMSNorm / SwiGLU /
+ *     rotary + grouped-query attention; the 2-D image builder calls (flatten, convolutions with a kernel larger
+ *     than 1x1, upconv2x2, maxpool, upsample2x) return -1 and leave the graph unchanged;
+ *   - activation value 5 selects GELU in addition to the reference's 0-4. The tensor-core kernels evaluate it
+ *     as v / (1 + exp(-v P(v^2))) with a fitted quadratic P, at most 2.6e-5 (absolute) away from the erf form;
+ *     the FP32-FMA and mma.sync kernels call erff. Both lie inside the output tolerance (rtol 2e-3, atol 1e-3).
  * Not thread-safe per handle, like the reference.
  */
 #ifndef K44WAVEC_H
@@ -46,11 +49,13 @@ int wavec_add_linear_f16(void *handle, const char *name, const char *in_tensor, 
 /* :747 — bf16 -> f32 -> f16 */
 int wavec_add_linear_bf16(void *handle, const char *name, const char *in_tensor, const char *out_tensor, int din, int dout,
                           int act, const uint16_t *w_bf16, const float *bias_f32, const char *residual_tensor);
-/* :761, :773, :783, :793, :803, :813 — not on the wave path: return -1 */
+/* :761, :773, :783 — 2-D image path: return -1 */
 int wavec_add_upconv2x2(void *handle, const char *name, const char *in_tensor, const char *out_tensor, int cin, int cout,
                         const float *w_f32, const float *bias_f32);
 int wavec_add_maxpool(void *handle, const char *name, const char *in_tensor, const char *out_tensor, int k, int stride, int pad);
 int wavec_add_upsample2x(void *handle, const char *name, const char *in_tensor, const char *out_tensor);
+/* :793, :803, :813 — element-wise / attention commands between the waves (kernels/common/kernel44_valu_pack.cuh:104-248);
+ * an RMSNorm scale is folded into the linears that consume it when fold_rmsnorm_gamma was set at wavec_create */
 int wavec_add_rmsnorm(void *handle, const char *name, const char *in_tensor, const char *out_tensor, int dim, float eps,
                       const float *gamma_f32, int pre_folded);
 int wavec_add_swiglu(void *handle, const char *name, const char *gate_tensor, const char *up_tensor, const char *out_tensor);

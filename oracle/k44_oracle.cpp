@@ -53,6 +53,22 @@ inline uint16_t f32_to_f16_rte(float f) {
     return (uint16_t)(sign | ((rounded - 0x38000000u) >> 13));
 }
 
+// Double -> half with ONE rounding (round to nearest, ties to even): the value is first rounded onto the half grid
+// in double arithmetic (spacing 2^(e-10) for a normal result, 2^-24 below 2^-14; division and product by a power of
+// two are exact, nearbyint uses the default rounding mode), then the exactly representable result is encoded.
+// Rounding through float first would round twice (a value a hair above a half-way point of the half grid can
+// land exactly on it as a float).
+inline uint16_t f64_to_f16_rte(double v) {
+    if (std::isnan(v)) return 0x7e00u;
+    const double a = std::fabs(v);
+    if (a >= 65520.0) return (uint16_t)((std::signbit(v) ? 0x8000u : 0u) | 0x7c00u);
+    int e = 0;
+    (void)std::frexp(a, &e);                          // a = m * 2^e, 0.5 <= m < 1  ->  a in [2^(e-1), 2^e)
+    const int spacing_exp = (a < 6.103515625e-05) ? -24 : (e - 1) - 10;
+    const double r = std::ldexp(std::nearbyint(std::ldexp(a, -spacing_exp)), spacing_exp);
+    return f32_to_f16_rte((float)(std::signbit(v) ? -r : r));   // exact: r is on the half grid
+}
+
 inline float f16_to_f32(uint16_t h) {
     const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
     const uint32_t em = h & 0x7fffu;
@@ -99,6 +115,10 @@ uint64_t k44o_fnv1a64(const uint8_t *data, uint64_t len) {
 
 void k44o_f32_to_f16(const float *src, uint16_t *dst, uint64_t n) {
     for (uint64_t i = 0; i < n; ++i) dst[i] = f32_to_f16_rte(src[i]);
+}
+
+void k44o_f64_to_f16(const double *src, uint16_t *dst, uint64_t n) {
+    for (uint64_t i = 0; i < n; ++i) dst[i] = f64_to_f16_rte(src[i]);
 }
 
 void k44o_f16_to_f32(const uint16_t *src, float *dst, uint64_t n) {
@@ -216,7 +236,7 @@ int k44o_wave_forward(uint16_t *canvas, uint64_t canvas_elems, const uint16_t *w
                     if (rr && cout_map) v += r;
                     v = activate(v, act);
                     if (rr && !cout_map) v += r;
-                    o[c] = f32_to_f16_rte((float)v);
+                    o[c] = f64_to_f16_rte(v);
                 }
             }
         }

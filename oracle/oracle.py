@@ -68,6 +68,7 @@ def lib() -> ctypes.CDLL:
         L.k44o_fnv1a64.restype = ctypes.c_uint64
         L.k44o_f32_to_f16.argtypes = [f32p, u16p, ctypes.c_uint64]
         L.k44o_f16_to_f32.argtypes = [u16p, f32p, ctypes.c_uint64]
+        L.k44o_f64_to_f16.argtypes = [ctypes.POINTER(ctypes.c_double), u16p, ctypes.c_uint64]
         L.k44o_rowmajor_to_wmma.argtypes = [u16p, u16p, ctypes.c_uint32, ctypes.c_uint32]
         L.k44o_wmma_to_rowmajor.argtypes = [u16p, u16p, ctypes.c_uint32, ctypes.c_uint32]
         L.k44o_wave_forward.argtypes = [
@@ -108,6 +109,14 @@ def f32_to_f16(a: np.ndarray) -> np.ndarray:
     a = np.ascontiguousarray(a, dtype=np.float32)
     out = np.empty(a.shape, dtype=np.uint16)
     lib().k44o_f32_to_f16(_p(a, f32p), _p(out, u16p), a.size)
+    return out
+
+
+def f64_to_f16(a: np.ndarray) -> np.ndarray:
+    """Double -> FP16 bits with a single rounding (what the wave oracle stores)."""
+    a = np.ascontiguousarray(a, dtype=np.float64)
+    out = np.empty(a.shape, dtype=np.uint16)
+    lib().k44o_f64_to_f16(_p(a, ctypes.POINTER(ctypes.c_double)), _p(out, u16p), a.size)
     return out
 
 
@@ -213,7 +222,7 @@ def wave_forward_numpy(canvas: np.ndarray, wave, plan) -> None:
             acc = _act_numpy(acc + r, wave.act) if wave.cout_map is not None else _act_numpy(acc, wave.act) + r
         else:
             acc = _act_numpy(acc, wave.act)
-        out_rows.append((oj, acc.astype(np.float32).astype(np.float16)))
+        out_rows.append((oj, acc.astype(np.float16)))       # one rounding, from double
     for oj, row in out_rows:
         cv[wave.y_off + oj * plan.pitch: wave.y_off + (oj + 1) * plan.pitch] = row
 

@@ -27,7 +27,7 @@ def _rows(canvas: np.ndarray, off: int, rows: int, pitch: int) -> np.ndarray:
 
 def _store(canvas: np.ndarray, off: int, val: np.ndarray, pitch: int) -> None:
     rows = val.shape[0]
-    canvas[off: off + rows * pitch] = val.astype(np.float32).astype(np.float16).reshape(-1).view(np.uint16)
+    canvas[off: off + rows * pitch] = val.astype(np.float16).reshape(-1).view(np.uint16)
 
 
 def rmsnorm(canvas, src_off, dst_off, dim, pitch, eps, gamma_bits=None):

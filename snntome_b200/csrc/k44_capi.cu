@@ -439,11 +439,6 @@ int k44b_infer_f32(void *plan, const float *h_in, int in_elems, float *h_out, in
     return P(plan)->exec.infer_f32(h_in, in_elems, h_out, out_elems, out_gpu_ms) ? 0 : set_error(P(plan)->exec.err);
 }
 
-int k44b_debug_trace(void *plan, long long *out16) {
-    if (!plan || !out16) return set_error("debug_trace: bad arguments");
-    return P(plan)->exec.read_trace(out16, 16) ? 0 : set_error(P(plan)->exec.err);
-}
-
 int k44b_plan_ipc_handles(void *plan, void *canvas_handle64, void *sync_handle64) {
     if (!plan || !canvas_handle64 || !sync_handle64) return set_error("plan_ipc_handles: bad arguments");
     return P(plan)->exec.ipc_handles(canvas_handle64, sync_handle64) ? 0 : set_error(P(plan)->exec.err);
@@ -464,11 +459,6 @@ void *k44b_plan_sync_ptr(void *plan) {
     void *p = P(plan)->exec.sync_ptr();
     if (!p) set_error(P(plan)->exec.err);
     return p;
-}
-
-int k44b_debug_trace_words(void *plan, long long *out, int count) {
-    if (!plan || !out) return set_error("debug_trace_words: bad arguments");
-    return P(plan)->exec.read_trace(out, count) ? 0 : set_error(P(plan)->exec.err);
 }
 
 uint64_t k44b_launch_count(void *plan) { return plan ? P(plan)->exec.launches() : 0; }

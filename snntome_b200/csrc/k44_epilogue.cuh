@@ -33,7 +33,7 @@ __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 
 // ---- peer exchange of neuron-sharded plans (see PeerArgs) ------------------------------------------------------
 // 16-byte piece of an output row -> the same element offset of every peer canvas
 __device__ __forceinline__ void store_to_peers(const PeerArgs *p, uint64_t elem_off, const uint4 &val) {
-    const uint32_t n = (p->dev_flags & 1u) ? 0u : p->n_peers;
+    const uint32_t n = p->n_peers;
     for (uint32_t q = 0; q < n; ++q) *reinterpret_cast<uint4 *>(p->canvas[q] + elem_off) = val;
 }
 // One thread per CTA, after the CTA's last store and a CTA barrier that all storing threads passed: one system-scope

@@ -506,7 +506,6 @@ bool Executor::add_wave(const HostWave &w) {
             }
             a.k_splits = 1; a.kstages_per_split = a.num_kstages;
             dw.desc = make_umma_desc(n_tile, 0);
-            if (const char *e = std::getenv("K44B_DEBUG_MODE")) dw.desc.debug = (uint32_t)std::atoi(e);
             ok = make_tensor_map(dw, std::min(n_tile, 128u) + 8u, false);   // aligned windows of up to 128 columns plus the 8 to their left, as plain rows
         } else if (dw.path == PATH_UMMA) {
             uint32_t n_tile = 64;
@@ -546,7 +545,6 @@ bool Executor::add_wave(const HostWave &w) {
             dw.use_cluster = cluster;
             dw.desc = make_umma_desc(n_tile, variant);
             dw.desc.small_wave = small ? 1u : 0u;
-            if (const char *e = std::getenv("K44B_DEBUG_MODE")) dw.desc.debug = (uint32_t)std::atoi(e);
             if (a.k_splits > 1 && !cluster) ok = reserve_scratch((size_t)mtiles * tiles64);
             ok = ok && make_tensor_map(dw, 64u, true);
         }
@@ -566,6 +564,28 @@ bool Executor::add_wave(const HostWave &w) {
     }
     if (w.has_residual) { lo = std::min(lo, w.res_off); hi = std::max(hi, w.res_off + (uint64_t)w.cout * pitch_); }
     dw.read_lo = lo; dw.read_hi = hi;
+    // A wave must not gather rows it writes: CTAs of one launch would race, and in a neuron-sharded plan a peer's stores
+    // of launch n would land in rows this rank's launch n still reads (residual rows may equal the output rows: each
+    // element is read and written by the same thread).
+    {
+        uint64_t wlo = dw.write_lo, whi = dw.write_hi;
+        if (!w.cout_map.empty()) { uint32_t mx = 0; for (uint16_t m : w.cout_map) mx = std::max<uint32_t>(mx, m); whi = w.y_off + ((uint64_t)mx + 1) * pitch_; dw.write_hi = std::max(dw.write_hi, whi); }
+        bool clash = false;
+        // (checked on the caller's tables: zero-weight padding slots, which the packer points wherever it likes, do not count)
+        if (!w.run_rows.empty()) {
+            for (uint32_t r : w.run_rows) { const uint64_t r0 = (uint64_t)r * pitch_; if (r0 < whi && wlo < r0 + (uint64_t)w.run_len * pitch_) { clash = true; break; } }
+        } else {
+            for (uint32_t g = 0; g < groups && !clash; ++g)
+                for (uint32_t sidx = 0; sidx < w.fan_in_raw; ++sidx) {
+                    const uint64_t e0 = w.x_base_off + w.idx[(size_t)g * w.fan_in + sidx];
+                    if ((e0 >= 8 ? e0 - 8 : 0) < whi && wlo < e0 + pitch_) { clash = true; break; }
+                }
+        }
+        if (clash) {
+            cudaFree(dw.d_weights); cudaFree(dw.d_gather); cudaFree(dw.d_bias); cudaFree(dw.d_map); cudaFree(dw.d_shifts);
+            return fail("wave '" + w.name + "' gathers rows that it writes (a wave cannot run in place)");
+        }
+    }
     dw.groupable = dw.path == PATH_UMMA && dw.use_cluster && w.cout_map.empty();
     waves_.push_back(dw);
     drop_graph();
@@ -758,8 +778,19 @@ bool Executor::infer_f16(const uint16_t *h_in, uint16_t *h_out, float *gpu_ms, c
     if (gpu_ms) *gpu_ms = t;
     uint32_t st = 0;
     if (!check(cudaMemcpy(&st, d_status_, 4, cudaMemcpyDeviceToHost), "status read")) return false;
-    if (st) { cudaMemset(d_status_, 0, 4); return fail(std::string("kernel status: ") + status_string(st)); }
+    if (st) { recover_after_abort(); return fail(std::string("kernel status: ") + status_string(st)); }
     return true;
+}
+
+// After a kernel gave up (any status bit), CTAs that returned early never reached the split-K arrival counters, and
+// the CTAs of a sharded launch may not all have been counted: partial sums, counters and the per-launch CTA count are
+// put back to their between-launches state so that the next execution starts clean.
+void Executor::recover_after_abort() {
+    cudaMemset(d_status_, 0, 4);
+    if (d_scratch_) cudaMemset(d_scratch_, 0, scratch_tiles_ * 64u * kTileM * sizeof(float));
+    if (d_counters_) cudaMemset(d_counters_, 0, scratch_tiles_ * sizeof(uint32_t));
+    if (d_sync_) cudaMemset(d_sync_ + kSyncDone, 0, sizeof(uint32_t));
+    cudaDeviceSynchronize();
 }
 
 bool Executor::read_status(uint32_t *status) {
@@ -769,7 +800,7 @@ bool Executor::read_status(uint32_t *status) {
         !check(cudaMemcpy(&st, d_status_, 4, cudaMemcpyDeviceToHost), "status read"))
         return false;
     if (status) *status = st;
-    if (st) { cudaMemset(d_status_, 0, 4); err = std::string("kernel status: ") + status_string(st); }
+    if (st) { recover_after_abort(); err = std::string("kernel status: ") + status_string(st); }
     return true;
 }
 
@@ -821,7 +852,6 @@ bool Executor::set_peers_raw(int rank, int world, void *const *canvas_ptrs, void
     if (!sync_ptr()) return false;
     PeerArgs pa;
     pa.sync = d_sync_;
-    if (const char *e = std::getenv("K44B_PEER_DEV")) pa.dev_flags = (uint32_t)std::atoi(e);
     for (int r = 0; r < world; ++r) {
         if (r == rank) continue;
         if (!canvas_ptrs[r] || !sync_ptrs[r]) return fail("set_peers: missing pointer for rank " + std::to_string(r));
@@ -836,13 +866,6 @@ bool Executor::set_peers_raw(int rank, int world, void *const *canvas_ptrs, void
     groups_valid_ = false;
     drop_graph();
     return true;
-}
-
-bool Executor::read_trace(long long *out, int count) {
-    if (!ready()) return fail("executor not initialised");
-    if (count < 0 || (size_t)count * sizeof(long long) + 8 > kStatusBytes) return fail("trace read: count out of range");
-    return check(cudaDeviceSynchronize(), "synchronise") &&
-           check(cudaMemcpy(out, reinterpret_cast<char *>(d_status_) + 8, (size_t)count * sizeof(long long), cudaMemcpyDeviceToHost), "trace read");
 }
 
 bool Executor::execute_timed(float *ms) {

@@ -52,7 +52,7 @@ struct DeviceWave {
 
 class Executor {
   public:
-    static constexpr size_t kStatusBytes = 4096;   // status word + development trace area
+    static constexpr size_t kStatusBytes = 256;    // status word (padded)
     ~Executor() { release(); }
     std::string err;
 
@@ -80,7 +80,6 @@ class Executor {
     bool set_peers_ipc(int rank, int world, const void *canvas_handles, const void *sync_handles);   // world x 64 bytes each, indexed by rank
     bool set_peers_raw(int rank, int world, void *const *canvas_ptrs, void *const *sync_ptrs);       // device pointers valid on this GPU, indexed by rank
     void *sync_ptr();
-    bool read_trace(long long *out, int count);                             // development aid: kernel milestone clocks
     bool weights_to_rowmajor(size_t wave, void *d_dst);            // unpack check: tiled -> [cout][fan_in]
 
     bool ready() const { return canvas_ != nullptr; }
@@ -97,6 +96,7 @@ class Executor {
     bool check(cudaError_t e, const char *what);
     bool make_tensor_map(DeviceWave &dw, uint32_t box_cols, bool swizzle128);
     bool reserve_scratch(size_t tiles);
+    void recover_after_abort();
     bool launch_one(DeviceWave &w, cudaStream_t stream);
     void drop_graph();
     void build_groups();

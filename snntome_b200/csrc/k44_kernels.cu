@@ -161,10 +161,6 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
     uint8_t *out_stage = ctl_ptr + 256;              // 128 rows x 80 bytes, one 32-row block per epilogue warp
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    // development aid (debug bit 16): CTA 0 records SM-clock timestamps of its milestones after the status word
-    const bool trace = (d.debug & 16u) && blockIdx.x == 0;
-    auto stamp = [&](int slot) { if (trace) reinterpret_cast<volatile long long *>(a.status + 2)[slot] = clock64(); };
-    if (threadIdx.x == 0) stamp(0);
     const uint32_t tiles_n = a.num_col_tiles64 / Cfg::kColBlocks;
     const uint32_t mtiles = (a.cout + kTileM - 1) / kTileM;
     const uint32_t splits = a.k_splits;
@@ -184,7 +180,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         *abort_word = 0;
         ptx::fence_mbar_init();
     }
-    if (warp == 1 && !(d.debug & 2u)) {
+    if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_addr(const_cast<uint32_t *>(tmem_slot)), Cfg::kTmemCols);
         ptx::tmem_relinquish();
     }
@@ -192,12 +188,6 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) stamp(1);
-    if (d.debug & 1u) {
-        __syncthreads();
-        if (warp == 1 && !(d.debug & 2u)) ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
-        return;
-    }
 
     auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
         const long long t0 = clock64();
@@ -245,7 +235,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                 if (lane == 0) {
                     ok = wait(empty_bar + 8u * stage, ph ^ 1u);
                     if (ok) {   // weights first: they do not need the run table
-                        ptx::mbar_arrive_expect_tx(full_bar + 8u * stage, (d.debug & 4u) ? kStageWBytes : Cfg::kStageBytes);
+                        ptx::mbar_arrive_expect_tx(full_bar + 8u * stage, Cfg::kStageBytes);
                         ptx::bulk_g2s(w_smem + stage * kStageWBytes, wsrc + (uint64_t)ks * (kStageWBytes / 16u), kStageWBytes,
                                       full_bar + 8u * stage, pol_w);
                     }
@@ -265,15 +255,13 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                     }
                     const uint32_t b = lane / (uint32_t)Cfg::kColBlocks, cb = lane % (uint32_t)Cfg::kColBlocks;
                     const uint32_t row = __shfl_sync(0xffffffffu, cached, (bi0 + b) & 31u) & kBoxRowMask;
-                    if (lane < per_stage && !(d.debug & 4u))
+                    if (lane < per_stage)
                         ptx::tma_load_2d(x_smem + stage * Cfg::kXBytes + cb * (kStageK * 128u) + b * a.box_h * 128u, &tmap,
                                          (int32_t)(ct * N_TILE + cb * 64u), (int32_t)row, full_bar + 8u * stage, pol_x);
                 }
-                if (issued == 0 && lane == 0) stamp(2);
                 ++issued;
             }
         }
-        if (lane == 0) stamp(9);
         if (!ok && lane == 0) {
             if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PRODUCER);
             *abort_word = 1u;
@@ -304,7 +292,6 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                     const uint32_t stage = consumed % STAGES, ph = (consumed / STAGES) & 1u;
                     ok = wait(full_bar + 8u * stage, ph);
                     if (!ok) break;
-                    if (consumed == 0) stamp(3);
                     ptx::tc_fence_after();
                     const uint64_t a0 = d.a_base | (uint64_t)(((w_smem + stage * kStageWBytes) >> 4) & 0x3fffu);
                     const uint64_t b0 = d.b_base | (uint64_t)(((x_smem + stage * Cfg::kXBytes) >> 4) & 0x3fffu);
@@ -316,7 +303,6 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                     ++consumed;
                 }
                 if (ok) ptx::umma_commit(tfull_bar + 8u * acc);     // accumulator complete
-                if (iter == 0) stamp(4);
             }
             if (!ok) {
                 if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_MMA);
@@ -339,7 +325,6 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
             epilogue_bar_sync();
             ok = epi_ok[iter & 1u] != 0u;
             if (!ok) break;
-            if (iter == 0 && threadIdx.x == 64u) stamp(5);
             ptx::tc_fence_after();
             const uint32_t r_in_tile = quarter * 32u + lane;
             const uint32_t j = mt * kTileM + r_in_tile;
@@ -356,12 +341,8 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                     float f[32];
 #pragma unroll
                     for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
-                    if (!(d.debug & 8u)) stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
+                    stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * N_TILE + c0, out_stage + quarter * (32u * 80u), lane);
                 }
-                ptx::tc_fence_before();
-                ptx::mbar_arrive(tempty_bar + 8u * acc);
-                if (iter == 0 && threadIdx.x == 64u) stamp(6);
-            } else if (d.debug & 8u) {
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(tempty_bar + 8u * acc);
             } else {
@@ -376,9 +357,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                 }
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(tempty_bar + 8u * acc);      // accumulator free: the next item's MMAs may start
-                if (iter == 0 && threadIdx.x == 64u) stamp(6);
                 __threadfence();
-                if (iter == 0 && threadIdx.x == 64u) stamp(10);
                 epilogue_bar_sync();
                 if (threadIdx.x == 64u) {
                     const uint32_t prev = atomicAdd(a.counters + tile, 1u);
@@ -400,7 +379,6 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
                     }
                     if (threadIdx.x == 64u) a.counters[tile] = 0u;
                 }
-                if (iter == 0 && threadIdx.x == 64u) stamp(7);
                 epilogue_bar_sync();                          // last_flag is rewritten by the next item
             }
         }
@@ -415,7 +393,6 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
     }
     ptx::tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) stamp(8);
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
@@ -530,7 +507,7 @@ __device__ __forceinline__ void finish_owned_t(const WaveArgs &a, const float *r
         }
         *reinterpret_cast<uint2 *>(dst) = make_uint2(pk[0], pk[1]);
         if (a.peers) {
-            const uint32_t n = (a.peers->dev_flags & 1u) ? 0u : a.peers->n_peers;
+            const uint32_t n = a.peers->n_peers;
             for (uint32_t q = 0; q < n; ++q) *reinterpret_cast<uint2 *>(a.peers->canvas[q] + a.y_off + o) = make_uint2(pk[0], pk[1]);
         }
     } else {
@@ -602,9 +579,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
     if (g == 1) a = grp.w[1];
     else if (g == 2) a = grp.w[2];
     else if (g == 3) a = grp.w[3];
-    const bool trace = (d.debug & 16u) && blockIdx.x == 0;       // development aid: milestone clocks of CTA 0
-    auto stamp = [&](int slot) { if (trace) reinterpret_cast<volatile long long *>(a.status + 2)[slot] = clock64(); };
-    if (threadIdx.x == 0) stamp(0);
     const uint32_t tile = cid - grp.first_cluster[g], rank = cluster_rank();
     const uint32_t tiles_n = a.num_col_tiles64;
     const uint32_t mt = tile / tiles_n, ct = tile % tiles_n;
@@ -637,7 +611,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) stamp(1);
     if (S > 1) cluster_arrive();            // phase A: "this CTA is alive"; waited for before the first remote write
     grid_launch_dependents();               // the next wave may start its own set-up and weight prefetch
 
@@ -665,7 +638,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         // the run table is static too: fetch its first entries before waiting for the previous wave
         uint32_t cached_base = (ks0 * boxes_per_stage) & ~31u;
         uint32_t cached = (cached_base + lane < a.boxes_per_group) ? __ldg(rows + cached_base + lane) : 0u;
-        if (lane == 0) stamp(2);
         grid_dependency_wait();             // everything below reads rows the previous wave wrote
         bool ok = true;
         if (a.peers) {                       // ... and, in a neuron-sharded plan, rows the peers stored into this canvas
@@ -677,7 +649,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
             ok = __shfl_sync(0xffffffffu, okp, 0) != 0u;
         }
         fence_proxy_async_global();
-        if (lane == 0) stamp(3);
         uint32_t issued = 0;
         for (uint32_t ks = ks0; ks < ks1 && ok; ++ks, ++issued) {
             const uint32_t stage = issued % kStages, ph = (issued / kStages) & 1u;
@@ -702,9 +673,7 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
                 if (lane == 0)
                     ptx::tma_load_2d(x_smem + stage * kXBytes + b * a.box_h * 128u, &tmap, (int32_t)(ct * 64u), (int32_t)row, full_bar + 8u * stage, pol_x);
             }
-            if (lane == 0 && issued == 0) stamp(4);
         }
-        if (lane == 0) stamp(5);
         if (!ok && lane == 0) {
             if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PRODUCER);
             *abort_word = 1u;
@@ -726,7 +695,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
                 const uint32_t stage = consumed % kStages, ph = (consumed / kStages) & 1u;
                 ok = wait(full_bar + 8u * stage, ph);
                 if (!ok) break;
-                if (consumed == 0) stamp(6);
                 ptx::tc_fence_after();
                 const uint64_t a0 = d.a_base | (uint64_t)(((w_smem + stage * kStageWBytes) >> 4) & 0x3fffu);
                 const uint64_t b0 = d.b_base | (uint64_t)(((x_smem + stage * kXBytes) >> 4) & 0x3fffu);
@@ -735,7 +703,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
                     ptx::umma_f16(tmem_base, a0 + (uint64_t)(k4 * d.a_k_step), b0 + (uint64_t)(k4 * d.b_k_step), d.idesc, (ks != ks0 || k4 != 0u) ? 1u : 0u);
                 ptx::umma_commit(empty_bar + 8u * stage);
             }
-            stamp(7);
             if (ok) ptx::umma_commit(tfull_bar);
             else { if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_MMA); *abort_word = 1u; }
         }
@@ -749,7 +716,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         __syncwarp();
         grid_dependency_wait();             // already satisfied (the operands depended on it); orders this thread's own accesses
         const bool ok = epi_ok[0] != 0u;
-        if (threadIdx.x == 64u) stamp(8);
         if (!ok && threadIdx.x == 64u) { if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_EPILOGUE); *abort_word = 1u; }
         ptx::tc_fence_after();
         const uint32_t rows_owned = kTileM / S;
@@ -758,7 +724,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         // that share an owner write one contiguous run per store instruction
         const uint32_t slot_off = (rank * 16u * (rows_owned + 1u) + row_local) * 16u;   // +1: padding row against bank conflicts on the read side
         if (S > 1) cluster_wait();          // phase A complete: every CTA of the cluster is running
-        if (threadIdx.x == 64u) stamp(9);
         const uint32_t remote = S > 1 ? map_to_rank(recv_smem + slot_off, owner) : 0u;
 #pragma unroll 1
         for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
@@ -784,7 +749,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         }
     }
     // ---------------- exchange complete -> every CTA finishes the rows it owns ----------------
-    if (threadIdx.x == 64u) stamp(10);
     ptx::tc_fence_before();
     __syncwarp();
     if (S > 1) {
@@ -794,7 +758,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
     } else {
         __syncthreads();
     }
-    if (threadIdx.x == 64u) stamp(11);
     if (warp >= 2 && *abort_word == 0u) {
         const uint32_t t = threadIdx.x - 64u;                       // 0..127
         switch (S) {
@@ -805,7 +768,6 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         default: finish_owned<16>(a, recv, t, mt, ct, rank); break;
         }
     }
-    if (threadIdx.x == 64u) stamp(12);
     __syncthreads();                         // with peers: orders the storing threads' writes before thread 0's fence
     if (a.peers && threadIdx.x == 0) peer_signal_done(a.peers, gridDim.x);
     if (warp == 1) {

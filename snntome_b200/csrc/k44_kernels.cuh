@@ -54,7 +54,6 @@ struct PeerArgs {
     uint32_t *arrive[kMaxPeers] = {};     // this rank's word in each peer's sync block
     uint32_t *sync = nullptr;             // own sync block: [0..6] the peers' launch counts, [8] CTAs done in the running launch, [9] launches completed
     uint32_t n_peers = 0;
-    uint32_t dev_flags = 0;               // development switch: 1 skip the data stores (timing experiments only)
 };
 constexpr uint32_t kSyncWords = 16, kSyncDone = 8, kSyncEpoch = 9;
 
@@ -134,7 +133,6 @@ struct UmmaDesc {
     uint32_t n_tile = 64;
     uint32_t small_wave = 0;              // 1: 4-stage, two-CTAs-per-SM variant (N_TILE 64 only)
     unsigned long long wait_cycles = 0;   // bound for every barrier wait
-    uint32_t debug = 0;                   // development switches (0 in production)
 };
 
 cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s);

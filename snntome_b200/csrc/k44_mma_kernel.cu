@@ -182,14 +182,22 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
     };
 
     // neuron-sharded plans: the rows this launch gathers were stored into this canvas by the peers' previous launches
+    // (the grid is not persistent: once one CTA has given up on a peer, the status bit tells every later CTA not to wait
+    // again, so a missing peer costs one wait period and not one per batch of resident CTAs; a launch that gave up reads and
+    // stores nothing and only counts its CTAs as done)
+    bool peers_ready = true;
     if (a.peers) {
         __shared__ uint32_t peer_ok;
         if (tid == 0) {
-            peer_ok = peer_wait_ready(a.peers, wait_cycles) ? 1u : 0u;
-            if (!peer_ok) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PEER);
+            uint32_t ok = (*reinterpret_cast<volatile uint32_t *>(a.status) & (uint32_t)ST_TIMEOUT_PEER) ? 0u : 1u;
+            if (ok) ok = peer_wait_ready(a.peers, wait_cycles) ? 1u : 0u;
+            if (!ok) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PEER);
+            peer_ok = ok;
         }
         __syncthreads();
+        peers_ready = peer_ok != 0u;
     }
+    if (peers_ready) {
 
     // prologue: table entries of the first 2D stages, then the rows of the first D stages
     for (uint32_t ks = 0; ks < 2u * D; ++ks) issue_table(ks);
@@ -254,11 +262,12 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
                 const __half2 out = __floats2half2_rn(v0, v1);
                 *reinterpret_cast<__half2 *>(a.canvas + a.y_off + o) = out;
                 if (a.peers) {
-                    const uint32_t n = (a.peers->dev_flags & 1u) ? 0u : a.peers->n_peers;
+                    const uint32_t n = a.peers->n_peers;
                     for (uint32_t q = 0; q < n; ++q) *reinterpret_cast<__half2 *>(a.peers->canvas[q] + a.y_off + o) = out;
                 }
             }
         }
+    }   // peers_ready
     if (a.peers) {
         __syncthreads();                    // orders every thread's peer stores before thread 0's system-scope fence
         if (tid == 0) peer_signal_done(a.peers, gridDim.x);

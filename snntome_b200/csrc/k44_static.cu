@@ -27,6 +27,11 @@ constexpr size_t kStaticBytes = kStatusBytes + kCounterBytes + (size_t)kMaxTiles
 // [status | counters | partial-sum tiles]; about 2 MiB, held by every GPU that loads the library until exit.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;       // driver entry point, looked up once (first set-up)
+
 struct DeviceSlot {
     bool ready = false;
     unsigned char *base = nullptr;   // device address of g_static_scratch on this device
@@ -62,6 +67,13 @@ int setup_current_device(DeviceSlot **out) {
         if (e != cudaSuccess || !ptr) return fail(std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
         e = cudaDeviceGetAttribute(&s.num_sms, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) return fail(std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
+        if (!g_encode) {
+            void *fn = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn)
+                return fail("cuTensorMapEncodeTiled is not available from the driver");
+            g_encode = (EncodeTiledFn)fn;
+        }
         e = k44b::umma_kernel_setup();
         if (e != cudaSuccess) return fail(std::string("kernel attribute setup: ") + cudaGetErrorString(e));
         e = cudaMemset(ptr, 0, kStaticBytes);
@@ -74,19 +86,12 @@ int setup_current_device(DeviceSlot **out) {
 }
 
 int encode_canvas_map(CUtensorMap *map, void *canvas, uint64_t canvas_elems, uint32_t pitch, uint32_t box_h) {
-    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    void *fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn)
-        return fail("cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[2] = {pitch, canvas_elems / pitch};
     const cuuint64_t strides[1] = {(cuuint64_t)pitch * 2u};
     const cuuint32_t box[2] = {64u, box_h};
     const cuuint32_t estr[2] = {1u, 1u};
-    const CUresult r = ((EncodeFn)fn)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, canvas, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, canvas, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
 }
 
@@ -118,9 +123,14 @@ int k44b_wave_forward_static(void *d_canvas, uint64_t canvas_elems, uint32_t pit
                            std::to_string(kMaxTiles) + " (K44B_STATIC_MAX_TILES)"));
     if (k_splits == 0 || k_splits > kstages) return report(fail("k_splits must be between 1 and ceil(fan_in / 64)"));
 
+    cudaStream_t s = (cudaStream_t)stream;
+    {   // every call reads the status word back and waits for the stream: none of that may be recorded into a graph
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)
+            return report(fail("the stream is being captured: this call synchronises the stream and cannot be part of a capture"));
+    }
     DeviceSlot *slot = nullptr;
     if (setup_current_device(&slot) != 0) return report(-1);
-    cudaStream_t s = (cudaStream_t)stream;
     uint32_t *status = reinterpret_cast<uint32_t *>(slot->base);
     uint32_t *counters = reinterpret_cast<uint32_t *>(slot->base + kStatusBytes);
     float *partial = reinterpret_cast<float *>(slot->base + kStatusBytes + kCounterBytes);

@@ -272,6 +272,12 @@ class NativePlan:
             raise NativeError(f"status {st.value:#x}: {last_error()}")
         return st.value
 
+    def status_code(self) -> int:
+        """Like `status`, but a non-zero kernel status is returned instead of raised (the word is cleared either way)."""
+        st = ctypes.c_uint32(0)
+        self._lib.k44b_status(self._ptr, ctypes.byref(st))
+        return st.value
+
     def infer_f32(self, x: np.ndarray, out_elems: int):
         x32 = np.ascontiguousarray(x, dtype=np.float32)
         out = np.empty(out_elems, dtype=np.float32)

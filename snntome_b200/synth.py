@@ -129,6 +129,28 @@ def dense_chain(seed: int, dims: list[int], columns: int, act: int = ACT_NONE, g
                 name="dense_chain")
 
 
+def token_shift_plan(seed: int, *, rows_in: int = 256, cout: int = 256, runs: int = 8, run_len: int = 16, frames: int = 2,
+                     frame_len: int = 256, group: int = 128, act: int = ACT_NONE, waves: int = 2, max_shift: int = 7) -> Plan:
+    """Receptive-field token-shift plan: `frames` sequences of `frame_len` tokens side by side in every row; every run of
+    `run_len` rows is read 0..max_shift tokens earlier, with zero padding at the start of each frame."""
+    rng = np.random.default_rng(seed)
+    pitch = frames * frame_len
+    fan_in = runs * run_len
+    ws, total = [], rows_in
+    for wi in range(waves):
+        groups = cout // group
+        starts = run_starts(seed, wi, groups, runs, run_len, total)
+        idx = expand_runs(starts, run_len, pitch)
+        sh_run = rng.integers(0, max_shift + 1, size=(groups, runs)).astype(np.uint8)
+        shifts = np.repeat(sh_run, run_len, axis=1)
+        wt = f16_bits(rng.normal(0, (1.0 / fan_in) ** 0.5, (cout, fan_in)))
+        ws.append(Wave(cout=cout, group=group, fan_in=fan_in, idx=idx, weights=wt, bias=None, y_off=total * pitch, act=act,
+                       shifts=shifts, frame_len=frame_len, name=f"shift{wi}"))
+        total += cout
+    return Plan(canvas_elems=total * pitch, pitch=pitch, columns=pitch, input_off=0, input_c=rows_in,
+                output_off=(total - cout) * pitch, output_c=cout, waves=ws, name="token_shift")
+
+
 def random_input(plan: Plan, seed: int, dist: str = "uniform") -> np.ndarray:
     """FP16 bit patterns for the input rows, [input_c, pitch]; columns >= plan.columns are zero."""
     rng = np.random.default_rng(seed)

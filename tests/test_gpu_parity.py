@@ -229,6 +229,18 @@ def test_bad_plan_is_rejected_before_launch():
         NativePlan.from_plan(plan)
 
 
+def test_wave_that_gathers_its_own_output_rows_is_rejected():
+    """A wave cannot run in place (CTAs of one launch would race; on a sharded plan a peer's stores would land in rows still
+    being read): rejected when the wave is added. Residual rows equal to the output rows stay legal."""
+    plan = synth.config0()
+    w = plan.waves[1]
+    w.idx[2, 5] = w.y_off + 3 * plan.pitch             # a real synapse pointing into the wave's own output rows
+    with pytest.raises(native.NativeError, match="in place"):
+        NativePlan.from_plan(plan)
+    ok = synth.dense_chain(seed=3, dims=[256, 256, 256], columns=64, residual_from={2: 2})   # residual = own output rows
+    NativePlan.from_plan(ok).close()
+
+
 @pytest.mark.parametrize("cluster", [1, 0])
 @pytest.mark.parametrize("splits", [0, 2, 3, 7, 32])
 def test_split_k_small_waves(splits, cluster, monkeypatch):

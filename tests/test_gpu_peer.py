@@ -135,3 +135,82 @@ def test_missing_peer_ends_the_wait_with_a_status_bit(monkeypatch):
         ok, err, k = O.compare(got[a:b], want[a:b], RTOL, ATOL)
         assert ok, (w.name, err, k)
     npn.close()
+
+
+def test_missing_peer_on_the_small_group_kernel_costs_one_wait_period(monkeypatch):
+    """The mma.sync kernel's grid is not persistent: a rank's half of a group-16 wave of 65536 neurons x 2 column tiles is 4096 CTAs. With a
+    peer that never shows up the CTAs resident first wait out the (shortened) bound together; every later CTA sees the status
+    bit and neither waits nor touches the canvas. The launch therefore ends after about one wait period, not one per batch of
+    resident CTAs, and writes nothing."""
+    import time
+    import torch
+    monkeypatch.setenv("K44B_WAIT_MS", "200")
+    plan = synth.sparse_plan(seed=131, input_rows=2048, waves=2, cout=65536, runs=4, run_len=16, columns=128, group=16, act=ACT_RELU)
+    p0 = NativePlan.from_plan(shard.shard_plan(plan, 0, 2), device=0)
+    p1 = NativePlan.from_plan(shard.shard_plan(plan, 1, 2), device=0)      # never executes
+    assert p0.wave_info(1).path == 3
+    cps, sps = [p0.canvas_ptr, p1.canvas_ptr], [p0.sync_ptr, p1.sync_ptr]
+    p0.set_peers_raw(0, 2, cps, sps)
+    p1.set_peers_raw(1, 2, cps, sps)
+    x = synth.random_input(plan, 132)
+    xt = torch.from_numpy(np.ascontiguousarray(x).view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    p0.canvas_tensor()[plan.input_off: plan.input_off + xt.numel()] = xt
+    p0.execute_wave(0)
+    torch.cuda.synchronize()
+    assert p0.status() == 0
+    w1 = shard.shard_plan(plan, 0, 2).waves[1]
+    before = p0.canvas_tensor()[w1.y_off: w1.y_off + w1.cout * plan.pitch].clone()
+    t0 = time.perf_counter()
+    p0.execute_wave(1)                    # 4096 CTAs on this rank; needs the peer's launch 0, which never comes
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    with pytest.raises(NativeError) as ei:
+        p0.status()
+    assert "peer" in str(ei.value).lower()
+    assert dt < 1.5, f"launch with a missing peer took {dt:.2f} s: CTAs waited batch after batch"
+    after = p0.canvas_tensor()[w1.y_off: w1.y_off + w1.cout * plan.pitch]
+    assert torch.equal(before, after)     # a launch that gave up stores nothing
+    p0.close(); p1.close()
+
+
+def test_split_k_plan_is_clean_again_after_a_timeout(monkeypatch):
+    """Split-K waves (partial sums in a global FP32 scratch, K44B_CLUSTER=0) on two ranks: rank 0 runs ahead, its second launch
+    gives up on the missing peer, the status read puts scratch, arrival counters and the launch bookkeeping back to their
+    between-launches state; then the peer catches up and the whole plan, run in order on both ranks, matches the oracle."""
+    import torch
+    monkeypatch.setenv("K44B_WAIT_MS", "200")
+    monkeypatch.setenv("K44B_CLUSTER", "0")
+    plan = synth.dense_chain(seed=133, dims=[1024, 512, 512], columns=64, act=ACT_SILU, weight_std=0.04)
+    x = synth.random_input(plan, 134, dist="normal")
+    want = O.run_plan(plan, x)
+    plans = [NativePlan.from_plan(shard.shard_plan(plan, r, 2), device=0) for r in range(2)]
+    assert plans[0].wave_info(0).k_splits > 1
+    xt = torch.from_numpy(np.ascontiguousarray(x).view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    for p in plans:
+        p.canvas_tensor()[plan.input_off: plan.input_off + xt.numel()] = xt
+    cps, sps = [p.canvas_ptr for p in plans], [p.sync_ptr for p in plans]
+    for r, p in enumerate(plans):
+        p.set_peers_raw(r, 2, cps, sps)
+    plans[0].execute_wave(0)
+    plans[0].execute_wave(1)              # waits for the peer's first launch: times out
+    torch.cuda.synchronize()
+    with pytest.raises(NativeError):
+        plans[0].status()
+    plans[1].execute_wave(0)              # the peer catches up: both ranks have now issued two launches
+    plans[1].execute_wave(1)
+    torch.cuda.synchronize()
+    assert plans[1].status() == 0
+    for i in range(len(plan.waves)):      # and the plan runs in order on both
+        for p in plans:
+            p.execute_wave(i)
+    got = []
+    for p in plans:
+        assert p.status() == 0
+        got.append(p.canvas_tensor().cpu().numpy().view(np.uint16))
+    for r in range(2):
+        for w in plan.waves:
+            a, b = w.y_off, w.y_off + w.cout * plan.pitch
+            ok, err, k = O.compare(got[r][a:b], want[a:b], RTOL, ATOL)
+            assert ok, (r, w.name, err, k)
+    for p in plans:
+        p.close()

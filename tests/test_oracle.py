@@ -52,6 +52,23 @@ def test_f32_to_f16_matches_numpy_rte():
     assert np.array_equal(O.f32_to_f16(x), want)
 
 
+def test_f64_to_f16_rounds_once():
+    """The wave oracle stores its double results with one rounding: equal to numpy's float64 -> float16 everywhere,
+    including values a hair off a half-way point of the half grid, where rounding through float32 first goes wrong."""
+    rng = np.random.default_rng(5)
+    halves = np.arange(0, 0x7bff, dtype=np.uint16).view(np.float16).astype(np.float64)
+    mid = (halves[:-1] + halves[1:]) / 2                               # exact half-way points (ties)
+    eps = np.abs(mid) * 2.0 ** -40 + 2.0 ** -60                        # far below float32 resolution
+    vals = np.concatenate([mid, mid + eps, mid - eps, -mid, -(mid + eps), rng.normal(0, 10, 20000), rng.normal(0, 1e-5, 20000),
+                           rng.uniform(-7e4, 7e4, 20000), [0.0, -0.0, 65519.999, 65520.0, -65520.0, 1e300, -1e300, 2.0 ** -25, 2.0 ** -25 * 1.0000001]])
+    with np.errstate(over="ignore"):
+        want = vals.astype(np.float16).view(np.uint16)
+    got = O.f64_to_f16(vals)
+    assert np.array_equal(got, want)
+    twice = vals.astype(np.float32).astype(np.float16).view(np.uint16)
+    assert (twice != want).any()                                        # the case this guards against exists in the set
+
+
 def test_f32_to_f16_nan_stays_nan():
     x = np.array([np.nan, -np.nan], dtype=np.float32)
     got = O.f32_to_f16(x)

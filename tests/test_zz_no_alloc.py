@@ -89,6 +89,70 @@ def test_static_scratch_wave_matches_plan_path_twice():
     npn.close()
 
 
+@pytest.mark.parametrize("case", ["direct_epilogue", "groups_of_128", "partial_last_tile_no_bias"])
+def test_static_scratch_other_shapes_and_no_allocation(case):
+    """More shapes through the allocation-free entry point, each against the oracle: one CTA per tile with the epilogue written
+    straight from tensor memory (k_splits = 1), three groups of 128 neurons with their own run lists, and a wave whose last
+    128-neuron tile is partly empty (208 rows) with no bias. The second call of each case also checks the property the entry
+    point exists for: the device's free memory is the same before and after the call."""
+    import torch
+    lib = get_lib()
+    if case == "direct_epilogue":
+        plan = synth.dense_chain(seed=311, dims=[512, 256], columns=64, act=ACT_SILU, weight_std=0.05)
+        k_splits, group = 1, None
+    elif case == "groups_of_128":
+        plan = synth.sparse_plan(seed=312, input_rows=2048, waves=1, cout=384, runs=8, run_len=32, columns=128, group=128)
+        k_splits, group = 2, 128
+    else:
+        plan = synth.dense_chain(seed=313, dims=[320, 208], columns=64, weight_std=0.05)
+        k_splits, group = 3, None
+    wave = plan.waves[0]
+    if case == "partial_last_tile_no_bias":
+        wave.bias = None
+    x = synth.random_input(plan, 314)
+    want = O.run_plan(plan, x)
+    rows_per_box, rows = native.analyze_gather(wave, plan.pitch, plan.canvas_elems)
+    assert rows_per_box in (8, 16, 32, 64)
+    xt = torch.from_numpy(x.view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    d_rows = torch.from_numpy(rows.astype(np.int32)).cuda()
+    d_w = torch.from_numpy(pack_tiled(wave.weights).view(np.int16)).cuda()
+    d_bias = torch.from_numpy(wave.bias.view(np.int16)).cuda() if wave.bias is not None else None
+    canvas = torch.zeros(plan.canvas_elems, dtype=torch.float16, device="cuda")
+    canvas[plan.input_off: plan.input_off + xt.numel()] = xt
+    a, b = wave.y_off, wave.y_off + wave.cout * plan.pitch
+    for call in range(2):
+        canvas[a:b] = 0
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        rc, msg = call_static(lib, canvas, plan, wave, d_w, d_rows, rows_per_box, d_bias, group or wave.cout, k_splits=k_splits)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert rc == 0, msg
+        if call == 1:       # (the first call on a device may load the kernels' module)
+            assert free_after == free_before, f"free device memory changed by {free_before - free_after} bytes across the call"
+        got = canvas.cpu().numpy().view(np.uint16)
+        ok, err, k = O.compare(got[a:b], want[a:b], RTOL, ATOL)
+        assert ok, (case, f"call {call}", err, k)
+
+
+def test_static_scratch_refuses_a_capturing_stream():
+    """Every call waits for the stream and reads a status word back, which cannot be recorded into a graph: a call made on a
+    stream that is being captured is refused with a message and leaves the capture intact."""
+    import torch
+    lib = get_lib()
+    dummy = torch.zeros(64 * 64 * 4, dtype=torch.float16, device="cuda")
+    rows = torch.zeros(8, dtype=torch.int32, device="cuda")
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    err = ctypes.create_string_buffer(512)
+    with torch.cuda.graph(g, stream=side):
+        rc = lib.k44b_wave_forward_static(ctypes.c_void_p(dummy.data_ptr()), dummy.numel(), 64, ctypes.c_void_p(dummy.data_ptr()),
+                                          ctypes.c_void_p(rows.data_ptr()), 64, None, 128, 128, 64, 0, 64 * 64, 1,
+                                          ctypes.c_void_p(side.cuda_stream), err, 512)
+        dummy.add_(0)       # something capturable, so the graph is not empty
+    assert rc == -1 and "captur" in err.value.decode()
+
+
 def test_static_scratch_rejects_oversize_wave():
     import torch
     lib = get_lib()
