@@ -503,15 +503,15 @@ def decode_main(args) -> None:
 PRUNED = dict(hidden=4096, layers=32, kv=1024, ffn=14336, vocab=128256, columns=256, cluster=32, keep=0.10)
 
 
-def sharded_measure(layers: int, steps: int, warmup: int, rank: int, local_rank: int, world: int, breakdown: bool = True) -> dict:
-    """Llama-3-8B shaped wave chain; every 128-neuron group keeps 10 % of its 32-row input clusters (uniform,
-    seeded); the lm_head stays dense. Rank r owns rows [r*cout/n, (r+1)*cout/n) of every wave and only their
-    weights; the rows of every wave reach all replicas of the canvas (see K44B_SHARD_MODE below). The default process
-    group must already exist when world > 1. Every rank returns the same result line (a dict); a kernel status other
-    than zero on any rank is reported in it as "error" instead of raised, so that all ranks keep taking the same path."""
+def build_pruned_plan(layers: int, rank: int, local_rank: int, world: int):
+    """The cluster-pruned 8B wave chain, this rank's share: Llama-3-8B shaped linears (q, k, v, o, gate, up, down per layer,
+    dense lm_head); every 128-neuron group keeps 10 % of its 32-row input clusters (uniform, seeded); rank r holds rows
+    [r*cout/n, (r+1)*cout/n) of every wave and only their weights; the canvas is replicated. Returns (plan, info): info has
+    the tensors' first rows (`rows`), per wave (output offset of the whole wave, its elements, this rank's block elements)
+    in `waves`, per wave the run-start table of this rank's groups and the run length in `tables`, and the kept parameter
+    count."""
     import torch
-    import torch.distributed as dist
-    from snntome_b200 import shard, synth
+    from snntome_b200 import synth
     from snntome_b200._lib import WaveDesc
     from snntome_b200.native import NativePlan, fill_normal_f16
     cfg = dict(PRUNED, layers=layers)
@@ -523,6 +523,7 @@ def sharded_measure(layers: int, steps: int, warmup: int, rank: int, local_rank:
         rows[name] = cur; cur += n
     plan = NativePlan.create(cur * pitch, pitch, C, device=local_rank)
     waves = []       # (y_off, cout_total, block_elems)
+    tables = []      # (run starts [groups, runs], run_len, first row of this rank's block, residual tensor's first row or None, act)
     kept_params = 0
     scratch = torch.empty(max(V // world * H, 1), dtype=torch.float16, device="cuda")
 
@@ -557,6 +558,7 @@ def sharded_measure(layers: int, steps: int, warmup: int, rank: int, local_rank:
         d.name = name.encode()
         plan.add_wave_desc(d)
         waves.append((rows[dst] * pitch, cout * pitch, blk * pitch))
+        tables.append((starts, run_len, rows[dst] + r0, (rows[res] + r0) if res else None, act))
         kept_params += cout * fan_in
 
     x_in, x_out, wi = "x0", "x1", 0
@@ -569,11 +571,40 @@ def sharded_measure(layers: int, steps: int, warmup: int, rank: int, local_rank:
     add("lm_head", wi, x_in, "logits", H, V, dense=True)
     del scratch
     torch.cuda.empty_cache()
+    return plan, {"rows": rows, "waves": waves, "tables": tables, "kept_params": kept_params, "cfg": cfg, "vocab_rows": V, "pitch": pitch}
+
+
+def sharded_measure(layers: int, steps: int, warmup: int, rank: int, local_rank: int, world: int, breakdown: bool = True) -> dict:
+    """The cluster-pruned 8B wave chain (see build_pruned_plan), neuron-sharded: the rows of every wave reach all replicas of
+    the canvas (see K44B_SHARD_MODE below). The default process group must already exist when world > 1. Every rank returns
+    the same result line (a dict); a kernel status other than zero on any rank is reported in it as "error" instead of
+    raised, so that all ranks keep taking the same path."""
+    import torch
+    import torch.distributed as dist
+    from snntome_b200 import shard
+    from snntome_b200.native import fill_normal_f16
+    plan, info = build_pruned_plan(layers, rank, local_rank, world)
+    rows, waves, kept_params, cfg, V, pitch = info["rows"], info["waves"], info["kept_params"], info["cfg"], info["vocab_rows"], info["pitch"]
+    H, C = cfg["hidden"], cfg["columns"]
     canvas = plan.canvas_tensor()
-    fill_normal_f16(canvas[: H * pitch], 4242, 1.0)       # same input on every rank (replicated canvas)
-    torch.cuda.synchronize()
     stream = torch.cuda.current_stream()
     nw = plan.num_waves
+    mode = os.environ.get("K44B_SHARD_MODE", "peer")
+    slack, signal = None, None
+    if world > 1 and mode == "peer":
+        slack = shard.connect_peers(plan, rank, world)
+        # what one dependent launch costs at least: ranks 0 and 1 bounce a count word (alone, and behind a 16 KiB payload — one
+        # 128 x 64 output block — stored into the peer's canvas and a system-scope fence), before the input is written
+        try:
+            if rank < 2:
+                rt0 = plan.peer_latency(1 - rank, rank == 0, 2000, 0, stream)
+                rt16 = plan.peer_latency(1 - rank, rank == 0, 2000, 16384, stream)
+                signal = {"round_trip_us_word_only": rt0 / 1e3, "round_trip_us_16KiB_block_fence_word": rt16 / 1e3}
+        except Exception as exc:
+            signal = {"error": str(exc)}
+        dist.barrier()
+    fill_normal_f16(canvas[: H * pitch], 4242, 1.0)       # same input on every rank (replicated canvas)
+    torch.cuda.synchronize()
 
     def eager_step():
         st = torch.cuda.current_stream()
@@ -588,11 +619,8 @@ def sharded_measure(layers: int, steps: int, warmup: int, rank: int, local_rank:
     #   peer  (default) the wave kernels store their rows into every canvas themselves (peer-mapped memory) and order
     #         their launches against the peers' through counter words; a step is one CUDA graph, no collective call;
     #   nccl  one in-place all-gather per wave after its launch (the plain baseline); nccl-graph: the same, captured.
-    mode = os.environ.get("K44B_SHARD_MODE", "peer")
     graph = None
-    if world > 1 and mode == "peer":
-        shard.connect_peers(plan, rank, world)
-    elif world > 1 and mode == "nccl-graph":
+    if world > 1 and mode == "nccl-graph":
         eager_step()                      # NCCL communicator set-up and lazy initialisation happen outside the capture
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
@@ -669,7 +697,10 @@ def sharded_measure(layers: int, steps: int, warmup: int, rank: int, local_rank:
                                                                     "nccl": "in-place NCCL all-gather after every wave", "nccl-graph": "in-place NCCL all-gather after every wave, captured in one CUDA graph"}[mode]),
                        "exchange_mode": "none" if world == 1 else mode,
                        "bytes_received_per_rank_per_step": gather_bytes,
-                       "nvlink_time_bound_ms": gather_bytes / 770e9 * 1e3},
+                       "nvlink_time_bound_ms": gather_bytes / 770e9 * 1e3,
+                       "launches_per_step": int(launches // max(steps, 1)) if launches else None,
+                       "launches_that_wait_for_the_launch_before": int((slack == 0).sum()) if slack is not None else None,
+                       "signal": signal},
             "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9, "peak": peak,
                          "peak_kind": f"of {kind}", "unit": "GB/s", "frac": kept_params * 2.0 / world / (ms_step * 1e-3) / 1e9 / peak, "traffic": None},
             "per_wave_us_direct_launch": wave_us,
@@ -1052,6 +1083,8 @@ def main() -> None:
             sharded.update({"exchange_mode": sh["config"]["exchange_mode"], "exchange": sh["config"]["exchange"],
                             "bytes_received_per_rank_per_step": sh["config"]["bytes_received_per_rank_per_step"],
                             "nvlink_time_bound_ms": sh["config"]["nvlink_time_bound_ms"], "workload": sh["config"]["workload"],
+                            "launches_per_step": sh["config"]["launches_per_step"], "signal": sh["config"]["signal"],
+                            "launches_that_wait_for_the_launch_before": sh["config"]["launches_that_wait_for_the_launch_before"],
                             "waves_per_step": sh["config"]["waves_per_step"]})
             if "error" in sh:
                 sharded["error"] = sh["error"]

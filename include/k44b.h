@@ -121,8 +121,10 @@ int k44b_plan_get_next_tokens(void *plan, int32_t *h_tokens, uint32_t n, void *s
 /* ---- neuron sharding over the GPUs of one box (no counterpart in the reference, which is single-GPU) ----
  * Every rank holds a plan with its rows of every wave and a full-size canvas. After k44b_plan_set_peers_* the wave
  * kernels store each output row into the rank's own canvas and into the peers' canvases (peer-mapped memory over
- * NVLink), and a launch starts reading only when every peer has finished the launches before it (one 32-bit word per
- * peer, bounded wait: status bit 5 on expiry). All ranks must issue the same sequence of launches. Supported for waves
+ * NVLink; the streaming tcgen05 kernel sends whole 128-row x 64-column tiles with tensor copies out of shared memory,
+ * the other kernels 16-byte pieces), and a launch starts reading only when every peer has finished the launches before
+ * it (one 32-bit word per peer, bounded wait: status bit 5 on expiry). All ranks must issue the same sequence of launches.
+ * Rank r must hold rows [r * cout / world, (r + 1) * cout / world) of every wave. Supported for waves
  * that run on the tcgen05 kernels or on the mma.sync kernel (small neuron groups); plans with token-shifted waves,
  * element-wise commands or waves forced onto the FP32-FMA kernel are rejected. world <= 8.
  *   ipc_handles:    64-byte CUDA IPC handles of this plan's canvas and sync block, to be sent to the other processes
@@ -132,6 +134,25 @@ int k44b_plan_ipc_handles(void *plan, void *canvas_handle64, void *sync_handle64
 int k44b_plan_set_peers_ipc(void *plan, int rank, int world, const void *canvas_handles, const void *sync_handles);
 int k44b_plan_set_peers_raw(void *plan, int rank, int world, void *const *canvas_ptrs, void *const *sync_ptrs);
 void *k44b_plan_sync_ptr(void *plan);
+/* Launch ordering by region instead of by launch count (optional, after set_peers_*). A step of the plan is a fixed
+ * sequence of launches (waves that cannot observe each other share one). launch_hulls writes, per launch, the canvas
+ * element intervals it may read and write: out[launch][4] = {read_lo, read_hi, write_lo, write_hi}, half-open. The
+ * caller collects the tables of all ranks and passes them, [world][launches][4], to set_peer_hulls on every rank; from
+ * then on a launch waits only for the peers' nearest earlier launch that it depends on (whose rows it reads, whose reads
+ * it overwrites, or whose rows it overwrites — on any rank, across step boundaries too) instead of for all of them.
+ * Without this call every launch waits for all earlier launches of every peer. compute_peer_slack is the host arithmetic
+ * behind it: out_slack[launch] = how many of the launches just before it need not be waited for. */
+/* Signalling round trip between this rank and one peer (after set_peers_*; both ranks call it with the same iters and
+ * payload_bytes, exactly one of them with initiator != 0, and no other work of the plan in flight): `iters` times a payload
+ * (payload_bytes, a multiple of 16, stored at the start of the peer's canvas — use a scratch plan; 0 for none), one
+ * system-scope fence and one count word, answered the same way by the peer. This is the sequence a sharded launch ends and
+ * the next one starts with, so the result (nanoseconds per round trip; the call waits for `stream`) is the floor of what
+ * each dependent launch of a sharded step costs. Bounded waits: fails with a message if the peer does not answer. */
+int k44b_plan_peer_latency(void *plan, int peer_rank, int initiator, uint32_t iters, uint32_t payload_bytes, float *out_ns_per_round_trip, void *stream);
+int k44b_plan_num_launches(void *plan);
+int k44b_plan_launch_hulls(void *plan, uint64_t *out, uint64_t capacity_launches);
+int k44b_plan_set_peer_hulls(void *plan, int world, const uint64_t *hulls, uint64_t launches);
+void k44b_compute_peer_slack(const uint64_t *hulls, int world, uint64_t launches, uint32_t *out_slack);
 
 /* Number of kernels this plan has launched so far. */
 uint64_t k44b_launch_count(void *plan);

@@ -94,6 +94,11 @@ PROTOTYPES = {
     "k44b_plan_set_peers_ipc": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "k44b_plan_set_peers_raw": (c_int, [c_void_p, c_int, c_int, POINTER(c_void_p), POINTER(c_void_p)]),
     "k44b_plan_sync_ptr": (c_void_p, [c_void_p]),
+    "k44b_plan_peer_latency": (c_int, [c_void_p, c_int, c_int, c_uint32, c_uint32, POINTER(c_float), c_void_p]),
+    "k44b_plan_num_launches": (c_int, [c_void_p]),
+    "k44b_plan_launch_hulls": (c_int, [c_void_p, POINTER(c_uint64), c_uint64]),
+    "k44b_plan_set_peer_hulls": (c_int, [c_void_p, c_int, POINTER(c_uint64), c_uint64]),
+    "k44b_compute_peer_slack": (None, [POINTER(c_uint64), c_int, c_uint64, POINTER(c_uint32)]),
     "k44b_launch_count": (c_uint64, [c_void_p]),
     "k44b_wave_weights_rowmajor": (c_int, [c_void_p, c_int, c_void_p]),
     "k44b_wave_forward_static": (c_int, [c_void_p, c_uint64, c_uint32, c_void_p, c_void_p, c_uint32, c_void_p, c_uint32, c_uint32, c_uint32,

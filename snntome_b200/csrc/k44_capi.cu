@@ -454,6 +454,30 @@ int k44b_plan_set_peers_raw(void *plan, int rank, int world, void *const *canvas
     return P(plan)->exec.set_peers_raw(rank, world, canvas_ptrs, sync_ptrs) ? 0 : set_error(P(plan)->exec.err);
 }
 
+int k44b_plan_num_launches(void *plan) {
+    if (!plan) return set_error("plan_num_launches: bad arguments");
+    return (int)P(plan)->exec.num_launches();
+}
+
+int k44b_plan_launch_hulls(void *plan, uint64_t *out, uint64_t capacity) {
+    if (!plan || !out) return set_error("plan_launch_hulls: bad arguments");
+    return P(plan)->exec.launch_hulls(out, (size_t)capacity) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_plan_set_peer_hulls(void *plan, int world, const uint64_t *hulls, uint64_t launches) {
+    if (!plan || !hulls) return set_error("plan_set_peer_hulls: bad arguments");
+    return P(plan)->exec.set_peer_hulls(world, hulls, (size_t)launches) ? 0 : set_error(P(plan)->exec.err);
+}
+
+void k44b_compute_peer_slack(const uint64_t *hulls, int world, uint64_t launches, uint32_t *out_slack) {
+    if (hulls && out_slack && world > 0) k44b::compute_peer_slack(hulls, world, (size_t)launches, out_slack);
+}
+
+int k44b_plan_peer_latency(void *plan, int peer_rank, int initiator, uint32_t iters, uint32_t payload_bytes, float *out_ns_per_round_trip, void *stream) {
+    if (!plan) return set_error("plan_peer_latency: bad arguments");
+    return P(plan)->exec.peer_latency(peer_rank, initiator != 0, iters, payload_bytes, out_ns_per_round_trip, (cudaStream_t)stream) ? 0 : set_error(P(plan)->exec.err);
+}
+
 void *k44b_plan_sync_ptr(void *plan) {
     if (!plan) { set_error("plan_sync_ptr: bad arguments"); return nullptr; }
     void *p = P(plan)->exec.sync_ptr();

@@ -47,25 +47,33 @@ __device__ __forceinline__ void peer_signal_done(const PeerArgs *p, uint32_t cta
         p->sync[kSyncDone] = 0u;
         const uint32_t epoch = p->sync[kSyncEpoch] + 1u;
         p->sync[kSyncEpoch] = epoch;
+        // one system-scope fence orders everything this launch stored (the other CTAs' stores through their own fences and
+        // the counter) before the count words below; the words themselves can then be plain system-scope stores that go out
+        // back to back instead of each waiting for the one before it
         __threadfence_system();
         const uint32_t n = p->n_peers;
-        for (uint32_t q = 0; q < n; ++q) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p->arrive[q]), "r"(epoch) : "memory");
+        for (uint32_t q = 0; q < n; ++q) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p->arrive[q]), "r"(epoch) : "memory");
     }
 }
-// One thread, before the launch reads the canvas: every peer must have finished as many launches as this rank has.
+// One thread, before the launch reads the canvas: every peer must have finished the launches this one depends on — all but
+// the last `slack` of the launches this rank has completed itself (slack 0: every earlier launch; the host raises it for
+// launches that neither read what the peers' latest launches write nor overwrite what they read).
 // Bounded: returns false when a peer does not show up within `limit` cycles.
-__device__ __forceinline__ bool peer_wait_ready(const PeerArgs *p, unsigned long long limit) {
-    const uint32_t need = *reinterpret_cast<volatile uint32_t *>(p->sync + kSyncEpoch);
+__device__ __forceinline__ bool peer_wait_ready(const PeerArgs *p, unsigned long long limit, uint32_t slack) {
+    const uint32_t need = *reinterpret_cast<volatile uint32_t *>(p->sync + kSyncEpoch) - slack;
     const uint32_t n = p->n_peers;
     const long long t0 = clock64();
-    for (uint32_t q = 0; q < n; ++q) {
-        for (;;) {
+    for (;;) {
+        bool all = true;
+        for (uint32_t q = 0; q < n; ++q) {
             uint32_t v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p->sync + q) : "memory");
-            if ((int32_t)(v - need) >= 0) break;
-            if ((unsigned long long)(clock64() - t0) > limit) return false;
+            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p->sync + q) : "memory");
+            all = all && (int32_t)(v - need) >= 0;
         }
+        if (all) break;
+        if ((unsigned long long)(clock64() - t0) > limit) return false;
     }
+    __threadfence_system();        // acquire side: the peers' rows stored before their count words are visible from here on
     return true;
 }
 
@@ -145,6 +153,62 @@ __device__ __forceinline__ void stage_and_store_t(const WaveArgs &a, const float
         }
     }
     __syncwarp();
+}
+
+// ---- tile store through shared memory and tensor copies --------------------------------------------------------
+// The 128 epilogue threads build a 128-row x 64-column block of the output tile in shared memory (rows of 128 bytes, the
+// 16-byte chunk c of row r at chunk position c ^ (r & 7): the 128-byte swizzle, so that the eight rows a quarter-warp
+// writes at once fall into distinct banks) and one thread hands the block to the copy engine: one tensor copy into this
+// rank's canvas and, in a neuron-sharded plan, one per peer canvas (WaveArgs::out_maps). The tensor maps describe exactly
+// the wave's output rows ([cout][pitch] from y_off), so rows of a partial last tile are clipped by the copy itself.
+// This function converts the 32 values (one neuron, 32 columns = half a block) a thread holds and parks them in the block.
+template <int ACT, bool RES>
+__device__ __forceinline__ void stage_half_block_t(const WaveArgs &a, const float (&v)[32], float bias, bool live, uint32_t j,
+                                                   uint64_t col0, uint32_t block_smem, uint32_t r, uint32_t half) {
+    uint32_t pk[16];
+    if (RES) {
+        const uint4 *rsrc = reinterpret_cast<const uint4 *>(a.canvas + a.res_off + (uint64_t)j * a.pitch + col0);
+        uint4 rv[4];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) rv[q4] = live ? rsrc[q4] : make_uint4(0, 0, 0, 0);
+        const __half2 *rh = reinterpret_cast<const __half2 *>(rv);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const float2 rr = __half22float2(rh[e]);
+            const __half2 h2 = __floats2half2_rn(act_fast<ACT>(v[2 * e] + bias) + rr.x, act_fast<ACT>(v[2 * e + 1] + bias) + rr.y);
+            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const __half2 h2 = __floats2half2_rn(act_fast<ACT>(v[2 * e] + bias), act_fast<ACT>(v[2 * e + 1] + bias));
+            pk[e] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+    }
+    const uint32_t row_addr = block_smem + r * 128u;
+#pragma unroll
+    for (uint32_t q4 = 0; q4 < 4u; ++q4)
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((half * 4u + q4) ^ (r & 7u)) << 4)), "r"(pk[4 * q4]),
+                     "r"(pk[4 * q4 + 1]), "r"(pk[4 * q4 + 2]), "r"(pk[4 * q4 + 3])
+                     : "memory");
+}
+
+// (no output-row map on this path: the residual is added after the activation)
+__device__ __forceinline__ void stage_half_block(const WaveArgs &a, const float (&v)[32], float bias, bool live, uint32_t j, uint64_t col0,
+                                                 uint32_t block_smem, uint32_t r, uint32_t half) {
+#define K44B_STAGE_CASE(ACT)                                                                                      \
+    if (a.has_residual) stage_half_block_t<ACT, true>(a, v, bias, live, j, col0, block_smem, r, half);            \
+    else stage_half_block_t<ACT, false>(a, v, bias, live, j, col0, block_smem, r, half);                          \
+    break;
+    switch (a.act) {
+    case 1: K44B_STAGE_CASE(1)
+    case 2: K44B_STAGE_CASE(2)
+    case 3: K44B_STAGE_CASE(3)
+    case 4: K44B_STAGE_CASE(4)
+    case 5: K44B_STAGE_CASE(5)
+    default: K44B_STAGE_CASE(0)
+    }
+#undef K44B_STAGE_CASE
 }
 
 template <int ACT>

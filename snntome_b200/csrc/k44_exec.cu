@@ -133,6 +133,26 @@ GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_ele
     return gp;
 }
 
+void compute_peer_slack(const uint64_t *hulls, int world, size_t launches, uint32_t *out_slack) {
+    struct H { uint64_t rlo, rhi, wlo, whi; };
+    std::vector<H> u(launches, H{~0ull, 0, ~0ull, 0});
+    for (int r = 0; r < world; ++r)
+        for (size_t n = 0; n < launches; ++n) {
+            const uint64_t *h = hulls + ((size_t)r * launches + n) * 4u;
+            if (h[0] < h[1]) { u[n].rlo = std::min(u[n].rlo, h[0]); u[n].rhi = std::max(u[n].rhi, h[1]); }
+            if (h[2] < h[3]) { u[n].wlo = std::min(u[n].wlo, h[2]); u[n].whi = std::max(u[n].whi, h[3]); }
+        }
+    auto overlap = [](uint64_t a0, uint64_t a1, uint64_t b0, uint64_t b1) { return a0 < a1 && b0 < b1 && a0 < b1 && b0 < a1; };
+    for (size_t n = 0; n < launches; ++n) {
+        uint32_t slack = 0;
+        for (size_t back = 1; back <= launches; ++back, ++slack) {          // launch n - back, cyclically
+            const H &m = u[(n + launches - back % launches) % launches], &c = u[n];
+            if (overlap(m.wlo, m.whi, c.rlo, c.rhi) || overlap(m.rlo, m.rhi, c.wlo, c.whi) || overlap(m.wlo, m.whi, c.wlo, c.whi)) break;
+        }
+        out_slack[n] = std::min<uint32_t>(slack, launches ? (uint32_t)launches - 1u : 0u);
+    }
+}
+
 // tcgen05 shared-memory operand descriptors (64-bit): start address >> 4 in bits 0-13, leading-dimension
 // byte offset >> 4 in bits 16-29, stride-dimension byte offset >> 4 in bits 32-45, descriptor version 1 in
 // bits 46-47, layout type in bits 61-63 (2 = 128-byte swizzle).
@@ -176,7 +196,7 @@ bool Executor::check(cudaError_t e, const char *what) {
 void Executor::release() {
     if (device_ >= 0) cudaSetDevice(device_);
     for (auto &w : waves_) {
-        cudaFree(w.d_weights); cudaFree(w.d_gather); cudaFree(w.d_bias); cudaFree(w.d_map); cudaFree(w.d_idx_table); cudaFree(w.d_shifts);
+        cudaFree(w.d_weights); cudaFree(w.d_gather); cudaFree(w.d_bias); cudaFree(w.d_map); cudaFree(w.d_idx_table); cudaFree(w.d_shifts); cudaFree(w.d_out_maps);
     }
     waves_.clear();
     drop_graph();
@@ -230,7 +250,9 @@ bool Executor::begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t
     return true;
 }
 
-bool Executor::make_tensor_map(DeviceWave &dw, uint32_t box_cols, bool swizzle128) {
+// Tensor map over `rows` rows of `pitch_` FP16 elements starting at `base` (a device address valid on this GPU: the own
+// canvas or a peer's mapping), boxes of box_cols x box_rows.
+bool Executor::encode_map(CUtensorMap *map, void *base, uint64_t rows, uint32_t box_cols, uint32_t box_rows, bool swizzle128) {
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -242,13 +264,32 @@ bool Executor::make_tensor_map(DeviceWave &dw, uint32_t box_cols, bool swizzle12
             return fail("cuTensorMapEncodeTiled is not available from the driver");
         encode = (EncodeFn)fn;
     }
-    const cuuint64_t dims[2] = {pitch_, canvas_elems_ / pitch_};
+    const cuuint64_t dims[2] = {pitch_, rows};
     const cuuint64_t strides[1] = {(cuuint64_t)pitch_ * 2u};
-    const cuuint32_t box[2] = {box_cols, dw.args.box_h};
+    const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1u, 1u};
-    const CUresult r = encode(&dw.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, canvas_, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                               swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return true;
+}
+
+bool Executor::make_tensor_map(DeviceWave &dw, uint32_t box_cols, bool swizzle128) {
+    return encode_map(&dw.tmap, canvas_, canvas_elems_ / pitch_, box_cols, dw.args.box_h, swizzle128);
+}
+
+// Output tensor maps of a wave on the streaming tcgen05 kernel: entry 0 covers the wave's rows in this rank's canvas,
+// entries 1.. the same rows in the peers' canvases (`peer_canvases`, n of them; may be null).
+bool Executor::upload_out_maps(DeviceWave &dw, void *const *peer_canvases, uint32_t n) {
+    std::vector<CUtensorMap> maps(1u + n);
+    const uint32_t box_rows = std::min<uint32_t>(kTileM, dw.args.cout);
+    if (!encode_map(&maps[0], canvas_ + dw.args.y_off, dw.args.cout, 64u, box_rows, true)) return false;
+    for (uint32_t q = 0; q < n; ++q)
+        if (!encode_map(&maps[1u + q], (__half *)peer_canvases[q] + dw.args.y_off, dw.args.cout, 64u, box_rows, true)) return false;
+    if (!dw.d_out_maps && !check(cudaMalloc(&dw.d_out_maps, (1u + kMaxPeers) * sizeof(CUtensorMap)), "output tensor map allocation")) return false;
+    if (!check(cudaMemcpy(dw.d_out_maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice), "output tensor map upload")) return false;
+    dw.args.out_maps = (const CUtensorMap *)dw.d_out_maps;
+    dw.args.n_out_maps = 1u + n;
     return true;
 }
 
@@ -547,10 +588,14 @@ bool Executor::add_wave(const HostWave &w) {
             dw.desc.small_wave = small ? 1u : 0u;
             if (a.k_splits > 1 && !cluster) ok = reserve_scratch((size_t)mtiles * tiles64);
             ok = ok && make_tensor_map(dw, 64u, true);
+            // streaming waves without an output-row map write their tiles with tensor copies out of shared memory
+            bool tile_copies = !small && w.cout_map.empty();
+            if (const char *e = std::getenv("K44B_TILE_COPIES")) tile_copies = tile_copies && std::atoi(e) != 0;
+            if (ok && tile_copies) ok = upload_out_maps(dw, nullptr, 0);
         }
     }
     if (!ok) {
-        cudaFree(dw.d_weights); cudaFree(dw.d_gather); cudaFree(dw.d_bias); cudaFree(dw.d_map); cudaFree(dw.d_shifts);
+        cudaFree(dw.d_weights); cudaFree(dw.d_gather); cudaFree(dw.d_bias); cudaFree(dw.d_map); cudaFree(dw.d_shifts); cudaFree(dw.d_out_maps);
         return false;
     }
     // canvas intervals for the scheduler's independence test
@@ -582,11 +627,12 @@ bool Executor::add_wave(const HostWave &w) {
                 }
         }
         if (clash) {
-            cudaFree(dw.d_weights); cudaFree(dw.d_gather); cudaFree(dw.d_bias); cudaFree(dw.d_map); cudaFree(dw.d_shifts);
+            cudaFree(dw.d_weights); cudaFree(dw.d_gather); cudaFree(dw.d_bias); cudaFree(dw.d_map); cudaFree(dw.d_shifts); cudaFree(dw.d_out_maps);
             return fail("wave '" + w.name + "' gathers rows that it writes (a wave cannot run in place)");
         }
     }
     dw.groupable = dw.path == PATH_UMMA && dw.use_cluster && w.cout_map.empty();
+    peer_slack_.clear();
     waves_.push_back(dw);
     drop_graph();
     groups_valid_ = false;
@@ -683,19 +729,61 @@ void Executor::build_groups() {
         }
         g.args.total_clusters = first;
     }
+    for (size_t gi = 0; gi < groups_.size(); ++gi) {
+        const uint32_t sl = peer_slack_.size() == groups_.size() ? peer_slack_[gi] : 0u;
+        groups_[gi].peer_slack = sl;
+        for (uint32_t k = 0; k < groups_[gi].args.count; ++k) groups_[gi].args.w[k].peer_slack = sl;
+    }
     groups_valid_ = true;
+}
+
+size_t Executor::num_launches() {
+    if (!groups_valid_) build_groups();
+    return groups_.size();
+}
+
+bool Executor::launch_hulls(uint64_t *out, size_t capacity) {
+    if (!ready()) return fail("executor not initialised");
+    if (!groups_valid_) build_groups();
+    if (capacity < groups_.size()) return fail("launch_hulls: buffer too small");
+    for (size_t gi = 0; gi < groups_.size(); ++gi) {
+        uint64_t h[4] = {~0ull, 0, ~0ull, 0};
+        for (size_t k : groups_[gi].waves) {
+            const DeviceWave &w = waves_[k];
+            if (w.read_lo < w.read_hi) { h[0] = std::min(h[0], w.read_lo); h[1] = std::max(h[1], w.read_hi); }
+            if (w.write_lo < w.write_hi) { h[2] = std::min(h[2], w.write_lo); h[3] = std::max(h[3], w.write_hi); }
+        }
+        if (h[0] > h[1]) h[0] = h[1] = 0;
+        if (h[2] > h[3]) h[2] = h[3] = 0;
+        std::memcpy(out + gi * 4u, h, sizeof h);
+    }
+    return true;
+}
+
+bool Executor::set_peer_hulls(int world, const uint64_t *hulls, size_t launches) {
+    if (!ready()) return fail("executor not initialised");
+    if (!d_peers_) return fail("set_peer_hulls: the peers have not been set");
+    if (!groups_valid_) build_groups();
+    if (world != peer_world_) return fail("set_peer_hulls: world size differs from set_peers");
+    if (launches != groups_.size()) return fail("set_peer_hulls: the table has " + std::to_string(launches) + " launches per rank, this plan has " + std::to_string(groups_.size()));
+    peer_slack_.assign(launches, 0u);
+    compute_peer_slack(hulls, world, launches, peer_slack_.data());
+    groups_valid_ = false;       // rebuilt with the new values at the next execution
+    drop_graph();
+    return true;
 }
 
 bool Executor::launch_group(size_t gi, cudaStream_t stream) {
     LaunchGroup &g = groups_[gi];
     DeviceWave &w0 = waves_[g.waves[0]];
-    if (g.waves.size() == 1 && !w0.use_cluster) return launch_one(w0, stream);
+    if (g.waves.size() == 1 && !w0.use_cluster) return launch_one(w0, stream, g.peer_slack);
     ++launches_;
     return check(launch_wave_umma_cluster(g.args, w0.desc, w0.tmap, pdl_, num_sms_, stream), ("launch of wave group starting at '" + w0.name + "'").c_str());
 }
 
-bool Executor::launch_one(DeviceWave &w, cudaStream_t stream) {
+bool Executor::launch_one(DeviceWave &w, cudaStream_t stream, uint32_t peer_slack) {
     cudaError_t e;
+    w.args.peer_slack = peer_slack;
     if (w.is_aux) {
         launches_ += (w.aux.kind == AUX_ROPE_ATTN || w.aux.kind == AUX_DECODE_ATTN) ? 3u : (w.aux.kind == AUX_ARGMAX ? 2u : 1u);
         return check(launch_aux(w.aux, pdl_, stream), ("launch of '" + w.name + "'").c_str());
@@ -862,9 +950,37 @@ bool Executor::set_peers_raw(int rank, int world, void *const *canvas_ptrs, void
     }
     if (!d_peers_ && !check(cudaMalloc(&d_peers_, sizeof(PeerArgs)), "peer table allocation")) return false;
     if (!check(cudaMemcpy(d_peers_, &pa, sizeof(PeerArgs), cudaMemcpyHostToDevice), "peer table upload")) return false;
-    for (auto &w : waves_) w.args.peers = d_peers_;
+    std::vector<void *> peer_canvases;
+    for (int r = 0; r < world; ++r)
+        if (r != rank) peer_canvases.push_back(canvas_ptrs[r]);
+    for (auto &w : waves_) {
+        w.args.peers = d_peers_;
+        if (w.d_out_maps && !upload_out_maps(w, peer_canvases.data(), (uint32_t)peer_canvases.size())) return false;
+    }
+    peer_rank_ = rank; peer_world_ = world;
+    peer_canvas_.assign(canvas_ptrs, canvas_ptrs + world);
+    peer_sync_.assign(sync_ptrs, sync_ptrs + world);
+    peer_canvas_[rank] = nullptr; peer_sync_[rank] = nullptr;
     groups_valid_ = false;
     drop_graph();
+    return true;
+}
+
+bool Executor::peer_latency(int peer_rank, bool initiator, uint32_t iters, uint32_t payload_bytes, float *ns, cudaStream_t stream) {
+    if (!ready() || !d_peers_) return fail("peer_latency: the peers have not been set");
+    if (peer_rank < 0 || peer_rank >= peer_world_ || peer_rank == peer_rank_ || !peer_sync_[peer_rank]) return fail("peer_latency: bad peer rank");
+    if (iters == 0 || iters > 1000000u || payload_bytes % 16u || (uint64_t)payload_bytes > canvas_elems_ * 2u) return fail("peer_latency: bad iteration count or payload size");
+    if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
+    unsigned long long *d_out = reinterpret_cast<unsigned long long *>(d_sync_ + 12);       // words 12..15 of the own sync block
+    const cudaError_t e = launch_peer_pingpong(d_sync_ + kSyncProbe, (uint32_t *)peer_sync_[peer_rank] + kSyncProbe, peer_canvas_[peer_rank], payload_bytes,
+                                               initiator, iters, probe_base_, make_umma_desc(64, 0).wait_cycles, d_out, stream);
+    if (!check(e, "latency probe launch")) return false;
+    ++launches_;
+    probe_base_ += iters;
+    unsigned long long h[2] = {0, 0};
+    if (!check(cudaMemcpyAsync(h, d_out, sizeof h, cudaMemcpyDeviceToHost, stream), "latency probe result") || !check(cudaStreamSynchronize(stream), "latency probe")) return false;
+    if (h[1] != iters) return fail("peer_latency: timed out waiting for the peer after " + std::to_string(h[1]) + " round trips");
+    if (ns) *ns = (float)((double)h[0] / (double)iters);
     return true;
 }
 

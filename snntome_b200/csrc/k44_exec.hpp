@@ -24,6 +24,14 @@ struct GatherPlan {
     std::string why_not;                 // reason the tensor-core path cannot be used
 };
 
+// Launch ordering of neuron-sharded plans. `hulls` holds, for every rank and every launch of a step, the canvas element
+// intervals the launch may read and write: [world][launches][4] = {read_lo, read_hi, write_lo, write_hi} (half-open).
+// A launch must wait until every peer has completed the nearest earlier launch (of the same step or, cyclically, of the
+// step before) whose rows it reads, whose reads it overwrites or whose rows it overwrites, on any rank; the launches after
+// that one may still be running on the peers. out_slack[n] = how many of the launches just before launch n need not be
+// waited for (0 = wait for all of them). Pure host arithmetic.
+void compute_peer_slack(const uint64_t *hulls, int world, size_t launches, uint32_t *out_slack);
+
 // Pure host analysis (unit-testable without a device).
 GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_elems);
 bool validate_wave(const HostWave &w, uint32_t pitch, uint32_t num_tiles, uint64_t canvas_elems, std::string &err);
@@ -42,6 +50,7 @@ struct DeviceWave {
     bool umma_capable = false;
     std::string fma_reason;
     void *d_weights = nullptr, *d_gather = nullptr, *d_bias = nullptr, *d_map = nullptr, *d_shifts = nullptr;
+    void *d_out_maps = nullptr;          // output tensor maps (own canvas + peers) of a streaming tcgen05 wave
     uint32_t *d_idx_table = nullptr;     // expanded table kept for the FMA path when boxes are used too
     uint64_t synapses = 0;               // logical_cout * fan_in_raw
     uint64_t read_lo = 0, read_hi = 0;   // canvas element interval this wave may read (gathers and residual)
@@ -80,6 +89,15 @@ class Executor {
     bool set_peers_ipc(int rank, int world, const void *canvas_handles, const void *sync_handles);   // world x 64 bytes each, indexed by rank
     bool set_peers_raw(int rank, int world, void *const *canvas_ptrs, void *const *sync_ptrs);       // device pointers valid on this GPU, indexed by rank
     void *sync_ptr();
+    // Signalling round trip with one peer (both ranks call this with the same iters / payload, one of them as initiator):
+    // `iters` times a payload of payload_bytes (a multiple of 16, written to the start of the peer's canvas; 0 = none), a
+    // system-scope fence and a count word, answered the same way. Synchronises `stream`; returns nanoseconds per round trip.
+    bool peer_latency(int peer_rank, bool initiator, uint32_t iters, uint32_t payload_bytes, float *ns_per_round_trip, cudaStream_t stream);
+    // launches per step (waves that share a launch count once) and their read / write intervals, [launches][4] as above
+    size_t num_launches();
+    bool launch_hulls(uint64_t *out, size_t capacity);
+    // the same table from every rank, [world][launches][4]: lets launches skip the wait for peers' launches they do not depend on
+    bool set_peer_hulls(int world, const uint64_t *hulls, size_t launches);
     bool weights_to_rowmajor(size_t wave, void *d_dst);            // unpack check: tiled -> [cout][fan_in]
 
     bool ready() const { return canvas_ != nullptr; }
@@ -95,13 +113,16 @@ class Executor {
     bool fail(const std::string &m) { err = m; return false; }
     bool check(cudaError_t e, const char *what);
     bool make_tensor_map(DeviceWave &dw, uint32_t box_cols, bool swizzle128);
+    bool encode_map(CUtensorMap *map, void *base, uint64_t rows, uint32_t box_cols, uint32_t box_rows, bool swizzle128);
+    bool upload_out_maps(DeviceWave &dw, void *const *peer_canvases, uint32_t n);
     bool reserve_scratch(size_t tiles);
     void recover_after_abort();
-    bool launch_one(DeviceWave &w, cudaStream_t stream);
+    bool launch_one(DeviceWave &w, cudaStream_t stream, uint32_t peer_slack = 0);
     void drop_graph();
     void build_groups();
     bool launch_group(size_t gi, cudaStream_t stream);
-    struct LaunchGroup { std::vector<size_t> waves; WaveGroupArgs args; };
+    struct LaunchGroup { std::vector<size_t> waves; WaveGroupArgs args; uint32_t peer_slack = 0; };
+    std::vector<uint32_t> peer_slack_;   // per launch of a step; empty: every launch waits for all earlier ones
     std::vector<LaunchGroup> groups_;
     bool groups_valid_ = false;
 
@@ -128,6 +149,9 @@ class Executor {
     uint32_t *d_sync_ = nullptr;          // kSyncWords words, allocated on first use
     PeerArgs *d_peers_ = nullptr;
     std::vector<void *> ipc_opened_;      // peer mappings to close on release
+    int peer_rank_ = 0, peer_world_ = 1;
+    std::vector<void *> peer_canvas_, peer_sync_;   // indexed by rank (own entries null)
+    uint32_t probe_base_ = 0;
     size_t scratch_tiles_ = 0;
     cudaGraphExec_t graph_exec_ = nullptr;
     bool pdl_ = true;                    // programmatic dependent launch between consecutive small waves

@@ -131,8 +131,13 @@ struct UmmaCfg {
     static constexpr int kStages = STAGES_SEL == 1 ? 4 : ((N_TILE == 64) ? 8 : (N_TILE == 128 ? 6 : 4));
     static constexpr int kCtasPerSm = STAGES_SEL == 1 ? 2 : 1;
     static constexpr uint32_t kTmemCols = 2u * N_TILE;
-    static constexpr uint32_t kOutStageBytes = 128u * 80u;                           // epilogue staging: 128 rows x (64 + 16 pad) bytes
-    static constexpr uint32_t kSmemBytes = 1024u /*alignment slack*/ + (uint32_t)kStages * kStageBytes + 256u + kOutStageBytes;
+    // epilogue staging. One CTA per SM: two blocks of 128 rows x 128 bytes (one 64-column block of the output tile each, handed
+    // to the copy engine in turn; the per-warp staging of the register-store path lives in the same space). Two CTAs per SM:
+    // 128 rows x (64 + 16 pad) bytes for the register-store path only.
+    static constexpr bool kTmaOut = STAGES_SEL == 0;
+    static constexpr uint32_t kOutBlockBytes = 128u * 128u;
+    static constexpr uint32_t kOutStageBytes = kTmaOut ? 2u * kOutBlockBytes : 128u * 80u;
+    static constexpr uint32_t kSmemBytes = 1024u /*alignment slack*/ + (uint32_t)kStages * kStageBytes + kOutStageBytes + 256u;
 };
 
 
@@ -150,7 +155,8 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t w_smem = smem_base;
     const uint32_t x_smem = smem_base + (uint32_t)STAGES * kStageWBytes;
-    const uint32_t ctl = x_smem + (uint32_t)STAGES * Cfg::kXBytes;
+    const uint32_t out_smem = x_smem + (uint32_t)STAGES * Cfg::kXBytes;      // 1024-byte aligned (all stage sizes are multiples of 1024)
+    const uint32_t ctl = out_smem + Cfg::kOutStageBytes;
     const uint32_t full_bar = ctl, empty_bar = ctl + 8u * STAGES;
     const uint32_t tfull_bar = ctl + 16u * STAGES, tempty_bar = tfull_bar + 16u;
     uint8_t *ctl_ptr = smem_raw + (ctl - ptx::smem_addr(smem_raw));
@@ -158,7 +164,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
     volatile uint32_t *abort_word = tmem_slot + 1;
     volatile uint32_t *last_flag = tmem_slot + 2;
     volatile uint32_t *epi_ok = tmem_slot + 4;       // two slots, alternating per item
-    uint8_t *out_stage = ctl_ptr + 256;              // 128 rows x 80 bytes, one 32-row block per epilogue warp
+    uint8_t *out_stage = smem_raw + (out_smem - ptx::smem_addr(smem_raw));   // register-store path: 128 rows x 80 bytes, one 32-row block per epilogue warp
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t tiles_n = a.num_col_tiles64 / Cfg::kColBlocks;
@@ -217,7 +223,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         if (a.peers) {                       // neuron-sharded plan: the peers' rows of the previous launches must have arrived
             uint32_t okp = 1u;
             if (lane == 0) {
-                okp = peer_wait_ready(a.peers, d.wait_cycles) ? 1u : 0u;
+                okp = peer_wait_ready(a.peers, d.wait_cycles, a.peer_slack) ? 1u : 0u;
                 asm volatile("fence.proxy.async.global;" ::: "memory");   // rows written by peers' plain stores -> this thread's tensor copies
                 if (!okp) { atomicOr(a.status, (uint32_t)ST_TIMEOUT_PEER); *abort_word = 1u; }
             }
@@ -314,6 +320,8 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         // ---------------- epilogue ----------------
         const uint32_t quarter = warp & 3u;                  // TMEM lanes this warp may read
         const bool has_map = a.cout_map != nullptr;
+        const bool tma_out = a.out_maps != nullptr && !has_map && splits == 1u;
+        uint32_t blocks_out = 0;                             // 64-column blocks handed to the copy engine so far
         uint32_t iter = 0;
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++iter) {
@@ -332,7 +340,37 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
             const uint32_t oj = (live && has_map) ? a.cout_map[j] : j;
             const float bias = (live && a.bias) ? __half2float(a.bias[j]) : 0.0f;
             const uint64_t o = (uint64_t)oj * a.pitch + (uint64_t)ct * N_TILE;
-            if (splits == 1u) {
+            if (Cfg::kTmaOut && tma_out) {
+                // per 64-column block: wait until the copy that last read this staging block is done with it, convert and park
+                // the block, hand it to the copy engine (own canvas and peers)
+#pragma unroll 1
+                for (uint32_t cb = 0; cb < (uint32_t)Cfg::kColBlocks; ++cb, ++blocks_out) {
+                    const uint32_t block_smem = out_smem + (blocks_out & 1u) * Cfg::kOutBlockBytes;
+                    if (threadIdx.x == 64u) ptx::bulk_wait_group_read<1>();
+                    epilogue_bar_sync();
+#pragma unroll 1
+                    for (uint32_t half = 0; half < 2u; ++half) {
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * N_TILE + cb * 64u + half * 32u, v);
+                        ptx::tmem_ld_wait();
+                        float f[32];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
+                        stage_half_block(a, f, bias, live, j, (uint64_t)ct * N_TILE + cb * 64u + half * 32u, block_smem, r_in_tile, half);
+                    }
+                    if (cb + 1u == (uint32_t)Cfg::kColBlocks) {      // accumulator read out: the next item's MMAs may start
+                        ptx::tc_fence_before();
+                        ptx::mbar_arrive(tempty_bar + 8u * acc);
+                    }
+                    ptx::fence_proxy_async();                        // this thread's shared-memory stores -> visible to the copy engine
+                    epilogue_bar_sync();
+                    if (threadIdx.x == 64u) {
+                        const int32_t x = (int32_t)(ct * (uint32_t)N_TILE + cb * 64u), y = (int32_t)(mt * kTileM);
+                        for (uint32_t m = 0; m < a.n_out_maps; ++m) ptx::tma_store_2d(a.out_maps + m, x, y, block_smem);
+                        ptx::bulk_commit_group();
+                    }
+                }
+            } else if (splits == 1u) {
 #pragma unroll 1
                 for (uint32_t c0 = 0; c0 < (uint32_t)N_TILE; c0 += 32u) {
                     uint32_t v[32];
@@ -385,6 +423,10 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         if (!ok && lane == 0) {
             if (*abort_word == 0u) atomicOr(a.status, (uint32_t)ST_TIMEOUT_EPILOGUE);
             *abort_word = 1u;
+        }
+        if (Cfg::kTmaOut && tma_out && threadIdx.x == 64u) {
+            ptx::bulk_wait_group<0>();       // the tile copies have been written (and no longer read this CTA's shared memory)
+            ptx::fence_proxy_async_global(); // ... and are ordered before this thread's generic-proxy fence and counter below
         }
         if (a.peers) {                       // this CTA's rows are stored here and on every peer: count it as done
             epilogue_bar_sync();             // the storing threads' writes are ordered before the one fence below (cumulativity)
@@ -643,7 +685,7 @@ k44_wave_umma_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const __g
         if (a.peers) {                       // ... and, in a neuron-sharded plan, rows the peers stored into this canvas
             uint32_t okp = 1u;
             if (lane == 0) {
-                okp = peer_wait_ready(a.peers, d.wait_cycles) ? 1u : 0u;
+                okp = peer_wait_ready(a.peers, d.wait_cycles, a.peer_slack) ? 1u : 0u;
                 if (!okp) { atomicOr(a.status, (uint32_t)ST_TIMEOUT_PEER); *abort_word = 1u; }
             }
             ok = __shfl_sync(0xffffffffu, okp, 0) != 0u;

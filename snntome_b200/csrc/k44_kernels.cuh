@@ -55,7 +55,7 @@ struct PeerArgs {
     uint32_t *sync = nullptr;             // own sync block: [0..6] the peers' launch counts, [8] CTAs done in the running launch, [9] launches completed
     uint32_t n_peers = 0;
 };
-constexpr uint32_t kSyncWords = 16, kSyncDone = 8, kSyncEpoch = 9;
+constexpr uint32_t kSyncWords = 16, kSyncDone = 8, kSyncEpoch = 9, kSyncProbe = 10;   // [10] the latency probe's counter word, [12..13] its result
 
 struct WaveArgs {
     // tensors
@@ -86,6 +86,12 @@ struct WaveArgs {
     float *scratch = nullptr;             // [tiles][N_TILE][128] FP32, all zero between launches
     uint32_t *counters = nullptr;         // [tiles], all zero between launches
     const PeerArgs *peers = nullptr;      // device memory; null unless the plan is neuron-sharded over several GPUs
+    uint32_t peer_slack = 0;              // sharded plans: how many of the peers' latest launches this launch need not wait for
+    // Output through tensor copies (streaming tcgen05 kernel, waves without an output-row map): device array of tensor maps
+    // over the wave's output rows, [cout][pitch] FP16 from y_off, boxes of 64 columns x 128 rows, 128-byte swizzle;
+    // [0] = this rank's canvas, [1 .. n_out_maps-1] = the same rows in the peers' canvases. Null: stores from registers.
+    const CUtensorMap *out_maps = nullptr;
+    uint32_t n_out_maps = 0;
 };
 
 // Element-wise / attention steps between waves (k44_valu.cu)
@@ -146,6 +152,10 @@ cudaError_t launch_wave_umma_cluster(const WaveGroupArgs &g, const UmmaDesc &d, 
 cudaError_t launch_wave_umma_shift(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
 cudaError_t mma_kernel_setup();        // same for the mma.sync kernel
 cudaError_t umma_kernel_setup();       // opt in to large dynamic shared memory (once per device)
+
+// signalling round trip between two sharded ranks (k44_peer.cu); d_out: [0] nanoseconds, [1] completed round trips
+cudaError_t launch_peer_pingpong(uint32_t *own_word, uint32_t *peer_word, void *peer_payload, uint32_t payload_bytes, bool initiator, uint32_t iters,
+                                 uint32_t base, unsigned long long wait_cycles, unsigned long long *d_out, cudaStream_t s);
 
 // packer kernels
 cudaError_t launch_repack_wmma_to_tiled(const uint4 *src_wmma, uint4 *dst, uint32_t cout, uint32_t fan_in, cudaStream_t s);

@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
         __shared__ uint32_t peer_ok;
         if (tid == 0) {
             uint32_t ok = (*reinterpret_cast<volatile uint32_t *>(a.status) & (uint32_t)ST_TIMEOUT_PEER) ? 0u : 1u;
-            if (ok) ok = peer_wait_ready(a.peers, wait_cycles) ? 1u : 0u;
+            if (ok) ok = peer_wait_ready(a.peers, wait_cycles, a.peer_slack) ? 1u : 0u;
             if (!ok) atomicOr(a.status, (uint32_t)ST_TIMEOUT_PEER);
             peer_ok = ok;
         }
@@ -239,34 +239,46 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
     cp_async_wait<0>();
     if (bad) atomicOr(a.status, (uint32_t)ST_BAD_INDEX);
 
-    // epilogue: accumulator (m, n): rows lane/4 and lane/4 + 8 of the 16-row block, columns (lane%4)*2 + {0,1} of the 8-column block
+    // epilogue: accumulator (m, n): rows lane/4 and lane/4 + 8 of the 16-row block, columns (lane%4)*2 + {0,1} of the 8-column
+    // block. The finished values are parked in shared memory (the gather ring is free by now) and leave as whole 16-byte
+    // pieces, 128 contiguous bytes per row — to this canvas and, in a sharded plan, to every peer's.
     const bool has_map = a.cout_map != nullptr;
+    __syncthreads();                        // every warp is done reading the last stage
+    __half *const tile_out = reinterpret_cast<__half *>(xs_gen);       // [MT * 16][kPitch]
 #pragma unroll
     for (int m = 0; m < (int)MW; ++m)
 #pragma unroll
         for (int hrow = 0; hrow < 2; ++hrow) {
-            const uint32_t j = j0 + (wr * MW + (uint32_t)m) * 16u + (lane >> 2) + (uint32_t)hrow * 8u;
+            const uint32_t rl = (wr * MW + (uint32_t)m) * 16u + (lane >> 2) + (uint32_t)hrow * 8u;
+            const uint32_t j = j0 + rl;
             if (j >= a.cout) continue;
             const uint32_t oj = has_map ? a.cout_map[j] : j;
             const float b = a.bias ? __half2float(a.bias[j]) : 0.0f;
 #pragma unroll
             for (int n = 0; n < (int)NW; ++n) {
-                const uint64_t o = (uint64_t)oj * a.pitch + (uint64_t)tile * 64u + wc * (NW * 8u) + (uint32_t)n * 8u + (lane & 3u) * 2u;
+                const uint32_t col = wc * (NW * 8u) + (uint32_t)n * 8u + (lane & 3u) * 2u;
                 float r0 = 0.f, r1 = 0.f;
                 if (a.has_residual) {
-                    const float2 rr = __half22float2(*reinterpret_cast<const __half2 *>(a.canvas + a.res_off + o));
+                    const float2 rr = __half22float2(*reinterpret_cast<const __half2 *>(a.canvas + a.res_off + (uint64_t)oj * a.pitch + (uint64_t)tile * 64u + col));
                     r0 = rr.x; r1 = rr.y;
                 }
                 const float v0 = finish_value(acc[m][n][hrow * 2 + 0], b, r0, a.act, a.has_residual != 0, has_map);
                 const float v1 = finish_value(acc[m][n][hrow * 2 + 1], b, r1, a.act, a.has_residual != 0, has_map);
-                const __half2 out = __floats2half2_rn(v0, v1);
-                *reinterpret_cast<__half2 *>(a.canvas + a.y_off + o) = out;
-                if (a.peers) {
-                    const uint32_t n = a.peers->n_peers;
-                    for (uint32_t q = 0; q < n; ++q) *reinterpret_cast<__half2 *>(a.peers->canvas[q] + a.y_off + o) = out;
-                }
+                *reinterpret_cast<__half2 *>(tile_out + rl * kPitch + col) = __floats2half2_rn(v0, v1);
             }
         }
+    __syncthreads();
+#pragma unroll
+    for (uint32_t p = tid; p < MT * 16u * 8u; p += 128u) {
+        const uint32_t rl = p >> 3, pc = p & 7u;
+        const uint32_t j = j0 + rl;
+        if (j >= a.cout) continue;
+        const uint32_t oj = has_map ? a.cout_map[j] : j;
+        const uint64_t off = a.y_off + (uint64_t)oj * a.pitch + (uint64_t)tile * 64u + pc * 8u;
+        const uint4 val = *reinterpret_cast<const uint4 *>(tile_out + rl * kPitch + pc * 8u);
+        *reinterpret_cast<uint4 *>(a.canvas + off) = val;
+        if (a.peers) store_to_peers(a.peers, off, val);
+    }
     }   // peers_ready
     if (a.peers) {
         __syncthreads();                    // orders every thread's peer stores before thread 0's system-scope fence

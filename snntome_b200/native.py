@@ -254,6 +254,32 @@ class NativePlan:
         if self._lib.k44b_plan_set_peers_raw(self._ptr, int(rank), int(world), arr(*canvas_ptrs), arr(*sync_ptrs)) != 0:
             raise NativeError(f"set_peers_raw: {last_error()}")
 
+    def peer_latency(self, peer_rank: int, initiator: bool, iters: int = 1000, payload_bytes: int = 0, stream=None) -> float:
+        """Nanoseconds per signalling round trip with `peer_rank` (see k44b_plan_peer_latency); both ranks must call it."""
+        ns = ctypes.c_float(0.0)
+        if self._lib.k44b_plan_peer_latency(self._ptr, int(peer_rank), int(bool(initiator)), int(iters), int(payload_bytes), ctypes.byref(ns),
+                                            ctypes.c_void_p(self._stream_ptr(stream))) != 0:
+            raise NativeError(f"peer_latency: {last_error()}")
+        return float(ns.value)
+
+    def launch_hulls(self) -> np.ndarray:
+        """uint64 [launches, 4]: per launch of a step, the canvas intervals {read_lo, read_hi, write_lo, write_hi} it may touch."""
+        n = self._lib.k44b_plan_num_launches(self._ptr)
+        if n < 0:
+            raise NativeError(f"num_launches: {last_error()}")
+        out = np.zeros((n, 4), dtype=np.uint64)
+        if n and self._lib.k44b_plan_launch_hulls(self._ptr, out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint64)), n) != 0:
+            raise NativeError(f"launch_hulls: {last_error()}")
+        return out
+
+    def set_peer_hulls(self, hulls: np.ndarray) -> None:
+        """`hulls`: uint64 [world, launches, 4], the `launch_hulls()` tables of all ranks, indexed by rank."""
+        h = np.ascontiguousarray(hulls, dtype=np.uint64)
+        if h.ndim != 3 or h.shape[2] != 4:
+            raise NativeError("set_peer_hulls: expected an array of shape [world, launches, 4]")
+        if self._lib.k44b_plan_set_peer_hulls(self._ptr, int(h.shape[0]), h.ctypes.data_as(ctypes.POINTER(ctypes.c_uint64)), int(h.shape[1])) != 0:
+            raise NativeError(f"set_peer_hulls: {last_error()}")
+
     @property
     def canvas_ptr(self) -> int:
         return int(self._lib.k44b_canvas_ptr(self._ptr))
@@ -296,6 +322,15 @@ class NativePlan:
         if self._lib.k44b_wave_weights_rowmajor(self._ptr, wave, ctypes.c_void_p(t.data_ptr())) != 0:
             raise NativeError(f"weights_rowmajor: {last_error()}")
         return t
+
+
+def compute_peer_slack(hulls: np.ndarray) -> np.ndarray:
+    """Host-only: per launch, how many of the launches just before it a sharded rank need not wait for (see k44b.h)."""
+    h = np.ascontiguousarray(hulls, dtype=np.uint64)
+    out = np.zeros(h.shape[1], dtype=np.uint32)
+    get_lib().k44b_compute_peer_slack(h.ctypes.data_as(ctypes.POINTER(ctypes.c_uint64)), int(h.shape[0]), int(h.shape[1]),
+                                      out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)))
+    return out
 
 
 def fill_normal_f16(tensor, seed: int, scale: float) -> None:

@@ -105,13 +105,25 @@ class NeuronShardedRunner:
             self.exchange(i)
 
 
-def connect_peers(native_plan, rank: int, world: int) -> None:
+def connect_peers(native_plan, rank: int, world: int):
     """Exchange the CUDA IPC handles of every rank's canvas and sync block over the default process group and hand
     them to the library: from then on the wave kernels store their rows into all canvases and order their launches
-    against the peers' themselves, so a step needs no collective call (and can be one CUDA graph)."""
+    against the peers' themselves, so a step needs no collective call (and can be one CUDA graph). Returns, per launch of a
+    step, how many of the launches just before it the launch need not wait for on the peers (None if the ranks' plans
+    do not have the same number of launches, in which case every launch waits for all earlier ones)."""
     import torch.distributed as dist
     mine = native_plan.ipc_handles()
     everyone = [None] * world
     dist.all_gather_object(everyone, mine)
     native_plan.set_peers_ipc(rank, world, [h[0] for h in everyone], [h[1] for h in everyone])
+    # order launches by the rows they touch: every rank learns which canvas intervals each launch of every rank reads and
+    # writes, so that a launch waits only for the peers' launches it really depends on
+    hulls = [None] * world
+    dist.all_gather_object(hulls, native_plan.launch_hulls())
+    slack = None
+    if len({h.shape for h in hulls}) == 1:
+        from .native import compute_peer_slack
+        native_plan.set_peer_hulls(np.stack(hulls))
+        slack = compute_peer_slack(np.stack(hulls))
     dist.barrier()          # every rank has its mappings before anybody launches
+    return slack

@@ -243,3 +243,25 @@ def test_more_than_65535_neuron_blocks_of_a_small_group(path_name):
         a = (rows_in + g * group) * pitch
         ok, err, k = O.compare(got[a:a + group * pitch], want, RTOL, ATOL)
         assert ok, (g, err, k)
+
+
+def test_pruned_8b_chain_full_size_sampled_groups():
+    """BASELINE configs[4] on one GPU at its full size (Llama-3-8B shapes, 32 layers, 90 % of the 32-row input clusters of every
+    128-neuron group removed, dense lm_head, 256 columns): the chain is walked wave by wave and sampled groups of sampled
+    waves — with and without residual, SiLU, the dense lm_head — are recomputed by the oracle from the device's own inputs."""
+    import torch
+    import bench
+    import pruned_check
+    from snntome_b200.native import fill_normal_f16
+    layers = int(os.environ.get("K44B_TEST_LAYERS", "32"))
+    plan, info = bench.build_pruned_plan(layers, 0, 0, 1)
+    canvas = plan.canvas_tensor()
+    fill_normal_f16(canvas[: info["cfg"]["hidden"] * info["pitch"]], 4242, 1.0)
+    picks = set(pruned_check.sampled_waves(plan.num_waves))
+    for wi in range(plan.num_waves):
+        plan.execute_wave(wi)
+        if wi in picks:
+            assert plan.status() == 0
+            pruned_check.check_wave(plan, info, wi, canvas)
+    assert plan.status() == 0
+    plan.close()

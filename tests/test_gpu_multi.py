@@ -113,3 +113,70 @@ def test_two_gpu_peer_stores_match_oracle(tmp_path, group):
             ok, err, k = O.compare(got[a:b], want[a:b], 2e-3, 1e-3)
             assert ok, (r, w.name, err, k)
     assert np.array_equal(np.load(tmp_path / "fused0.npy"), np.load(tmp_path / "fused1.npy"))
+
+
+def _worker_pruned(rank, world, port, out_dir, layers):
+    import sys
+    import torch
+    import torch.distributed as dist
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path[:0] = [here, os.path.dirname(here)]
+    os.environ["K44B_WAIT_MS"] = "500"               # if a rank stops, its peer's launches give up quickly instead of after 2 s each
+    import bench
+    import pruned_check
+    from snntome_b200.native import fill_normal_f16
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        plan, info = bench.build_pruned_plan(layers, rank, rank, world)
+        canvas = plan.canvas_tensor()
+        fill_normal_f16(canvas[: info["cfg"]["hidden"] * info["pitch"]], 4242, 1.0)
+        torch.cuda.synchronize()
+        shard.connect_peers(plan, rank, world)
+        picks = set(pruned_check.sampled_waves(plan.num_waves))
+        worst = 0.0
+        for wi in range(plan.num_waves):
+            plan.execute_wave(wi)
+            if wi in picks:                          # both ranks stop at the same waves
+                st = plan.status_code()
+                assert st == 0, f"rank {rank}: kernel status {st:#x} at wave {wi}"
+                worst = max(worst, pruned_check.check_wave(plan, info, wi, canvas, seed=rank))
+                dist.barrier()
+        # then whole steps as one graph (grouped launches, region-ordered waits): every replica of the canvas must end up identical
+        for _ in range(3):
+            plan.execute_graph()
+        torch.cuda.synchronize()
+        st = plan.status_code()
+        dist.barrier()
+        assert st == 0, f"rank {rank}: kernel status {st:#x} after the graph steps"
+        lo = info["rows"]["logits"] * info["pitch"]
+        logits = canvas[lo: lo + info["vocab_rows"] * info["pitch"]]
+        digest = torch.stack([logits.view(torch.int16).to(torch.int64).sum(), logits.float().abs().sum().to(torch.int64)])
+        both = [torch.zeros_like(digest) for _ in range(world)]
+        dist.all_gather(both, digest)
+        assert all(torch.equal(b, both[0]) for b in both), f"replicas of the logits differ: {both}"
+        assert bool(torch.isfinite(logits.float()).all())
+        with open(os.path.join(out_dir, f"pruned{rank}.txt"), "w") as f:
+            f.write(f"{worst}\n")
+        dist.barrier()
+        plan.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_pruned_8b_chain_sampled_groups_and_identical_replicas(tmp_path):
+    """BASELINE configs[4], neuron-sharded over two GPUs with the wave kernels exchanging the rows themselves: sampled groups of
+    sampled waves against the oracle on every rank (each rank checks rows it computed, from inputs that include rows its peer
+    stored), then three steps as one CUDA graph with grouped launches, after which the logits of both replicas must be equal
+    bit for bit."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    layers = int(os.environ.get("K44B_TEST_LAYERS", "32"))
+    mp.spawn(_worker_pruned, args=(2, _free_port(), str(tmp_path), layers), nprocs=2, join=True)
+    for r in range(2):
+        assert float((tmp_path / f"pruned{r}.txt").read_text()) < 0.1

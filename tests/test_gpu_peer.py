@@ -52,6 +52,23 @@ def test_streaming_waves_store_to_every_canvas(world):
         assert np.array_equal(got[r], got[0])
 
 
+def test_streaming_waves_send_their_tiles_with_tensor_copies():
+    """More 128-neuron tiles per rank than SMs: the persistent streaming kernel, whose epilogue hands each 128 x 64 output block
+    to the copy engine once per canvas (own and peers'). 160 tiles per rank, a partial last column block of valid columns, a
+    residual on the second wave."""
+    plan = synth.sparse_plan(seed=191, input_rows=2048, waves=2, cout=2 * 80 * 128, runs=4, run_len=32, columns=100, group=128, act=ACT_SILU)
+    plan.waves[1].has_residual, plan.waves[1].res_off = True, plan.waves[0].y_off
+    x = synth.random_input(plan, 192)
+    want = O.run_plan(plan, x)
+    got = run_sharded_on_one_gpu(plan, x, 2)
+    for r in range(2):
+        for w in plan.waves:
+            a, b = w.y_off, w.y_off + w.cout * plan.pitch
+            ok, err, k = O.compare(got[r][a:b], want[a:b], RTOL, ATOL)
+            assert ok, (r, w.name, err, k)
+    assert np.array_equal(got[0], got[1])
+
+
 def test_small_waves_with_residual_store_to_every_canvas():
     """Dense chain at decode size: every wave runs on the cluster kernel (K splits reduced through distributed shared
     memory); the second wave adds a residual that a peer produced."""

@@ -80,3 +80,47 @@ def test_column_slice_covers_all_columns_once():
             assert c0 % granule == 0
             seen[c0:c1] += 1
         assert (seen == 1).all()
+
+
+def _slack_reference(hulls):
+    """The ordering rule restated: union the intervals over the ranks; launch n may skip waiting for the launches just before
+    it until it meets one (cyclically, the step before included) whose writes meet its reads, whose reads meet its writes, or
+    whose writes meet its writes."""
+    world, L, _ = hulls.shape
+    u = []
+    for n in range(L):
+        r = [(int(h[n, 0]), int(h[n, 1])) for h in hulls if h[n, 0] < h[n, 1]]
+        w = [(int(h[n, 2]), int(h[n, 3])) for h in hulls if h[n, 2] < h[n, 3]]
+        u.append(((min(a for a, _ in r), max(b for _, b in r)) if r else None, (min(a for a, _ in w), max(b for _, b in w)) if w else None))
+    meet = lambda a, b: a is not None and b is not None and a[0] < b[1] and b[0] < a[1]
+    out = []
+    for n in range(L):
+        s = 0
+        for back in range(1, L + 1):
+            m = u[(n - back) % L]
+            if meet(m[1], u[n][0]) or meet(m[0], u[n][1]) or meet(m[1], u[n][1]):
+                break
+            s += 1
+        out.append(min(s, L - 1))
+    return np.array(out, dtype=np.uint32)
+
+
+def test_launch_ordering_rule_matches_its_restatement_and_a_decoder_layer_by_hand():
+    from snntome_b200.native import compute_peer_slack
+    rng = np.random.default_rng(17)
+    for _ in range(200):
+        world, L = int(rng.integers(1, 5)), int(rng.integers(1, 12))
+        lo = rng.integers(0, 50, size=(world, L, 2)) * 64
+        ln = rng.integers(0, 6, size=(world, L, 2)) * 64              # empty intervals occur
+        hulls = np.stack([lo[..., 0], lo[..., 0] + ln[..., 0], lo[..., 1], lo[..., 1] + ln[..., 1]], axis=-1).astype(np.uint64)
+        assert np.array_equal(compute_peer_slack(hulls), _slack_reference(hulls))
+    # one decoder layer, tensors x, q|k|v, h, g, u, y as disjoint row ranges: launches qkv, o, gate, up, down
+    T = {name: (i * 1000, i * 1000 + 1000) for i, name in enumerate(["x", "qkv", "h", "g", "u", "y"])}
+    span = lambda *names: (min(T[n][0] for n in names), max(T[n][1] for n in names))
+    launches = [(span("x"), span("qkv")), (span("x", "qkv"), span("h")), (span("h"), span("g")), (span("h"), span("u")), (span("h", "g"), span("y"))]
+    hulls = np.array([[[r[0], r[1], w[0], w[1]] for r, w in launches]] * 2, dtype=np.uint64)
+    slack = compute_peer_slack(hulls)
+    assert slack[1] == 0 and slack[2] == 0          # o reads q, gate reads h: each waits for the launch just before it
+    assert slack[3] == 1                            # up reads h (written two launches earlier) and touches nothing of gate's
+    assert slack[4] == 1                            # down reads g and h: gate wrote g two launches back; up only read h and wrote u
+    assert slack[0] == 3                            # qkv overwrites q|k|v, which o (four launches back, cyclically) reads
