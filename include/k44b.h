@@ -46,12 +46,14 @@ typedef struct k44b_wave_desc {
 } k44b_wave_desc;
 
 typedef struct k44b_wave_info_t {
-    uint32_t cout, group, fan_in, box_rows;   /* box_rows: rows fetched per TMA box, 0 on the index path */
+    uint32_t cout, group, fan_in, box_rows;   /* box_rows: canvas rows per gather-table entry (8..64: tensor boxes; 1: single rows), 0 on the index path */
     int32_t path;                             /* 0 FP32-FMA kernel, 1 tcgen05 kernels, 2 element-wise / attention command, 3 general kernel on mma.sync */
     uint32_t n_tile;                          /* columns per tile on the tcgen05 path */
     uint32_t k_splits;                        /* K splits per tile (partial sums meet in FP32 scratch) */
     uint64_t synapses;                        /* logical_cout * fan_in_raw */
     uint64_t weight_bytes;                    /* packed size on the device */
+    uint32_t m_blocks;                        /* 128-neuron blocks per tile on the streaming tcgen05 kernel (2: tiles of 256 neurons) */
+    uint32_t cta_pairs;                       /* 1: those two blocks sit on a pair of CTAs (M = 256 MMAs) */
 } k44b_wave_info_t;
 
 /* Create an empty plan bound to `device`: allocates and zeroes the canvas (canvas_elems FP16, rows of
@@ -203,8 +205,10 @@ uint64_t k44b_fnv1a64(const uint8_t *data, uint64_t len);
 void k44b_f32_to_f16(const float *src, uint16_t *dst, uint64_t n);
 void k44b_rowmajor_to_wmma(const uint16_t *src, uint16_t *dst, uint32_t cout, uint32_t fan_in);
 void k44b_wmma_to_rowmajor(const uint16_t *src, uint16_t *dst, uint32_t cout, uint32_t fan_in);
-/* Host-only gather analysis: returns rows per box (8/16/32/64) when the tcgen05 path applies, 0 when
- * it does not; out_box_rows (optional, capacity in entries) receives the run table. */
+/* Host-only gather analysis: returns the rows per table entry — 8/16/32/64 when the gather lists are runs of whole boxes
+ * (fetched as tensor boxes), 1 when they are scattered single rows (one entry per synapse, fetched row by row) — or 0 when
+ * the offsets are not whole rows (element-granular shifts: general kernels, index table); out_box_rows (optional, capacity
+ * in entries) receives the table, padded per group to whole 64-synapse stages. */
 int k44b_analyze_gather(const k44b_wave_desc *wave, uint32_t pitch, uint64_t canvas_elems, uint32_t *out_box_rows,
                         uint64_t capacity, uint64_t *out_count);
 

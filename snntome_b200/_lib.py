@@ -27,6 +27,7 @@ class WaveInfo(ctypes.Structure):
     _fields_ = [
         ("cout", c_uint32), ("group", c_uint32), ("fan_in", c_uint32), ("box_rows", c_uint32),
         ("path", c_int32), ("n_tile", c_uint32), ("k_splits", c_uint32), ("synapses", c_uint64), ("weight_bytes", c_uint64),
+        ("m_blocks", c_uint32), ("cta_pairs", c_uint32),
     ]
 
 

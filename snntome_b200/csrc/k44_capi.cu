@@ -403,6 +403,8 @@ int k44b_wave_info(void *plan, int wave, k44b_wave_info_t *out) {
     out->path = w.path; out->n_tile = w.path == PATH_UMMA ? w.desc.n_tile : 64;
     out->k_splits = w.path == PATH_UMMA ? w.args.k_splits : 1;
     out->synapses = w.synapses; out->weight_bytes = w.weight_bytes;
+    out->m_blocks = (w.path == PATH_UMMA && !w.use_cluster && !w.use_shift) ? (w.desc.pair ? 2u : w.desc.m_blocks) : 1u;
+    out->cta_pairs = (w.path == PATH_UMMA && !w.use_cluster && !w.use_shift) ? w.desc.pair : 0u;
     return 0;
 }
 

@@ -115,7 +115,12 @@ GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_ele
             while (h >= 8 && r.len % h) h >>= 1;
     const uint32_t tail = (kStageK - w.fan_in % kStageK) % kStageK;
     while (h >= 8 && tail % h) h >>= 1;
-    if (h < 8) { gp.why_not = "runs are not made of whole 8-row blocks"; return gp; }
+    if (h < 8) {
+        // scattered rows (the reference's own benchmark tables: one sorted random row per synapse): one table entry per
+        // synapse; the streaming tcgen05 kernel fetches them row by row, the general kernels read the same table
+        if (gp.max_shift > 0) { gp.why_not = "shifted runs must be made of whole 8-row blocks"; return gp; }
+        h = 1;
+    }
     if (gp.max_shift > 0 && h < 16 && !gp.small_group) { gp.why_not = "shifted runs must be made of whole 16-row blocks"; return gp; }
     if (gp.max_shift > 8) { gp.why_not = "token shifts above 8 columns"; return gp; }
     if (total_rows > kBoxRowMask) { gp.why_not = "canvas has more than 2^28 rows"; return gp; }
@@ -177,6 +182,7 @@ UmmaDesc make_umma_desc(uint32_t n_tile, int variant) {
     // (bit 16 = 1), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
     d.idesc = (1u << 4) | (1u << 16) | ((n_tile >> 3) << 17) | ((kTileM >> 4) << 24);
     d.wait_cycles = 4000000000ull;     // about two seconds at boost clock
+    if (const char *e = std::getenv("K44B_ROWS_MODE")) { const int m = std::atoi(e); if (m == 1 || m == 2) d.rows_mode = (uint32_t)m; }
     if (const char *e = std::getenv("K44B_WAIT_MS")) {     // bound of every in-kernel wait, in milliseconds at ~2 GHz
         const long ms = std::atol(e);
         if (ms > 0 && ms <= 60000) d.wait_cycles = (unsigned long long)ms * 2000000ull;
@@ -533,6 +539,12 @@ bool Executor::add_wave(const HostWave &w) {
             if (!allow) { dw.umma_capable = false; dw.fma_reason = flen % 64u ? "token-shifted runs with frames that are not whole column tiles" : "token-shifted runs"; }
             else dw.use_shift = true;
         }
+        // scattered single rows are fetched by the streaming tcgen05 kernel only; a wave with fewer tiles than SMs (which would
+        // take the small-wave kernel) stays on the warp-level tensor path
+        if (dw.umma_capable && gp.box_h == 1u && (uint64_t)mtiles * tiles64 < (uint64_t)num_sms_) {
+            dw.umma_capable = false;
+            dw.fma_reason = "scattered rows in a wave with fewer 128-neuron tiles than SMs";
+        }
         // waves the tcgen05 kernels cannot take run on the warp-level tensor path; the FP32-FMA kernel only when asked for
         dw.path = force_path_ == 0 ? PATH_FMA : (dw.umma_capable ? PATH_UMMA : PATH_MMA);
         if (const char *e = std::getenv("K44B_GENERAL_MMA")) if (dw.path == PATH_MMA && std::atoi(e) == 0) dw.path = PATH_FMA;
@@ -563,6 +575,7 @@ bool Executor::add_wave(const HostWave &w) {
             uint32_t splits = 1;
             bool small = (uint64_t)mtiles * (tiles64 / (n_tile / 64u)) < (uint64_t)num_sms_;
             if (const char *e = std::getenv("K44B_SMALL_WAVE")) small = std::atoi(e) != 0;
+            if (gp.box_h == 1u) small = false;
             bool cluster = false;
             if (small) {
                 n_tile = 64;
@@ -592,6 +605,38 @@ bool Executor::add_wave(const HostWave &w) {
             bool tile_copies = !small && w.cout_map.empty();
             if (const char *e = std::getenv("K44B_TILE_COPIES")) tile_copies = tile_copies && std::atoi(e) != 0;
             if (ok && tile_copies) ok = upload_out_maps(dw, nullptr, 0);
+            // Tensor-bound waves (256-column tiles) whose neuron groups span an even number of 128-neuron blocks run tiles of
+            // 256 neurons: two blocks share one gathered operand, which halves the operand bytes each flop pulls through L2.
+            // Needs enough such tiles to fill the GPU and the tile-copy epilogue.
+            {
+                bool two = ok && tile_copies && n_tile == 256u && a.k_splits == 1u && (a.mtiles_per_group % 2u) == 0u &&
+                      (uint64_t)((mtiles + 1u) / 2u) * (tiles64 / 4u) >= (uint64_t)num_sms_ && !(gp.box_h == 1u && dw.desc.rows_mode == 2u);
+                // preferred for such waves: the two blocks on a pair of CTAs (M = 256 MMAs), see k44_pair_kernel.cu
+                bool pair = two && (mtiles % 2u) == 0u && 2u * (kStageK / std::max(gp.box_h, 1u)) <= 32u;
+                if (const char *e = std::getenv("K44B_PAIR")) pair = pair && std::atoi(e) != 0; else pair = false;
+                if (const char *e = std::getenv("K44B_M_BLOCKS")) two = two && std::atoi(e) == 2; else two = false;   // two blocks on one CTA: measured no gain, on request only
+                if (pair) {
+                    two = false;
+                    dw.desc.pair = 1u;
+                    dw.desc.idesc = (1u << 4) | (1u << 16) | ((256u >> 3) << 17) | ((256u >> 4) << 24);   // M = 256, N = 256
+                    // the packed weights as a 2-D tensor: rows of 128 bytes (64 halves), one 128-row box = one 16 KiB block
+                    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+                    void *fn = nullptr;
+                    cudaDriverEntryPointQueryResult q;
+                    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) ok = fail("cuTensorMapEncodeTiled is not available from the driver");
+                    if (ok) {
+                        const cuuint64_t dims[2] = {64u, (cuuint64_t)mtiles * a.num_kstages * kTileM};
+                        const cuuint64_t strides[1] = {128u};
+                        const cuuint32_t box[2] = {64u, kTileM};
+                        const cuuint32_t estr[2] = {1u, 1u};
+                        const CUresult r = ((EncodeFn)fn)(&dw.wmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dw.d_weights, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        if (r != CUDA_SUCCESS) ok = fail("cuTensorMapEncodeTiled (weights) failed with code " + std::to_string((int)r));
+                    }
+                }
+                dw.desc.m_blocks = two ? 2u : 1u;
+            }
         }
     }
     if (!ok) {
@@ -796,10 +841,14 @@ bool Executor::launch_one(DeviceWave &w, cudaStream_t stream, uint32_t peer_slac
         e = launch_wave_umma_cluster(g, w.desc, w.tmap, pdl_, num_sms_, stream);
     } else if (w.path == PATH_UMMA && w.use_shift) {
         e = launch_wave_umma_shift(w.args, w.desc, w.tmap, num_sms_, stream);
+    } else if (w.path == PATH_UMMA && w.desc.pair && !w.args.peers) {
+        e = launch_wave_umma_pair(w.args, w.desc, w.tmap, w.wmap, num_sms_, stream);
     } else if (w.path == PATH_UMMA) {
         w.args.scratch = d_scratch_;
         w.args.counters = d_counters_;
-        e = launch_wave_umma(w.args, w.desc, w.tmap, num_sms_, stream);
+        UmmaDesc dd = w.desc;
+        if (dd.pair) { dd.pair = 0; dd.idesc = make_umma_desc(dd.n_tile, 0).idesc; }     // sharded plans: the one-CTA kernel
+        e = launch_wave_umma(w.args, dd, w.tmap, num_sms_, stream);
     } else if (w.path == PATH_MMA) {
         e = launch_wave_mma(w.args, make_umma_desc(64, 0).wait_cycles, stream);
     } else {

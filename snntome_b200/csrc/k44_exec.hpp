@@ -44,6 +44,7 @@ struct DeviceWave {
     WaveArgs args;
     UmmaDesc desc;
     CUtensorMap tmap;
+    CUtensorMap wmap;                    // CTA-pair kernel: the packed weights as rows of 128 bytes
     int path = PATH_FMA;
     bool use_cluster = false;            // small wave: K splits form a cluster and reduce through shared memory
     bool use_shift = false;              // token-shifted runs: tensor-core kernel with aligner warps

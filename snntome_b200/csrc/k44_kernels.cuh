@@ -139,11 +139,23 @@ struct UmmaDesc {
     uint32_t n_tile = 64;
     uint32_t small_wave = 0;              // 1: 4-stage, two-CTAs-per-SM variant (N_TILE 64 only)
     unsigned long long wait_cycles = 0;   // bound for every barrier wait
+    uint32_t rows_mode = 1;               // scattered single rows: 1 asynchronous 16-byte copies from four extra warps, 2 gather-mode tensor copies (measured slower)
+    uint32_t pair = 0;                    // 1: the wave runs on CTA pairs (tiles of 256 neurons x 256 columns, M = 256 MMAs)
+    uint32_t m_blocks = 1;                // 128-neuron blocks per tile: 2 = tiles of 256 neurons sharing one gathered operand (256-column tiles only)
 };
 
 cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s);
 cudaError_t launch_wave_mma(const WaveArgs &a, unsigned long long wait_cycles, cudaStream_t s);   // general path on mma.sync (k44_mma_kernel.cu); wait_cycles bounds the peer wait
 cudaError_t launch_wave_umma(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
+// per tile width (k44_stream_n64.cu, _n128.cu, _n256.cu): launch, and opt-in to large dynamic shared memory
+cudaError_t launch_wave_umma_n64(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
+cudaError_t launch_wave_umma_n128(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
+cudaError_t launch_wave_umma_n256(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
+// tiles of 256 neurons x 256 columns on CTA pairs (k44_pair_kernel.cu); wmap: the packed weights as rows of 128 bytes, boxes of 128 rows
+cudaError_t launch_wave_umma_pair(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, const CUtensorMap &wmap, int num_sms, cudaStream_t s);
+cudaError_t umma_setup_n64();
+cudaError_t umma_setup_n128();
+cudaError_t umma_setup_n256();
 // small waves: one item per CTA, the K splits of a tile form a cluster (k_splits in {1,2,4,8}) and reduce through
 // distributed shared memory; dependent_launch adds the programmatic-dependent-launch attribute
 cudaError_t launch_wave_umma_cluster(const WaveGroupArgs &g, const UmmaDesc &d, const CUtensorMap &tmap, bool dependent_launch, int num_sms, cudaStream_t s);

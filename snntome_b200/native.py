@@ -347,7 +347,7 @@ def analyze_gather(w: Wave, pitch: int, canvas_elems: int):
     """Host-only: returns (rows per box or 0, run table as uint32 array)."""
     lib = get_lib()
     d, keep = wave_desc(w)
-    cap = (w.cout // w.group) * ((w.fan_in + 63) // 64 * 64 // 8)
+    cap = (w.cout // w.group) * ((w.fan_in + 63) // 64 * 64)       # at most one entry per synapse (scattered rows)
     out = np.zeros(cap, dtype=np.uint32)
     cnt = ctypes.c_uint64(0)
     h = lib.k44b_analyze_gather(ctypes.byref(d), int(pitch), int(canvas_elems), out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)),

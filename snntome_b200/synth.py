@@ -78,6 +78,30 @@ def sparse_plan(*, seed: int, input_rows: int, waves: int, cout: int, runs: int,
                 output_c=cout, waves=ws, name=name)
 
 
+def scattered_rows_plan(*, seed: int, input_rows: int, waves: int, cout: int, fan_in: int, columns: int, group: int = 128,
+                        act: int = ACT_RELU, bias_scale: float = 0.01, chained: bool = True) -> Plan:
+    """The reference benchmark's kind of gather table (whitepaper/sparse_wmma_kernel/tests/benchmark_common.cuh:81-111): every
+    neuron group draws `fan_in` single rows uniformly (with replacement) and sorts them — no runs. With `chained` a wave
+    may also draw rows of the waves before it (so that the waves depend on each other); otherwise all waves read the input
+    rows only, like the benchmark's independent waves over one substrate."""
+    pitch = (columns + 63) // 64 * 64
+    assert fan_in % 32 == 0 and fan_in >= 64 and cout % group == 0 and cout % 16 == 0
+    rng = np.random.default_rng(seed)
+    ws = []
+    for w in range(waves):
+        rows_avail = input_rows + (w * cout if chained else 0)
+        groups = cout // group
+        rows = uniform_int(seed, 3000 + w, np.arange(groups * fan_in, dtype=np.uint64), rows_avail).astype(np.int64).reshape(groups, fan_in)
+        rows.sort(axis=1)
+        wt = f16_bits(rng.normal(0.0, (1.0 / fan_in) ** 0.5, size=(cout, fan_in)))
+        bias = f16_bits(bias_scale * rng.normal(0.0, 1.0, size=cout)) if bias_scale else None
+        ws.append(Wave(cout=cout, group=group, fan_in=fan_in, idx=(rows * pitch).astype(np.uint32), weights=wt, bias=bias,
+                       y_off=(input_rows + w * cout) * pitch, act=act, cin=rows_avail, src_off=0, name=f"scattered{w}", w_out=columns))
+    total_rows = input_rows + waves * cout
+    return Plan(canvas_elems=total_rows * pitch, pitch=pitch, columns=columns, input_off=0, input_c=input_rows,
+                output_off=(input_rows + (waves - 1) * cout) * pitch, output_c=cout, waves=ws, name="scattered_rows")
+
+
 def config0(seed: int = 1234, group: int = 128) -> Plan:
     """Tiny connectome: 4096 input rows, 2 waves x 1024 neurons, fan-in 256 = 16 runs of 16 rows,
     ReLU, 32 columns."""

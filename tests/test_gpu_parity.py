@@ -440,3 +440,73 @@ def test_general_tensor_path_with_row_map_residual_and_partial_block():
         w.fan_in_raw = w.fan_in                            # the zero-weight padding slots moved with the roll
     x = synth.random_input(plan, 52, dist="normal")
     check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_MMA), O.run_plan(plan, x))
+
+
+@pytest.mark.parametrize("rows_mode", [2, 1])
+@pytest.mark.parametrize("columns,n_tile,cout", [(64, 64, 160 * 128), (256, 128, 80 * 128), (200, 256, 160 * 128), (512, 256, 75 * 128 + 64)])
+def test_scattered_single_rows_on_the_streaming_tensor_kernel(columns, n_tile, cout, rows_mode, monkeypatch):
+    """Gather tables the way the reference's benchmark draws them — one sorted random row per synapse, no runs — on waves with
+    more 128-neuron tiles than SMs: the streaming tcgen05 kernel fetches the rows itself, four per gather-mode tensor copy
+    (mode 2, the default) or one by one with row-fetching warps (mode 1). Tile widths 64 / 128 / 256, a partial last neuron
+    tile, valid columns that do not fill the last tile, a second wave that gathers rows the first one wrote; the FP32-FMA
+    kernel reads the same table as the cross-check."""
+    monkeypatch.setenv("K44B_N_TILE", str(n_tile))
+    monkeypatch.setenv("K44B_ROWS_MODE", str(rows_mode))
+    plan = synth.scattered_rows_plan(seed=500 + n_tile + columns, input_rows=3000, waves=2, cout=cout, fan_in=160, columns=columns, group=cout if cout % 128 else 128,
+                                     act=ACT_SILU)
+    x = synth.random_input(plan, 501, dist="normal")
+    want = O.run_plan(plan, x)
+    import torch
+    npn = NativePlan.from_plan(plan, device=0, force_path=PATH_AUTO)
+    for i in range(npn.num_waves):
+        info = npn.wave_info(i)
+        assert info.path == PATH_UMMA and info.box_rows == 1 and info.n_tile == n_tile, (info.path, info.box_rows, info.n_tile)
+    canvas = npn.canvas_tensor()
+    canvas[plan.input_off: plan.input_off + x.size] = torch.from_numpy(np.ascontiguousarray(x).view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    npn.execute()
+    assert npn.status() == 0
+    check(plan, canvas.cpu().numpy().view(np.uint16), want)
+    npn.close()
+    check(plan, run_gpu(plan, x, PATH_FMA, expect_path=PATH_FMA), want)
+
+
+def test_scattered_rows_in_a_small_wave_stay_on_the_general_tensor_path():
+    plan = synth.scattered_rows_plan(seed=601, input_rows=2000, waves=2, cout=1024, fan_in=128, columns=128, group=128)
+    x = synth.random_input(plan, 602)
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_MMA), O.run_plan(plan, x))
+
+
+@pytest.mark.parametrize("mode", ["cta_pairs", "one_cta"])
+@pytest.mark.parametrize("case", ["runs_groups_of_256", "scattered_rows_groups_of_512", "one_group_partial_last_block"])
+def test_tiles_of_256_neurons_share_one_operand(case, mode, monkeypatch):
+    """Waves with 256-column tiles whose neuron groups span an even number of 128-neuron blocks, with enough tiles to fill the
+    GPU, run tiles of 256 neurons: two blocks with their own weights and accumulators on one gathered operand — by default on a
+    pair of CTAs (M = 256 MMAs, each CTA staging half of the operand's columns), on request on one CTA. Run-structured and
+    scattered-row gathers, bias, residual, GELU, a partial last 128-neuron block, a second wave reading the first."""
+    import torch
+    if mode == "one_cta":
+        monkeypatch.setenv("K44B_PAIR", "0")
+        monkeypatch.setenv("K44B_M_BLOCKS", "2")
+    else:
+        monkeypatch.setenv("K44B_PAIR", "1")
+    if case == "runs_groups_of_256":
+        plan = synth.sparse_plan(seed=701, input_rows=4096, waves=2, cout=2 * 128 * 74, runs=4, run_len=32, columns=512, group=256, act=ACT_GELU)
+        plan.waves[1].has_residual, plan.waves[1].res_off = True, plan.waves[0].y_off
+    elif case == "scattered_rows_groups_of_512":
+        plan = synth.scattered_rows_plan(seed=702, input_rows=5000, waves=2, cout=512 * 37, fan_in=160, columns=512, group=512, act=ACT_SILU)
+    else:
+        cout = 2 * 128 * 148 - 64
+        plan = synth.sparse_plan(seed=703, input_rows=2048, waves=1, cout=cout, runs=2, run_len=64, columns=200, group=cout, act=ACT_RELU)
+    x = synth.random_input(plan, 704, dist="normal")
+    want = O.run_plan(plan, x)
+    npn = NativePlan.from_plan(plan, device=0)
+    for i in range(npn.num_waves):
+        info = npn.wave_info(i)
+        assert info.path == PATH_UMMA and info.n_tile == 256 and info.m_blocks == 2, (info.path, info.n_tile, info.m_blocks)
+        assert info.cta_pairs == (1 if mode == "cta_pairs" else 0)
+    canvas = npn.canvas_tensor()
+    canvas[plan.input_off: plan.input_off + x.size] = torch.from_numpy(np.ascontiguousarray(x).view(np.int16).reshape(-1)).cuda().view(torch.float16)
+    npn.execute()
+    assert npn.status() == 0
+    check(plan, canvas.cpu().numpy().view(np.uint16), want)
+    npn.close()
