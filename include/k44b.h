@@ -43,7 +43,20 @@ typedef struct k44b_wave_desc {
      * their frame of `frame_len` columns (0 = the whole row) is below the shift read zero. */
     const uint8_t *shifts;
     uint32_t frame_len;
+    /* 2-D image planes (optional; K44ResDesc tile tables, wavec/k44_plan_types.hpp:517-569): with num_tiles != 0 the wave walks
+     * `num_tiles` tiles of 64 consecutive elements of a plane; tile t gathers relative to tile_off_x[t] and stores at
+     * tile_off_y[t] — or, with tile_mask != 0, at 4 * (tile_off_y[t] & 0xffff), writing only the 4-element quads whose bit
+     * 16 + q of tile_off_y[t] is set; output (and residual) rows are `plane_stride` elements apart. `idx` is required (tap
+     * offsets, any alignment); such waves run on the general kernels. */
+    const uint32_t *tile_off_x;
+    const uint32_t *tile_off_y;
+    uint32_t num_tiles;
+    uint32_t tile_mask;
+    uint32_t plane_stride;
 } k44b_wave_desc;
+
+/* geometry of a haloed image plane set: pixel (y, x) of plane c at c * plane_stride + (y + 1) * w_pad + 4 + x */
+typedef struct k44b_plane_geom { uint32_t h, w, w_pad, plane_stride; } k44b_plane_geom;
 
 typedef struct k44b_wave_info_t {
     uint32_t cout, group, fan_in, box_rows;   /* box_rows: canvas rows per gather-table entry (8..64: tensor boxes; 1: single rows), 0 on the index path */
@@ -54,6 +67,8 @@ typedef struct k44b_wave_info_t {
     uint64_t weight_bytes;                    /* packed size on the device */
     uint32_t m_blocks;                        /* 128-neuron blocks per tile on the streaming tcgen05 kernel (2: tiles of 256 neurons) */
     uint32_t cta_pairs;                       /* 1: those two blocks sit on a pair of CTAs (M = 256 MMAs) */
+    uint32_t weights_in_tmem;                 /* token-shift kernel holding a work item's weight tile in tensor memory: column tiles per work item (0: not that kernel) */
+    uint32_t reserved0;
 } k44b_wave_info_t;
 
 /* Create an empty plan bound to `device`: allocates and zeroes the canvas (canvas_elems FP16, rows of
@@ -109,6 +124,13 @@ int k44b_plan_add_decode_attn(void *plan, const char *name, uint64_t q_off, uint
                               uint64_t kcache_off, uint64_t vcache_off, uint32_t h_q, uint32_t h_kv, uint32_t head_dim, uint32_t max_seq,
                               float rope_theta, int llama3_scaling);
 int k44b_plan_set_decode_pos(void *plan, int pos, void *stream);
+/* Weight-free image commands between waves (kernels/common/kernel44_valu_pack.cuh:30-103), on `planes` channel planes from
+ * src_off (geometry `in`) to dst_off (geometry `out`); offsets are canvas elements. op: 7 max-pool 2x2 stride 2, 8 max-pool 5x5
+ * stride 1 pad 2, 9 nearest upsample x2, 10 space-to-depth 2x2 (`planes` input channels -> 4 * planes half-resolution planes
+ * 4c + 2 * row parity + column parity), 11 scatter of the four phase planes q * planes + c of a 2x2 transposed convolution
+ * into `planes` double-resolution planes, 12 halo clear of the destination planes (`in` ignored). */
+int k44b_plan_add_image_op(void *plan, int op, const char *name, uint64_t src_off, uint64_t dst_off, uint32_t planes,
+                           const k44b_plane_geom *in, const k44b_plane_geom *out);
 /* Token I/O on the device (no counterpart in the reference, whose boundary is host F32 tensors): an embedding gather —
  * column b of the destination becomes row tokens[b] of an FP16 table [vocab][dim] that the caller keeps in device memory —
  * and a greedy arg-max over the rows of a tensor per column (lowest row wins ties). With advance != 0 the arg-max also

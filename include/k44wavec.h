@@ -6,8 +6,12 @@
  *   - a GPU runtime error never terminates the process (the reference calls exit(), :54-62): the
  *     call returns -1 and k44b_last_error() (k44b.h) holds the reason;
  *   - 1-D token graphs compile: Input / linear (1x1 convolution) / split / slice / concat / RMSNorm / SwiGLU /
- *     rotary + grouped-query attention; the 2-D image builder calls (flatten, convolutions with a kernel larger
- *     than 1x1, upconv2x2, maxpool, upsample2x) return -1 and leave the graph unchanged;
+ *     rotary + grouped-query attention. 2-D image graphs (one input with h > 1, w a multiple of 4) compile: convolutions
+ *     1x1 (stride 1, pad 0) and 3x3 (pad 1, stride 1 or 2) with bias / activation / residual, split / slice / concat,
+ *     max-pool 2x2 stride 2 and 5x5 stride 1 pad 2, nearest 2x upsampling, 2x2 stride-2 transposed convolution. Planes are
+ *     stored with one halo row above and below and four halo elements left (kernels/common/kernel44_valu_pack.cuh:30-103);
+ *     wavec_gpu_infer_f32 takes and returns dense [c][h][w] FP32 images. A call outside that set (flatten, other kernel
+ *     sizes, mixing the two kinds of graph) returns -1 and leaves the graph unchanged;
  *   - activation value 5 selects GELU in addition to the reference's 0-4. The tensor-core kernels evaluate it
  *     as v / (1 + exp(-v P(v^2))) with a fitted quadratic P, at most 2.6e-5 (absolute) away from the erf form;
  *     the FP32-FMA and mma.sync kernels call erff. Both lie inside the output tolerance (rtol 2e-3, atol 1e-3).
@@ -28,11 +32,12 @@ void wavec_destroy(void *handle);
 /* :669 — frees the GPU state only */
 int wavec_gpu_release(void *handle);
 
-/* :685 — only is_1d inputs (h == 1) are accepted */
+/* :685 — is_1d (h == 1) token inputs, or one image input with h > 1 and w a multiple of 4 */
 int wavec_add_input(void *handle, const char *name, int c, int h, int w, int is_1d);
-/* :694 — not on the 1-D wave path: returns -1 */
+/* :694 — not built (no consumer on the wave path): returns -1 */
 int wavec_add_flatten(void *handle, const char *name, const char *in_tensor, const char *out_tensor);
-/* :704 — accepted for kh == kw == 1, stride 1, pad 0 (a linear); otherwise -1 */
+/* :704 — token graphs: kh == kw == 1, stride 1, pad 0 (a linear). Image graphs: 1x1 / stride 1 / pad 0 and 3x3 / pad 1 /
+ * stride 1 or 2; weights [cout][cin][kh][kw]. Otherwise -1 */
 int wavec_add_conv2d(void *handle, const char *name, const char *in_tensor, const char *out_tensor, int cin, int cout,
                      int kh, int kw, int stride, int pad, int act, const float *w_f32, const float *bias_f32,
                      const char *residual_tensor);
@@ -49,7 +54,8 @@ int wavec_add_linear_f16(void *handle, const char *name, const char *in_tensor, 
 /* :747 — bf16 -> f32 -> f16 */
 int wavec_add_linear_bf16(void *handle, const char *name, const char *in_tensor, const char *out_tensor, int din, int dout,
                           int act, const uint16_t *w_bf16, const float *bias_f32, const char *residual_tensor);
-/* :761, :773, :783 — 2-D image path: return -1 */
+/* :761, :773, :783 — image graphs only. upconv2x2: weights [cout][cin][4] with the output phase 2 * (y & 1) + (x & 1)
+ * innermost; maxpool: (k, stride, pad) = (2, 2, 0) or (5, 1, 2) */
 int wavec_add_upconv2x2(void *handle, const char *name, const char *in_tensor, const char *out_tensor, int cin, int cout,
                         const float *w_f32, const float *bias_f32);
 int wavec_add_maxpool(void *handle, const char *name, const char *in_tensor, const char *out_tensor, int k, int stride, int pad);

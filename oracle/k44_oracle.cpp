@@ -251,6 +251,57 @@ int k44o_wave_forward(uint16_t *canvas, uint64_t canvas_elems, const uint16_t *w
     return 0;
 }
 
+// One wave over 2-D image planes (wavec/k44_plan_types.hpp:517-569, kernels/cuda/kernel44_cuda_pack.cuh:116-124, 190-216):
+// tile t gathers 64 consecutive elements from x_base + tile_off_x[t] + idx[j/G][s] and stores 64 results at
+// y_off + j * plane_stride + tile offset, where the tile offset is tile_off_y[t], or — masked layouts — 4 * (tile_off_y[t] &
+// 0xffff) with only those 4-element quads q written whose bit 16 + q of tile_off_y[t] is set. Residual after the activation
+// (image waves carry no row map). Double accumulation, one rounding. Returns -1 if anything would leave the canvas.
+int k44o_wave_forward_2d(uint16_t *canvas, uint64_t canvas_elems, const uint16_t *w_row_major, const uint32_t *idx, const uint16_t *bias,
+                         uint32_t cout, uint32_t group, uint32_t B, int act, int has_residual, uint64_t y_off, uint64_t res_off,
+                         uint64_t x_base_off, uint32_t plane_stride, const uint32_t *tile_off_x, const uint32_t *tile_off_y, uint32_t num_tiles,
+                         int tile_mask) {
+    uint32_t max_idx = 0;
+    for (uint64_t i = 0; i < (uint64_t)(cout / group) * B; ++i) max_idx = idx[i] > max_idx ? idx[i] : max_idx;
+    auto y_of = [&](uint32_t t) -> uint64_t { return tile_mask ? (uint64_t)(tile_off_y[t] & 0xffffu) << 2 : tile_off_y[t]; };
+    for (uint32_t t = 0; t < num_tiles; ++t) {
+        if (x_base_off + tile_off_x[t] + max_idx + 64 > canvas_elems) return -1;
+        if (y_off + (uint64_t)(cout - 1) * plane_stride + y_of(t) + 64 > canvas_elems) return -1;
+        if (has_residual && res_off + (uint64_t)(cout - 1) * plane_stride + y_of(t) + 64 > canvas_elems) return -1;
+    }
+    std::vector<uint16_t> out((size_t)cout * num_tiles * 64);
+#pragma omp parallel for schedule(dynamic, 4)
+    for (int64_t j = 0; j < (int64_t)cout; ++j) {
+        const uint32_t *irow = idx + (uint64_t)(j / group) * B;
+        const double b = bias ? (double)f16_to_f32(bias[j]) : 0.0;
+        for (uint32_t t = 0; t < num_tiles; ++t) {
+            double acc[64];
+            for (int c = 0; c < 64; ++c) acc[c] = b;
+            const uint16_t *xt = canvas + x_base_off + tile_off_x[t];
+            for (uint32_t s = 0; s < B; ++s) {
+                const double w = (double)f16_to_f32(w_row_major[(uint64_t)j * B + s]);
+                const uint16_t *xr = xt + irow[s];
+                for (int c = 0; c < 64; ++c) acc[c] += w * (double)f16_to_f32(xr[c]);
+            }
+            const uint16_t *rr = has_residual ? canvas + res_off + (uint64_t)j * plane_stride + y_of(t) : nullptr;
+            uint16_t *o = out.data() + ((size_t)j * num_tiles + t) * 64;
+            for (int c = 0; c < 64; ++c) {
+                double v = activate(acc[c], act);
+                if (rr) v += (double)f16_to_f32(rr[c]);
+                o[c] = f64_to_f16_rte(v);
+            }
+        }
+    }
+    for (uint32_t j = 0; j < cout; ++j)
+        for (uint32_t t = 0; t < num_tiles; ++t) {
+            uint16_t *dst = canvas + y_off + (uint64_t)j * plane_stride + y_of(t);
+            const uint16_t *src = out.data() + ((size_t)j * num_tiles + t) * 64;
+            const uint32_t mask = tile_mask ? tile_off_y[t] >> 16 : 0xffffu;
+            for (uint32_t q = 0; q < 16; ++q)
+                if ((mask >> q) & 1u) std::memcpy(dst + 4 * q, src + 4 * q, 8);
+        }
+    return 0;
+}
+
 // Same arithmetic but with FP32 accumulation in 16-synapse chunks followed by the FP16 store —
 // "stage 3" of whitepaper/sparse_wmma_kernel/tests/error_collapse_test.cpp:297-347. Used only for
 // the sanity band on expected GPU-vs-exact error, never as the parity reference.

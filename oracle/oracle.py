@@ -77,6 +77,10 @@ def lib() -> ctypes.CDLL:
             ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32,
             u32p, u32p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, u8p, ctypes.c_uint32]
         L.k44o_wave_forward.restype = ctypes.c_int
+        L.k44o_wave_forward_2d.argtypes = [
+            u16p, ctypes.c_uint64, u16p, u32p, u16p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, ctypes.c_int,
+            ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, u32p, u32p, ctypes.c_uint32, ctypes.c_int]
+        L.k44o_wave_forward_2d.restype = ctypes.c_int
         L.k44o_dot_stage3.argtypes = [u16p, u16p, ctypes.c_uint32, ctypes.c_float, f32p]
         L.k44o_num_threads.restype = ctypes.c_int
         L.k44o_set_num_threads.argtypes = [ctypes.c_int]

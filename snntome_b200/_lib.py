@@ -19,7 +19,13 @@ class WaveDesc(ctypes.Structure):
         ("idx", c_void_p), ("run_rows", c_void_p), ("run_len", c_uint32), ("weights_on_device", c_uint32),
         ("weights", c_void_p), ("bias", c_void_p), ("cout_map", c_void_p), ("name", c_char_p),
         ("shifts", c_void_p), ("frame_len", c_uint32),
+        ("tile_off_x", c_void_p), ("tile_off_y", c_void_p), ("num_tiles", c_uint32), ("tile_mask", c_uint32), ("plane_stride", c_uint32),
     ]
+
+
+class PlaneGeom(ctypes.Structure):
+    """k44b_plane_geom (include/k44b.h)."""
+    _fields_ = [("h", c_uint32), ("w", c_uint32), ("w_pad", c_uint32), ("plane_stride", c_uint32)]
 
 
 class WaveInfo(ctypes.Structure):
@@ -27,7 +33,7 @@ class WaveInfo(ctypes.Structure):
     _fields_ = [
         ("cout", c_uint32), ("group", c_uint32), ("fan_in", c_uint32), ("box_rows", c_uint32),
         ("path", c_int32), ("n_tile", c_uint32), ("k_splits", c_uint32), ("synapses", c_uint64), ("weight_bytes", c_uint64),
-        ("m_blocks", c_uint32), ("cta_pairs", c_uint32),
+        ("m_blocks", c_uint32), ("cta_pairs", c_uint32), ("weights_in_tmem", c_uint32), ("reserved0", c_uint32),
     ]
 
 
@@ -87,6 +93,7 @@ PROTOTYPES = {
     "k44b_plan_add_decode_attn": (c_int, [c_void_p, c_char_p, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_uint32, c_uint32, c_uint32,
                                            c_uint32, c_float, c_int]),
     "k44b_plan_set_decode_pos": (c_int, [c_void_p, c_int, c_void_p]),
+    "k44b_plan_add_image_op": (c_int, [c_void_p, c_int, c_char_p, c_uint64, c_uint64, c_uint32, POINTER(PlaneGeom), POINTER(PlaneGeom)]),
     "k44b_plan_add_embedding": (c_int, [c_void_p, c_char_p, c_void_p, c_uint32, c_uint32, c_uint64]),
     "k44b_plan_add_argmax": (c_int, [c_void_p, c_char_p, c_uint64, c_uint32, c_int, c_uint32]),
     "k44b_plan_set_tokens": (c_int, [c_void_p, POINTER(ctypes.c_int32), c_uint32, c_void_p]),

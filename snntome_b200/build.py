@@ -11,7 +11,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libk44wavec.so"
-SOURCES = ["k44_kernels.cu", "k44_stream_n64.cu", "k44_stream_n128.cu", "k44_stream_n256.cu", "k44_pair_kernel.cu", "k44_shift_kernel.cu", "k44_mma_kernel.cu", "k44_valu.cu", "k44_exec.cu", "k44_capi.cu", "k44_static.cu", "k44_peer.cu"]
+SOURCES = ["k44_kernels.cu", "k44_stream_n64.cu", "k44_stream_n128.cu", "k44_stream_n256.cu", "k44_pair_kernel.cu", "k44_shift_kernel.cu", "k44_shift_ws_kernel.cu", "k44_mma_kernel.cu", "k44_valu.cu", "k44_image.cu", "k44_exec.cu", "k44_capi.cu", "k44_static.cu", "k44_peer.cu"]
 HEADERS = ["k44_host.hpp", "k44_tcff.hpp", "k44_graph.hpp", "k44_kernels.cuh", "k44_epilogue.cuh", "k44_ptx.cuh", "k44_stream_kernel.cuh", "k44_exec.hpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

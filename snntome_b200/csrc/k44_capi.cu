@@ -88,6 +88,16 @@ bool desc_to_wave(const k44b_wave_desc *d, HostWave &w, std::string &err) {
         w.shifts.assign(d->shifts, d->shifts + n);
     }
     w.frame_len = d->frame_len;
+    if (d->num_tiles) {
+        if (!d->tile_off_x || !d->tile_off_y || !d->plane_stride || !d->idx || d->weights_on_device) {
+            err = "image wave: tile tables, plane stride, an index table and host weights are required";
+            return false;
+        }
+        w.pitch2d = d->plane_stride;
+        w.tile_mask = d->tile_mask != 0;
+        w.tile_off_x.assign(d->tile_off_x, d->tile_off_x + d->num_tiles);
+        w.tile_off_y.assign(d->tile_off_y, d->tile_off_y + d->num_tiles);
+    }
     return true;
 }
 
@@ -125,14 +135,30 @@ int wavec_add_flatten(void *handle, const char *, const char *, const char *) { 
 
 int wavec_add_conv2d(void *handle, const char *name, const char *in, const char *out, int cin, int cout, int kh, int kw,
                      int stride, int pad, int act, const float *w_f32, const float *bias_f32, const char *res) {
-    if (kh != 1 || kw != 1 || stride != 1 || pad != 0) return unsupported(handle, "spatial convolution");
-    return wavec_add_linear_f32(handle, name, in, out, cin, cout, act, w_f32, bias_f32, res);
+    Handle *h = H(handle);
+    if (!h) return set_error("null handle");
+    if (!h->graph.is_2d) {       // token graphs: a 1x1 convolution is a linear
+        if (kh != 1 || kw != 1 || stride != 1 || pad != 0) return set_error("add_conv2d: spatial convolutions need a 2-D image input");
+        return wavec_add_linear_f32(handle, name, in, out, cin, cout, act, w_f32, bias_f32, res);
+    }
+    if (cin <= 0 || cout <= 0 || kh <= 0 || kw <= 0) return set_error("add_conv2d: bad dimensions");
+    std::vector<uint16_t> w((size_t)cin * cout * kh * kw, 0);
+    if (w_f32) for (size_t i = 0; i < w.size(); ++i) w[i] = float_to_half(w_f32[i]);
+    return h->graph.add_conv(name, in, out, cin, cout, kh, kw, stride, pad, act, std::move(w), bias_f32, res) ? 0 : set_error(h->graph.error);
 }
 
 int wavec_add_conv2d_f16(void *handle, const char *name, const char *in, const char *out, int cin, int cout, int kh, int kw,
                          int stride, int pad, int act, const uint16_t *w_f16, const float *bias_f32, const char *res) {
-    if (kh != 1 || kw != 1 || stride != 1 || pad != 0) return unsupported(handle, "spatial convolution");
-    return wavec_add_linear_f16(handle, name, in, out, cin, cout, act, w_f16, bias_f32, res);
+    Handle *h = H(handle);
+    if (!h) return set_error("null handle");
+    if (!h->graph.is_2d) {
+        if (kh != 1 || kw != 1 || stride != 1 || pad != 0) return set_error("add_conv2d: spatial convolutions need a 2-D image input");
+        return wavec_add_linear_f16(handle, name, in, out, cin, cout, act, w_f16, bias_f32, res);
+    }
+    if (cin <= 0 || cout <= 0 || kh <= 0 || kw <= 0) return set_error("add_conv2d: bad dimensions");
+    std::vector<uint16_t> w((size_t)cin * cout * kh * kw, 0);
+    if (w_f16) std::memcpy(w.data(), w_f16, w.size() * 2);
+    return h->graph.add_conv(name, in, out, cin, cout, kh, kw, stride, pad, act, std::move(w), bias_f32, res) ? 0 : set_error(h->graph.error);
 }
 
 int wavec_add_linear_f32(void *handle, const char *name, const char *in, const char *out, int din, int dout, int act,
@@ -159,11 +185,21 @@ int wavec_add_linear_bf16(void *handle, const char *name, const char *in, const 
     return add_linear_common(handle, name, in, out, din, dout, act, std::move(w), bias_f32, res);
 }
 
-int wavec_add_upconv2x2(void *handle, const char *, const char *, const char *, int, int, const float *, const float *) {
-    return unsupported(handle, "transposed convolution");
+int wavec_add_upconv2x2(void *handle, const char *name, const char *in, const char *out, int cin, int cout, const float *w_f32, const float *bias_f32) {
+    if (!handle) return set_error("null handle");
+    if (cin <= 0 || cout <= 0 || !w_f32) return set_error("add_upconv2x2: bad arguments");
+    std::vector<uint16_t> w((size_t)cin * cout * 4u);
+    for (size_t i = 0; i < w.size(); ++i) w[i] = float_to_half(w_f32[i]);
+    return H(handle)->graph.add_upconv(name, in, out, cin, cout, std::move(w), bias_f32) ? 0 : set_error(H(handle)->graph.error);
 }
-int wavec_add_maxpool(void *handle, const char *, const char *, const char *, int, int, int) { return unsupported(handle, "max-pool"); }
-int wavec_add_upsample2x(void *handle, const char *, const char *, const char *) { return unsupported(handle, "upsample"); }
+int wavec_add_maxpool(void *handle, const char *name, const char *in, const char *out, int k, int stride, int pad) {
+    if (!handle) return set_error("null handle");
+    return H(handle)->graph.add_pool(name, in, out, k, stride, pad) ? 0 : set_error(H(handle)->graph.error);
+}
+int wavec_add_upsample2x(void *handle, const char *name, const char *in, const char *out) {
+    if (!handle) return set_error("null handle");
+    return H(handle)->graph.add_upsample(name, in, out) ? 0 : set_error(H(handle)->graph.error);
+}
 int wavec_add_rmsnorm(void *handle, const char *name, const char *in, const char *out, int dim, float eps, const float *gamma_f32, int pre_folded) {
     if (!handle) return set_error("null handle");
     return H(handle)->graph.add_rmsnorm(name, in, out, dim, eps, gamma_f32, pre_folded) ? 0 : set_error(H(handle)->graph.error);
@@ -360,6 +396,17 @@ int k44b_plan_get_next_tokens(void *plan, int32_t *h_tokens, uint32_t n, void *s
     return r == cudaSuccess ? 0 : set_error(std::string("plan_get_next_tokens: ") + cudaGetErrorString(r));
 }
 
+int k44b_plan_add_image_op(void *plan, int op, const char *name, uint64_t src_off, uint64_t dst_off, uint32_t planes,
+                           const k44b_plane_geom *in, const k44b_plane_geom *out) {
+    if (!plan || !out || op < AUX_MAXPOOL2 || op > AUX_HALO_CLEAR || (op != AUX_HALO_CLEAR && !in)) return set_error("plan_add_image_op: bad arguments");
+    HostWave w;
+    w.kind = op; w.name = name ? name : "image_op"; w.src_off = src_off; w.y_off = dst_off; w.cout = w.logical_cout = planes;
+    auto conv = [](const k44b_plane_geom *g) { HostWave::Geom2D r; r.H = g->h; r.W = g->w; r.W_pad = g->w_pad; r.ch_stride = g->plane_stride; return r; };
+    w.out2d = conv(out);
+    w.in2d = in ? conv(in) : w.out2d;
+    return P(plan)->exec.add_wave(w) ? 0 : set_error(P(plan)->exec.err);
+}
+
 int k44b_plan_set_decode_pos(void *plan, int pos, void *stream) {
     if (!plan || pos < 0) return set_error("plan_set_decode_pos: bad arguments");
     int *d = P(plan)->exec.decode_pos_ptr();
@@ -405,6 +452,8 @@ int k44b_wave_info(void *plan, int wave, k44b_wave_info_t *out) {
     out->synapses = w.synapses; out->weight_bytes = w.weight_bytes;
     out->m_blocks = (w.path == PATH_UMMA && !w.use_cluster && !w.use_shift) ? (w.desc.pair ? 2u : w.desc.m_blocks) : 1u;
     out->cta_pairs = (w.path == PATH_UMMA && !w.use_cluster && !w.use_shift) ? w.desc.pair : 0u;
+    out->weights_in_tmem = (w.path == PATH_UMMA && w.use_shift) ? w.desc.ws_chunk : 0u;
+    out->reserved0 = 0u;
     return 0;
 }
 

@@ -225,6 +225,7 @@ void Executor::release() {
     if (ev0_) { cudaEventDestroy(ev0_); ev0_ = nullptr; }
     if (ev1_) { cudaEventDestroy(ev1_); ev1_ = nullptr; }
     canvas_elems_ = 0;
+    is_2d_ = false;
 }
 
 bool Executor::begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t columns, int force_path) {
@@ -416,6 +417,30 @@ bool Executor::add_aux(const HostWave &w) {
         dw.write_lo = 0; dw.write_hi = 0;
         break;
     }
+    case AUX_MAXPOOL2: case AUX_MAXPOOL5: case AUX_UPSAMPLE2: case AUX_S2D: case AUX_UPCONV_SCATTER: case AUX_HALO_CLEAR: {
+        // planes of a 2-D image tensor: geometry from the plan, everything range-checked here
+        const auto &gi = w.in2d, &go = w.out2d;
+        x.h_in = gi.H; x.w_in = gi.W; x.wpad_in = gi.W_pad; x.cs_in = gi.ch_stride;
+        x.h_out = go.H; x.w_out = go.W; x.wpad_out = go.W_pad; x.cs_out = go.ch_stride;
+        const uint32_t src_planes = w.kind == AUX_UPCONV_SCATTER ? 4u * w.cout : w.cout;
+        const uint32_t dst_planes = w.kind == AUX_S2D ? 4u * w.cout : w.cout;
+        auto plane_ok = [&](const HostWave::Geom2D &g) { return g.H && g.W && g.W_pad >= g.W + 4u && (uint64_t)(g.H + 2u) * g.W_pad <= (uint64_t)g.ch_stride + 8u; };
+        if (!w.cout || !plane_ok(go) || (w.kind != AUX_HALO_CLEAR && !plane_ok(gi))) return fail("image command '" + w.name + "': bad plane geometry");
+        if (w.y_off + (uint64_t)dst_planes * go.ch_stride > canvas_elems_) return fail("image command '" + w.name + "' writes outside the canvas");
+        if (w.kind != AUX_HALO_CLEAR && w.src_off + (uint64_t)src_planes * gi.ch_stride > canvas_elems_) return fail("image command '" + w.name + "' reads outside the canvas");
+        bool shape_ok = true;
+        switch (w.kind) {
+        case AUX_MAXPOOL2: case AUX_S2D: shape_ok = gi.H == 2u * go.H && gi.W == 2u * go.W; break;
+        case AUX_UPSAMPLE2: case AUX_UPCONV_SCATTER: shape_ok = go.H == 2u * gi.H && go.W == 2u * gi.W; break;
+        case AUX_MAXPOOL5: shape_ok = gi.H == go.H && gi.W == go.W; break;
+        default: break;
+        }
+        if (!shape_ok) return fail("image command '" + w.name + "': source and destination sizes do not fit the operation");
+        if (w.kind != AUX_HALO_CLEAR) { rlo = w.src_off; rhi = w.src_off + (uint64_t)src_planes * gi.ch_stride; }
+        else { rlo = 0; rhi = 0; }
+        dw.write_lo = w.y_off; dw.write_hi = w.y_off + (uint64_t)dst_planes * go.ch_stride;
+        break;
+    }
     default: return fail("unknown command kind");
     }
     dw.read_lo = rlo; dw.read_hi = rhi;
@@ -426,10 +451,90 @@ bool Executor::add_aux(const HostWave &w) {
     return true;
 }
 
+// A wave over 2-D image planes (convolution taps as element offsets relative to per-tile anchors, outputs at per-tile plane
+// offsets, optionally masked by 4-element quads): always on the general kernels — the warp-level tensor path, or the FP32-FMA
+// kernel when forced — whose gathers take any element alignment. The role of the reference's unaligned token-shift kernel
+// for image layouts (kernels/cuda/kernel44_cuda_pack.cuh:242-264; wavec/k44_wave_executor.cu:245-255).
+bool Executor::add_wave_2d(const HostWave &w) {
+    auto bad = [&](const std::string &m) { return fail("wave '" + w.name + "': " + m); };
+    const uint32_t tiles = (uint32_t)w.tile_off_x.size();
+    if (!tiles || w.tile_off_y.size() != tiles) return bad("tile tables missing or of different lengths");
+    if (w.cout == 0 || w.cout % 16u || w.group == 0 || w.cout % w.group || w.group % 16u) return bad("row count / group size must be multiples of 16");
+    if (w.fan_in == 0 || w.fan_in % 8u || w.fan_in_raw > w.fan_in) return bad("bad fan-in");
+    if (w.y_off % 4u || w.res_off % 4u || w.pitch2d % 4u) return bad("plane offsets must be multiples of 4 elements");
+    if (!w.cout_map.empty() || !w.shifts.empty() || !w.run_rows.empty()) return bad("row maps, shift tables and run tables do not apply to image waves");
+    const uint32_t groups = w.cout / w.group;
+    if (w.idx.size() != (size_t)groups * w.fan_in) return bad("gather table has the wrong size");
+    if (w.w_wmma.size() != (size_t)w.cout * w.fan_in) return bad("weight block has the wrong size");
+    if (!w.bias.empty() && w.bias.size() != w.cout) return bad("bias has the wrong size");
+    if (w.act < 0 || w.act > ACT_GELU) return bad("unknown activation");
+    uint32_t max_idx = 0, max_tx = 0, max_ty = 0;
+    for (uint32_t g = 0; g < groups; ++g)
+        for (uint32_t k = 0; k < w.fan_in_raw; ++k) max_idx = std::max(max_idx, w.idx[(size_t)g * w.fan_in + k]);
+    for (uint32_t t = 0; t < tiles; ++t) {
+        max_tx = std::max(max_tx, w.tile_off_x[t]);
+        max_ty = std::max(max_ty, w.tile_mask ? (w.tile_off_y[t] & 0xffffu) << 2 : w.tile_off_y[t]);
+    }
+    if (w.x_base_off + (uint64_t)max_tx + max_idx + 64u > canvas_elems_) return bad("a gather leaves the canvas");
+    if (w.y_off + (uint64_t)(w.cout - 1u) * w.pitch2d + max_ty + 64u > canvas_elems_) return bad("output planes leave the canvas");
+    if (w.has_residual && w.res_off + (uint64_t)(w.cout - 1u) * w.pitch2d + max_ty + 64u > canvas_elems_) return bad("residual planes leave the canvas");
+
+    DeviceWave dw;
+    dw.name = w.name;
+    dw.synapses = (uint64_t)w.logical_cout * w.fan_in_raw;
+    WaveArgs &a = dw.args;
+    a.canvas = canvas_; a.canvas_elems = canvas_elems_; a.status = d_status_;
+    a.y_off = w.y_off; a.res_off = w.res_off; a.x_base_off = w.x_base_off;
+    a.cout = w.cout; a.group = w.group; a.fan_in = w.fan_in;
+    a.num_kstages = (w.fan_in + kStageK - 1) / kStageK;
+    a.pitch = w.pitch2d; a.num_col_tiles64 = tiles;
+    a.act = w.act; a.has_residual = w.has_residual ? 1 : 0;
+    a.gather_mode = GATHER_IDX;
+    a.tile_mask = w.tile_mask ? 1u : 0u;
+    const uint32_t mtiles = (w.cout + kTileM - 1) / kTileM;
+    dw.weight_bytes = (uint64_t)mtiles * a.num_kstages * kStageWBytes;
+    void *stage = nullptr;
+    bool ok = check(cudaMalloc(&dw.d_weights, dw.weight_bytes), "weight allocation") &&
+              check(cudaMalloc(&stage, w.w_wmma.size() * 2), "staging allocation") &&
+              check(cudaMemcpy(stage, w.w_wmma.data(), w.w_wmma.size() * 2, cudaMemcpyHostToDevice), "weight upload") &&
+              check(launch_repack_wmma_to_tiled((const uint4 *)stage, (uint4 *)dw.d_weights, w.cout, w.fan_in, nullptr), "weight repack") &&
+              check(cudaDeviceSynchronize(), "weight repack");
+    cudaFree(stage);
+    a.w_tiles = (const uint4 *)dw.d_weights;
+    // gather table followed by the two tile tables in one allocation
+    std::vector<uint32_t> tab(w.idx);
+    tab.insert(tab.end(), w.tile_off_x.begin(), w.tile_off_x.end());
+    tab.insert(tab.end(), w.tile_off_y.begin(), w.tile_off_y.end());
+    ok = ok && check(cudaMalloc(&dw.d_gather, tab.size() * 4), "table allocation") &&
+         check(cudaMemcpy(dw.d_gather, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice), "table upload");
+    a.gather = (const uint32_t *)dw.d_gather;
+    a.tile_off_x = a.gather + w.idx.size();
+    a.tile_off_y = a.tile_off_x + tiles;
+    if (ok && !w.bias.empty() && w.has_bias) {
+        ok = check(cudaMalloc(&dw.d_bias, w.bias.size() * 2), "bias allocation") &&
+             check(cudaMemcpy(dw.d_bias, w.bias.data(), w.bias.size() * 2, cudaMemcpyHostToDevice), "bias upload");
+        a.bias = (const __half *)dw.d_bias;
+    }
+    if (!ok) { cudaFree(dw.d_weights); cudaFree(dw.d_gather); cudaFree(dw.d_bias); return false; }
+    dw.path = force_path_ == 0 ? PATH_FMA : PATH_MMA;
+    dw.fma_reason = "image planes (element-granular tap offsets, per-tile anchors)";
+    dw.write_lo = w.y_off; dw.write_hi = w.y_off + (uint64_t)w.cout * w.pitch2d;
+    dw.read_lo = w.x_base_off; dw.read_hi = std::min<uint64_t>(canvas_elems_, w.x_base_off + (uint64_t)max_tx + max_idx + 64u);
+    if (w.has_residual) { dw.read_lo = std::min(dw.read_lo, w.res_off); dw.read_hi = std::max(dw.read_hi, w.res_off + (uint64_t)w.cout * w.pitch2d); }
+    dw.groupable = false;
+    peer_slack_.clear();
+    waves_.push_back(dw);
+    drop_graph();
+    groups_valid_ = false;
+    return true;
+}
+
 bool Executor::add_wave(const HostWave &w) {
     if (w.kind != 0) return add_aux(w);
     if (!ready()) return fail("executor not initialised");
     if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
+    if (d_peers_) return fail("waves cannot be added after the peers were set");
+    if (w.pitch2d) return add_wave_2d(w);
     const uint32_t tiles64 = pitch_ / 64u;
     if (!validate_wave(w, pitch_, tiles64, canvas_elems_, err)) return false;
     if (w.w_wmma.empty() && !w.dev_weights_rowmajor) return fail("wave '" + w.name + "' has no weights");
@@ -559,6 +664,21 @@ bool Executor::add_wave(const HostWave &w) {
             }
             a.k_splits = 1; a.kstages_per_split = a.num_kstages;
             dw.desc = make_umma_desc(n_tile, 0);
+            // fan-in up to 512: the weight tile of a work item stays in tensor memory (tiles of 128 columns), which takes the
+            // weights out of the shared-memory traffic that bounds this kernel
+            a.gather_mode = GATHER_BOX; a.box_h = gp.box_h;
+            bool ws = n_tile >= 128u && flen % 128u == 0u && shift_ws_supported(a) && (uint64_t)mtiles * (tiles64 / 2u) >= (uint64_t)num_sms_;
+            if (const char *e = std::getenv("K44B_SHIFT_WS")) {       // 0: never, 2: whenever the wave qualifies, however few tiles it has
+                const int v = std::atoi(e);
+                ws = v == 2 ? (flen % 128u == 0u && shift_ws_supported(a)) : (ws && v != 0);
+            }
+            if (ws) {
+                dw.desc = make_umma_desc(128u, 0);
+                dw.desc.ws_chunk = shift_ws_chunk(mtiles, tiles64 / 2u, (uint32_t)num_sms_);
+                if (const char *e = std::getenv("K44B_WS_CHUNK")) { const int v = std::atoi(e); if (v > 0) dw.desc.ws_chunk = (uint32_t)v; }
+                if (const char *e = std::getenv("K44B_WS_GROUPS")) { const int v = std::atoi(e); if (v >= 1 && v <= 3) dw.desc.ws_groups = (uint32_t)v; }
+                n_tile = 128u;
+            }
             ok = make_tensor_map(dw, std::min(n_tile, 128u) + 8u, false);   // aligned windows of up to 128 columns plus the 8 to their left, as plain rows
         } else if (dw.path == PATH_UMMA) {
             uint32_t n_tile = 64;
@@ -612,8 +732,11 @@ bool Executor::add_wave(const HostWave &w) {
                 bool two = ok && tile_copies && n_tile == 256u && a.k_splits == 1u && (a.mtiles_per_group % 2u) == 0u &&
                       (uint64_t)((mtiles + 1u) / 2u) * (tiles64 / 4u) >= (uint64_t)num_sms_ && !(gp.box_h == 1u && dw.desc.rows_mode == 2u);
                 // preferred for such waves: the two blocks on a pair of CTAs (M = 256 MMAs), see k44_pair_kernel.cu
-                bool pair = two && (mtiles % 2u) == 0u && 2u * (kStageK / std::max(gp.box_h, 1u)) <= 32u;
-                if (const char *e = std::getenv("K44B_PAIR")) pair = pair && std::atoi(e) != 0; else pair = false;
+                bool pair = two && (mtiles % 2u) == 0u && (gp.box_h == 1u || 2u * (kStageK / gp.box_h) <= 32u);   // (boxes: one producer lane per box)
+                // (measured, reference-benchmark shapes: pairs 111 us against 127 us per pass for run tables when the GPU is not held
+                // back by its power cap, the same ~0.17 ms once it is; for scattered rows the pair's extra hop — CTA 1's copies are
+                // passed on to CTA 0's barrier — costs more than the halved fetch saves, so those stay on one CTA)
+                if (const char *e = std::getenv("K44B_PAIR")) pair = pair && std::atoi(e) != 0; else pair = pair && gp.box_h != 1u;
                 if (const char *e = std::getenv("K44B_M_BLOCKS")) two = two && std::atoi(e) == 2; else two = false;   // two blocks on one CTA: measured no gain, on request only
                 if (pair) {
                     two = false;
@@ -689,10 +812,19 @@ void Executor::set_io(uint64_t in_off, uint32_t in_c, uint64_t out_off, uint32_t
 }
 
 bool Executor::init(const HostPlan &plan, int device, int force_path) {
-    if (!begin(device, plan.canvas_elems, plan.layout.channel_stride, plan.layout.width, force_path)) return false;
+    // (an image plan has no plan-wide row pitch: every wave carries its tensor's plane stride; 64 stands in for the checks)
+    if (!begin(device, plan.canvas_elems, plan.is_2d ? 64u : plan.layout.channel_stride, plan.is_2d ? 64u : plan.layout.width, force_path)) return false;
+    is_2d_ = plan.is_2d; in2d_ = plan.in2d; out2d_ = plan.out2d;
     for (const auto &w : plan.waves)
         if (!add_wave(w)) { std::string keep = err; release(); err = keep; return false; }
     set_io(plan.input_off, plan.input_c, plan.output_off, plan.logical_output_c ? plan.logical_output_c : plan.output_c, plan.layout.width);
+    if (is_2d_) {
+        if ((uint64_t)in_off_ + (uint64_t)in_c_ * in2d_.ch_stride > canvas_elems_ || (uint64_t)out_off_ + (uint64_t)out_c_ * out2d_.ch_stride > canvas_elems_) {
+            release();
+            return fail("plan input / output planes leave the canvas");
+        }
+        return true;
+    }
     if ((uint64_t)in_off_ + (uint64_t)in_c_ * pitch_ > canvas_elems_ || (uint64_t)out_off_ + (uint64_t)out_c_ * pitch_ > canvas_elems_) {
         release();
         return fail("plan input / output region leaves the canvas");
@@ -840,7 +972,7 @@ bool Executor::launch_one(DeviceWave &w, cudaStream_t stream, uint32_t peer_slac
         g.total_clusters = ((w.args.cout + kTileM - 1) / kTileM) * w.args.num_col_tiles64;
         e = launch_wave_umma_cluster(g, w.desc, w.tmap, pdl_, num_sms_, stream);
     } else if (w.path == PATH_UMMA && w.use_shift) {
-        e = launch_wave_umma_shift(w.args, w.desc, w.tmap, num_sms_, stream);
+        e = w.desc.ws_chunk ? launch_wave_umma_shift_ws(w.args, w.desc, w.tmap, num_sms_, stream) : launch_wave_umma_shift(w.args, w.desc, w.tmap, num_sms_, stream);
     } else if (w.path == PATH_UMMA && w.desc.pair && !w.args.peers) {
         e = launch_wave_umma_pair(w.args, w.desc, w.tmap, w.wmap, num_sms_, stream);
     } else if (w.path == PATH_UMMA) {
@@ -983,7 +1115,7 @@ bool Executor::set_peers_raw(int rank, int world, void *const *canvas_ptrs, void
     if (!ready()) return fail("executor not initialised");
     if (world < 2 || world > kMaxPeers + 1 || rank < 0 || rank >= world) return fail("set_peers: bad rank / world size");
     for (const auto &w : waves_)
-        if ((w.path != PATH_UMMA && w.path != PATH_MMA) || w.use_shift)
+        if ((w.path != PATH_UMMA && w.path != PATH_MMA) || w.use_shift || w.args.tile_off_x)
             return fail("set_peers: '" + w.name + "' does not run on a kernel that stores to peers (" +
                         (w.use_shift ? std::string("token-shifted runs") : w.is_aux ? std::string("element-wise command") : std::string("FP32-FMA kernel")) + ")");
     if (!sync_ptr()) return false;
@@ -1052,17 +1184,22 @@ bool Executor::execute_timed(float *ms) {
 bool Executor::infer_f32(const float *h_in, int in_elems, float *h_out, int out_elems, float *gpu_ms) {
     if (!ready()) return fail("executor not initialised");
     if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
-    const size_t in_n = (size_t)in_c_ * io_width_, out_n = (size_t)out_c_ * io_width_;
+    const size_t in_n = is_2d_ ? (size_t)in_c_ * in2d_.H * in2d_.W : (size_t)in_c_ * io_width_;
+    const size_t out_n = is_2d_ ? (size_t)out_c_ * out2d_.H * out2d_.W : (size_t)out_c_ * io_width_;
     if (in_elems < 0 || (size_t)in_elems < in_n) return fail("input has fewer elements than the plan's input tensor");
     if (!d_in_f32_ && !check(cudaMalloc(&d_in_f32_, std::max<size_t>(in_n, 1) * 4), "input staging")) return false;
     if (!d_out_f32_ && !check(cudaMalloc(&d_out_f32_, std::max<size_t>(out_n, 1) * 4), "output staging")) return false;
     if (!check(cudaMemcpyAsync(d_in_f32_, h_in, in_n * 4, cudaMemcpyHostToDevice, nullptr), "input upload")) return false;
-    if (!check(launch_f32_to_canvas(d_in_f32_, canvas_ + in_off_, in_c_, io_width_, pitch_, nullptr), "input conversion")) return false;
+    if (is_2d_) {
+        if (!check(launch_f32_to_planes(d_in_f32_, canvas_ + in_off_, in_c_, in2d_.H, in2d_.W, in2d_.W_pad, in2d_.ch_stride, nullptr), "input conversion")) return false;
+    } else if (!check(launch_f32_to_canvas(d_in_f32_, canvas_ + in_off_, in_c_, io_width_, pitch_, nullptr), "input conversion")) return false;
     ++launches_;
     if (!check(cudaEventRecord(ev0_, nullptr), "event record")) return false;
     if (!execute(nullptr)) return false;
     if (!check(cudaEventRecord(ev1_, nullptr), "event record")) return false;
-    if (!check(launch_canvas_to_f32(canvas_ + out_off_, d_out_f32_, out_c_, io_width_, pitch_, nullptr), "output conversion")) return false;
+    if (is_2d_) {
+        if (!check(launch_planes_to_f32(canvas_ + out_off_, d_out_f32_, out_c_, out2d_.H, out2d_.W, out2d_.W_pad, out2d_.ch_stride, nullptr), "output conversion")) return false;
+    } else if (!check(launch_canvas_to_f32(canvas_ + out_off_, d_out_f32_, out_c_, io_width_, pitch_, nullptr), "output conversion")) return false;
     ++launches_;
     const size_t copy_n = std::min((size_t)std::max(out_elems, 0), out_n);
     if (!check(cudaMemcpy(h_out, d_out_f32_, copy_n * 4, cudaMemcpyDeviceToHost), "output download")) return false;

@@ -70,6 +70,7 @@ class Executor {
     bool begin(int device, uint64_t canvas_elems, uint32_t pitch, uint32_t columns, int force_path);
     bool add_wave(const HostWave &w);
     bool add_aux(const HostWave &w);                               // HostWave::kind != 0
+    bool add_wave_2d(const HostWave &w);                           // HostWave::pitch2d != 0: a wave over image planes
     int *tokens_ptr();                                             // device int32 [pitch]: token id per column (embedding gather input)
     int *next_tokens_ptr();                                        // device int32 [pitch]: result of the last arg-max command
     int *decode_pos_ptr();                                         // device word holding the position decode attention works at
@@ -151,6 +152,8 @@ class Executor {
     PeerArgs *d_peers_ = nullptr;
     std::vector<void *> ipc_opened_;      // peer mappings to close on release
     int peer_rank_ = 0, peer_world_ = 1;
+    bool is_2d_ = false;                 // image plan: dense [C][H][W] at the host boundary, haloed planes in the canvas
+    HostWave::Geom2D in2d_, out2d_;
     std::vector<void *> peer_canvas_, peer_sync_;   // indexed by rank (own entries null)
     uint32_t probe_base_ = 0;
     size_t scratch_tiles_ = 0;

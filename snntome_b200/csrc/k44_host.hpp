@@ -115,6 +115,67 @@ struct Layout1D {
     }
 };
 
+// ---- 2-D image layout (wavec/k44_plan_types.hpp:517-569, 576-600) ---------------------------------
+// A tensor [C][H][W] lives in C planes of `channel_stride` FP16 elements; a plane is the image with a zero halo around it
+// (one row above and below, four elements left of every row) so that the taps of a 3x3 convolution never need a bounds
+// check. Waves still work on tiles of 64 consecutive elements of a plane:
+//   * W a multiple of 64 ("aligned"): rows of W + 8 elements (4 halo + W + 4 halo), a tile is 64 pixels of one image row.
+//     tile_off_x is anchored one row up and one element left of the tile (so every tap offset is non-negative),
+//     tile_off_y at the tile's first pixel;
+//   * otherwise ("masked"): rows of W + 4 elements, tiles run on across the rows (the next row's left halo doubles as the
+//     right halo) and would overwrite halo elements, so every tile carries a 16-bit mask — bit q set iff the four elements
+//     4q .. 4q+3 of the tile are pixels (W is a multiple of 4) — packed into tile_off_y as
+//     (plane offset of the tile / 4) & 0xffff | mask << 16; such planes hold at most 2^18 elements.
+struct Layout2D {
+    uint32_t H = 0, W = 0, H_pad = 0, W_pad = 0;
+    uint32_t tiles_per_frame = 0, num_tiles = 0;
+    uint32_t single_stride = 0, channel_stride = 0;
+    bool masked = false;
+    std::vector<uint32_t> tile_off_x, tile_off_y;
+
+    bool init(uint32_t h, uint32_t w) {
+        H = h; W = w;
+        tile_off_x.clear(); tile_off_y.clear();
+        if (h == 0 || w == 0 || w % 4u) return false;
+        H_pad = H + 2u;
+        if (W % 64u == 0u) {
+            masked = false;
+            W_pad = W + 8u;
+            single_stride = H_pad * W_pad;
+            const uint32_t per_row = W / 64u;
+            tiles_per_frame = H * per_row;
+            for (uint32_t ty = 0; ty < H; ++ty)
+                for (uint32_t tx = 0; tx < per_row; ++tx) {
+                    tile_off_x.push_back(ty * W_pad + (4u + tx * 64u - 1u));
+                    tile_off_y.push_back((ty + 1u) * W_pad + (4u + tx * 64u));
+                }
+        } else {
+            masked = true;
+            W_pad = W + 4u;
+            tiles_per_frame = (H * W_pad + 63u) / 64u;
+            single_stride = (2u * W_pad + tiles_per_frame * 64u + 63u) & ~63u;
+            if (single_stride > (1u << 18)) return false;              // the packed tile offset has 16 bits of quads
+            for (uint32_t t = 0; t < tiles_per_frame; ++t) {
+                const uint32_t y1 = W_pad + 4u + t * 64u;
+                tile_off_x.push_back(y1 - W_pad - 1u);
+                uint32_t mask = 0;
+                for (uint32_t q = 0; q < 16u; ++q) {
+                    const uint32_t rel = t * 64u + q * 4u;
+                    if (rel / W_pad < H && rel % W_pad < W) mask |= 1u << q;
+                }
+                tile_off_y.push_back(((y1 >> 2) & 0xffffu) | (mask << 16));
+            }
+        }
+        channel_stride = single_stride;                                 // one frame per wave
+        num_tiles = tiles_per_frame;
+        return true;
+    }
+    // element of pixel (y, x) of channel plane `ch`
+    uint64_t offset(uint32_t ch, uint32_t y, uint32_t x) const { return (uint64_t)ch * channel_stride + (uint64_t)(y + 1u) * W_pad + 4u + x; }
+    // gather offset of tap (dy, dx), dy, dx >= -1, relative to a tile's tile_off_x, for the plane starting at `plane`
+    uint64_t tap(uint64_t plane, int dy, int dx) const { return plane + (uint64_t)(1 + dy) * W_pad + (uint64_t)(1 + dx); }
+};
+
 // ---- hardware presets (wavec/k44_plan_types.hpp:192-310); only name and unit count are surfaced ----
 struct TargetPreset {
     std::string name = "b200";
@@ -201,6 +262,16 @@ struct HostWave {
     float eps = 1e-5f, rope_theta = 10000.0f;
     uint32_t h_q = 0, h_kv = 0, head_dim = 0, seq_len = 0, max_seq = 0;
     bool llama3_scaling = false;
+    // 2-D image waves and commands (kinds 7..12): the layout of the tensor the tiles walk over. pitch2d != 0 marks them:
+    // rows are `pitch2d` (a plane's channel stride) apart instead of the plan's row pitch, and tile t reads from
+    // tile_off_x[t] and writes to tile_off_y[t] (packed with a quad mask when `tile_mask`), see Layout2D.
+    uint32_t pitch2d = 0;
+    bool tile_mask = false;
+    std::vector<uint32_t> tile_off_x, tile_off_y;
+    //   kind 7 max-pool 2x2 stride 2, 8 max-pool 5x5 stride 1 pad 2, 9 nearest upsample x2, 10 space-to-depth 2x2,
+    //   11 scatter of a 2x2 transposed convolution's four phase planes, 12 halo clear: `cout` planes from src_off
+    //   (geometry `in2d`) to y_off (geometry `out2d`)
+    struct Geom2D { uint32_t H = 0, W = 0, W_pad = 0, ch_stride = 0; } in2d, out2d;
 };
 
 struct HostPlan {
@@ -216,6 +287,9 @@ struct HostPlan {
     bool reuse_canvas = false;
     TargetPreset target;
     std::vector<HostWave> waves;
+    // 2-D image plans: geometry of the input and output tensors (dense [C][H][W] at the boundary, haloed planes in the canvas)
+    bool is_2d = false;
+    HostWave::Geom2D in2d, out2d;
 };
 
 }  // namespace k44b

@@ -39,8 +39,9 @@ __global__ void __launch_bounds__(256) k44_wave_fma_kernel(const WaveArgs a) {
     const uint32_t j0 = (blockIdx.x / a.num_col_tiles64) * kFmaRows;      // first neuron
     const uint32_t g = j0 / a.group;
     const uint32_t tid = threadIdx.x, c = tid & 63u, q = tid >> 6;
-    const __half *xbase = a.canvas + a.x_base_off + (uint64_t)tile * 64u;
-    const uint64_t x_limit = a.canvas_elems - a.x_base_off - (uint64_t)tile * 64u;   // exclusive bound for off + 64
+    const uint64_t tile_x = a.tile_off_x ? a.tile_off_x[tile] : (uint64_t)tile * 64u;       // where this tile's gathers are anchored
+    const __half *xbase = a.canvas + a.x_base_off + tile_x;
+    const uint64_t x_limit = a.canvas_elems - a.x_base_off - tile_x;   // exclusive bound for off + 64
     const uint32_t flen = a.frame_len ? a.frame_len : a.pitch;
     const uint32_t col_in_frame = (tile * 64u + c) % flen;
 
@@ -90,12 +91,18 @@ __global__ void __launch_bounds__(256) k44_wave_fma_kernel(const WaveArgs a) {
         __syncthreads();
     }
     if (bad) atomicOr(a.status, (uint32_t)ST_BAD_INDEX);
+    uint64_t tile_y = (uint64_t)tile * 64u;
+    if (a.tile_off_y) {
+        const uint32_t e = a.tile_off_y[tile];
+        tile_y = a.tile_mask ? (uint64_t)(e & 0xffffu) << 2 : e;
+        if (a.tile_mask && !((e >> (16u + (c >> 2))) & 1u)) return;        // this column's quad is halo, not pixels
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t j = j0 + q * 4 + i;
         if (j >= a.cout) continue;
         const uint32_t oj = a.cout_map ? a.cout_map[j] : j;
-        const uint64_t o = (uint64_t)oj * a.pitch + (uint64_t)tile * 64u + c;
+        const uint64_t o = (uint64_t)oj * a.pitch + tile_y + c;
         const float b = a.bias ? __half2float(a.bias[j]) : 0.0f;
         const float r = a.has_residual ? __half2float(a.canvas[a.res_off + o]) : 0.0f;
         a.canvas[a.y_off + o] = __float2half_rn(finish_value(acc[i], b, r, a.act, a.has_residual != 0, a.cout_map != nullptr));

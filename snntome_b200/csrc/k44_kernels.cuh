@@ -85,6 +85,12 @@ struct WaveArgs {
     uint32_t k_splits = 1, kstages_per_split = 0;
     float *scratch = nullptr;             // [tiles][N_TILE][128] FP32, all zero between launches
     uint32_t *counters = nullptr;         // [tiles], all zero between launches
+    // 2-D image waves (general kernels only): tile t gathers relative to tile_off_x[t] and stores at tile_off_y[t] inside a
+    // plane instead of at 64 * t; with tile_mask the entry is (plane offset / 4) & 0xffff | mask << 16 and only the 4-element
+    // quads whose mask bit is set are stored (wavec/k44_plan_types.hpp:517-569; kernels/cuda/kernel44_cuda_pack.cuh:116-123).
+    // `pitch` is then the plane stride of the output tensor and num_col_tiles64 the number of tiles of a plane.
+    const uint32_t *tile_off_x = nullptr, *tile_off_y = nullptr;
+    uint32_t tile_mask = 0;
     const PeerArgs *peers = nullptr;      // device memory; null unless the plan is neuron-sharded over several GPUs
     uint32_t peer_slack = 0;              // sharded plans: how many of the peers' latest launches this launch need not wait for
     // Output through tensor copies (streaming tcgen05 kernel, waves without an output-row map): device array of tensor maps
@@ -95,7 +101,9 @@ struct WaveArgs {
 };
 
 // Element-wise / attention steps between waves (k44_valu.cu)
-enum AuxKind : int { AUX_NONE = 0, AUX_RMSNORM = 1, AUX_SWIGLU = 2, AUX_ROPE_ATTN = 3, AUX_DECODE_ATTN = 4, AUX_EMBED = 5, AUX_ARGMAX = 6 };
+enum AuxKind : int { AUX_NONE = 0, AUX_RMSNORM = 1, AUX_SWIGLU = 2, AUX_ROPE_ATTN = 3, AUX_DECODE_ATTN = 4, AUX_EMBED = 5, AUX_ARGMAX = 6,
+                     // 2-D image glue on haloed planes (kernels/common/kernel44_valu_pack.cuh:30-103)
+                     AUX_MAXPOOL2 = 7, AUX_MAXPOOL5 = 8, AUX_UPSAMPLE2 = 9, AUX_S2D = 10, AUX_UPCONV_SCATTER = 11, AUX_HALO_CLEAR = 12 };
 struct AuxArgs {
     int kind = AUX_NONE;
     __half *canvas = nullptr;
@@ -115,11 +123,14 @@ struct AuxArgs {
     uint32_t vocab = 0, advance = 0;
     int *tokens = nullptr, *next_tokens = nullptr, *pos_rw = nullptr;
     unsigned long long *argmax_scratch = nullptr;                    // [row chunks][pitch] packed (value key, row)
+    // 2-D image commands: `rows` planes; source / destination geometry (pixels, padded row length, plane stride)
+    uint32_t h_in = 0, w_in = 0, wpad_in = 0, cs_in = 0, h_out = 0, w_out = 0, wpad_out = 0, cs_out = 0;
 };
 constexpr uint32_t kArgmaxChunk = 256;                               // rows per arg-max CTA
 constexpr uint32_t kDecodeChunk = 32;
 constexpr uint32_t kDecodeRow = 68;                                  // floats per partial result: 64 values, maximum, sum, 2 pad (16-byte aligned rows)                                // cache positions per partial-attention CTA
 cudaError_t launch_aux(const AuxArgs &a, bool dependent_launch, cudaStream_t s);
+cudaError_t launch_image_aux(const AuxArgs &a, cudaStream_t s);       // kinds AUX_MAXPOOL2 .. AUX_HALO_CLEAR (k44_image.cu)
 
 // Up to four mutually independent small waves launched as one grid (their clusters are numbered consecutively).
 constexpr int kMaxGroupWaves = 4;
@@ -142,6 +153,8 @@ struct UmmaDesc {
     uint32_t rows_mode = 1;               // scattered single rows: 1 asynchronous 16-byte copies from four extra warps, 2 gather-mode tensor copies (measured slower)
     uint32_t pair = 0;                    // 1: the wave runs on CTA pairs (tiles of 256 neurons x 256 columns, M = 256 MMAs)
     uint32_t m_blocks = 1;                // 128-neuron blocks per tile: 2 = tiles of 256 neurons sharing one gathered operand (256-column tiles only)
+    uint32_t ws_chunk = 0;                // token-shift kernel with the weights in tensor memory: column tiles per work item (0: not that kernel)
+    uint32_t ws_groups = 2;               // ... and its groups of four aligner warps (1..3), each taking every ws_groups-th step
 };
 
 cudaError_t launch_wave_fma(const WaveArgs &a, cudaStream_t s);
@@ -162,6 +175,10 @@ cudaError_t launch_wave_umma_cluster(const WaveGroupArgs &g, const UmmaDesc &d, 
 // token-shifted runs (box gather, shifts in the table entries): n_tile 64 or 128, frames must be whole tiles; the tensor
 // map describes the canvas with boxes of (n_tile + 8) columns x box_h rows and no swizzle
 cudaError_t launch_wave_umma_shift(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
+// the same with the weight tile of a work item held in tensor memory (k44_shift_ws_kernel.cu): fan-in up to 512, tiles of 128 columns
+cudaError_t launch_wave_umma_shift_ws(const WaveArgs &a, const UmmaDesc &d, const CUtensorMap &tmap, int num_sms, cudaStream_t s);
+bool shift_ws_supported(const WaveArgs &a);
+uint32_t shift_ws_chunk(uint32_t mtiles, uint32_t tiles_n, uint32_t num_sms);
 cudaError_t mma_kernel_setup();        // same for the mma.sync kernel
 cudaError_t umma_kernel_setup();       // opt in to large dynamic shared memory (once per device)
 
@@ -176,6 +193,9 @@ cudaError_t launch_tiled_to_rowmajor(const uint4 *src_tiled, uint4 *dst_rows, ui
 // host f32 [C][W] <-> canvas rows (FP16, pitch), on the device
 cudaError_t launch_f32_to_canvas(const float *src, __half *dst, uint32_t rows, uint32_t width, uint32_t pitch, cudaStream_t s);
 cudaError_t launch_canvas_to_f32(const __half *src, float *dst, uint32_t rows, uint32_t width, uint32_t pitch, cudaStream_t s);
+// dense F32 [C][H][W] <-> haloed FP16 planes (row length wpad, plane stride cs; pixel (y, x) at (y + 1) * wpad + 4 + x)
+cudaError_t launch_f32_to_planes(const float *src, __half *dst, uint32_t c, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, cudaStream_t s);
+cudaError_t launch_planes_to_f32(const __half *src, float *dst, uint32_t c, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, cudaStream_t s);
 // counter-based normal fill: element i gets scale * N(0,1) from a stateless hash of (seed, i)
 cudaError_t launch_fill_normal_f16(__half *dst, uint64_t n, uint64_t seed, float scale, cudaStream_t s);
 

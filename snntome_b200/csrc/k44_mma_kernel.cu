@@ -110,8 +110,9 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
     const uint32_t j0 = (blockIdx.x / a.num_col_tiles64) * (MT * 16u);      // first neuron of this CTA
     const uint32_t g = j0 / a.group;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const __half *xbase = a.canvas + a.x_base_off + (uint64_t)tile * 64u;
-    const uint64_t x_limit = a.canvas_elems - a.x_base_off - (uint64_t)tile * 64u;       // exclusive bound for off + 64
+    const uint64_t tile_x = a.tile_off_x ? a.tile_off_x[tile] : (uint64_t)tile * 64u;          // where this tile's gathers are anchored (2-D planes: a table)
+    const __half *xbase = a.canvas + a.x_base_off + tile_x;
+    const uint64_t x_limit = a.canvas_elems - a.x_base_off - tile_x;       // exclusive bound for off + 64
     const uint32_t flen = a.frame_len ? a.frame_len : a.pitch;
     const uint32_t tile_in_frame = (tile * 64u) % flen;
     const uint32_t nk = a.num_kstages;
@@ -162,10 +163,10 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
             else { off = e; sh = a.shifts ? a.shifts[(uint64_t)g * a.fan_in + s] : 0u; }
             if (off + 64u > x_limit) { off = 0; bad = true; }   // record and skip instead of faulting
             const uint32_t dst_off = st * kXBytesStage + (k * kPitch + piece * 8u) * 2u;
-            if (sh == 0u && ((a.x_base_off + off) & 7u) == 0u) {
+            if (sh == 0u && ((a.x_base_off + tile_x + off) & 7u) == 0u) {
                 cp_async_16(xs + dst_off, xbase + off + piece * 8u);
             } else {
-                const uint64_t elem = a.x_base_off + (uint64_t)tile * 64u + off + piece * 8u;
+                const uint64_t elem = a.x_base_off + tile_x + off + piece * 8u;
                 uint4 val;
                 if (unaligned_in_range(a.canvas_elems, elem, sh)) {
                     const uint64_t first = elem - sh, lo = first & ~7ull;
@@ -243,6 +244,13 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
     // block. The finished values are parked in shared memory (the gather ring is free by now) and leave as whole 16-byte
     // pieces, 128 contiguous bytes per row — to this canvas and, in a sharded plan, to every peer's.
     const bool has_map = a.cout_map != nullptr;
+    uint64_t tile_y = (uint64_t)tile * 64u;                 // where this tile's outputs go inside a row / plane
+    uint32_t quad_mask = 0xffffu;
+    if (a.tile_off_y) {
+        const uint32_t e = a.tile_off_y[tile];
+        tile_y = a.tile_mask ? (uint64_t)(e & 0xffffu) << 2 : e;
+        if (a.tile_mask) quad_mask = e >> 16;
+    }
     __syncthreads();                        // every warp is done reading the last stage
     __half *const tile_out = reinterpret_cast<__half *>(xs_gen);       // [MT * 16][kPitch]
 #pragma unroll
@@ -259,7 +267,7 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
                 const uint32_t col = wc * (NW * 8u) + (uint32_t)n * 8u + (lane & 3u) * 2u;
                 float r0 = 0.f, r1 = 0.f;
                 if (a.has_residual) {
-                    const float2 rr = __half22float2(*reinterpret_cast<const __half2 *>(a.canvas + a.res_off + (uint64_t)oj * a.pitch + (uint64_t)tile * 64u + col));
+                    const float2 rr = __half22float2(*reinterpret_cast<const __half2 *>(a.canvas + a.res_off + (uint64_t)oj * a.pitch + tile_y + col));
                     r0 = rr.x; r1 = rr.y;
                 }
                 const float v0 = finish_value(acc[m][n][hrow * 2 + 0], b, r0, a.act, a.has_residual != 0, has_map);
@@ -268,6 +276,18 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
             }
         }
     __syncthreads();
+    if (a.tile_off_y) {
+        // 2-D planes: tiles start on 8-byte boundaries only and may cover halo elements: 4-element quads, masked
+#pragma unroll
+        for (uint32_t p = tid; p < MT * 16u * 16u; p += 128u) {
+            const uint32_t rl = p >> 4, qd = p & 15u;
+            const uint32_t j = j0 + rl;
+            if (j >= a.cout || !((quad_mask >> qd) & 1u)) continue;
+            const uint32_t oj = has_map ? a.cout_map[j] : j;
+            *reinterpret_cast<uint2 *>(a.canvas + a.y_off + (uint64_t)oj * a.pitch + tile_y + qd * 4u) =
+                *reinterpret_cast<const uint2 *>(tile_out + rl * kPitch + qd * 4u);
+        }
+    } else {
 #pragma unroll
     for (uint32_t p = tid; p < MT * 16u * 8u; p += 128u) {
         const uint32_t rl = p >> 3, pc = p & 7u;
@@ -278,6 +298,7 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
         const uint4 val = *reinterpret_cast<const uint4 *>(tile_out + rl * kPitch + pc * 8u);
         *reinterpret_cast<uint4 *>(a.canvas + off) = val;
         if (a.peers) store_to_peers(a.peers, off, val);
+    }
     }
     }   // peers_ready
     if (a.peers) {

@@ -210,9 +210,11 @@ k44_wave_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap, const __grid
             decode(it, mp, ct);
             const uint32_t *rows = a.gather + (uint64_t)((2u * mp) / a.mtiles_per_group) * a.boxes_per_group + 16u * rw;
             const __half *col0 = a.canvas + (uint64_t)ct * kTileN + rank * kHalfN + chunk * 8u;
+            uint32_t nxt = (KS && lane < 16u) ? __ldg(rows + lane) : 0u;          // table entries travel one stage ahead of their use
             for (uint32_t ks = 0; ks < KS && ok; ++ks, ++issued) {
                 const uint32_t stage = issued % kStages, ph = (issued / kStages) & 1u;
-                const uint32_t cur = lane < 16u ? __ldg(rows + (uint64_t)ks * kStageK + lane) : 0u;
+                const uint32_t cur = nxt;
+                if (ks + 1u < KS && lane < 16u) nxt = __ldg(rows + (uint64_t)(ks + 1u) * kStageK + lane);
                 uint32_t okw = 1u;
                 if (lane == 0) okw = wait(empty_bar + 8u * stage, ph ^ 1u) ? 1u : 0u;
                 ok = __shfl_sync(0xffffffffu, okw, 0) != 0u;

@@ -311,10 +311,18 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
         auto step = [&](Cursor &c) { if (++c.ks >= c.ks1) seek(c, c.item + gridDim.x); };
         Cursor f;
         seek(f, blockIdx.x);
+        // this warp's 16 table entries travel one stage ahead of their use, so that their latency hides behind the previous
+        // stage's copies instead of standing in front of every stage
+        uint32_t nxt = (f.valid && lane < 16u) ? __ldg(f.rows + (uint64_t)f.ks * kStageK + lane) : 0u;
         uint32_t issued = 0;
         while (f.valid && ok) {
             const uint32_t stage = issued % STAGES, ph = (issued / STAGES) & 1u;
-            const uint32_t cur = lane < 16u ? __ldg(f.rows + (uint64_t)f.ks * kStageK + lane) : 0u;     // this warp's 16 rows of the stage
+            const uint32_t cur = nxt;                                                                     // this warp's 16 rows of the stage
+            {
+                Cursor g = f;
+                step(g);
+                nxt = (g.valid && lane < 16u) ? __ldg(g.rows + (uint64_t)g.ks * kStageK + lane) : 0u;
+            }
             uint32_t okw = 1u;
             if (lane == 0) okw = wait(empty_bar + 8u * stage, ph ^ 1u) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, okw, 0) != 0u;

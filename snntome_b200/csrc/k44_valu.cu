@@ -534,6 +534,9 @@ cudaError_t launch_aux(const AuxArgs &a, bool pdl, cudaStream_t s) {
         if (e == cudaSuccess) e = launch_k(k44_valu_argmax_final_kernel, dim3((a.pitch + 255u) / 256u), dim3(256), pdl, s, a);
         break;
     }
+    case AUX_MAXPOOL2: case AUX_MAXPOOL5: case AUX_UPSAMPLE2: case AUX_S2D: case AUX_UPCONV_SCATTER: case AUX_HALO_CLEAR:
+        e = launch_image_aux(a, s);
+        break;
     default: return cudaErrorInvalidValue;
     }
     return e;

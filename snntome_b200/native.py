@@ -7,7 +7,7 @@ from typing import Optional
 
 import numpy as np
 
-from ._lib import WaveDesc, WaveInfo, get_lib, last_error
+from ._lib import PlaneGeom, WaveDesc, WaveInfo, get_lib, last_error
 from .plan import Plan, Wave
 
 PATH_AUTO, PATH_FMA, PATH_UMMA = -1, 0, 1
@@ -216,6 +216,38 @@ class NativePlan:
     def add_argmax(self, src_off: int, rows: int, advance: bool = False, max_seq: int = 0, name: str = "argmax") -> None:
         if self._lib.k44b_plan_add_argmax(self._ptr, name.encode(), int(src_off), int(rows), int(bool(advance)), int(max_seq)) != 0:
             raise NativeError(f"add_argmax: {last_error()}")
+
+    # -- 2-D image planes -------------------------------------------------------------------------------------------------
+    IMAGE_OPS = {"maxpool2": 7, "maxpool5": 8, "upsample2": 9, "space_to_depth": 10, "upconv_scatter": 11, "halo_clear": 12}
+
+    def add_image_wave(self, *, cout, group, fan_in, idx, weights, bias, y_off, act, plane_stride, tile_off_x, tile_off_y, tile_mask,
+                       has_residual=False, res_off=0, x_base_off=0, fan_in_raw=0, logical_cout=0, name="conv") -> None:
+        """A wave over haloed image planes: `idx` [cout // group, fan_in] tap offsets, `weights` [cout, fan_in] FP16 bits (host),
+        tile tables as described in include/k44b.h."""
+        keep = [np.ascontiguousarray(idx, dtype=np.uint32), np.ascontiguousarray(weights, dtype=np.uint16),
+                np.ascontiguousarray(tile_off_x, dtype=np.uint32), np.ascontiguousarray(tile_off_y, dtype=np.uint32),
+                np.ascontiguousarray(bias, dtype=np.uint16) if bias is not None else None, name.encode()]
+        d = WaveDesc()
+        d.cout, d.logical_cout, d.group, d.fan_in, d.fan_in_raw = int(cout), int(logical_cout or cout), int(group), int(fan_in), int(fan_in_raw or fan_in)
+        d.act, d.has_residual, d.y_off, d.res_off, d.x_base_off = int(act), int(bool(has_residual)), int(y_off), int(res_off), int(x_base_off)
+        d.idx, d.weights, d.weights_on_device = keep[0].ctypes.data, keep[1].ctypes.data, 0
+        d.tile_off_x, d.tile_off_y, d.num_tiles = keep[2].ctypes.data, keep[3].ctypes.data, int(keep[2].size)
+        d.tile_mask, d.plane_stride = int(bool(tile_mask)), int(plane_stride)
+        d.bias = keep[4].ctypes.data if keep[4] is not None else None
+        d.name = keep[5]
+        rc = self._lib.k44b_plan_add_wave(self._ptr, ctypes.byref(d))
+        del keep
+        if rc != 0:
+            raise NativeError(f"add_image_wave: {last_error()}")
+
+    def add_image_op(self, op: str, src_off: int, dst_off: int, planes: int, geom_in, geom_out, name: str = "") -> None:
+        """`op` in IMAGE_OPS; geometries are (h, w, w_pad, plane_stride) tuples (geom_in may be None for halo_clear)."""
+        gi = PlaneGeom(*[int(v) for v in geom_in]) if geom_in is not None else None
+        go = PlaneGeom(*[int(v) for v in geom_out])
+        rc = self._lib.k44b_plan_add_image_op(self._ptr, self.IMAGE_OPS[op], (name or op).encode(), int(src_off), int(dst_off), int(planes),
+                                              ctypes.byref(gi) if gi is not None else None, ctypes.byref(go))
+        if rc != 0:
+            raise NativeError(f"add_image_op: {last_error()}")
 
     def set_tokens(self, tokens, stream=None) -> None:
         t = np.ascontiguousarray(tokens, dtype=np.int32)

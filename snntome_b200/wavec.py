@@ -94,7 +94,8 @@ class WavePlan:
 
 
 class WaveGraph:
-    """Graph builder (reference: wavec/wavec.py:211-344). Only the nodes of 1-D wave plans compile."""
+    """Graph builder (reference: wavec/wavec.py:211-344). 1-D token plans and 2-D image plans (convolutions 1x1 / 3x3 with stride
+    1 or 2, max-pools 2x2 / 5x5, nearest upsampling, 2x2 transposed convolution) compile."""
 
     def __init__(self, max_B_per_wave: int = 288, default_S: int = 0, kv_cache_max_seq: int = 2048,
                  fold_rmsnorm_gamma: bool = True, reuse_canvas: bool = False, batch_size: int = 1, target: str = "auto"):
@@ -161,7 +162,7 @@ class WaveGraph:
         _check(self._lib.wavec_add_concat(self._handle, name.encode(), len(in_blobs), self._names(in_blobs), out_blob.encode()), "add_concat")
         return out_blob
 
-    # Nodes outside the wave path: kept so that callers get a clear error instead of an AttributeError.
+    # Weight-free nodes between waves.
     def add_rmsnorm(self, name, in_blob, out_blob, dim, gamma, eps=1e-5, pre_folded=False):
         g = np.ascontiguousarray(gamma, dtype=np.float32)
         _check(self._lib.wavec_add_rmsnorm(self._handle, name.encode(), in_blob.encode(), out_blob.encode(), int(dim),
@@ -181,6 +182,15 @@ class WaveGraph:
 
     def add_upsample2x(self, name, in_blob, out_blob):
         _check(self._lib.wavec_add_upsample2x(self._handle, name.encode(), in_blob.encode(), out_blob.encode()), "add_upsample2x")
+
+    def add_upconv2x2(self, name, in_blob, out_blob, cin, cout, weights, bias=None):
+        """2x2 / stride-2 transposed convolution; `weights` [cout, cin, 4] with phase q = 2 * (y & 1) + (x & 1) innermost
+        (the C entry point exists in the reference, wavec/k44_wave_executor.cu:761; its Python wrapper has no method for it)."""
+        w32 = np.ascontiguousarray(weights, dtype=np.float32)
+        b32 = np.ascontiguousarray(bias, dtype=np.float32) if bias is not None else None
+        _check(self._lib.wavec_add_upconv2x2(self._handle, name.encode(), in_blob.encode(), out_blob.encode(), int(cin), int(cout),
+                                             w32.ctypes.data_as(_f32p), b32.ctypes.data_as(_f32p) if b32 is not None else None), "add_upconv2x2")
+        return out_blob
 
     def set_output(self, out_blob: str) -> None:
         _check(self._lib.wavec_set_output(self._handle, out_blob.encode()), "set_output")

@@ -371,6 +371,33 @@ def test_token_shift_tensor_path_with_bias_residual_and_many_tiles():
     check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_UMMA), want)
 
 
+@pytest.mark.parametrize("frames,frame_len,run_len,runs,cout,group,chunk", [(2, 256, 16, 8, 384, 128, 0), (1, 1024, 16, 32, 256, 128, 0), (3, 128, 32, 4, 208, 208, 0),
+                                                                           (4, 512, 16, 32, 1280 + 64, 1280 + 64, 0), (2, 2048, 64, 8, 2560, 128, 3)])
+def test_token_shift_with_the_weight_tile_in_tensor_memory(frames, frame_len, run_len, runs, cout, group, chunk, monkeypatch):
+    """Fan-in up to 512: a work item is one neuron tile times a run of column tiles, its weights are copied shared memory ->
+    tensor memory once (tcgen05.cp) and every MMA reads A from there. Cases: one and several items per CTA, fan-in 128 .. 512,
+    a partial last neuron tile, a last run of column tiles shorter than the others, bias and residual."""
+    monkeypatch.setenv("K44B_SHIFT_WS", "2")
+    if chunk:
+        monkeypatch.setenv("K44B_WS_CHUNK", str(chunk))      # 20 neuron tiles x 11 runs of column tiles: more work items than SMs
+    plan = shifted_plan(900 + frame_len + run_len, rows_in=512, runs=runs, run_len=run_len, frames=frames, frame_len=frame_len, cout=cout, group=group, waves=2, act=ACT_SILU)
+    rng = np.random.default_rng(19)
+    for w in plan.waves:
+        w.bias = synth.f16_bits(rng.normal(0, 0.1, w.cout))
+    w1 = plan.waves[1]
+    w1.has_residual, w1.res_off = True, plan.waves[0].y_off
+    x = synth.random_input(plan, 29, dist="normal")
+    want = O.run_plan(plan, x)
+    npn = NativePlan.from_plan(plan, device=0)
+    for i in range(npn.num_waves):
+        info = npn.wave_info(i)
+        assert info.path == PATH_UMMA and info.n_tile == 128 and info.weights_in_tmem > 0, (info.path, info.n_tile, info.weights_in_tmem)
+    npn.close()
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_UMMA), want)
+    monkeypatch.setenv("K44B_SHIFT_WS", "0")           # and the kernel that streams the weights through shared memory
+    check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_UMMA), want)
+
+
 def test_token_shift_frames_that_split_a_tile_fall_back():
     plan = shifted_plan(133, runs=8, run_len=16, frames=2, frame_len=96, cout=256)
     x = synth.random_input(plan, 25, dist="normal")

@@ -150,11 +150,13 @@ def test_canvas_reuses_dead_tensors():
 
 def test_unsupported_nodes_are_refused():
     g = WaveGraph()
-    with pytest.raises(WaveError):
-        g.add_input("img", 3, 32, 32)
+    with pytest.raises(WaveError, match="multiple of 4"):
+        g.add_input("img", 3, 32, 30)                 # image widths come in whole 4-pixel quads
     g.add_input("x", 64, 1, 1, is_1d=True)
-    with pytest.raises(WaveError, match="not part of the wave path"):
-        g.add_maxpool("p", "x", "y")
+    with pytest.raises(WaveError, match="already has its input"):
+        g.add_input("img", 3, 32, 32)
+    with pytest.raises(WaveError, match="2-D image input"):
+        g.add_maxpool("p", "x", "y")                  # image nodes need an image graph
     with pytest.raises(WaveError, match="head_dim"):
         g.add_rope_gqa_attn("a", "x", "x", "x", "y", 2, 1, 32)
     with pytest.raises(WaveError):
