@@ -760,7 +760,7 @@ def build_shift_plan(c: dict, device: int):
         d = WaveDesc()
         d.cout = d.logical_cout = c["cout"]
         d.cin = avail
-        d.group, d.fan_in, d.fan_in_raw, d.act, d.has_residual = c["group"], fan_in, fan_in, 5, 0
+        d.group, d.fan_in, d.fan_in_raw, d.act, d.has_residual = c["group"], fan_in, fan_in, int(c.get("act", 5)), 0
         d.y_off = avail * pitch
         d.run_rows, d.run_len = starts.ctypes.data, c["run_len"]
         d.shifts, d.frame_len = shifts.ctypes.data, c["tokens"]
@@ -789,6 +789,7 @@ def shift_main(args) -> None:
     from snntome_b200.native import fill_normal_f16
     c = dict(SHIFT)
     c["max_shift"] = max(0, min(8, args.max_shift))
+    c["act"] = args.shift_act
     if args.scale != 1.0:
         c["sequences"] = max(1, int(round(c["sequences"] * args.scale)))
     plan, _tables = build_shift_plan(c, local_rank)
@@ -846,7 +847,7 @@ def shift_main(args) -> None:
                 "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
                 "config": {"workload": "token-shift receptive fields: sequences x 4096 tokens per GPU, 2048 input channels, 4 waves x 8192 neurons, "
-                                       "fan-in 512 = 32 runs of 16 channels, shift 0..7 tokens per run, groups of 128, GELU",
+                                       "fan-in 512 = 32 runs of 16 channels, shift 0..7 tokens per run, groups of 128, " + {0: "no activation", 1: "ReLU", 2: "sigmoid", 3: "SiLU", 4: "leaky ReLU", 5: "GELU"}.get(c["act"], "?"),
                            "sequences_per_gpu": c["sequences"], "columns_per_gpu": pitch, "scale": args.scale, "max_shift": c["max_shift"],
                            "l2_policy": "substrate (0.13 - 2.3 GB) exceeds the 126 MB L2; no explicit flush"},
                 "roofline": {"bound": "tensor", "kernel": (f"k44_wave_umma_shift_kernel<{infos[0].n_tile}>" if c["max_shift"] else f"k44_wave_umma_kernel<{infos[0].n_tile}>") if infos[0].path == 1 else ("k44_wave_mma_kernel" if infos[0].path == 3 else "k44_wave_fma_kernel"),
@@ -1044,7 +1045,7 @@ def tiny_main(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default: 10; 2000 / 1000 / 500 for the decode, decode-full and token-shift workloads, whose steps are 1 - 2 ms, so that the clock sampler sees the timed region)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", type=float, default=float(os.environ.get("K44B_BENCH_SCALE", "1.0")))
@@ -1056,11 +1057,14 @@ def main() -> None:
     ap.add_argument("--columns", type=int, default=64, help="ultra-sparse workload: valid columns (batch) per GPU, 1..64")
     ap.add_argument("--group", type=int, default=128, choices=[16, 32, 64, 128],
                     help="ultra-sparse workload: neurons sharing one gather list (below 128: the general mma.sync kernel)")
+    ap.add_argument("--shift-act", type=int, default=5, help="token-shift workload: activation code of its waves (5 = GELU as the configuration names; 0 = none, to separate the epilogue's share)")
     ap.add_argument("--max-shift", type=int, default=7, help="token-shift workload: largest token shift drawn per run (0 = unshifted runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sharded", action="store_true", help="with several GPUs: skip the neuron-sharded sub-measurement")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = {"decode": 2000, "decode-full": 1000, "token-shift": 500}.get(args.workload, 10)
     if args.workload in ("decode", "decode-full"):
         return decode_main(args)
     if args.workload == "pruned-sharded":

@@ -676,7 +676,8 @@ bool Executor::add_wave(const HostWave &w) {
                 dw.desc = make_umma_desc(128u, 0);
                 dw.desc.ws_chunk = shift_ws_chunk(mtiles, tiles64 / 2u, (uint32_t)num_sms_);
                 if (const char *e = std::getenv("K44B_WS_CHUNK")) { const int v = std::atoi(e); if (v > 0) dw.desc.ws_chunk = (uint32_t)v; }
-                if (const char *e = std::getenv("K44B_WS_GROUPS")) { const int v = std::atoi(e); if (v >= 1 && v <= 3) dw.desc.ws_groups = (uint32_t)v; }
+                if (const char *e = std::getenv("K44B_WS_VARIANT")) dw.desc.ws_variant = std::atoi(e) != 0 ? 1u : 0u;
+                if (const char *e = std::getenv("K44B_WS_GROUPS")) { const int v = std::atoi(e); if (v >= 1 && v <= 2) dw.desc.ws_groups = (uint32_t)v; }
                 n_tile = 128u;
             }
             ok = make_tensor_map(dw, std::min(n_tile, 128u) + 8u, false);   // aligned windows of up to 128 columns plus the 8 to their left, as plain rows

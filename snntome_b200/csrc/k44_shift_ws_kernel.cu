@@ -33,14 +33,17 @@ namespace shiftws {
 constexpr int kN = 128;                             // columns per tile
 constexpr int kTabEntries = 32;                     // run-table entries of one item (fan-in 512 in 16-row runs)
 constexpr int kMaxKS = 8;                           // 64-synapse steps whose weights fit tensor memory
-constexpr int SL = 6, SB = 3, SW = 2;               // window ring, operand ring, weight ring
-constexpr uint32_t kXBytes = 2u * kStageK * 128u;                // operand stage: two 64-column blocks
+constexpr int kSub = 2;                             // 64-synapse steps per ring stage: one barrier round trip serves two of them
+constexpr int SL0 = 3, SB0 = 2, SW = 2;             // window ring, operand ring (variant 1: 2 and 3 stages), weight ring (blocks of one step)
+constexpr uint32_t kXBytes = 2u * kStageK * 128u;                // operand of one step: two 64-column blocks
 constexpr uint32_t kRawPitch = (uint32_t)(kN + 8) * 2u;          // bytes per window row (17 chunks of 16 bytes)
-constexpr uint32_t kRawBytes = kStageK * kRawPitch;
+constexpr uint32_t kRawBytes = kStageK * kRawPitch;              // window of one step
+constexpr uint32_t kXStage = kSub * kXBytes, kRawStage = kSub * kRawBytes;
 constexpr uint32_t kTmemCols = 512u;                             // accumulators at columns 0 / 128, weights at 256..511
 constexpr uint32_t kATmemCol = 256u;
-constexpr uint32_t kOutStageBytes = 128u * 80u;
-constexpr uint32_t kSmemBytes = 1024u + (uint32_t)SL * kRawBytes + (uint32_t)SB * kXBytes + (uint32_t)SW * kStageWBytes + 256u + kOutStageBytes + 2u * kTabEntries * 4u;
+constexpr uint32_t kOutStageBytes = 2u * 128u * 80u;            // one padded slot per epilogue thread
+constexpr int kFirstAligner = 10;                   // warps 0 producer, 1 MMA, 2-5 and 6-9 epilogue, 10.. aligners
+constexpr uint32_t kSmemBytes = 1024u + (uint32_t)SL0 * kRawStage + (uint32_t)SB0 * kXStage + (uint32_t)SW * kStageWBytes + 256u + kOutStageBytes + 2u * kTabEntries * 4u;
 constexpr int OC = kN / 16;                         // 16-byte chunks one aligner lane produces per row
 
 __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
@@ -72,15 +75,16 @@ __device__ __forceinline__ void shift_and_store(const uint4 (&raw)[OC + 1], uint
     }
 }
 
-template <int AG>
-__global__ void __launch_bounds__(192 + 128 * AG, 1)
+template <int AG, int V>
+__global__ void __launch_bounds__(32 * kFirstAligner + 128 * AG, 1)
 k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a, const UmmaDesc d) {
+    constexpr int SL = V ? 2 : 3, SB = V ? 3 : 2;          // the two rings share the same bytes: 3 + 2 or 2 + 3 stages
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t w_smem = smem_base;                                        // SW weight blocks
     const uint32_t x_smem = w_smem + (uint32_t)SW * kStageWBytes;             // SB operand stages (swizzled)
-    const uint32_t raw_smem = x_smem + (uint32_t)SB * kXBytes;                // SL windows (plain rows)
-    const uint32_t ctl = raw_smem + (uint32_t)SL * kRawBytes;
+    const uint32_t raw_smem = x_smem + (uint32_t)SB * kXStage;                // SL windows (plain rows)
+    const uint32_t ctl = raw_smem + (uint32_t)SL * kRawStage;
     const uint32_t lfull_bar = ctl, lempty_bar = lfull_bar + 8u * SL;         // window ring
     const uint32_t bfull_bar = lempty_bar + 8u * SL, bempty_bar = bfull_bar + 8u * SB;   // operand ring
     const uint32_t wfull_bar = bempty_bar + 8u * SB, wempty_bar = wfull_bar + 8u * SW;   // weight ring
@@ -89,7 +93,7 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
     uint8_t *ctl_ptr = smem_raw + (ctl - ptx::smem_addr(smem_raw));
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(ctl_ptr + 16 * SL + 16 * SB + 16 * SW + 40);
     volatile uint32_t *abort_word = tmem_slot + 1;
-    volatile uint32_t *epi_ok = tmem_slot + 2;
+    volatile uint32_t *epi_ok = tmem_slot + 2;             // [group][tile parity]
     uint8_t *out_stage = ctl_ptr + 256;
     const uint32_t tab_smem = ctl + 256u + kOutStageBytes;                    // two run-table buffers of kTabEntries words
 
@@ -100,7 +104,8 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
     const uint32_t chunks = (tiles_n + chunk - 1u) / chunk;
     const uint32_t total_items = mtiles * chunks;
     const uint32_t KS = a.num_kstages;
-    const uint32_t boxes_per_stage = kStageK / a.box_h;
+    const uint32_t ST = (KS + (uint32_t)kSub - 1u) / (uint32_t)kSub;           // ring stages per tile
+    const uint32_t boxes_per_step = kStageK / a.box_h;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SL; ++s) {
@@ -117,7 +122,7 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(tfull_bar + 8u * b, 1);
-            ptx::mbar_init(tempty_bar + 8u * b, 128);
+            ptx::mbar_init(tempty_bar + 8u * b, 256);
         }
         ptx::mbar_init(adone_bar, 1);
         *abort_word = 0;
@@ -132,6 +137,7 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+        if (ptx::mbar_try_wait(bar, parity)) return true;      // the common case costs one instruction
         const long long t0 = clock64();
         for (uint32_t it = 0;; ++it) {
             if (ptx::mbar_try_wait(bar, parity)) return true;
@@ -149,7 +155,7 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
         ct1 = ct0 + chunk < tiles_n ? ct0 + chunk : tiles_n;
     };
     const uint32_t my_items = blockIdx.x < total_items ? (total_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
-    const uint32_t per_item = KS * boxes_per_stage;                            // table entries of one item (<= kTabEntries, checked by the launcher)
+    const uint32_t per_item = KS * boxes_per_step;                             // table entries of one item (<= kTabEntries, checked by the launcher)
 
     if (warp == 0) {
         // ---------------- producer: weights once per item, substrate windows per tile ----------------
@@ -170,36 +176,39 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncwarp();
             if (it + 1u < my_items) prefetch_entries(it + 1u);
-            if (lane < boxes_per_stage) {                      // lane b issues box b of every step; lane 0 also the weights and the byte counts
+            if (lane < (uint32_t)kSub * boxes_per_step) {       // lane b issues box b of every stage; lane 0 also the weights and the byte counts
                 uint32_t mt, ct0, ct1;
                 decode(blockIdx.x + it * gridDim.x, mt, ct0, ct1);
                 const uint4 *wsrc = a.w_tiles + (uint64_t)mt * KS * (kStageWBytes / 16u);
                 const uint32_t tab_it = tab_smem + (it & 1u) * (kTabEntries * 4u);
                 for (uint32_t ct = ct0; ct < ct1 && ok; ++ct) {
                     const int32_t x0 = (int32_t)(ct * (uint32_t)kN) - 8;          // columns left of the row start read as zero
-                    for (uint32_t ks = 0; ks < KS; ++ks, ++issued) {
+                    for (uint32_t st = 0; st < ST; ++st, ++issued) {
+                        const uint32_t nsub = min((uint32_t)kSub, KS - st * (uint32_t)kSub);
                         if (ct == ct0 && lane == 0) {
-                            const uint32_t ws = wissued % SW, wph = (wissued / SW) & 1u;
-                            ok = wait(wempty_bar + 8u * ws, wph ^ 1u);
-                            if (ok) {
-                                ptx::mbar_arrive_expect_tx(wfull_bar + 8u * ws, kStageWBytes);
-                                ptx::bulk_g2s(w_smem + ws * kStageWBytes, wsrc + (uint64_t)ks * (kStageWBytes / 16u), kStageWBytes, wfull_bar + 8u * ws, pol);
+                            for (uint32_t sb = 0; sb < nsub && ok; ++sb, ++wissued) {
+                                const uint32_t ws = wissued % SW, wph = (wissued / SW) & 1u;
+                                ok = wait(wempty_bar + 8u * ws, wph ^ 1u);
+                                if (ok) {
+                                    ptx::mbar_arrive_expect_tx(wfull_bar + 8u * ws, kStageWBytes);
+                                    ptx::bulk_g2s(w_smem + ws * kStageWBytes, wsrc + (uint64_t)(st * kSub + sb) * (kStageWBytes / 16u), kStageWBytes, wfull_bar + 8u * ws, pol);
+                                }
                             }
-                            ++wissued;
                         }
                         const uint32_t stage = issued % SL, ph = (issued / SL) & 1u;
-                        uint32_t e;
-                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(tab_it + (ks * boxes_per_stage + lane) * 4u) : "memory");
+                        const bool mine = lane < nsub * boxes_per_step;
+                        uint32_t e = 0;
+                        if (mine) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(tab_it + (st * (uint32_t)kSub * boxes_per_step + lane) * 4u) : "memory");
                         ok = ok && wait(lempty_bar + 8u * stage, ph ^ 1u);
                         if (!ok) break;
-                        if (lane == 0) ptx::mbar_arrive_expect_tx(lfull_bar + 8u * stage, kRawBytes);
-                        ptx::tma_load_2d(raw_smem + stage * kRawBytes + lane * a.box_h * kRawPitch, &tmap, x0, (int32_t)(e & kBoxRowMask), lfull_bar + 8u * stage, pol);
+                        if (lane == 0) ptx::mbar_arrive_expect_tx(lfull_bar + 8u * stage, nsub * kRawBytes);
+                        if (mine) ptx::tma_load_2d(raw_smem + stage * kRawStage + lane * a.box_h * kRawPitch, &tmap, x0, (int32_t)(e & kBoxRowMask), lfull_bar + 8u * stage, pol);
                     }
                 }
             }
             ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
             issued = __shfl_sync(0xffffffffu, issued, 0);
-            wissued = __shfl_sync(0xffffffffu, wissued, 0);
+            wissued = __shfl_sync(0xffffffffu, wissued, 0);       // (only lane 0 counts weight blocks)
             if (!ok) break;
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -240,27 +249,33 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
                     if (!ok) break;
                     ptx::tc_fence_after();
                     const uint32_t d_tmem = tmem_base + acc * kN;
-                    for (uint32_t ks = 0; ks < KS; ++ks, ++g) {
+                    for (uint32_t st = 0; st < ST; ++st, ++g) {
+                        const uint32_t nsub = min((uint32_t)kSub, KS - st * (uint32_t)kSub);
                         if (ct == ct0) {
-                            const uint32_t ws = wg % SW, wph = (wg / SW) & 1u;
-                            ok = wait(wfull_bar + 8u * ws, wph);
-                            if (!ok) break;
-                            ptx::tc_fence_after();
-                            const uint64_t a0 = d.a_base | (uint64_t)(((w_smem + ws * kStageWBytes) >> 4) & 0x3fffu);
+                            for (uint32_t sb = 0; sb < nsub && ok; ++sb, ++wg) {
+                                const uint32_t ws = wg % SW, wph = (wg / SW) & 1u, ks = st * (uint32_t)kSub + sb;
+                                ok = wait(wfull_bar + 8u * ws, wph);
+                                if (!ok) break;
+                                ptx::tc_fence_after();
+                                const uint64_t a0 = d.a_base | (uint64_t)(((w_smem + ws * kStageWBytes) >> 4) & 0x3fffu);
 #pragma unroll
-                            for (uint32_t k4 = 0; k4 < kStageK / 16u; ++k4)
-                                ptx::tmem_cp_128x256b(a_tmem + ks * 32u + k4 * 8u, a0 + (uint64_t)(k4 * d.a_k_step));
-                            ptx::umma_commit(wempty_bar + 8u * ws);       // block reusable once the copies have read it
-                            ++wg;
+                                for (uint32_t k4 = 0; k4 < kStageK / 16u; ++k4)
+                                    ptx::tmem_cp_128x256b(a_tmem + ks * 32u + k4 * 8u, a0 + (uint64_t)(k4 * d.a_k_step));
+                                ptx::umma_commit(wempty_bar + 8u * ws);       // block reusable once the copies have read it
+                            }
+                            if (!ok) break;
                         }
                         const uint32_t bs = g % SB, bph = (g / SB) & 1u;
                         ok = wait(bfull_bar + 8u * bs, bph);
                         if (!ok) break;
                         ptx::tc_fence_after();
-                        const uint64_t b0 = d.b_base | (uint64_t)(((x_smem + bs * kXBytes) >> 4) & 0x3fffu);
+                        for (uint32_t sb = 0; sb < nsub; ++sb) {
+                            const uint32_t ks = st * (uint32_t)kSub + sb;
+                            const uint64_t b0 = d.b_base | (uint64_t)(((x_smem + bs * kXStage + sb * kXBytes) >> 4) & 0x3fffu);
 #pragma unroll
-                        for (uint32_t k4 = 0; k4 < kStageK / 16u; ++k4)
-                            ptx::umma_f16_a_tmem(d_tmem, a_tmem + ks * 32u + k4 * 8u, b0 + (uint64_t)(k4 * d.b_k_step), d.idesc, (ks != 0u || k4 != 0u) ? 1u : 0u);
+                            for (uint32_t k4 = 0; k4 < kStageK / 16u; ++k4)
+                                ptx::umma_f16_a_tmem(d_tmem, a_tmem + ks * 32u + k4 * 8u, b0 + (uint64_t)(k4 * d.b_k_step), d.idesc, (ks != 0u || k4 != 0u) ? 1u : 0u);
+                        }
                         ptx::umma_commit(bempty_bar + 8u * bs);
                     }
                     if (ok) ptx::umma_commit(tfull_bar + 8u * acc);
@@ -273,9 +288,12 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
             }
         }
         __syncwarp();
-    } else if (warp < 6) {
-        // ---------------- epilogue ----------------
-        const uint32_t quarter = warp & 3u;
+    } else if (warp < (uint32_t)kFirstAligner) {
+        // ---------------- epilogue: two groups of four warps, 64 columns of every tile each ----------------
+        // (one warp per scheduler and group: a lone warp issues an instruction every several cycles, and at fan-in 512 the
+        // epilogue of a GELU wave costs more issue time than the tile's MMAs — one group alone bounded the kernel)
+        const uint32_t quarter = warp & 3u, eg = (warp - 2u) >> 2;
+        const uint32_t first_thread = 64u + 128u * eg;
         const bool has_map = a.cout_map != nullptr;
         bool ok = true;
         uint32_t tc = 0;
@@ -288,20 +306,20 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
             const float bias = (live && a.bias) ? __half2float(a.bias[j]) : 0.0f;
             for (uint32_t ct = ct0; ct < ct1 && ok; ++ct, ++tc) {
                 const uint32_t acc = tc & 1u;
-                if (threadIdx.x == 64u) epi_ok[tc & 1u] = wait(tfull_bar + 8u * acc, (tc >> 1) & 1u) ? 1u : 0u;
-                epilogue_bar_sync();
-                ok = epi_ok[tc & 1u] != 0u;
+                if (threadIdx.x == first_thread) epi_ok[2u * eg + (tc & 1u)] = wait(tfull_bar + 8u * acc, (tc >> 1) & 1u) ? 1u : 0u;
+                asm volatile("bar.sync %0, 128;" ::"r"(1u + eg) : "memory");
+                ok = epi_ok[2u * eg + (tc & 1u)] != 0u;
                 if (!ok) break;
                 ptx::tc_fence_after();
 #pragma unroll 1
-                for (uint32_t c0 = 0; c0 < (uint32_t)kN; c0 += 32u) {
+                for (uint32_t c0 = 64u * eg; c0 < 64u * eg + 64u; c0 += 32u) {
                     uint32_t v[32];
                     ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * kN + c0, v);
                     ptx::tmem_ld_wait();
                     float f[32];
 #pragma unroll
                     for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
-                    stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * kN + c0, out_stage + quarter * (32u * 80u), lane);
+                    stage_and_store(a, f, bias, has_map, live, oj, (uint64_t)ct * kN + c0, out_stage + (4u * eg + quarter) * (32u * 80u), lane);
                 }
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(tempty_bar + 8u * acc);
@@ -313,8 +331,8 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
         }
     } else {
         // ---------------- aligners ----------------
-        const uint32_t sw = (warp - 6u) & 3u;               // this warp: rows 16*sw .. 16*sw + 15 of every window of its group's steps
-        const uint32_t grp = (warp - 6u) >> 2;
+        const uint32_t sw = (warp - (uint32_t)kFirstAligner) & 3u;               // this warp: rows 16*sw .. 16*sw + 15 of every window of its group's steps
+        const uint32_t grp = (warp - (uint32_t)kFirstAligner) >> 2;
         const uint32_t r = lane & 15u, half = lane >> 4;    // 8 consecutive rows per shared-memory phase: conflict-free both ways
         const uint32_t krow = 16u * sw + r;
         const uint32_t first_chunk = half * (uint32_t)OC;
@@ -336,30 +354,31 @@ k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const Wa
             if (it + 1u < my_items) tab_next = fetch(it + 1u);
             for (uint32_t ct = ct0; ct < ct1 && ok; ++ct) {
                 const bool frame_start = ((ct * (uint32_t)kN) % flen) == 0u;     // the 8 columns to the left belong to another frame
-                for (uint32_t ks = 0; ks < KS; ++ks, ++g) {
+                for (uint32_t st = 0; st < ST; ++st, ++g) {
                     if (AG > 1 && g % (uint32_t)AG != grp) continue;
+                    const uint32_t nsub = min((uint32_t)kSub, KS - st * (uint32_t)kSub);
                     const uint32_t ls = g % SL, lph = (g / SL) & 1u, bs = g % SB, bph = (g / SB) & 1u;
-                    const uint32_t sh = __shfl_sync(0xffffffffu, tab, ks) >> 28;
-                    uint32_t okw = 1u;
-                    if (lane == 0) okw = (wait(lfull_bar + 8u * ls, lph) && wait(bempty_bar + 8u * bs, bph ^ 1u)) ? 1u : 0u;
-                    ok = __shfl_sync(0xffffffffu, okw, 0) != 0u;
+                    ok = __all_sync(0xffffffffu, (wait(lfull_bar + 8u * ls, lph) && wait(bempty_bar + 8u * bs, bph ^ 1u)) ? 1 : 0) != 0;
                     if (!ok) break;
-                    uint4 buf[OC + 1];
-                    const uint32_t src = raw_smem + ls * kRawBytes + krow * kRawPitch + first_chunk * 16u;
+                    for (uint32_t sb = 0; sb < nsub; ++sb) {
+                        const uint32_t sh = __shfl_sync(0xffffffffu, tab, st * (uint32_t)kSub + sb) >> 28;
+                        uint4 buf[OC + 1];
+                        const uint32_t src = raw_smem + ls * kRawStage + sb * kRawBytes + krow * kRawPitch + first_chunk * 16u;
 #pragma unroll
-                    for (int i = 0; i <= OC; ++i) buf[i] = lds_v4(src + 16u * (uint32_t)i);
-                    if (half == 0u && frame_start) buf[0] = make_uint4(0u, 0u, 0u, 0u);
-                    const uint32_t dst_row = x_smem + bs * kXBytes + krow * 128u;
-                    switch (sh) {
-                    case 0: shift_and_store<0>(buf, dst_row, first_chunk, krow); break;
-                    case 1: shift_and_store<1>(buf, dst_row, first_chunk, krow); break;
-                    case 2: shift_and_store<2>(buf, dst_row, first_chunk, krow); break;
-                    case 3: shift_and_store<3>(buf, dst_row, first_chunk, krow); break;
-                    case 4: shift_and_store<4>(buf, dst_row, first_chunk, krow); break;
-                    case 5: shift_and_store<5>(buf, dst_row, first_chunk, krow); break;
-                    case 6: shift_and_store<6>(buf, dst_row, first_chunk, krow); break;
-                    case 7: shift_and_store<7>(buf, dst_row, first_chunk, krow); break;
-                    default: shift_and_store<8>(buf, dst_row, first_chunk, krow); break;
+                        for (int i = 0; i <= OC; ++i) buf[i] = lds_v4(src + 16u * (uint32_t)i);
+                        if (half == 0u && frame_start) buf[0] = make_uint4(0u, 0u, 0u, 0u);
+                        const uint32_t dst_row = x_smem + bs * kXStage + sb * kXBytes + krow * 128u;
+                        switch (sh) {
+                        case 0: shift_and_store<0>(buf, dst_row, first_chunk, krow); break;
+                        case 1: shift_and_store<1>(buf, dst_row, first_chunk, krow); break;
+                        case 2: shift_and_store<2>(buf, dst_row, first_chunk, krow); break;
+                        case 3: shift_and_store<3>(buf, dst_row, first_chunk, krow); break;
+                        case 4: shift_and_store<4>(buf, dst_row, first_chunk, krow); break;
+                        case 5: shift_and_store<5>(buf, dst_row, first_chunk, krow); break;
+                        case 6: shift_and_store<6>(buf, dst_row, first_chunk, krow); break;
+                        case 7: shift_and_store<7>(buf, dst_row, first_chunk, krow); break;
+                        default: shift_and_store<8>(buf, dst_row, first_chunk, krow); break;
+                        }
                     }
                     ptx::fence_proxy_async();          // generic-proxy stores -> visible to the tensor core's async proxy
                     __syncwarp();
@@ -414,22 +433,22 @@ cudaError_t launch_wave_umma_shift_ws(const WaveArgs &a, const UmmaDesc &d, cons
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
+    using KernelFn = void (*)(const CUtensorMap, const WaveArgs, const UmmaDesc);
+    static const KernelFn fns[4] = {shiftws::k44_wave_umma_shift_ws_kernel<1, 0>, shiftws::k44_wave_umma_shift_ws_kernel<2, 0>,
+                                    shiftws::k44_wave_umma_shift_ws_kernel<1, 1>, shiftws::k44_wave_umma_shift_ws_kernel<2, 1>};
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        e = cudaFuncSetAttribute(shiftws::k44_wave_umma_shift_ws_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shiftws::kSmemBytes);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(shiftws::k44_wave_umma_shift_ws_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shiftws::kSmemBytes);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(shiftws::k44_wave_umma_shift_ws_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shiftws::kSmemBytes);
-        if (e != cudaSuccess) return e;
+        for (KernelFn f : fns) {
+            e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shiftws::kSmemBytes);
+            if (e != cudaSuccess) return e;
+        }
         attr_done[dev] = true;
     }
     const uint32_t mtiles = (a.cout + kTileM - 1) / kTileM;
     const uint32_t tiles_n = a.num_col_tiles64 / 2u;
     const uint32_t items = mtiles * ((tiles_n + d.ws_chunk - 1u) / d.ws_chunk);
     const uint32_t grid = items < (uint32_t)num_sms ? items : (uint32_t)num_sms;
-    switch (d.ws_groups) {
-    case 1: shiftws::k44_wave_umma_shift_ws_kernel<1><<<grid, 192 + 128, shiftws::kSmemBytes, s>>>(tmap, a, d); break;
-    case 3: shiftws::k44_wave_umma_shift_ws_kernel<3><<<grid, 192 + 384, shiftws::kSmemBytes, s>>>(tmap, a, d); break;
-    default: shiftws::k44_wave_umma_shift_ws_kernel<2><<<grid, 192 + 256, shiftws::kSmemBytes, s>>>(tmap, a, d); break;
-    }
+    const uint32_t ag = d.ws_groups == 1u ? 1u : 2u, v = d.ws_variant ? 1u : 0u;
+    fns[v * 2u + (ag - 1u)]<<<grid, 32 * shiftws::kFirstAligner + 128 * ag, shiftws::kSmemBytes, s>>>(tmap, a, d);
     return cudaGetLastError();
 }
 

@@ -115,6 +115,7 @@ k44_wave_umma_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a,
     const uint32_t tmem_base = *tmem_slot;
 
     auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+        if (ptx::mbar_try_wait(bar, parity)) return true;      // the common case costs one instruction
         const long long t0 = clock64();
         for (uint32_t it = 0;; ++it) {
             if (ptx::mbar_try_wait(bar, parity)) return true;

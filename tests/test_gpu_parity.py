@@ -132,6 +132,48 @@ def test_token_shift_offsets_use_general_path():
     check(plan, run_gpu(plan, x, PATH_AUTO, expect_path=PATH_MMA), O.run_plan(plan, x))
 
 
+@pytest.mark.parametrize("group,cout,tiles,residual,row_map", [(16, 96, 3, False, False), (32, 128, 2, True, False), (64, 192, 4, False, True),
+                                                              (128, 384, 3, True, True), (128, 256, 5, False, False)])
+def test_raw_offset_token_shifts_spread(group, cout, tiles, residual, row_map):
+    """The reference's own token-shift form: gather offsets that are a row start minus a few elements, so that a shifted tap
+    reads the tail of the previous canvas row at the start of its own (kernels/cuda/kernel44_cuda_pack.cuh:153-159) — no zero
+    padding, no frames. Groups of 16 .. 128 neurons with their own lists, several column tiles, bias, residual added after
+    or (with a row map) before the activation, on the general tensor kernel and on the FP32-FMA kernel."""
+    rng = np.random.default_rng(7000 + group + cout)
+    pitch, rows_in, B = 64 * tiles, 96, 96
+    groups = cout // group
+    shifts = rng.integers(0, 8, size=(groups, B))
+    rows = rng.integers(1, rows_in, size=(groups, B))
+    idx = (rows * pitch - shifts).astype(np.uint32)
+    w = synth.f16_bits(rng.normal(0, 0.15, (cout, B)))
+    bias = synth.f16_bits(rng.normal(0, 0.1, cout))
+    res_off = (rows_in + cout) * pitch
+    wave = Wave(cout=cout, group=group, fan_in=B, idx=idx, weights=w, bias=bias, y_off=rows_in * pitch, act=ACT_SILU,
+                has_residual=residual, res_off=res_off if residual else 0)
+    if row_map:
+        wave.cout_map = rng.permutation(cout).astype(np.uint16)
+    plan = Plan(canvas_elems=(rows_in + 2 * cout) * pitch, pitch=pitch, columns=pitch - 9, input_off=0, input_c=rows_in,
+                output_off=rows_in * pitch, output_c=cout, waves=[wave])
+    x = synth.random_input(plan, 33, dist="normal")
+    canvas0 = np.zeros(plan.canvas_elems, dtype=np.uint16)
+    canvas0[: x.size] = x.reshape(-1)
+    if residual:
+        canvas0[res_off: res_off + cout * pitch] = synth.f16_bits(rng.normal(0, 0.5, cout * pitch))
+    want = canvas0.copy()
+    O.wave_forward(want, wave, plan)
+    for path, expect in ((PATH_AUTO, PATH_MMA), (PATH_FMA, PATH_FMA)):
+        import torch
+        npn = NativePlan.from_plan(plan, device=0, force_path=path)
+        assert npn.wave_info(0).path == expect
+        cv = npn.canvas_tensor()
+        cv.copy_(torch.from_numpy(canvas0.view(np.int16)).cuda().view(torch.float16))
+        npn.execute()
+        assert npn.status() == 0
+        got = cv.cpu().numpy().view(np.uint16)
+        npn.close()
+        check(plan, got, want)
+
+
 def test_minimum_size_wave():
     plan = synth.dense_chain(seed=80, dims=[8, 3], columns=1, act=ACT_SIGMOID)
     assert plan.waves[0].cout == 16 and plan.waves[0].fan_in == 64
