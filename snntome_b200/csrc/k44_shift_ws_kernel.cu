@@ -1,23 +1,27 @@
 // Receptive-field token shift on the tensor cores with the weights held in tensor memory (sm_100a).
 //
-// The token-shift kernel of k44_shift_kernel.cu is bound by shared-memory bandwidth, not by the tensor pipe: per 64-synapse
-// step every byte of the realigned operand crosses shared memory four times (window written by the tensor copy, read by the
-// aligners, written back realigned, read by the MMA) and the weight block twice (written by the bulk copy, read by the MMA).
+// In the token-shift kernel of k44_shift_kernel.cu every byte of the realigned operand crosses shared memory four times per
+// 64-synapse step (window written by the tensor copy, read by the aligners, written back realigned, read by the MMA) and the
+// weight block twice (written by the bulk copy, read by the MMA), each with its own barrier round trip.
 // A wave whose fan-in is at most 512 has weight tiles of 128 neurons x 512 synapses = 128 KiB, which fit 256 of the 512
 // tensor-memory columns as the A operand of tcgen05.mma. This kernel therefore makes a work item one neuron tile times a
 // run of consecutive column tiles: the weight tile is copied shared memory -> tensor memory once per item (tcgen05.cp
 // 128x256b out of the same packed blocks the streaming kernels use), and every MMA of the item reads A from tensor memory,
 // so that in the steady state shared memory carries the substrate operand only.
 //
-//   warp 0      per item: the 16 KiB weight blocks of the neuron tile (bulk copies into a two-block ring), then per column tile
-//               and 64-synapse step the aligned window [t0 - 8, t0 + 128) of the step's substrate rows (one tensor copy per run);
-//   warps 6..   ("aligners", AG groups of four warps) realign the window rows by the run's shift into the 128-byte-swizzled
-//               operand ring; group g takes the steps g, g + AG, ...: a step is a chain of dependent latencies (barrier, shared-
-//               memory loads, shifts, stores, proxy fence, arrival) of about a thousand cycles for one group, four times the
-//               step's MMA time, so several steps have to be in flight;
-//   warp 1      one thread: tcgen05.cp of the weight blocks while the first column tile runs, tcgen05.mma (A in tensor memory,
-//               B = operand ring, M 128 x N 128 x K 16) into one of two accumulators;
-//   warps 2-5   epilogue out of tensor memory, overlapping the next tile.
+//   warp 0        per item: the 16 KiB weight blocks of the neuron tile (bulk copies into a two-block ring), then per column
+//                 tile and ring stage (two 64-synapse steps) the aligned windows [t0 - 8, t0 + 128) of the stage's substrate
+//                 rows (one tensor copy per run, one lane per copy);
+//   warp 1        one thread: tcgen05.cp of the weight blocks while the item's first column tile runs, tcgen05.mma (A in tensor
+//                 memory, B = operand ring, M 128 x N 128 x K 16, eight per stage) into one of two accumulators;
+//   warps 2-5, 6-9  epilogue out of tensor memory, one group per 64-column half of the tile, overlapping the next tile;
+//   warps 10..    ("aligners", AG groups of four warps) realign the window rows by the run's shift into the 128-byte-swizzled
+//                 operand ring; group g takes the stages g, g + AG, ...
+//
+// Why the roles look like this: a role that is one warp issues an instruction every ~9 cycles, so what bounds such a pipeline
+// is the number of barrier round trips and instructions per role and step, not bytes. Hence two steps per stage, a first
+// barrier try before the clock is read for the bounded wait, whole-warp waits in the aligners, and two groups for each of the
+// two roles with real arithmetic (with one epilogue group the GELU of a 128 x 128 tile took longer than the tile's MMAs).
 //
 // Items are numbered column-run-major, so that the CTAs working at the same time read the same columns of the substrate
 // and share them through L2. Every wait is bounded; on expiry the kernel records a status bit, stops and frees its tensor

@@ -76,6 +76,35 @@ def test_dense_chain_all_activations(act, path):
     check(plan, run_gpu(plan, x, path, expect_path=path), O.run_plan(plan, x))
 
 
+@pytest.mark.parametrize("act", [ACT_SIGMOID, ACT_SILU, ACT_GELU])
+@pytest.mark.parametrize("path", [PATH_UMMA, PATH_MMA, PATH_FMA])
+def test_smooth_activations_over_every_fp16_pre_activation(act, path):
+    """Every finite FP16 value in [-24, 24] (subnormals and both zeros included) goes through the epilogue as the
+    pre-activation: a wave whose neuron j copies input row j % 64 (one weight of 1.0). The tensor-core epilogue evaluates the
+    smooth activations with the hardware tanh and, for GELU, a fitted logit; the general kernels call expf / erff. All of them
+    must stay inside rtol 2e-3 / atol 1e-3 of the oracle's double-precision exp / erf forms over the whole range, in particular
+    on the negative tail where the result is tiny and only the absolute bound protects it."""
+    bits = np.arange(0x10000, dtype=np.uint32).astype(np.uint16)
+    vals = bits.view(np.float16).astype(np.float32)
+    bits = bits[np.isfinite(vals) & (np.abs(vals) <= 24.0)]
+    rows_in, cout = 64, 128
+    pitch = (bits.size + rows_in * 64 - 1) // (rows_in * 64) * 64
+    x = np.zeros((rows_in, pitch), dtype=np.uint16)
+    x.reshape(-1)[: bits.size] = np.random.default_rng(3).permutation(bits)
+    group = cout if path != PATH_MMA else 16               # groups of 16 with lists of their own: the general tensor kernel
+    groups = cout // group
+    idx = np.stack([np.roll(np.arange(64, dtype=np.uint32) * pitch, g) for g in range(groups)])      # group g lists row r at position (r + g) % 64
+    w = np.zeros((cout, 64), dtype=np.float16)
+    j = np.arange(cout)
+    w[j, (j % 64 + j // group) % 64] = 1.0
+    wave = Wave(cout=cout, group=group, fan_in=64, idx=idx, weights=w.view(np.uint16), bias=None, y_off=rows_in * pitch, act=act)
+    plan = Plan(canvas_elems=(rows_in + cout) * pitch, pitch=pitch, columns=pitch, input_off=0, input_c=rows_in,
+                output_off=rows_in * pitch, output_c=cout, waves=[wave])
+    want = O.run_plan(plan, x)
+    got = run_gpu(plan, x, PATH_AUTO if path == PATH_MMA else path, expect_path=path)
+    check(plan, got, want)
+
+
 @pytest.mark.parametrize("path", [PATH_FMA, PATH_UMMA])
 def test_ragged_sizes_and_tail_stage(path):
     # fan-in 96 (half-filled last stage), 80 output rows (partial 128-row tile), one group
@@ -516,7 +545,7 @@ def test_general_tensor_path_with_row_map_residual_and_partial_block():
 def test_scattered_single_rows_on_the_streaming_tensor_kernel(columns, n_tile, cout, rows_mode, monkeypatch):
     """Gather tables the way the reference's benchmark draws them — one sorted random row per synapse, no runs — on waves with
     more 128-neuron tiles than SMs: the streaming tcgen05 kernel fetches the rows itself, four per gather-mode tensor copy
-    (mode 2, the default) or one by one with row-fetching warps (mode 1). Tile widths 64 / 128 / 256, a partial last neuron
+    (mode 2) or one by one with row-fetching warps (mode 1, the default). Tile widths 64 / 128 / 256, a partial last neuron
     tile, valid columns that do not fill the last tile, a second wave that gathers rows the first one wrote; the FP32-FMA
     kernel reads the same table as the cross-check."""
     monkeypatch.setenv("K44B_N_TILE", str(n_tile))
