@@ -1042,6 +1042,151 @@ def tiny_main(args) -> None:
                       "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": int(npn.launch_count)}))
 
 
+def build_image_graph(size: int = 640, width: float = 1.0, seed: int = 7):
+    """A detector backbone + two neck stages in the style of the reference's image example (wavec/examples/example_yolov8.py):
+    3 x size x size input; 3x3 / stride-2 convolutions down to size / 32; C2f blocks (1x1, slice, n bottlenecks of two 3x3 with a
+    shortcut, concat, 1x1) of 32 / 64 / 128 / 256 channels; SPPF; nearest upsampling + concat + C2f back up to size / 8. SiLU
+    everywhere, random weights N(0, 1 / fan-in). Built with the reference's graph-builder calls."""
+    from snntome_b200.wavec import WaveGraph
+    rng = np.random.default_rng(seed)
+    ch = lambda c: max(16, int(round(c * width / 16)) * 16)
+
+    def wt(cout, cin, k):
+        return (rng.standard_normal((cout, cin, k, k)) * (1.0 / (cin * k * k)) ** 0.5).astype(np.float32), (rng.standard_normal(cout) * 0.02).astype(np.float32)
+
+    g = WaveGraph(max_B_per_wave=288, reuse_canvas=False)    # every tensor its own zero-initialised region: no halo clears between the waves
+    g.add_input("images", c=3, h=size, w=size, is_1d=False)
+    uid = [0]
+
+    def conv(x, cin, cout, k, stride=1, act="silu", res=None):
+        uid[0] += 1
+        y = f"t{uid[0]}"
+        w, b = wt(cout, cin, k)
+        g.add_conv2d(f"conv{uid[0]}", x, y, cin, cout, k, k, w, b, stride=stride, pad=k // 2, act=act, res_blob=res)
+        return y
+
+    def c2f(x, cin, cout, n, shortcut):
+        c = cout // 2
+        y = conv(x, cin, 2 * c, 1)
+        uid[0] += 1
+        a, b = f"t{uid[0]}a", f"t{uid[0]}b"
+        g.add_slice(f"split{uid[0]}", y, [a, b], [c, c])
+        parts, last = [a, b], b
+        for _ in range(n):
+            h = conv(last, c, c, 3)
+            last = conv(h, c, c, 3, res=last if shortcut else None)
+            parts.append(last)
+        uid[0] += 1
+        cat = f"t{uid[0]}"
+        g.add_concat(f"cat{uid[0]}", parts, cat)
+        return conv(cat, (2 + n) * c, cout, 1)
+
+    def sppf(x, c):
+        y = conv(x, c, c // 2, 1)
+        pools, last = [y], y
+        for i in range(3):
+            uid[0] += 1
+            p = f"t{uid[0]}"
+            g.add_maxpool(f"pool{uid[0]}", last, p, kernel_size=5, stride=1, pad=2)
+            pools.append(p); last = p
+        uid[0] += 1
+        cat = f"t{uid[0]}"
+        g.add_concat(f"cat{uid[0]}", pools, cat)
+        return conv(cat, 2 * c, c, 1)
+
+    def up_cat(x, skip):
+        uid[0] += 1
+        u, cat = f"t{uid[0]}u", f"t{uid[0]}c"
+        g.add_upsample2x(f"up{uid[0]}", x, u)
+        g.add_concat(f"cat{uid[0]}", [u, skip], cat)
+        return cat
+
+    c1, c2, c3, c4, c5 = ch(16), ch(32), ch(64), ch(128), ch(256)
+    x = conv("images", 3, c1, 3, stride=2)                 # size / 2
+    x = conv(x, c1, c2, 3, stride=2)                       # size / 4
+    x = c2f(x, c2, c2, 1, True)
+    x = conv(x, c2, c3, 3, stride=2)                       # size / 8
+    p3 = c2f(x, c3, c3, 2, True)
+    x = conv(p3, c3, c4, 3, stride=2)                      # size / 16
+    p4 = c2f(x, c4, c4, 2, True)
+    x = conv(p4, c4, c5, 3, stride=2)                      # size / 32
+    x = c2f(x, c5, c5, 1, True)
+    p5 = sppf(x, c5)
+    x = c2f(up_cat(p5, p4), c5 + c4, c4, 1, False)         # size / 16
+    out = c2f(up_cat(x, p3), c4 + c3, c3, 1, False)        # size / 8
+    g.set_output(out)
+    return g, rng
+
+
+def image_main(args) -> None:
+    """The 2-D image path: one detector-style network per inference through the reference-facing builder API. `value` times the
+    compiled plan replayed as one CUDA graph with the image resident in the canvas; `e2e` is `wavec_gpu_infer_f32` with a dense
+    host FP32 image in and the feature map out."""
+    import torch
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    size = max(128, int(round(640 * args.scale / 128)) * 128)      # every stride-2 convolution needs an input width that is a multiple of 8
+    t_build = time.perf_counter()
+    g, rng = build_image_graph(size)
+    plan = g.compile()
+    plan.init_gpu(device=local_rank)
+    build_s = time.perf_counter() - t_build
+    summ = plan.summary
+    x = rng.standard_normal((3, size, size)).astype(np.float32)
+    out, _ = plan.infer_f32(x)                               # fills the canvas with a real image, warms everything up
+    assert np.isfinite(out).all()
+    npn = plan.native
+    stream = torch.cuda.current_stream()
+    steps = args.steps if args.steps else 200
+    warmup = max(3, args.warmup)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(warmup):
+        npn.execute_graph(stream)
+    torch.cuda.synchronize()
+    l0 = npn.launch_count
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(steps):
+        npn.execute_graph(stream)
+    t1.record(stream)
+    torch.cuda.synchronize()
+    assert npn.status() == 0
+    ms_step = t0.elapsed_time(t1) / steps
+    launches = npn.launch_count - l0
+    clocks = sampler.stop()
+    e_steps = max(5, min(steps, 50))
+    t_e = time.perf_counter()
+    for _ in range(e_steps):
+        out, _ = plan.infer_f32(x)
+    e_ms = (time.perf_counter() - t_e) * 1e3 / e_steps
+    gflop = float(summ.get("total_gflops", 0.0))
+    kinds = {}
+    for c in summ.get("cmds", []):
+        kinds[c["type"]] = kinds.get(c["type"], 0) + 1
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    achieved = gflop / ms_step            # GFLOP / ms = TFLOP/s
+    print(json.dumps({"metric": "images/s (detector backbone + neck, one image per inference)", "value": 1e3 / ms_step, "unit": "images/s", "n_gpus": 1,
+                      "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+                      "config": {"workload": f"3 x {size} x {size} image; stride-2 3x3 convolutions to 1/32, C2f blocks of 32 / 64 / 128 / 256 channels, SPPF, two upsample + concat + C2f "
+                                             f"stages; SiLU; built with wavec_add_conv2d / _maxpool / _upsample2x / _slice / _concat", "image_size": size,
+                                 "commands": kinds, "gflop_per_image": gflop, "canvas_bytes": int(summ.get("canvas_bytes", 0)),
+                                 "l2_policy": "the whole canvas fits L2: launch- and latency-bound by construction (one image per inference)"},
+                      "roofline": {"bound": "tensor", "kernel": "k44_wave_mma_kernel (image tiles)", "achieved": achieved, "peak": peak,
+                                   "peak_kind": "of measured (burst dense bf16)" if peaks else "of fallback", "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None},
+                      "cpu_baseline": None,
+                      "e2e": {"value": 1e3 / e_ms, "unit": "images/s", "ms_per_step": e_ms, "steps": e_steps, "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": int(out.nbytes),
+                              "api": "wavec_gpu_infer_f32 (dense host FP32 image in, feature map out, blocking)"},
+                      "gpu_launches": int(launches), "build_and_upload_s": build_s, "clocks": clocks}))
+    plan.release_gpu()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1049,7 +1194,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", type=float, default=float(os.environ.get("K44B_BENCH_SCALE", "1.0")))
-    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "decode-full", "pruned-sharded", "token-shift", "tiny", "whitepaper"])
+    ap.add_argument("--workload", default="ultra-sparse", choices=["ultra-sparse", "decode", "decode-full", "pruned-sharded", "token-shift", "tiny", "whitepaper", "image"])
     ap.add_argument("--wp-row", default="g512_b2048_c4096", choices=sorted(WHITEPAPER_ROWS), help="whitepaper workload: which of the reference benchmark's rows")
     ap.add_argument("--wp-gen", default="rows", choices=["rows", "runs"], help="whitepaper workload: single sorted random rows (the reference's generator) or runs of 64 rows")
     ap.add_argument("--wp-unmerged", action="store_true", help="whitepaper workload: launch the 16 waves of a pass one by one instead of as one wave")
@@ -1064,7 +1209,7 @@ def main() -> None:
     ap.add_argument("--no-sharded", action="store_true", help="with several GPUs: skip the neuron-sharded sub-measurement")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"decode": 2000, "decode-full": 1000, "token-shift": 500}.get(args.workload, 10)
+        args.steps = {"decode": 2000, "decode-full": 1000, "token-shift": 500, "image": 500}.get(args.workload, 10)
     if args.workload in ("decode", "decode-full"):
         return decode_main(args)
     if args.workload == "pruned-sharded":
@@ -1075,6 +1220,8 @@ def main() -> None:
         return tiny_main(args)
     if args.workload == "whitepaper":
         return whitepaper_main(args)
+    if args.workload == "image":
+        return image_main(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -14,6 +14,7 @@
 // registers. Nothing here waits on another CTA; in a neuron-sharded plan one thread waits (bounded) for the peer GPUs' previous
 // launches before the first gather, every output pair is also stored into the peers' canvases, and the CTA that finishes
 // last publishes the launch count (same protocol as the tcgen05 kernels).
+#include <cstdlib>
 #include "k44_kernels.cuh"
 #include "k44_epilogue.cuh"
 
@@ -312,7 +313,12 @@ __global__ void __launch_bounds__(128) k44_wave_mma_kernel(const WaveArgs a, con
 cudaError_t launch_wave_mma(const WaveArgs &a, unsigned long long wait_cycles, cudaStream_t s) {
     if (a.group % 16u) return cudaErrorInvalidValue;
     // the CTA's neurons must share one gather list: 64, 32 or 16 of them, whichever divides the group
-    const uint32_t rows = a.group % 64u == 0u ? 64u : (a.group % 32u == 0u ? 32u : 16u);
+    uint32_t rows = a.group % 64u == 0u ? 64u : (a.group % 32u == 0u ? 32u : 16u);
+    // a wave with fewer CTAs than four per SM (the deep layers of an image network: a 20 x 20 map is 7 pixel tiles)
+    // is cut into smaller neuron blocks: each CTA gathers the same rows again, but they come out of L2 and the wave's time
+    // is its longest CTA's K loop, not its bytes
+    static const uint64_t min_blocks = [] { const char *e = std::getenv("K44B_MMA_MIN_BLOCKS"); const long v = e ? std::atol(e) : 0; return v > 0 ? (uint64_t)v : 592ull; }();
+    while (rows > 16u && (uint64_t)a.num_col_tiles64 * ((a.cout + rows - 1u) / rows) < min_blocks) rows >>= 1;
     const uint64_t blocks = (uint64_t)a.num_col_tiles64 * ((a.cout + rows - 1u) / rows);
     if (blocks == 0 || blocks > 0x7fffffffull) return cudaErrorInvalidValue;
     const dim3 grid((uint32_t)blocks);
