@@ -1206,6 +1206,7 @@ def main() -> None:
     ap.add_argument("--max-shift", type=int, default=7, help="token-shift workload: largest token shift drawn per run (0 = unshifted runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-pipeline", action="store_true", help="end to end with one blocking k44b_infer_f16 call per step only")
     ap.add_argument("--no-sharded", action="store_true", help="with several GPUs: skip the neuron-sharded sub-measurement")
     args = ap.parse_args()
     if args.steps is None:
@@ -1348,16 +1349,35 @@ def main() -> None:
             plan.infer_f16(h_in.data_ptr(), h_out.data_ptr(), stream)
         t1.record(stream)
         barrier()
-        e_ms = t0.elapsed_time(t1)
+        serial_ms = t0.elapsed_time(t1)
+        # the same steps with every step's upload running under the waves of the step before it (k44b_infer_f16_begin / _next):
+        # the first upload is outside the timed region, the upload started by the last timed step is inside it and waited for,
+        # so the region holds e_steps uploads, e_steps executions and e_steps downloads (host clock around blocking calls)
+        pipe_ms = None
+        if not args.no_pipeline:
+            plan.infer_f16_begin(h_in.data_ptr())
+            plan.infer_f16_next(h_in.data_ptr(), h_out.data_ptr(), stream)          # warm-up of the staging path; leaves one input staged
+            barrier()
+            w0 = time.perf_counter()
+            for _ in range(e_steps):
+                plan.infer_f16_next(h_in.data_ptr(), h_out.data_ptr(), stream)
+            torch.cuda.synchronize()                                                # the upload started by the last step (the plan's copy stream)
+            pipe_ms = (time.perf_counter() - w0) * 1e3
+            plan.infer_f16_next(0, 0, stream)                                       # outside the region: consume the staged input
+        e_ms = serial_ms if pipe_ms is None else min(serial_ms, pipe_ms)
+        pipelined = pipe_ms is not None and pipe_ms < serial_ms
         if dist is not None:
-            t = torch.tensor([e_ms], device="cuda")
+            t = torch.tensor([e_ms, serial_ms], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e_ms = float(t.item())
+            e_ms, serial_ms = float(t[0].item()), float(t[1].item())
         e2e = {"value": flops_step * world / (e_ms / e_steps * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e_ms / e_steps,
                "steps": e_steps, "h2d_bytes_per_step": in_elems * 2, "d2h_bytes_per_step": out_rows * 64 * 2,
-               "api": "k44b_infer_f16 (host FP16 rows in, last wave's rows out, pinned memory)",
+               "api": ("k44b_infer_f16_begin / k44b_infer_f16_next (host FP16 rows in, last wave's rows out, pinned memory; each step's upload runs under the previous step's waves)"
+                       if pipelined else "k44b_infer_f16 (host FP16 rows in, last wave's rows out, pinned memory)"),
+               "ms_per_step_one_blocking_call_per_step": serial_ms / e_steps,
                "host_copy_bound": {"upload_ms_alone_max_over_ranks": copy_ms, "upload_gbs_per_rank": in_elems * 2 / (copy_ms * 1e-3) / 1e9,
-                                   "bound_ms_per_step": copy_ms + ms_per_step, "frac_of_bound": (copy_ms + ms_per_step) / (e_ms / e_steps),
+                                   "bound_ms_per_step": (max(copy_ms, ms_per_step) if pipelined else copy_ms + ms_per_step),
+                                   "frac_of_bound": (max(copy_ms, ms_per_step) if pipelined else copy_ms + ms_per_step) / (e_ms / e_steps),
                                    "pinned_on_gpu_numa_node": numa_cpus is not None},
                "checksum": float(h_out[: 64 * 1024].float().abs().sum().item())}
         del h_in, h_out

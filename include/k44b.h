@@ -100,6 +100,15 @@ int k44b_execute_wave(void *plan, int wave, void *stream);
  * NULL to skip that copy). Copies and waves run on `stream`; returns once the output has arrived.
  * out_gpu_ms = device time of the waves only. Use pinned host memory for asynchronous copies. */
 int k44b_infer_f16(void *plan, const uint16_t *h_in, uint16_t *h_out, float *out_gpu_ms, void *stream);
+/* The same for a stream of inferences whose uploads should run under the previous inference's waves (the host link is the
+ * bottleneck of plans with large inputs): k44b_infer_f16_begin starts the upload of an input into a staging buffer of
+ * input_c * pitch * 2 bytes (allocated at the first call) on the plan's own copy stream and returns at once;
+ * k44b_infer_f16_next completes the inference whose input is staged — device copy into the canvas, waves, output download on
+ * `stream`, blocking like k44b_infer_f16 — and, if h_in_next is not NULL, starts the next upload before it waits. h_in must
+ * stay valid until the k44b_infer_f16_next call that consumes it returns. -1 when nothing is staged / the staging is occupied.
+ * No counterpart in the reference (wavec_gpu_infer_f32 is one blocking call, wavec/k44_wave_executor.cu:972-986). */
+int k44b_infer_f16_begin(void *plan, const uint16_t *h_in);
+int k44b_infer_f16_next(void *plan, const uint16_t *h_in_next, uint16_t *h_out, float *out_gpu_ms, void *stream);
 /* Synchronise the plan's device and fetch-and-clear the kernels' status word (0 = ok). Returns -1 and
  * sets the error text when the status is non-zero. */
 int k44b_status(void *plan, uint32_t *status);

@@ -85,6 +85,8 @@ PROTOTYPES = {
     "k44b_execute_graph": (c_int, [c_void_p, c_void_p]),
     "k44b_execute_wave": (c_int, [c_void_p, c_int, c_void_p]),
     "k44b_infer_f16": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(c_float), c_void_p]),
+    "k44b_infer_f16_begin": (c_int, [c_void_p, c_void_p]),
+    "k44b_infer_f16_next": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(c_float), c_void_p]),
     "k44b_status": (c_int, [c_void_p, POINTER(c_uint32)]),
     "k44b_infer_f32": (c_int, [c_void_p, _f32p, c_int, _f32p, c_int, _f32p]),
     "k44b_plan_add_rmsnorm": (c_int, [c_void_p, c_char_p, c_uint64, c_uint64, c_uint32, c_float, _u16p]),

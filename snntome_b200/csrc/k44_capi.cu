@@ -472,6 +472,16 @@ int k44b_execute_wave(void *plan, int wave, void *stream) {
     return P(plan)->exec.execute_wave((size_t)wave, (cudaStream_t)stream) ? 0 : set_error(P(plan)->exec.err);
 }
 
+int k44b_infer_f16_begin(void *plan, const uint16_t *h_in) {
+    if (!plan) return set_error("null plan");
+    return P(plan)->exec.infer_f16_begin(h_in) ? 0 : set_error(P(plan)->exec.err);
+}
+
+int k44b_infer_f16_next(void *plan, const uint16_t *h_in_next, uint16_t *h_out, float *out_gpu_ms, void *stream) {
+    if (!plan) return set_error("null plan");
+    return P(plan)->exec.infer_f16_next(h_in_next, h_out, out_gpu_ms, (cudaStream_t)stream) ? 0 : set_error(P(plan)->exec.err);
+}
+
 int k44b_infer_f16(void *plan, const uint16_t *h_in, uint16_t *h_out, float *out_gpu_ms, void *stream) {
     if (!plan) return set_error("null plan");
     return P(plan)->exec.infer_f16(h_in, h_out, out_gpu_ms, (cudaStream_t)stream) ? 0 : set_error(P(plan)->exec.err);

@@ -223,6 +223,11 @@ void Executor::release() {
     cudaFree(d_in_f32_); d_in_f32_ = nullptr;
     cudaFree(d_out_f32_); d_out_f32_ = nullptr;
     if (ev0_) { cudaEventDestroy(ev0_); ev0_ = nullptr; }
+    if (copy_stream_) { cudaStreamSynchronize(copy_stream_); cudaStreamDestroy(copy_stream_); copy_stream_ = nullptr; }
+    if (ev_uploaded_) { cudaEventDestroy(ev_uploaded_); ev_uploaded_ = nullptr; }
+    if (ev_stage_free_) { cudaEventDestroy(ev_stage_free_); ev_stage_free_ = nullptr; }
+    if (d_stage_in_) { cudaFree(d_stage_in_); d_stage_in_ = nullptr; }
+    stage_pending_ = false;
     if (ev1_) { cudaEventDestroy(ev1_); ev1_ = nullptr; }
     canvas_elems_ = 0;
     is_2d_ = false;
@@ -1038,6 +1043,58 @@ bool Executor::infer_f16(const uint16_t *h_in, uint16_t *h_out, float *gpu_ms, c
     if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
     const size_t in_b = (size_t)in_c_ * pitch_ * 2, out_b = (size_t)out_c_ * pitch_ * 2;
     if (h_in && in_b && !check(cudaMemcpyAsync(canvas_ + in_off_, h_in, in_b, cudaMemcpyHostToDevice, stream), "input upload")) return false;
+    if (!check(cudaEventRecord(ev0_, stream), "event record")) return false;
+    if (!execute(stream)) return false;
+    if (!check(cudaEventRecord(ev1_, stream), "event record")) return false;
+    if (h_out && out_b && !check(cudaMemcpyAsync(h_out, canvas_ + out_off_, out_b, cudaMemcpyDeviceToHost, stream), "output download")) return false;
+    if (!check(cudaStreamSynchronize(stream), "wave execution")) return false;
+    float t = 0.f;
+    cudaEventElapsedTime(&t, ev0_, ev1_);
+    if (gpu_ms) *gpu_ms = t;
+    uint32_t st = 0;
+    if (!check(cudaMemcpy(&st, d_status_, 4, cudaMemcpyDeviceToHost), "status read")) return false;
+    if (st) { recover_after_abort(); return fail(std::string("kernel status: ") + status_string(st)); }
+    return true;
+}
+
+// Pipelined host I/O: `begin` uploads an inference's input rows into a staging buffer on a copy stream of its own; `next`
+// completes that inference — staging -> canvas (device copy), waves, output download, all on `stream` — and, before it
+// waits, starts the upload of the following inference's input, which then runs under this inference's waves and download.
+// The staging buffer costs input_c * pitch * 2 bytes of device memory and one device copy per inference; what it buys is
+// that the host link never idles while the GPU computes.
+bool Executor::infer_f16_begin(const uint16_t *h_in) {
+    if (!ready()) return fail("executor not initialised");
+    if (!h_in) return fail("infer_f16_begin: null input");
+    if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
+    const size_t in_b = (size_t)in_c_ * pitch_ * 2;
+    if (!in_b) return fail("infer_f16_begin: the plan has no input rows");
+    if (!copy_stream_) {
+        if (!check(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking), "copy stream") ||
+            !check(cudaEventCreateWithFlags(&ev_uploaded_, cudaEventDisableTiming), "event") ||
+            !check(cudaEventCreateWithFlags(&ev_stage_free_, cudaEventDisableTiming), "event") ||
+            !check(cudaMalloc(&d_stage_in_, in_b), "staging buffer allocation"))
+            return false;
+    }
+    if (stage_pending_) return fail("infer_f16_begin: the staged input has not been consumed yet");
+    if (!check(cudaStreamWaitEvent(copy_stream_, ev_stage_free_, 0), "stream wait") ||        // (an event never recorded counts as complete)
+        !check(cudaMemcpyAsync(d_stage_in_, h_in, in_b, cudaMemcpyHostToDevice, copy_stream_), "input upload") ||
+        !check(cudaEventRecord(ev_uploaded_, copy_stream_), "event record"))
+        return false;
+    stage_pending_ = true;
+    return true;
+}
+
+bool Executor::infer_f16_next(const uint16_t *h_in_next, uint16_t *h_out, float *gpu_ms, cudaStream_t stream) {
+    if (!ready()) return fail("executor not initialised");
+    if (!stage_pending_) return fail("infer_f16_next: no staged input (call infer_f16_begin first)");
+    if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
+    const size_t in_b = (size_t)in_c_ * pitch_ * 2, out_b = (size_t)out_c_ * pitch_ * 2;
+    if (!check(cudaStreamWaitEvent(stream, ev_uploaded_, 0), "stream wait") ||
+        !check(cudaMemcpyAsync(canvas_ + in_off_, d_stage_in_, in_b, cudaMemcpyDeviceToDevice, stream), "staging copy") ||
+        !check(cudaEventRecord(ev_stage_free_, stream), "event record"))
+        return false;
+    stage_pending_ = false;
+    if (h_in_next && !infer_f16_begin(h_in_next)) return false;          // runs under the waves below
     if (!check(cudaEventRecord(ev0_, stream), "event record")) return false;
     if (!execute(stream)) return false;
     if (!check(cudaEventRecord(ev1_, stream), "event record")) return false;

@@ -83,6 +83,9 @@ class Executor {
     bool execute_graph(cudaStream_t stream);                      // replay the wave list as one CUDA graph
     // host FP16 rows in canvas layout ([input_c][pitch] in, [output_c][pitch] out), copies on `stream`
     bool infer_f16(const uint16_t *h_in, uint16_t *h_out, float *gpu_ms, cudaStream_t stream);
+    // the same with the next inference's upload running under this inference's waves (staging buffer + copy stream)
+    bool infer_f16_begin(const uint16_t *h_in);
+    bool infer_f16_next(const uint16_t *h_in_next, uint16_t *h_out, float *gpu_ms, cudaStream_t stream);
     bool execute_timed(float *ms);                                 // default stream, event-timed, synchronous
     bool infer_f32(const float *h_in, int in_elems, float *h_out, int out_elems, float *gpu_ms);
     bool read_status(uint32_t *status);                            // synchronises the device
@@ -138,6 +141,10 @@ class Executor {
     uint32_t in_c_ = 0, out_c_ = 0, io_width_ = 0;
     float *d_in_f32_ = nullptr, *d_out_f32_ = nullptr;
     cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+    __half *d_stage_in_ = nullptr;                  // staging copy of the input rows for pipelined host I/O
+    cudaStream_t copy_stream_ = nullptr;
+    cudaEvent_t ev_uploaded_ = nullptr, ev_stage_free_ = nullptr;
+    bool stage_pending_ = false;
     uint64_t launches_ = 0;
     float *d_scratch_ = nullptr;
     uint32_t *d_counters_ = nullptr;

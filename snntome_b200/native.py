@@ -184,6 +184,20 @@ class NativePlan:
             raise NativeError(f"infer_f16: {last_error()}")
         return float(ms.value)
 
+    def infer_f16_begin(self, h_in_ptr: int) -> None:
+        """Start uploading an inference's input (host FP16 rows, pinned) into the staging buffer; returns at once."""
+        if self._lib.k44b_infer_f16_begin(self._ptr, ctypes.c_void_p(h_in_ptr)) != 0:
+            raise NativeError(f"infer_f16_begin: {last_error()}")
+
+    def infer_f16_next(self, h_in_next_ptr: int, h_out_ptr: int, stream=None) -> float:
+        """Complete the staged inference (blocking) and, if `h_in_next_ptr` is not 0, start the next upload under its waves."""
+        ms = ctypes.c_float(0.0)
+        rc = self._lib.k44b_infer_f16_next(self._ptr, ctypes.c_void_p(h_in_next_ptr or None), ctypes.c_void_p(h_out_ptr or None), ctypes.byref(ms),
+                                           ctypes.c_void_p(self._stream_ptr(stream)))
+        if rc != 0:
+            raise NativeError(f"infer_f16_next: {last_error()}")
+        return float(ms.value)
+
     # -- element-wise / attention commands between waves ----------------------------------------------------------
     def add_rmsnorm(self, src_off: int, dst_off: int, dim: int, eps: float = 1e-5, gamma_bits=None, name: str = "rmsnorm") -> None:
         g = None

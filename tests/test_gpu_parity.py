@@ -608,3 +608,33 @@ def test_tiles_of_256_neurons_share_one_operand(case, mode, monkeypatch):
     assert npn.status() == 0
     check(plan, canvas.cpu().numpy().view(np.uint16), want)
     npn.close()
+
+
+def test_pipelined_host_io_gives_the_same_rows_as_blocking_calls():
+    """k44b_infer_f16_begin / k44b_infer_f16_next: three different inputs in a row, each upload started while the inference before
+    it runs; every output must equal what one blocking k44b_infer_f16 call returns for the same input, and the misuse cases
+    (nothing staged, staging occupied) are refused."""
+    import torch
+    plan = synth.sparse_plan(seed=910, input_rows=2048, waves=2, cout=384, runs=8, run_len=32, columns=64, group=128, act=ACT_RELU)
+    npn = NativePlan.from_plan(plan, device=0)
+    in_elems, out_elems = plan.input_c * plan.pitch, plan.output_c * plan.pitch
+    xs = [torch.from_numpy(synth.random_input(plan, 920 + i, dist="normal").view(np.int16).reshape(-1).copy()).pin_memory() for i in range(3)]
+    outs = [torch.zeros(out_elems, dtype=torch.int16).pin_memory() for _ in range(3)]
+    want = []
+    for x in xs:
+        o = torch.zeros(out_elems, dtype=torch.int16).pin_memory()
+        npn.infer_f16(x.data_ptr(), o.data_ptr())
+        want.append(o.clone())
+        assert xs[0].numel() == in_elems
+    with pytest.raises(native.NativeError, match="no staged input"):
+        npn.infer_f16_next(0, outs[0].data_ptr())
+    npn.infer_f16_begin(xs[0].data_ptr())
+    with pytest.raises(native.NativeError, match="not been consumed"):
+        npn.infer_f16_begin(xs[1].data_ptr())
+    npn.infer_f16_next(xs[1].data_ptr(), outs[0].data_ptr())
+    npn.infer_f16_next(xs[2].data_ptr(), outs[1].data_ptr())
+    npn.infer_f16_next(0, outs[2].data_ptr())
+    for got, w in zip(outs, want):
+        assert torch.equal(got, w)
+    assert not torch.equal(want[0], want[1])
+    npn.close()
