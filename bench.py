@@ -1042,7 +1042,7 @@ def tiny_main(args) -> None:
                       "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": int(npn.launch_count)}))
 
 
-def build_image_graph(size: int = 640, width: float = 1.0, seed: int = 7):
+def build_image_graph(size: int = 640, width: float = 1.0, seed: int = 7, frames: int = 1):
     """A detector backbone + two neck stages in the style of the reference's image example (wavec/examples/example_yolov8.py):
     3 x size x size input; 3x3 / stride-2 convolutions down to size / 32; C2f blocks (1x1, slice, n bottlenecks of two 3x3 with a
     shortcut, concat, 1x1) of 32 / 64 / 128 / 256 channels; SPPF; nearest upsampling + concat + C2f back up to size / 8. SiLU
@@ -1054,7 +1054,7 @@ def build_image_graph(size: int = 640, width: float = 1.0, seed: int = 7):
     def wt(cout, cin, k):
         return (rng.standard_normal((cout, cin, k, k)) * (1.0 / (cin * k * k)) ** 0.5).astype(np.float32), (rng.standard_normal(cout) * 0.02).astype(np.float32)
 
-    g = WaveGraph(max_B_per_wave=288, reuse_canvas=False)    # every tensor its own zero-initialised region: no halo clears between the waves
+    g = WaveGraph(max_B_per_wave=288, reuse_canvas=False, batch_size=frames)    # every tensor its own zero-initialised region: no halo clears between the waves
     g.add_input("images", c=3, h=size, w=size, is_1d=False)
     uid = [0]
 
@@ -1127,12 +1127,13 @@ def image_main(args) -> None:
     torch.cuda.set_device(local_rank)
     size = max(128, int(round(640 * args.scale / 128)) * 128)      # every stride-2 convolution needs an input width that is a multiple of 8
     t_build = time.perf_counter()
-    g, rng = build_image_graph(size)
+    frames = max(1, args.frames)
+    g, rng = build_image_graph(size, frames=frames)
     plan = g.compile()
     plan.init_gpu(device=local_rank)
     build_s = time.perf_counter() - t_build
     summ = plan.summary
-    x = rng.standard_normal((3, size, size)).astype(np.float32)
+    x = rng.standard_normal((frames, 3, size, size) if frames > 1 else (3, size, size)).astype(np.float32)
     out, _ = plan.infer_f32(x)                               # fills the canvas with a real image, warms everything up
     assert np.isfinite(out).all()
     npn = plan.native
@@ -1171,17 +1172,17 @@ def image_main(args) -> None:
         pass
     peak = float(peaks.get("bf16_tflops", 1590.0))
     achieved = gflop / ms_step            # GFLOP / ms = TFLOP/s
-    print(json.dumps({"metric": "images/s (detector backbone + neck, one image per inference)", "value": 1e3 / ms_step, "unit": "images/s", "n_gpus": 1,
+    print(json.dumps({"metric": f"images/s (detector backbone + neck, {frames} image{'s' if frames > 1 else ''} per inference)", "value": frames * 1e3 / ms_step, "unit": "images/s", "n_gpus": 1,
                       "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                       "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
                       "config": {"workload": f"3 x {size} x {size} image; stride-2 3x3 convolutions to 1/32, C2f blocks of 32 / 64 / 128 / 256 channels, SPPF, two upsample + concat + C2f "
-                                             f"stages; SiLU; built with wavec_add_conv2d / _maxpool / _upsample2x / _slice / _concat", "image_size": size,
+                                             f"stages; SiLU; built with wavec_add_conv2d / _maxpool / _upsample2x / _slice / _concat", "image_size": size, "frames_per_inference": frames,
                                  "commands": kinds, "gflop_per_image": gflop, "canvas_bytes": int(summ.get("canvas_bytes", 0)),
-                                 "l2_policy": "the whole canvas fits L2: launch- and latency-bound by construction (one image per inference)"},
+                                 "l2_policy": "the whole canvas fits L2 at one frame: launch- and latency-bound by construction"},
                       "roofline": {"bound": "tensor", "kernel": "k44_wave_mma_kernel (image tiles)", "achieved": achieved, "peak": peak,
                                    "peak_kind": "of measured (burst dense bf16)" if peaks else "of fallback", "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None},
                       "cpu_baseline": None,
-                      "e2e": {"value": 1e3 / e_ms, "unit": "images/s", "ms_per_step": e_ms, "steps": e_steps, "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": int(out.nbytes),
+                      "e2e": {"value": frames * 1e3 / e_ms, "unit": "images/s", "ms_per_step": e_ms, "steps": e_steps, "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": int(out.nbytes),
                               "api": "wavec_gpu_infer_f32 (dense host FP32 image in, feature map out, blocking)"},
                       "gpu_launches": int(launches), "build_and_upload_s": build_s, "clocks": clocks}))
     plan.release_gpu()
@@ -1204,6 +1205,7 @@ def main() -> None:
                     help="ultra-sparse workload: neurons sharing one gather list (below 128: the general mma.sync kernel)")
     ap.add_argument("--shift-act", type=int, default=5, help="token-shift workload: activation code of its waves (5 = GELU as the configuration names; 0 = none, to separate the epilogue's share)")
     ap.add_argument("--max-shift", type=int, default=7, help="token-shift workload: largest token shift drawn per run (0 = unshifted runs)")
+    ap.add_argument("--frames", type=int, default=1, help="image workload: images per inference (wavec_set_batch_size; at most 9 at 640 x 640)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-pipeline", action="store_true", help="end to end with one blocking k44b_infer_f16 call per step only")

@@ -10,8 +10,8 @@
  *     1x1 (stride 1, pad 0) and 3x3 (pad 1, stride 1 or 2) with bias / activation / residual, split / slice / concat,
  *     max-pool 2x2 stride 2 and 5x5 stride 1 pad 2, nearest 2x upsampling, 2x2 stride-2 transposed convolution. Planes are
  *     stored with one halo row above and below and four halo elements left (kernels/common/kernel44_valu_pack.cuh:30-103);
- *     wavec_gpu_infer_f32 takes and returns dense [c][h][w] FP32 images. A call outside that set (flatten, other kernel
- *     sizes, mixing the two kinds of graph) returns -1 and leaves the graph unchanged;
+ *     wavec_gpu_infer_f32 takes and returns dense [c][h][w] FP32 images ([frame][c][h][w] after wavec_set_batch_size(frames)).
+ *     A call outside that set (flatten, other kernel sizes, mixing the two kinds of graph) returns -1 and leaves the graph unchanged;
  *   - activation value 5 selects GELU in addition to the reference's 0-4. The tensor-core kernels evaluate the smooth
  *     activations with the hardware tanh (relative error up to 2^-11): sigmoid = 0.5 + 0.5 tanh(v / 2), SiLU likewise, GELU
  *     as v (0.5 + 0.5 tanh(v P(v^2) / 2)) with a fitted quadratic P whose exact form is at most 2.6e-5 (absolute) away

@@ -427,9 +427,14 @@ bool Executor::add_aux(const HostWave &w) {
         const auto &gi = w.in2d, &go = w.out2d;
         x.h_in = gi.H; x.w_in = gi.W; x.wpad_in = gi.W_pad; x.cs_in = gi.ch_stride;
         x.h_out = go.H; x.w_out = go.W; x.wpad_out = go.W_pad; x.cs_out = go.ch_stride;
+        x.frames = std::max(1u, go.frames);
+        x.fs_in = gi.frame_stride ? gi.frame_stride : gi.ch_stride; x.fs_out = go.frame_stride ? go.frame_stride : go.ch_stride;
+        if (w.kind != AUX_HALO_CLEAR && std::max(1u, gi.frames) != x.frames) return fail("image command '" + w.name + "': input and output hold different numbers of frames");
+        if ((uint64_t)x.frames * x.fs_out > go.ch_stride || (w.kind != AUX_HALO_CLEAR && (uint64_t)x.frames * x.fs_in > gi.ch_stride))
+            return fail("image command '" + w.name + "': the frames do not fit the channel stride");
         const uint32_t src_planes = w.kind == AUX_UPCONV_SCATTER ? 4u * w.cout : w.cout;
         const uint32_t dst_planes = w.kind == AUX_S2D ? 4u * w.cout : w.cout;
-        auto plane_ok = [&](const HostWave::Geom2D &g) { return g.H && g.W && g.W_pad >= g.W + 4u && (uint64_t)(g.H + 2u) * g.W_pad <= (uint64_t)g.ch_stride + 8u; };
+        auto plane_ok = [&](const HostWave::Geom2D &g) { return g.H && g.W && g.W_pad >= g.W + 4u && (uint64_t)(g.H + 2u) * g.W_pad <= (uint64_t)(g.frame_stride ? g.frame_stride : g.ch_stride) + 8u; };
         if (!w.cout || !plane_ok(go) || (w.kind != AUX_HALO_CLEAR && !plane_ok(gi))) return fail("image command '" + w.name + "': bad plane geometry");
         if (w.y_off + (uint64_t)dst_planes * go.ch_stride > canvas_elems_) return fail("image command '" + w.name + "' writes outside the canvas");
         if (w.kind != AUX_HALO_CLEAR && w.src_off + (uint64_t)src_planes * gi.ch_stride > canvas_elems_) return fail("image command '" + w.name + "' reads outside the canvas");
@@ -1242,21 +1247,21 @@ bool Executor::execute_timed(float *ms) {
 bool Executor::infer_f32(const float *h_in, int in_elems, float *h_out, int out_elems, float *gpu_ms) {
     if (!ready()) return fail("executor not initialised");
     if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
-    const size_t in_n = is_2d_ ? (size_t)in_c_ * in2d_.H * in2d_.W : (size_t)in_c_ * io_width_;
-    const size_t out_n = is_2d_ ? (size_t)out_c_ * out2d_.H * out2d_.W : (size_t)out_c_ * io_width_;
+    const size_t in_n = is_2d_ ? (size_t)std::max(1u, in2d_.frames) * in_c_ * in2d_.H * in2d_.W : (size_t)in_c_ * io_width_;
+    const size_t out_n = is_2d_ ? (size_t)std::max(1u, out2d_.frames) * out_c_ * out2d_.H * out2d_.W : (size_t)out_c_ * io_width_;
     if (in_elems < 0 || (size_t)in_elems < in_n) return fail("input has fewer elements than the plan's input tensor");
     if (!d_in_f32_ && !check(cudaMalloc(&d_in_f32_, std::max<size_t>(in_n, 1) * 4), "input staging")) return false;
     if (!d_out_f32_ && !check(cudaMalloc(&d_out_f32_, std::max<size_t>(out_n, 1) * 4), "output staging")) return false;
     if (!check(cudaMemcpyAsync(d_in_f32_, h_in, in_n * 4, cudaMemcpyHostToDevice, nullptr), "input upload")) return false;
     if (is_2d_) {
-        if (!check(launch_f32_to_planes(d_in_f32_, canvas_ + in_off_, in_c_, in2d_.H, in2d_.W, in2d_.W_pad, in2d_.ch_stride, nullptr), "input conversion")) return false;
+        if (!check(launch_f32_to_planes(d_in_f32_, canvas_ + in_off_, in_c_, in2d_.H, in2d_.W, in2d_.W_pad, in2d_.ch_stride, std::max(1u, in2d_.frames), in2d_.frame_stride ? in2d_.frame_stride : in2d_.ch_stride, nullptr), "input conversion")) return false;
     } else if (!check(launch_f32_to_canvas(d_in_f32_, canvas_ + in_off_, in_c_, io_width_, pitch_, nullptr), "input conversion")) return false;
     ++launches_;
     if (!check(cudaEventRecord(ev0_, nullptr), "event record")) return false;
     if (!execute(nullptr)) return false;
     if (!check(cudaEventRecord(ev1_, nullptr), "event record")) return false;
     if (is_2d_) {
-        if (!check(launch_planes_to_f32(canvas_ + out_off_, d_out_f32_, out_c_, out2d_.H, out2d_.W, out2d_.W_pad, out2d_.ch_stride, nullptr), "output conversion")) return false;
+        if (!check(launch_planes_to_f32(canvas_ + out_off_, d_out_f32_, out_c_, out2d_.H, out2d_.W, out2d_.W_pad, out2d_.ch_stride, std::max(1u, out2d_.frames), out2d_.frame_stride ? out2d_.frame_stride : out2d_.ch_stride, nullptr), "output conversion")) return false;
     } else if (!check(launch_canvas_to_f32(canvas_ + out_off_, d_out_f32_, out_c_, io_width_, pitch_, nullptr), "output conversion")) return false;
     ++launches_;
     const size_t copy_n = std::min((size_t)std::max(out_elems, 0), out_n);

@@ -390,7 +390,6 @@ class WaveGraph {
     // (else 1), and the same along x. A 2x2 transposed convolution is a 1x1 wave producing the planes q * cout + c of the four
     // output phases at input resolution, followed by the scatter into the double-resolution tensor.
     bool compile_2d() {
-        if (batch_size > 1) return fail("compile: image graphs run one image per inference (batch size 1)");
         struct Shape { uint32_t c = 0, h = 0, w = 0; };
         std::map<std::string, Shape> shape;
         std::map<std::pair<uint32_t, uint32_t>, Layout2D> layouts;
@@ -399,7 +398,7 @@ class WaveGraph {
             auto it = layouts.find(key);
             if (it == layouts.end()) {
                 Layout2D l;
-                if (!l.init(h, w)) return nullptr;
+                if (!l.init(h, w, std::max(1u, batch_size))) return nullptr;
                 it = layouts.emplace(key, std::move(l)).first;
             }
             return &it->second;
@@ -479,8 +478,8 @@ class WaveGraph {
         }
         if (!shape.count(output_tensor)) output_tensor = nodes.back().outs[0];
         for (auto &kv : shape)
-            if (!layout_of(kv.second.h, kv.second.w)) return fail("compile: tensor " + kv.first + " has no plane layout (width must be a multiple of 4, planes at most 2^18 elements unless the width is a multiple of 64)");
-        plan.batch_size = 1;
+            if (!layout_of(kv.second.h, kv.second.w)) return fail("compile: tensor " + kv.first + " has no plane layout (width must be a multiple of 4; all frames of a plane at most 2^18 elements unless the width is a multiple of 64)");
+        plan.batch_size = std::max(1u, batch_size);
         plan.is_2d = true;
         plan.layout.init(64, 1);
         plan.target = target;
@@ -553,7 +552,7 @@ class WaveGraph {
 
         // ---- command emission ----
         std::map<std::string, std::vector<uint64_t>> planes_of;     // tensor -> canvas offset of every channel's plane
-        auto geom = [&](const Layout2D *l) { HostWave::Geom2D g; g.H = l->H; g.W = l->W; g.W_pad = l->W_pad; g.ch_stride = l->channel_stride; return g; };
+        auto geom = [&](const Layout2D *l) { HostWave::Geom2D g; g.H = l->H; g.W = l->W; g.W_pad = l->W_pad; g.ch_stride = l->channel_stride; g.frames = l->frames; g.frame_stride = l->single_stride; return g; };
         auto contiguous2d = [&](const std::vector<uint64_t> &pl, const Layout2D *l) {
             for (size_t c = 1; c < pl.size(); ++c) if (pl[c] != pl[0] + (uint64_t)c * l->channel_stride) return false;
             return !pl.empty();
@@ -607,9 +606,9 @@ class WaveGraph {
             w.w_wmma.resize(rm.size());
             rowmajor_to_wmma(rm.data(), w.w_wmma.data(), w.cout, w.fan_in);
             const double gf = 2.0 * (double)w.fan_in_raw * (double)cout_logical * (double)l->H * (double)l->W / 1e9;
-            w.gflops = gf;
+            w.gflops = gf * l->frames;
             plan.single_frame_gflops += gf;
-            plan.total_gflops += gf;
+            plan.total_gflops += gf * l->frames;
             plan.total_w_bytes += (uint64_t)w.cout * w.fan_in * 2;
             plan.total_idx_bytes += w.idx.size() * 4 + w.bias.size() * 2;
             plan.waves.push_back(std::move(w));

@@ -126,6 +126,8 @@ struct Layout1D {
 //     right halo) and would overwrite halo elements, so every tile carries a 16-bit mask — bit q set iff the four elements
 //     4q .. 4q+3 of the tile are pixels (W is a multiple of 4) — packed into tile_off_y as
 //     (plane offset of the tile / 4) & 0xffff | mask << 16; such planes hold at most 2^18 elements.
+// Several frames per wave (wavec_set_batch_size): the frames of one channel lie one after the other, `single_stride` apart
+// (channel_stride = frames * single_stride, wavec/k44_plan_types.hpp:498-516), and the tile tables list every frame's tiles.
 struct Layout2D {
     uint32_t H = 0, W = 0, H_pad = 0, W_pad = 0;
     uint32_t tiles_per_frame = 0, num_tiles = 0;
@@ -133,8 +135,10 @@ struct Layout2D {
     bool masked = false;
     std::vector<uint32_t> tile_off_x, tile_off_y;
 
-    bool init(uint32_t h, uint32_t w) {
-        H = h; W = w;
+    uint32_t frames = 1;
+
+    bool init(uint32_t h, uint32_t w, uint32_t nframes = 1) {
+        H = h; W = w; frames = nframes ? nframes : 1u;
         tile_off_x.clear(); tile_off_y.clear();
         if (h == 0 || w == 0 || w % 4u) return false;
         H_pad = H + 2u;
@@ -154,7 +158,7 @@ struct Layout2D {
             W_pad = W + 4u;
             tiles_per_frame = (H * W_pad + 63u) / 64u;
             single_stride = (2u * W_pad + tiles_per_frame * 64u + 63u) & ~63u;
-            if (single_stride > (1u << 18)) return false;              // the packed tile offset has 16 bits of quads
+            if ((uint64_t)single_stride * frames > (1u << 18)) return false;   // the packed tile offset has 16 bits of quads
             for (uint32_t t = 0; t < tiles_per_frame; ++t) {
                 const uint32_t y1 = W_pad + 4u + t * 64u;
                 tile_off_x.push_back(y1 - W_pad - 1u);
@@ -166,8 +170,15 @@ struct Layout2D {
                 tile_off_y.push_back(((y1 >> 2) & 0xffffu) | (mask << 16));
             }
         }
-        channel_stride = single_stride;                                 // one frame per wave
-        num_tiles = tiles_per_frame;
+        if ((uint64_t)single_stride * frames > 0x7fffffffull) return false;
+        channel_stride = single_stride * frames;
+        num_tiles = tiles_per_frame * frames;
+        for (uint32_t f = 1; f < frames; ++f)                           // the other frames' tiles: the same offsets, one frame on
+            for (uint32_t t = 0; t < tiles_per_frame; ++t) {
+                tile_off_x.push_back(tile_off_x[t] + f * single_stride);
+                tile_off_y.push_back(masked ? ((((tile_off_y[t] & 0xffffu) + f * (single_stride >> 2)) & 0xffffu) | (tile_off_y[t] & 0xffff0000u))
+                                            : tile_off_y[t] + f * single_stride);
+            }
         return true;
     }
     // element of pixel (y, x) of channel plane `ch`
@@ -271,7 +282,7 @@ struct HostWave {
     //   kind 7 max-pool 2x2 stride 2, 8 max-pool 5x5 stride 1 pad 2, 9 nearest upsample x2, 10 space-to-depth 2x2,
     //   11 scatter of a 2x2 transposed convolution's four phase planes, 12 halo clear: `cout` planes from src_off
     //   (geometry `in2d`) to y_off (geometry `out2d`)
-    struct Geom2D { uint32_t H = 0, W = 0, W_pad = 0, ch_stride = 0; } in2d, out2d;
+    struct Geom2D { uint32_t H = 0, W = 0, W_pad = 0, ch_stride = 0, frames = 1, frame_stride = 0; } in2d, out2d;
 };
 
 struct HostPlan {

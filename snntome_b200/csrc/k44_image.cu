@@ -20,17 +20,26 @@ __device__ __forceinline__ void unpack(uint64_t i, uint32_t h, uint32_t w, uint3
     y = (uint32_t)(t % h);
     c = (uint32_t)(t / h);
 }
+// the same with several frames per channel: linear index over [plane][frame][y][x]
+__device__ __forceinline__ void unpack(uint64_t i, uint32_t frames, uint32_t h, uint32_t w, uint32_t &c, uint32_t &f, uint32_t &y, uint32_t &x) {
+    x = (uint32_t)(i % w);
+    uint64_t t = i / w;
+    y = (uint32_t)(t % h);
+    t /= h;
+    f = (uint32_t)(t % frames);
+    c = (uint32_t)(t / frames);
+}
 
 __global__ void k44_image_maxpool2_kernel(const AuxArgs a) {
     const __half *src = a.canvas + a.src_off;
     __half *dst = a.canvas + a.dst_off;
-    const uint64_t total = (uint64_t)a.rows * a.h_out * a.w_out;
+    const uint64_t total = (uint64_t)a.rows * a.frames * a.h_out * a.w_out;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        uint32_t c, y, x;
-        unpack(i, a.h_out, a.w_out, c, y, x);
-        const __half *p = src + (uint64_t)c * a.cs_in + px(2u * y, 2u * x, a.wpad_in);
+        uint32_t c, f, y, x;
+        unpack(i, a.frames, a.h_out, a.w_out, c, f, y, x);
+        const __half *p = src + (uint64_t)c * a.cs_in + (uint64_t)f * a.fs_in + px(2u * y, 2u * x, a.wpad_in);
         const float m = fmaxf(fmaxf(__half2float(p[0]), __half2float(p[1])), fmaxf(__half2float(p[a.wpad_in]), __half2float(p[a.wpad_in + 1u])));
-        dst[(uint64_t)c * a.cs_out + px(y, x, a.wpad_out)] = __float2half_rn(m);
+        dst[(uint64_t)c * a.cs_out + (uint64_t)f * a.fs_out + px(y, x, a.wpad_out)] = __float2half_rn(m);
     }
 }
 
@@ -38,11 +47,11 @@ __global__ void k44_image_maxpool2_kernel(const AuxArgs a) {
 __global__ void k44_image_maxpool5_kernel(const AuxArgs a) {
     const __half *src = a.canvas + a.src_off;
     __half *dst = a.canvas + a.dst_off;
-    const uint64_t total = (uint64_t)a.rows * a.h_out * a.w_out;
+    const uint64_t total = (uint64_t)a.rows * a.frames * a.h_out * a.w_out;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        uint32_t c, y, x;
-        unpack(i, a.h_out, a.w_out, c, y, x);
-        const __half *plane = src + (uint64_t)c * a.cs_in;
+        uint32_t c, f, y, x;
+        unpack(i, a.frames, a.h_out, a.w_out, c, f, y, x);
+        const __half *plane = src + (uint64_t)c * a.cs_in + (uint64_t)f * a.fs_in;
         float m = -65504.0f;
 #pragma unroll
         for (int dy = -2; dy <= 2; ++dy) {
@@ -54,18 +63,18 @@ __global__ void k44_image_maxpool5_kernel(const AuxArgs a) {
                 if (xx >= 0 && xx < (int)a.w_in) m = fmaxf(m, __half2float(plane[px((uint32_t)yy, (uint32_t)xx, a.wpad_in)]));
             }
         }
-        dst[(uint64_t)c * a.cs_out + px(y, x, a.wpad_out)] = __float2half_rn(m);
+        dst[(uint64_t)c * a.cs_out + (uint64_t)f * a.fs_out + px(y, x, a.wpad_out)] = __float2half_rn(m);
     }
 }
 
 __global__ void k44_image_upsample2_kernel(const AuxArgs a) {
     const __half *src = a.canvas + a.src_off;
     __half *dst = a.canvas + a.dst_off;
-    const uint64_t total = (uint64_t)a.rows * a.h_out * a.w_out;
+    const uint64_t total = (uint64_t)a.rows * a.frames * a.h_out * a.w_out;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        uint32_t c, y, x;
-        unpack(i, a.h_out, a.w_out, c, y, x);
-        dst[(uint64_t)c * a.cs_out + px(y, x, a.wpad_out)] = src[(uint64_t)c * a.cs_in + px(y >> 1, x >> 1, a.wpad_in)];
+        uint32_t c, f, y, x;
+        unpack(i, a.frames, a.h_out, a.w_out, c, f, y, x);
+        dst[(uint64_t)c * a.cs_out + (uint64_t)f * a.fs_out + px(y, x, a.wpad_out)] = src[(uint64_t)c * a.cs_in + (uint64_t)f * a.fs_in + px(y >> 1, x >> 1, a.wpad_in)];
     }
 }
 
@@ -73,12 +82,12 @@ __global__ void k44_image_upsample2_kernel(const AuxArgs a) {
 __global__ void k44_image_s2d_kernel(const AuxArgs a) {
     const __half *src = a.canvas + a.src_off;
     __half *dst = a.canvas + a.dst_off;
-    const uint64_t total = (uint64_t)a.rows * 4u * a.h_out * a.w_out;         // a.rows = input channels
+    const uint64_t total = (uint64_t)a.rows * 4u * a.frames * a.h_out * a.w_out;         // a.rows = input channels
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        uint32_t c4, y, x;
-        unpack(i, a.h_out, a.w_out, c4, y, x);
+        uint32_t c4, f, y, x;
+        unpack(i, a.frames, a.h_out, a.w_out, c4, f, y, x);
         const uint32_t c = c4 >> 2, py = (c4 >> 1) & 1u, pxx = c4 & 1u;
-        dst[(uint64_t)c4 * a.cs_out + px(y, x, a.wpad_out)] = src[(uint64_t)c * a.cs_in + px(2u * y + py, 2u * x + pxx, a.wpad_in)];
+        dst[(uint64_t)c4 * a.cs_out + (uint64_t)f * a.fs_out + px(y, x, a.wpad_out)] = src[(uint64_t)c * a.cs_in + (uint64_t)f * a.fs_in + px(2u * y + py, 2u * x + pxx, a.wpad_in)];
     }
 }
 
@@ -87,12 +96,12 @@ __global__ void k44_image_s2d_kernel(const AuxArgs a) {
 __global__ void k44_image_upconv_scatter_kernel(const AuxArgs a) {
     const __half *src = a.canvas + a.src_off;
     __half *dst = a.canvas + a.dst_off;
-    const uint64_t total = (uint64_t)a.rows * a.h_out * a.w_out;              // a.rows = output channels
+    const uint64_t total = (uint64_t)a.rows * a.frames * a.h_out * a.w_out;              // a.rows = output channels
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        uint32_t c, y, x;
-        unpack(i, a.h_out, a.w_out, c, y, x);
+        uint32_t c, f, y, x;
+        unpack(i, a.frames, a.h_out, a.w_out, c, f, y, x);
         const uint32_t q = ((y & 1u) << 1) | (x & 1u);
-        dst[(uint64_t)c * a.cs_out + px(y, x, a.wpad_out)] = src[(uint64_t)(q * a.rows + c) * a.cs_in + px(y >> 1, x >> 1, a.wpad_in)];
+        dst[(uint64_t)c * a.cs_out + (uint64_t)f * a.fs_out + px(y, x, a.wpad_out)] = src[(uint64_t)(q * a.rows + c) * a.cs_in + (uint64_t)f * a.fs_in + px(y >> 1, x >> 1, a.wpad_in)];
     }
 }
 
@@ -101,26 +110,29 @@ __global__ void k44_image_halo_clear_kernel(const AuxArgs a) {
     __half *dst = a.canvas + a.dst_off;
     const uint64_t total = (uint64_t)a.rows * a.cs_out;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint32_t e = (uint32_t)(i % a.cs_out);
+        const uint32_t e = (uint32_t)(i % a.cs_out) % a.fs_out;        // element inside its frame
         const uint32_t row = e / a.wpad_out, col = e % a.wpad_out;
         const bool pixel = row >= 1u && row <= a.h_out && col >= 4u && col < 4u + a.w_out;
         if (!pixel) dst[i] = __float2half(0.0f);
     }
 }
 
-__global__ void k44_f32_to_planes_kernel(const float *__restrict__ src, __half *__restrict__ dst, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, uint64_t total) {
+// dense [frame][channel][y][x] FP32 at the host boundary <-> planes (channel-major, the frames of a channel side by side)
+__global__ void k44_f32_to_planes_kernel(const float *__restrict__ src, __half *__restrict__ dst, uint32_t channels, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs,
+                                         uint32_t fs, uint64_t total) {
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        uint32_t c, y, x;
-        unpack(i, h, w, c, y, x);
-        dst[(uint64_t)c * cs + px(y, x, wpad)] = __float2half_rn(src[i]);
+        uint32_t f, c, y, x;
+        unpack(i, channels, h, w, f, c, y, x);
+        dst[(uint64_t)c * cs + (uint64_t)f * fs + px(y, x, wpad)] = __float2half_rn(src[i]);
     }
 }
 
-__global__ void k44_planes_to_f32_kernel(const __half *__restrict__ src, float *__restrict__ dst, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, uint64_t total) {
+__global__ void k44_planes_to_f32_kernel(const __half *__restrict__ src, float *__restrict__ dst, uint32_t channels, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs,
+                                         uint32_t fs, uint64_t total) {
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        uint32_t c, y, x;
-        unpack(i, h, w, c, y, x);
-        dst[i] = __half2float(src[(uint64_t)c * cs + px(y, x, wpad)]);
+        uint32_t f, c, y, x;
+        unpack(i, channels, h, w, f, c, y, x);
+        dst[i] = __half2float(src[(uint64_t)c * cs + (uint64_t)f * fs + px(y, x, wpad)]);
     }
 }
 
@@ -132,8 +144,8 @@ inline uint32_t grid_of(uint64_t total) {
 }  // namespace
 
 cudaError_t launch_image_aux(const AuxArgs &a, cudaStream_t s) {
-    if (!a.rows || !a.h_out || !a.w_out || !a.wpad_out || !a.cs_out) return cudaErrorInvalidValue;
-    const uint64_t out_px = (uint64_t)a.rows * a.h_out * a.w_out;
+    if (!a.rows || !a.h_out || !a.w_out || !a.wpad_out || !a.cs_out || !a.frames || !a.fs_out) return cudaErrorInvalidValue;
+    const uint64_t out_px = (uint64_t)a.rows * a.frames * a.h_out * a.w_out;
     switch (a.kind) {
     case AUX_MAXPOOL2: k44_image_maxpool2_kernel<<<grid_of(out_px), 256, 0, s>>>(a); break;
     case AUX_MAXPOOL5: k44_image_maxpool5_kernel<<<grid_of(out_px), 256, 0, s>>>(a); break;
@@ -146,15 +158,15 @@ cudaError_t launch_image_aux(const AuxArgs &a, cudaStream_t s) {
     return cudaGetLastError();
 }
 
-cudaError_t launch_f32_to_planes(const float *src, __half *dst, uint32_t c, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, cudaStream_t s) {
-    const uint64_t total = (uint64_t)c * h * w;
-    k44_f32_to_planes_kernel<<<grid_of(total), 256, 0, s>>>(src, dst, h, w, wpad, cs, total);
+cudaError_t launch_f32_to_planes(const float *src, __half *dst, uint32_t c, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, uint32_t frames, uint32_t fs, cudaStream_t s) {
+    const uint64_t total = (uint64_t)frames * c * h * w;
+    k44_f32_to_planes_kernel<<<grid_of(total), 256, 0, s>>>(src, dst, c, h, w, wpad, cs, fs, total);
     return cudaGetLastError();
 }
 
-cudaError_t launch_planes_to_f32(const __half *src, float *dst, uint32_t c, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, cudaStream_t s) {
-    const uint64_t total = (uint64_t)c * h * w;
-    k44_planes_to_f32_kernel<<<grid_of(total), 256, 0, s>>>(src, dst, h, w, wpad, cs, total);
+cudaError_t launch_planes_to_f32(const __half *src, float *dst, uint32_t c, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, uint32_t frames, uint32_t fs, cudaStream_t s) {
+    const uint64_t total = (uint64_t)frames * c * h * w;
+    k44_planes_to_f32_kernel<<<grid_of(total), 256, 0, s>>>(src, dst, c, h, w, wpad, cs, fs, total);
     return cudaGetLastError();
 }
 

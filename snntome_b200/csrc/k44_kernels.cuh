@@ -125,6 +125,7 @@ struct AuxArgs {
     unsigned long long *argmax_scratch = nullptr;                    // [row chunks][pitch] packed (value key, row)
     // 2-D image commands: `rows` planes; source / destination geometry (pixels, padded row length, plane stride)
     uint32_t h_in = 0, w_in = 0, wpad_in = 0, cs_in = 0, h_out = 0, w_out = 0, wpad_out = 0, cs_out = 0;
+    uint32_t frames = 1, fs_in = 0, fs_out = 0;      // frames per channel and their strides (cs = frames * fs)
 };
 constexpr uint32_t kArgmaxChunk = 256;                               // rows per arg-max CTA
 constexpr uint32_t kDecodeChunk = 32;
@@ -195,8 +196,8 @@ cudaError_t launch_tiled_to_rowmajor(const uint4 *src_tiled, uint4 *dst_rows, ui
 cudaError_t launch_f32_to_canvas(const float *src, __half *dst, uint32_t rows, uint32_t width, uint32_t pitch, cudaStream_t s);
 cudaError_t launch_canvas_to_f32(const __half *src, float *dst, uint32_t rows, uint32_t width, uint32_t pitch, cudaStream_t s);
 // dense F32 [C][H][W] <-> haloed FP16 planes (row length wpad, plane stride cs; pixel (y, x) at (y + 1) * wpad + 4 + x)
-cudaError_t launch_f32_to_planes(const float *src, __half *dst, uint32_t c, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, cudaStream_t s);
-cudaError_t launch_planes_to_f32(const __half *src, float *dst, uint32_t c, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, cudaStream_t s);
+cudaError_t launch_f32_to_planes(const float *src, __half *dst, uint32_t c, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, uint32_t frames, uint32_t fs, cudaStream_t s);
+cudaError_t launch_planes_to_f32(const __half *src, float *dst, uint32_t c, uint32_t h, uint32_t w, uint32_t wpad, uint32_t cs, uint32_t frames, uint32_t fs, cudaStream_t s);
 // counter-based normal fill: element i gets scale * N(0,1) from a stateless hash of (seed, i)
 cudaError_t launch_fill_normal_f16(__half *dst, uint64_t n, uint64_t seed, float scale, cudaStream_t s);
 

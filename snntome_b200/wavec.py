@@ -71,11 +71,13 @@ class WavePlan:
         self._gpu_initialized = False
 
     def infer_f32(self, x: np.ndarray) -> Tuple[np.ndarray, float]:
-        """x: dense FP32 [C, 1, W] (or [C, W]); returns (output [C_out, 1, W], device milliseconds of the waves)."""
+        """x: dense FP32 [C, 1, W] (or [C, W]) for token graphs, [C, H, W] for image graphs ([B, C, H, W] when the graph was built
+        with batch_size B > 1); returns (output in the same arrangement, device milliseconds of the waves)."""
         self.init_gpu()
         x32 = np.ascontiguousarray(x, dtype=np.float32)
         c, h, w = tuple(self.summary["output_shape"])
-        out = np.empty((c, h, w), dtype=np.float32)
+        b = int(self.summary.get("batch_size", 1))
+        out = np.empty((b, c, h, w) if (h > 1 and b > 1) else (c, h, w), dtype=np.float32)
         ms = ctypes.c_float(0.0)
         rc = self._lib.wavec_gpu_infer_f32(self._handle, x32.ctypes.data_as(_f32p), int(x32.size),
                                            out.ctypes.data_as(_f32p), int(out.size), ctypes.byref(ms))

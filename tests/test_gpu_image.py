@@ -167,3 +167,69 @@ def test_strided_convolution_pooling_upsampling_and_transposed_convolution_throu
     err = np.abs(got.astype(np.float64) - want).max()
     cos = float((got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want)))
     assert err < 1.5e-2 and cos > 0.9999, (err, cos)
+
+
+@pytest.mark.parametrize("H,W,frames", [(64, 64, 3), (48, 40, 2)])
+def test_several_frames_per_wave(H, W, frames):
+    """wavec_set_batch_size on an image graph: the frames of a channel lie side by side in the canvas, every wave and glue
+    command covers all of them, and wavec_gpu_infer_f32 takes and returns dense [frame][channel][y][x]. Each frame must equal
+    the numpy model of that frame alone (stem + C2f + SPPF block; whole-tile and masked layouts; recycled regions)."""
+    from snntome_b200.wavec import WaveGraph
+    g, P = _yolo_block(np.random.default_rng(42), H, W, True)
+    g._lib.wavec_set_batch_size(g._handle, frames)
+    plan = g.compile()
+    assert plan.summary["batch_size"] == frames
+    rng = np.random.default_rng(77)
+    xs = (rng.standard_normal((frames,) + P["x"].shape) * 0.25).astype(np.float16).astype(np.float32)
+    got, _ = plan.infer_f32(xs)
+    assert got.shape[0] == frames
+    for f in range(frames):
+        Pf = dict(P, x=xs[f])
+        want = yolo_block_reference(Pf)
+        g64 = got[f].astype(np.float64)
+        err = np.abs(g64 - want).max()
+        cos = float((g64 * want).sum() / (np.linalg.norm(g64) * np.linalg.norm(want)))
+        assert err < 1e-2 and cos > 0.9999, (f, err, cos)
+    assert np.abs(got[0] - got[1]).max() > 1e-3           # the frames really differ
+
+
+def test_several_frames_through_strided_and_transposed_convolutions():
+    """The encoder / decoder graph (space-to-depth, 2x2 pooling, upsampling, transposed-convolution scatter) with two frames."""
+    from snntome_b200.wavec import WaveGraph
+    rng = np.random.default_rng(5)
+    r = lambda *s, k=0.15: (rng.standard_normal(s) * k).astype(np.float16).astype(np.float32)
+    H, W, F = 32, 48, 2
+    xs = r(F, 4, H, W, k=0.5)
+    w_d, b_d = r(16, 4, 3, 3), r(16, k=0.05)
+    w_u, b_u = r(8, 16, 4), r(8, k=0.05)
+    w_o, b_o = r(8, 12, 3, 3), r(8, k=0.05)
+    w_p, b_p = r(8, 16, 1, 1), r(8, k=0.05)
+    g = WaveGraph(reuse_canvas=True, batch_size=F)
+    g.add_input("x", 4, H, W)
+    g.add_conv2d("down", "x", "d", 4, 16, 3, 3, w_d, b_d, stride=2, pad=1, act="relu")
+    g.add_upconv2x2("up", "d", "u", 16, 8, w_u, b_u)
+    g.add_concat("cat", ["u", "x"], "ux")
+    g.add_conv2d("mix", "ux", "m", 12, 8, 3, 3, w_o, b_o, stride=1, pad=1, act="silu")
+    g.add_maxpool("pool", "d", "dp", kernel_size=2, stride=2, pad=0)
+    g.add_upsample2x("up1", "dp", "dq")
+    g.add_upsample2x("up2", "dq", "dr")
+    g.add_conv2d("proj", "dr", "out", 16, 8, 1, 1, w_p, b_p, stride=1, pad=0, act="none", res_blob="m")
+    g.set_output("out")
+    plan = g.compile()
+    got, _ = plan.infer_f32(xs)
+    for f in range(F):
+        x = xs[f]
+        d = np.maximum(I.conv2d_direct(x, w_d, b_d, 2, 1), 0)
+        u = np.zeros((8, H, W))
+        for py in range(2):
+            for px in range(2):
+                u[:, py::2, px::2] = np.einsum("oi,iyx->oyx", w_u[:, :, 2 * py + px].astype(np.float64), d) + b_u[:, None, None]
+        z = I.conv2d_direct(np.concatenate([u, x]), w_o, b_o, 1, 1)
+        m = z / (1 + np.exp(-z))
+        dp = d.reshape(16, 8, 2, 12, 2).max(axis=(2, 4))
+        dr = np.repeat(np.repeat(dp, 4, axis=1), 4, axis=2)
+        want = I.conv2d_direct(dr, w_p, b_p, 1, 0) + m
+        g64 = got[f].astype(np.float64)
+        err = np.abs(g64 - want).max()
+        cos = float((g64 * want).sum() / (np.linalg.norm(g64) * np.linalg.norm(want)))
+        assert err < 1.5e-2 and cos > 0.9999, (f, err, cos)

@@ -165,3 +165,22 @@ def test_image_graph_rejects_what_it_cannot_lay_out():
     g.add_conv2d("bad", "z", "q", 8, 8, 1, 1, np.zeros((8, 8, 1, 1), np.float32), pad=0, res_blob="y")   # residual at another resolution
     with pytest.raises(WaveError, match="wrong shape"):
         g.compile()
+
+
+def test_several_frames_per_wave_scale_the_plan():
+    """wavec_set_batch_size on an image graph: channel stride = frames x frame stride, every tile table lists all frames'
+    tiles, arithmetic and canvas scale with the frame count; masked layouts refuse frame counts whose planes leave the
+    16-bit quad offset of their tile table."""
+    g1, _ = _yolo_block(np.random.default_rng(42), 48, 40, False)
+    s1 = g1.compile().summary
+    g3, _ = _yolo_block(np.random.default_rng(42), 48, 40, False)
+    g3._lib.wavec_set_batch_size(g3._handle, 3)
+    s3 = g3.compile().summary
+    assert s3["batch_size"] == 3 and s1["batch_size"] == 1
+    assert abs(s3["total_gflops"] - 3 * s1["total_gflops"]) < 1e-6 * s3["total_gflops"] + 1e-4
+    assert 2.9 * s1["canvas_elems"] < s3["canvas_elems"] < 3.1 * s1["canvas_elems"]
+    assert s3["input_shape"] == s1["input_shape"] and s3["output_shape"] == s1["output_shape"]
+    big, _ = _yolo_block(np.random.default_rng(42), 48, 40, False)
+    big._lib.wavec_set_batch_size(big._handle, 200)          # 200 x 2304 elements per masked plane > 2^18
+    with pytest.raises(WaveError, match="no plane layout"):
+        big.compile()
