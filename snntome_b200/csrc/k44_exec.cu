@@ -166,7 +166,7 @@ static uint64_t smem_desc_bits(uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t 
            ((uint64_t)layout << 61);
 }
 
-UmmaDesc make_umma_desc(uint32_t n_tile, int variant) {
+UmmaDesc make_umma_desc(uint32_t n_tile) {
     UmmaDesc d;
     d.n_tile = n_tile;
     // A = weights, K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart; a K=16 step
@@ -176,7 +176,7 @@ UmmaDesc make_umma_desc(uint32_t n_tile, int variant) {
     // B = substrate tile, MN-major (columns contiguous), 128-byte swizzle: each synapse row is 128 bytes (64
     // columns); 8-row groups 1024 bytes apart (stride dimension = K); further 64-column blocks 8 KiB apart
     // (leading dimension = N). A K=16 step moves 16 rows = 2048 bytes.
-    d.b_base = (variant == 1) ? smem_desc_bits(1024, kStageK * 128u, 2) : smem_desc_bits(kStageK * 128u, 1024, 2);
+    d.b_base = smem_desc_bits(kStageK * 128u, 1024, 2);
     d.b_k_step = 2048 >> 4;
     // instruction descriptor: FP32 accumulate (bit 4), A/B FP16 (0), A K-major (bit 15 = 0), B MN-major
     // (bit 16 = 1), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
@@ -673,7 +673,7 @@ bool Executor::add_wave(const HostWave &w) {
                 if ((v == 64 || v == 128 || v == 256) && tiles64 % (v / 64u) == 0u && flen % v == 0u) n_tile = v;
             }
             a.k_splits = 1; a.kstages_per_split = a.num_kstages;
-            dw.desc = make_umma_desc(n_tile, 0);
+            dw.desc = make_umma_desc(n_tile);
             // fan-in up to 512: the weight tile of a work item stays in tensor memory (tiles of 128 columns), which takes the
             // weights out of the shared-memory traffic that bounds this kernel
             a.gather_mode = GATHER_BOX; a.box_h = gp.box_h;
@@ -683,10 +683,9 @@ bool Executor::add_wave(const HostWave &w) {
                 ws = v == 2 ? (flen % 128u == 0u && shift_ws_supported(a)) : (ws && v != 0);
             }
             if (ws) {
-                dw.desc = make_umma_desc(128u, 0);
+                dw.desc = make_umma_desc(128u);
                 dw.desc.ws_chunk = shift_ws_chunk(mtiles, tiles64 / 2u, (uint32_t)num_sms_);
                 if (const char *e = std::getenv("K44B_WS_CHUNK")) { const int v = std::atoi(e); if (v > 0) dw.desc.ws_chunk = (uint32_t)v; }
-                if (const char *e = std::getenv("K44B_WS_VARIANT")) dw.desc.ws_variant = std::atoi(e) != 0 ? 1u : 0u;
                 if (const char *e = std::getenv("K44B_WS_GROUPS")) { const int v = std::atoi(e); if (v >= 1 && v <= 2) dw.desc.ws_groups = (uint32_t)v; }
                 n_tile = 128u;
             }
@@ -699,8 +698,6 @@ bool Executor::add_wave(const HostWave &w) {
                 const uint32_t v = (uint32_t)std::atoi(e);
                 if ((v == 64 || v == 128 || v == 256) && tiles64 % (v / 64u) == 0u) n_tile = v;
             }
-            int variant = 0;
-            if (const char *e = std::getenv("K44B_UMMA_VARIANT")) variant = std::atoi(e);
             // Small waves (fewer tiles than SMs): 64-column tiles, two CTAs per SM, and the fan-in cut into
             // K splits so that every SM streams a share of the weights.
             uint32_t splits = 1;
@@ -728,7 +725,7 @@ bool Executor::add_wave(const HostWave &w) {
             a.kstages_per_split = (a.num_kstages + splits - 1) / splits;
             a.k_splits = cluster ? splits : (a.num_kstages + a.kstages_per_split - 1) / a.kstages_per_split;
             dw.use_cluster = cluster;
-            dw.desc = make_umma_desc(n_tile, variant);
+            dw.desc = make_umma_desc(n_tile);
             dw.desc.small_wave = small ? 1u : 0u;
             if (a.k_splits > 1 && !cluster) ok = reserve_scratch((size_t)mtiles * tiles64);
             ok = ok && make_tensor_map(dw, 64u, true);
@@ -990,10 +987,10 @@ bool Executor::launch_one(DeviceWave &w, cudaStream_t stream, uint32_t peer_slac
         w.args.scratch = d_scratch_;
         w.args.counters = d_counters_;
         UmmaDesc dd = w.desc;
-        if (dd.pair) { dd.pair = 0; dd.idesc = make_umma_desc(dd.n_tile, 0).idesc; }     // sharded plans: the one-CTA kernel
+        if (dd.pair) { dd.pair = 0; dd.idesc = make_umma_desc(dd.n_tile).idesc; }     // sharded plans: the one-CTA kernel
         e = launch_wave_umma(w.args, dd, w.tmap, num_sms_, stream);
     } else if (w.path == PATH_MMA) {
-        e = launch_wave_mma(w.args, make_umma_desc(64, 0).wait_cycles, stream);
+        e = launch_wave_mma(w.args, make_umma_desc(64).wait_cycles, stream);
     } else {
         e = launch_wave_fma(w.args, stream);
     }
@@ -1217,7 +1214,7 @@ bool Executor::peer_latency(int peer_rank, bool initiator, uint32_t iters, uint3
     if (!check(cudaSetDevice(device_), "cudaSetDevice")) return false;
     unsigned long long *d_out = reinterpret_cast<unsigned long long *>(d_sync_ + 12);       // words 12..15 of the own sync block
     const cudaError_t e = launch_peer_pingpong(d_sync_ + kSyncProbe, (uint32_t *)peer_sync_[peer_rank] + kSyncProbe, peer_canvas_[peer_rank], payload_bytes,
-                                               initiator, iters, probe_base_, make_umma_desc(64, 0).wait_cycles, d_out, stream);
+                                               initiator, iters, probe_base_, make_umma_desc(64).wait_cycles, d_out, stream);
     if (!check(e, "latency probe launch")) return false;
     ++launches_;
     probe_base_ += iters;

@@ -35,7 +35,7 @@ void compute_peer_slack(const uint64_t *hulls, int world, size_t launches, uint3
 // Pure host analysis (unit-testable without a device).
 GatherPlan analyze_gather(const HostWave &w, uint32_t pitch, uint64_t canvas_elems);
 bool validate_wave(const HostWave &w, uint32_t pitch, uint32_t num_tiles, uint64_t canvas_elems, std::string &err);
-UmmaDesc make_umma_desc(uint32_t n_tile, int variant);
+UmmaDesc make_umma_desc(uint32_t n_tile);
 
 struct DeviceWave {
     std::string name;

@@ -155,7 +155,6 @@ struct UmmaDesc {
     uint32_t pair = 0;                    // 1: the wave runs on CTA pairs (tiles of 256 neurons x 256 columns, M = 256 MMAs)
     uint32_t m_blocks = 1;                // 128-neuron blocks per tile: 2 = tiles of 256 neurons sharing one gathered operand (256-column tiles only)
     uint32_t ws_chunk = 0;                // token-shift kernel with the weights in tensor memory: column tiles per work item (0: not that kernel)
-    uint32_t ws_variant = 0;              // ... 0: 3 window + 2 operand stages, 1: 2 + 3
     uint32_t ws_groups = 2;               // ... and its groups of four aligner warps (1 or 2), each taking every ws_groups-th stage
 };
 

@@ -38,7 +38,7 @@ constexpr int kN = 128;                             // columns per tile
 constexpr int kTabEntries = 32;                     // run-table entries of one item (fan-in 512 in 16-row runs)
 constexpr int kMaxKS = 8;                           // 64-synapse steps whose weights fit tensor memory
 constexpr int kSub = 2;                             // 64-synapse steps per ring stage: one barrier round trip serves two of them
-constexpr int SL0 = 3, SB0 = 2, SW = 2;             // window ring, operand ring (variant 1: 2 and 3 stages), weight ring (blocks of one step)
+constexpr int SL = 3, SB = 2, SW = 2;               // window ring, operand ring, weight ring (blocks of one step); 2 + 3 instead of 3 + 2 was 10 % slower
 constexpr uint32_t kXBytes = 2u * kStageK * 128u;                // operand of one step: two 64-column blocks
 constexpr uint32_t kRawPitch = (uint32_t)(kN + 8) * 2u;          // bytes per window row (17 chunks of 16 bytes)
 constexpr uint32_t kRawBytes = kStageK * kRawPitch;              // window of one step
@@ -47,7 +47,7 @@ constexpr uint32_t kTmemCols = 512u;                             // accumulators
 constexpr uint32_t kATmemCol = 256u;
 constexpr uint32_t kOutStageBytes = 2u * 128u * 80u;            // one padded slot per epilogue thread
 constexpr int kFirstAligner = 10;                   // warps 0 producer, 1 MMA, 2-5 and 6-9 epilogue, 10.. aligners
-constexpr uint32_t kSmemBytes = 1024u + (uint32_t)SL0 * kRawStage + (uint32_t)SB0 * kXStage + (uint32_t)SW * kStageWBytes + 256u + kOutStageBytes + 2u * kTabEntries * 4u;
+constexpr uint32_t kSmemBytes = 1024u + (uint32_t)SL * kRawStage + (uint32_t)SB * kXStage + (uint32_t)SW * kStageWBytes + 256u + kOutStageBytes + 2u * kTabEntries * 4u;
 constexpr int OC = kN / 16;                         // 16-byte chunks one aligner lane produces per row
 
 __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
@@ -79,10 +79,9 @@ __device__ __forceinline__ void shift_and_store(const uint4 (&raw)[OC + 1], uint
     }
 }
 
-template <int AG, int V>
+template <int AG>
 __global__ void __launch_bounds__(32 * kFirstAligner + 128 * AG, 1)
 k44_wave_umma_shift_ws_kernel(const __grid_constant__ CUtensorMap tmap, const WaveArgs a, const UmmaDesc d) {
-    constexpr int SL = V ? 2 : 3, SB = V ? 3 : 2;          // the two rings share the same bytes: 3 + 2 or 2 + 3 stages
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t w_smem = smem_base;                                        // SW weight blocks
@@ -438,8 +437,7 @@ cudaError_t launch_wave_umma_shift_ws(const WaveArgs &a, const UmmaDesc &d, cons
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     using KernelFn = void (*)(const CUtensorMap, const WaveArgs, const UmmaDesc);
-    static const KernelFn fns[4] = {shiftws::k44_wave_umma_shift_ws_kernel<1, 0>, shiftws::k44_wave_umma_shift_ws_kernel<2, 0>,
-                                    shiftws::k44_wave_umma_shift_ws_kernel<1, 1>, shiftws::k44_wave_umma_shift_ws_kernel<2, 1>};
+    static const KernelFn fns[2] = {shiftws::k44_wave_umma_shift_ws_kernel<1>, shiftws::k44_wave_umma_shift_ws_kernel<2>};
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
         for (KernelFn f : fns) {
             e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shiftws::kSmemBytes);
@@ -451,8 +449,8 @@ cudaError_t launch_wave_umma_shift_ws(const WaveArgs &a, const UmmaDesc &d, cons
     const uint32_t tiles_n = a.num_col_tiles64 / 2u;
     const uint32_t items = mtiles * ((tiles_n + d.ws_chunk - 1u) / d.ws_chunk);
     const uint32_t grid = items < (uint32_t)num_sms ? items : (uint32_t)num_sms;
-    const uint32_t ag = d.ws_groups == 1u ? 1u : 2u, v = d.ws_variant ? 1u : 0u;
-    fns[v * 2u + (ag - 1u)]<<<grid, 32 * shiftws::kFirstAligner + 128 * ag, shiftws::kSmemBytes, s>>>(tmap, a, d);
+    const uint32_t ag = d.ws_groups == 1u ? 1u : 2u;
+    fns[ag - 1u]<<<grid, 32 * shiftws::kFirstAligner + 128 * ag, shiftws::kSmemBytes, s>>>(tmap, a, d);
     return cudaGetLastError();
 }
 

@@ -159,7 +159,7 @@ int k44b_wave_forward_static(void *d_canvas, uint64_t canvas_elems, uint32_t pit
     a.k_splits = (kstages + a.kstages_per_split - 1) / a.kstages_per_split;
     a.scratch = partial;
     a.counters = counters;
-    UmmaDesc d = make_umma_desc(64, 0);
+    UmmaDesc d = make_umma_desc(64);
     d.small_wave = 1;
     CUtensorMap map;
     if (encode_canvas_map(&map, d_canvas, canvas_elems, pitch, rows_per_box) != 0) return report(-1);
