@@ -52,13 +52,14 @@ struct UmmaCfg {
 // epilogue, stores the rows and leaves scratch and counter zeroed for the next launch. Nobody waits.
 // ROWS_MODE != 0: the gather table holds one canvas row per synapse (scattered single rows, box_h == 1), the kind of table
 // the reference's own benchmark draws.
+//   1  (default) four extra warps fetch them with 16-byte asynchronous copies straight into the swizzled layout (one warp
+//      instruction = one row piece of up to 512 contiguous bytes) and report completion on the stage's barrier, warp 0 only
+//      streams the weights — the way the producer threads of the reference's tcgen05 kernel work
+//      (kernels/cuda/kernel44_cuda_pack.cuh:481-491);
 //   2  warp 0 fetches them with gather-mode tensor copies: one instruction brings four rows, each from its own canvas row,
 //      64 columns wide, into four consecutive 128-byte rows of the swizzled operand stage; byte counting on the stage's
-//      barrier as for boxes;
-//   1  four extra warps fetch them with 16-byte asynchronous copies straight into the swizzled layout (one warp instruction =
-//      one row piece of up to 512 contiguous bytes) and report completion on the stage's barrier, warp 0 only streams the
-//      weights — the way the producer threads of the reference's tcgen05 kernel work (kernels/cuda/kernel44_cuda_pack.cuh:
-//      481-491); kept for comparison (K44B_ROWS_MODE=1).
+//      barrier as for boxes. Measured 3.4 times slower than mode 1 (the copy engine's cost is per 128-byte row piece); kept
+//      for comparison (K44B_ROWS_MODE=2).
 constexpr int kRowWarps = 4;
 template <int N_TILE, int STAGES_SEL, int ROWS_MODE, int MB = 1>
 __global__ void __launch_bounds__(kUmmaThreads + (ROWS_MODE == 1 ? 32 * kRowWarps : 0), UmmaCfg<N_TILE, STAGES_SEL, MB>::kCtasPerSm)
