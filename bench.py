@@ -850,7 +850,7 @@ def shift_main(args) -> None:
                                        "fan-in 512 = 32 runs of 16 channels, shift 0..7 tokens per run, groups of 128, " + {0: "no activation", 1: "ReLU", 2: "sigmoid", 3: "SiLU", 4: "leaky ReLU", 5: "GELU"}.get(c["act"], "?"),
                            "sequences_per_gpu": c["sequences"], "columns_per_gpu": pitch, "scale": args.scale, "max_shift": c["max_shift"],
                            "l2_policy": "substrate (0.13 - 2.3 GB) exceeds the 126 MB L2; no explicit flush"},
-                "roofline": {"bound": "tensor", "kernel": (f"k44_wave_umma_shift_kernel<{infos[0].n_tile}>" if c["max_shift"] else f"k44_wave_umma_kernel<{infos[0].n_tile}>") if infos[0].path == 1 else ("k44_wave_mma_kernel" if infos[0].path == 3 else "k44_wave_fma_kernel"),
+                "roofline": {"bound": "tensor", "kernel": (("k44_wave_umma_shift_ws_kernel" if infos[0].weights_in_tmem else f"k44_wave_umma_shift_kernel<{infos[0].n_tile}>") if c["max_shift"] else f"k44_wave_umma_kernel<{infos[0].n_tile}>") if infos[0].path == 1 else ("k44_wave_mma_kernel" if infos[0].path == 3 else "k44_wave_fma_kernel"),
                              "achieved": achieved, "peak": peak, "peak_kind": f"of {kind}", "unit": "TFLOP/s", "frac": achieved / peak,
                              "flops_per_launch": flops_wave, "per_wave_ms": per_wave, "traffic": None},
                 "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "kernel_paths": [i.path for i in infos], "clocks": clocks}
