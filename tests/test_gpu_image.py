@@ -233,3 +233,22 @@ def test_several_frames_through_strided_and_transposed_convolutions():
         err = np.abs(g64 - want).max()
         cos = float((g64 * want).sum() / (np.linalg.norm(g64) * np.linalg.norm(want)))
         assert err < 1.5e-2 and cos > 0.9999, (f, err, cos)
+
+
+def test_detector_network_frames_equal_single_image_runs():
+    """The benchmark's detector backbone + neck at 384 x 384 (plane widths 384 .. 12: whole-tile and masked layouts, five
+    stride-2 convolutions, SPPF, two upsample + concat stages): a plan built for three frames must return, frame by frame,
+    exactly the bits the one-frame plan returns for the same image — same weights, same arithmetic, only the layout differs."""
+    import bench
+    size = 384
+    g1, rng = bench.build_image_graph(size, seed=11, frames=1)
+    p1 = g1.compile()
+    g3, _ = bench.build_image_graph(size, seed=11, frames=3)
+    p3 = g3.compile()
+    xs = np.random.default_rng(12).standard_normal((3, 3, size, size)).astype(np.float32)
+    got3, _ = p3.infer_f32(xs)
+    assert got3.shape == (3, 64, size // 8, size // 8) and np.isfinite(got3).all()
+    for f in range(3):
+        one, _ = p1.infer_f32(xs[f])
+        assert np.array_equal(one, got3[f]), f"frame {f}: max abs difference {np.abs(one - got3[f]).max()}"
+    assert np.abs(got3[0] - got3[1]).max() > 1e-3
