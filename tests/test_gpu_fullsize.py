@@ -265,3 +265,43 @@ def test_pruned_8b_chain_full_size_sampled_groups():
             pruned_check.check_wave(plan, info, wi, canvas)
     assert plan.status() == 0
     plan.close()
+
+
+@pytest.mark.parametrize("gen,row", [("runs", "g512_b2048_c4096"), ("rows", "g512_b2048_c4096"), ("runs", "g256_b1024_c8192")])
+def test_reference_benchmark_regime_sampled_groups(gen, row):
+    """The reference benchmark's plan (groups of 512 / 256 neurons, fan-in 2048 / 1024, 512 columns, 16 waves merged into one)
+    over a 2 M-row substrate (2 GB, beyond L2): run tables take the CTA-pair kernel (M = 256 MMAs), the reference's single
+    scattered rows the row-fetching warps. Sampled groups against the oracle on the rows the device gathered."""
+    import torch
+    import bench
+    from snntome_b200.native import fill_normal_f16
+    spec = bench.WHITEPAPER_ROWS[row]
+    cin = 2_000_000
+    plan, tables = bench.build_whitepaper_plan(spec, cin, 0, gen, True)
+    pitch, B, G = spec["columns"], spec["fan_in"], spec["group"]
+    canvas = plan.canvas_tensor()
+    fill_normal_f16(canvas[: cin * pitch], 21, 1.0)
+    plan.execute()
+    assert plan.status() == 0
+    info = plan.wave_info(0)
+    assert info.path == PATH_UMMA and info.n_tile == 256
+    assert (info.cta_pairs == 1 and info.box_rows == 64) if gen == "runs" else info.box_rows == 1
+    rows_tab, run_len, out_row0, cout = tables[0]
+    wrm = plan.weights_rowmajor(0)
+    cv2 = canvas.view(-1, pitch)
+    rng = np.random.default_rng(8)
+    for g in rng.choice(rows_tab.shape[0], size=3, replace=False):
+        rows = (torch.from_numpy(rows_tab[g].astype(np.int64))[:, None] + torch.arange(run_len)[None, :]).reshape(-1).cuda()
+        x = cv2[rows].cpu().numpy().view(np.uint16)                         # [B, pitch]
+        j0 = int(g) * G + int(rng.integers(0, G // 128)) * 128              # one 128-neuron block of the group
+        wg = wrm[j0: j0 + 128].cpu().numpy().view(np.uint16)
+        got = cv2[out_row0 + j0: out_row0 + j0 + 128].cpu().numpy().view(np.uint16)
+        idx = (np.arange(B, dtype=np.uint32) * pitch)[None, :]
+        wave = Wave(cout=128, group=128, fan_in=B, idx=idx, weights=wg, bias=None, y_off=B * pitch, act=ACT_NONE)
+        mini = Plan(canvas_elems=(B + 128) * pitch, pitch=pitch, columns=pitch, input_off=0, input_c=B, output_off=B * pitch, output_c=128, waves=[wave])
+        want = O.run_plan(mini, x)[B * pitch:]
+        ok, err, k = O.compare(got.reshape(-1), want, RTOL, ATOL)
+        assert ok, f"group {g}: max abs err {err} at {k}"
+    del wrm
+    plan.close()
+    torch.cuda.empty_cache()
