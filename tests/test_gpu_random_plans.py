@@ -58,3 +58,47 @@ def test_random_plan_matches_the_oracle(seed):
             check(plan, run_gpu(plan, x, PATH_FMA), want)
     except AssertionError as e:
         raise AssertionError(f"{notes}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_token_shift_plan_on_the_kernel_with_weights_in_tensor_memory(seed, monkeypatch):
+    """Seeded token-shift plans forced onto the kernel that keeps a work item's weight tile in tensor memory: neuron count
+    (partial last tile included), group size, run length 16 / 32 / 64, fan-in 64 .. 512 (odd numbers of 64-synapse steps
+    included), frames of 128 .. 1024 tokens, activation, bias, residual, and the number of column tiles per work item."""
+    from snntome_b200.native import NativePlan, PATH_UMMA
+    from test_gpu_parity import shifted_plan
+    rng = np.random.default_rng(7000 + seed)
+    run_len = int(rng.choice([16, 32, 64]))
+    fan_in = int(rng.choice([64, 128, 192, 256, 320, 448, 512]))
+    while fan_in % run_len:
+        fan_in += 64
+    fan_in = min(fan_in, 512)
+    frame_len = int(rng.choice([128, 256, 384, 512, 1024]))
+    frames = int(rng.integers(1, 4))
+    group = int(rng.choice([128, 256]))
+    cout = group * int(rng.integers(1, 5))
+    if rng.random() < 0.4:
+        cout_single = cout + int(rng.choice([16, 48, 80]))           # one group with a partial last 128-neuron tile
+        cout = group = cout_single
+    monkeypatch.setenv("K44B_SHIFT_WS", "2")
+    monkeypatch.setenv("K44B_WS_CHUNK", str(int(rng.integers(1, 6))))
+    monkeypatch.setenv("K44B_WS_GROUPS", str(int(rng.integers(1, 3))))
+    plan = shifted_plan(8000 + seed, rows_in=int(rng.choice([256, 512])), runs=fan_in // run_len, run_len=run_len, frames=frames, frame_len=frame_len,
+                        cout=cout, group=group, waves=2, act=int(rng.choice(ACTS)))
+    for w in plan.waves:
+        if rng.random() < 0.6:
+            w.bias = synth.f16_bits(rng.normal(0, 0.1, w.cout))
+    if rng.random() < 0.5:
+        plan.waves[1].has_residual, plan.waves[1].res_off = True, plan.waves[0].y_off
+    notes = f"cout {cout}, group {group}, fan-in {fan_in}, run_len {run_len}, {frames} x {frame_len} tokens"
+    x = synth.random_input(plan, 400 + seed, dist="normal")
+    want = O.run_plan(plan, x)
+    npn = NativePlan.from_plan(plan, device=0)
+    try:
+        assert all(npn.wave_info(i).path == PATH_UMMA and npn.wave_info(i).weights_in_tmem > 0 for i in range(npn.num_waves)), notes
+    finally:
+        npn.close()
+    try:
+        check(plan, run_gpu(plan, x, PATH_AUTO), want)
+    except AssertionError as e:
+        raise AssertionError(f"{notes}: {e}") from None
