@@ -24,7 +24,7 @@ typedef struct k44b_wave_desc {
     uint32_t group;           /* neurons sharing one gather list (K44ExecCmd::cluster_size) */
     uint32_t fan_in;          /* padded synapses per neuron, multiple of 8 (K44ExecCmd::B) */
     uint32_t fan_in_raw;      /* slots >= fan_in_raw must carry zero weights (K44ExecCmd::B_raw) */
-    int32_t act;              /* 0 none, 1 relu, 2 sigmoid, 3 silu, 4 leaky-relu(0.1), 5 gelu (erf form; the tensor-core kernels use a fitted tanh form, see k44wavec.h) */
+    int32_t act;              /* 0 none, 1 relu, 2 sigmoid, 3 silu, 4 leaky-relu(0.1), 5 gelu (erf form; the tensor-core kernels use a fit within 2.6e-5 of it) */
     uint32_t has_residual;
     uint64_t y_off;           /* canvas element offset of output row 0 */
     uint64_t src_off;         /* informational */

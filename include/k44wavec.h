@@ -12,11 +12,10 @@
  *     stored with one halo row above and below and four halo elements left (kernels/common/kernel44_valu_pack.cuh:30-103);
  *     wavec_gpu_infer_f32 takes and returns dense [c][h][w] FP32 images ([frame][c][h][w] after wavec_set_batch_size(frames)).
  *     A call outside that set (flatten, other kernel sizes, mixing the two kinds of graph) returns -1 and leaves the graph unchanged;
- *   - activation value 5 selects GELU in addition to the reference's 0-4. The tensor-core kernels evaluate the smooth
- *     activations with the hardware tanh (relative error up to 2^-11): sigmoid = 0.5 + 0.5 tanh(v / 2), SiLU likewise, GELU
- *     as v (0.5 + 0.5 tanh(v P(v^2) / 2)) with a fitted quadratic P whose exact form is at most 2.6e-5 (absolute) away
- *     from the erf form; the FP32-FMA and mma.sync kernels call expf / erff. All lie inside the output tolerance
- *     (rtol 2e-3, atol 1e-3) for every FP16 pre-activation.
+ *   - activation value 5 selects GELU in addition to the reference's 0-4. The tensor-core kernels evaluate it
+ *     as v / (1 + exp(-v P(v^2))) with a fitted quadratic P, at most 2.6e-5 (absolute) away from the erf form;
+ *     the FP32-FMA and mma.sync kernels call erff. Both lie inside the output tolerance (rtol 2e-3, atol 1e-3)
+ *     for every FP16 pre-activation (checked by a sweep over all of them).
  * Not thread-safe per handle, like the reference.
  */
 #ifndef K44WAVEC_H

@@ -80,36 +80,30 @@ __device__ __forceinline__ bool peer_wait_ready(const PeerArgs *p, unsigned long
 // Branch-free activation for the tensor-core epilogue: the activation kind is a template parameter so that the
 // 32 values a thread converts are independent straight-line code (a per-element runtime switch serialises them
 // behind branch latency when only one warp runs per scheduler).
-// The smooth activations go through the hardware tanh (one special-function instruction per value): the special-function
-// unit is the busiest pipe of a GELU epilogue at small fan-in (80 % of its peak with the exp + reciprocal forms, which need
-// two such instructions per value).
-//   sigmoid(v) = 0.5 + 0.5 tanh(v / 2),   silu(v) = v / 2 + (v / 2) tanh(v / 2)
-//   GELU(v) = v * Phi(v), Phi(v) = 1 / (1 + exp(-v * P(v^2))) = 0.5 + 0.5 tanh(v * P(v^2) / 2): the logit of the normal
-//   distribution function is odd and smooth, and a quadratic P in v^2, fitted on |v| <= 9 (beyond it Phi is 0 or 1 to 1e-11;
-//   v^2 is clamped for the polynomial only), reproduces the erf form of GELU to 2.6e-5 absolute before the error of the
-//   hardware tanh. (libm's erff costs several times as much and made the epilogue of GELU waves the bottleneck of the
-//   tensor-core kernels.) The coefficients below are those of P / 2.
-// tanh.approx.f32 has a relative error of up to 2^-11; in these forms that is at most 2.5e-4 * |v| on the result, inside
-// rtol 2e-3 * |result| + atol 1e-3 wherever the result is of the order of v, and the sweep over every FP16 pre-activation
-// in tests/test_gpu_parity.py checks the rest of the range against the erf / exp forms of the oracle.
-__device__ __forceinline__ float tanh_fast(float x) {
-    float t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
-    return t;
-}
+// GELU(v) = v * Phi(v) with Phi(v) = 1 / (1 + exp(-v * P(v^2))): the logit of the normal distribution function is
+// odd and smooth, and a quadratic P in v^2, fitted on |v| <= 9 (beyond it Phi is 0 or 1 to 1e-11 and v is clamped
+// for the exponent only), reproduces the erf form of GELU to 2.6e-5 absolute — forty times below the FP16 rounding
+// of the stored result at |v| = 2. Two special-function instructions and eight FP32 operations per value, no
+// branch. (libm's erff costs several times as much and made the epilogue of GELU waves the bottleneck of the
+// tensor-core kernels.) The coefficients carry the factor -log2(e) of the base-2 exponential.
+// A variant with one special-function instruction per value — sigmoid, SiLU and this GELU through tanh.approx — stayed inside
+// the output tolerance for every FP16 pre-activation, but it is ten times less accurate (up to 2.5e-4 * |v|) and bought under
+// 1 % on the power-capped token-shift benchmark; it was dropped.
 __device__ __forceinline__ float gelu_fast(float v) {
-    const float v2 = fminf(v * v, 81.0f);
-    float q = fmaf(v2, -0.00035227281f, 0.037010305f);
-    q = fmaf(v2, q, 0.79750276f);
-    const float hv = 0.5f * v;
-    return fmaf(hv, tanh_fast(v * q), hv);
+    const float vc = fminf(fmaxf(v, -9.0f), 9.0f);
+    const float v2 = vc * vc;
+    float p = fmaf(v2, 0.0010164447594434023f, -0.10678916424512863f);
+    p = fmaf(v2, p, -2.3011064529418945f);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(vc * p));       // exp(-v P(v^2))
+    return __fdividef(v, 1.0f + e);
 }
 
 template <int ACT>
 __device__ __forceinline__ float act_fast(float v) {
     if (ACT == 1) return fmaxf(v, 0.0f);
-    if (ACT == 2) return fmaf(0.5f, tanh_fast(0.5f * v), 0.5f);
-    if (ACT == 3) { const float hv = 0.5f * v; return fmaf(hv, tanh_fast(hv), hv); }
+    if (ACT == 2) return __fdividef(1.0f, 1.0f + __expf(-v));
+    if (ACT == 3) return __fdividef(v, 1.0f + __expf(-v));
     if (ACT == 4) return fmaxf(v, 0.1f * v);
     if (ACT == 5) return gelu_fast(v);
     return v;

@@ -10,7 +10,7 @@ from snntome_b200 import synth
 from snntome_b200.native import PATH_AUTO, PATH_FMA
 from snntome_b200.plan import ACT_GELU, ACT_LEAKY_RELU, ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU
 
-from test_gpu_parity import check, run_gpu
+from test_gpu_parity import check, check_per_wave, run_gpu
 
 pytestmark = pytest.mark.gpu
 ACTS = [ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, ACT_LEAKY_RELU, ACT_GELU]
@@ -100,5 +100,42 @@ def test_random_token_shift_plan_on_the_kernel_with_weights_in_tensor_memory(see
         npn.close()
     try:
         check(plan, run_gpu(plan, x, PATH_AUTO), want)
+    except AssertionError as e:
+        raise AssertionError(f"{notes}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_plan_on_cta_pairs(seed):
+    """Seeded plans large enough for tiles of 256 neurons x 256 columns on CTA pairs (cta_group::2): group size 256 / 512 /
+    all neurons, run length 8 .. 64, fan-in 128 .. 512, 512 .. 1024 columns of which the last tile may be partly valid,
+    activation, bias, a second wave that adds the first as residual."""
+    from snntome_b200.native import NativePlan, PATH_UMMA
+    rng = np.random.default_rng(7500 + seed)
+    run_len = int(rng.choice([8, 16, 32, 64]))
+    fan_in = int(rng.choice([128, 192, 256, 384, 512]))
+    columns = int(rng.choice([512, 768, 1024]))
+    blocks = -(-148 // (columns // 256)) + int(rng.integers(0, 6))          # 256-neuron blocks: at least one pair tile per SM
+    group = int(rng.choice([256, 512]))
+    blocks += (-blocks) % (group // 256)
+    cout = 256 * blocks
+    if rng.random() < 0.3:
+        group = cout
+    valid = columns - int(rng.choice([0, 0, 40, 63]))                      # the row pitch stays a whole number of 256-column tiles
+    plan = synth.sparse_plan(seed=600 + seed, input_rows=4096, waves=2, cout=cout, runs=fan_in // run_len, run_len=run_len, columns=valid, group=group,
+                             act=int(rng.choice(ACTS)), bias_scale=0.05 if rng.random() < 0.6 else 0.0)
+    assert plan.pitch == columns
+    if rng.random() < 0.5:
+        plan.waves[1].has_residual, plan.waves[1].res_off = True, plan.waves[0].y_off
+    notes = f"cout {cout}, group {group}, fan-in {fan_in}, run_len {run_len}, columns {valid} of {plan.pitch}"
+    x = synth.random_input(plan, 500 + seed, dist="normal")
+    npn = NativePlan.from_plan(plan, device=0)
+    try:
+        for i in range(npn.num_waves):
+            info = npn.wave_info(i)
+            assert info.path == PATH_UMMA and info.n_tile == 256 and info.cta_pairs == 1, (notes, info.path, info.n_tile, info.cta_pairs)
+    finally:
+        npn.close()
+    try:
+        check_per_wave(plan, run_gpu(plan, x, PATH_AUTO))
     except AssertionError as e:
         raise AssertionError(f"{notes}: {e}") from None
