@@ -139,3 +139,76 @@ def test_random_plan_on_cta_pairs(seed):
         check_per_wave(plan, run_gpu(plan, x, PATH_AUTO))
     except AssertionError as e:
         raise AssertionError(f"{notes}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_scattered_rows_plan_on_the_streaming_kernel(seed):
+    """Seeded plans whose gather lists are single sorted random rows (the reference benchmark's generator), large enough for the
+    streaming tcgen05 kernel with row-fetching warps: tile widths 64 / 128 / 256 by column count, groups of 128 / 256 / 512,
+    fan-in 64 .. 320 (tails of a 64-synapse step included), bias, activation; every wave checked on what the device gathered."""
+    from snntome_b200.native import NativePlan, PATH_UMMA
+    rng = np.random.default_rng(7700 + seed)
+    columns = int(rng.choice([64, 128, 256, 512]))
+    group = int(rng.choice([128, 256, 512]))
+    tiles_per_block = max(1, columns // 64)
+    cout = group * max(1, -(-160 // (tiles_per_block * (group // 128))) + int(rng.integers(0, 3)))
+    fan_in = int(rng.choice([64, 96, 160, 256, 320]))
+    valid = columns - int(rng.choice([0, 0, 17]))
+    plan = synth.scattered_rows_plan(seed=900 + seed, input_rows=int(rng.choice([3000, 8192])), waves=2, cout=cout, fan_in=fan_in, columns=valid, group=group,
+                                     act=int(rng.choice(ACTS)))
+    for w in plan.waves:
+        if rng.random() < 0.5:
+            w.bias = synth.f16_bits(rng.normal(0, 0.1, w.cout))
+    notes = f"cout {cout}, group {group}, fan-in {fan_in}, columns {valid} of {plan.pitch}"
+    x = synth.random_input(plan, 600 + seed, dist="normal")
+    npn = NativePlan.from_plan(plan, device=0)
+    try:
+        for i in range(npn.num_waves):
+            info = npn.wave_info(i)
+            assert info.path == PATH_UMMA and info.box_rows == 1, (notes, info.path, info.box_rows)
+    finally:
+        npn.close()
+    try:
+        check_per_wave(plan, run_gpu(plan, x, PATH_AUTO))
+    except AssertionError as e:
+        raise AssertionError(f"{notes}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_token_shift_plan_with_weights_through_shared_memory(seed, monkeypatch):
+    """Seeded token-shift plans on the aligner kernel that streams its weights through shared memory (the one that serves fan-in
+    above 512): fan-in 128 .. 1024, tile widths 64 / 128 / 256, run lengths 16 / 32 / 64, bias, residual."""
+    from snntome_b200.native import NativePlan, PATH_UMMA
+    from test_gpu_parity import shifted_plan
+    rng = np.random.default_rng(7900 + seed)
+    run_len = int(rng.choice([16, 32, 64]))
+    fan_in = int(rng.choice([128, 256, 576, 640, 768, 1024]))
+    while fan_in % run_len:
+        fan_in += 64
+    n_tile = int(rng.choice([64, 128, 256]))
+    frame_len = n_tile * int(rng.integers(1, 4))
+    frames = int(rng.integers(1, 3))
+    group = int(rng.choice([128, 256]))
+    cout = group * int(rng.integers(1, 4))
+    monkeypatch.setenv("K44B_SHIFT_WS", "0")
+    monkeypatch.setenv("K44B_N_TILE", str(n_tile))
+    plan = shifted_plan(8100 + seed, rows_in=1024, runs=fan_in // run_len, run_len=run_len, frames=frames, frame_len=frame_len, cout=cout, group=group,
+                        waves=2, act=int(rng.choice(ACTS)))
+    for w in plan.waves:
+        if rng.random() < 0.6:
+            w.bias = synth.f16_bits(rng.normal(0, 0.1, w.cout))
+    if rng.random() < 0.5:
+        plan.waves[1].has_residual, plan.waves[1].res_off = True, plan.waves[0].y_off
+    notes = f"cout {cout}, group {group}, fan-in {fan_in}, run_len {run_len}, {frames} x {frame_len} tokens, tile {n_tile}"
+    x = synth.random_input(plan, 700 + seed, dist="normal")
+    npn = NativePlan.from_plan(plan, device=0)
+    try:
+        for i in range(npn.num_waves):
+            info = npn.wave_info(i)
+            assert info.path == PATH_UMMA and info.weights_in_tmem == 0 and info.n_tile == n_tile, (notes, info.path, info.weights_in_tmem, info.n_tile)
+    finally:
+        npn.close()
+    try:
+        check_per_wave(plan, run_gpu(plan, x, PATH_AUTO))
+    except AssertionError as e:
+        raise AssertionError(f"{notes}: {e}") from None
