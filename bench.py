@@ -1189,6 +1189,9 @@ def image_main(args) -> None:
 
 
 def main() -> None:
+    # stdout carries one JSON line and nothing else: NCCL's version banner (printed at NCCL_DEBUG=VERSION) goes to a level that keeps quiet
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None, help="timed steps (default: 10; 2000 / 1000 / 500 for the decode, decode-full and token-shift workloads, whose steps are 1 - 2 ms, so that the clock sampler sees the timed region)")
