@@ -119,6 +119,23 @@ def pinned_near_gpu(n_elems: int, device: int):
     return t, (len(cpus) if before is not None else None)
 
 
+def init_nccl(dist, local_rank: int) -> None:
+    """NCCL process group with this rank's GPU. NCCL writes its version banner to stdout while the first communicator is set
+    up; stdout carries one JSON line and nothing else, so file descriptor 1 points at stderr until a first collective is through."""
+    import torch
+    sys.stdout.flush()
+    saved = os.dup(1)
+    try:
+        os.dup2(2, 1)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.barrier()
+        torch.cuda.synchronize()
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -398,7 +415,7 @@ def decode_main(args) -> None:
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        init_nccl(dist, local_rank)
     cfg = dict(DECODER, layers=args.layers)
     full = args.workload == "decode-full"
     ctx = 512
@@ -721,7 +738,7 @@ def sharded_main(args) -> None:
     rank = int(os.environ.get("RANK", "0")); local_rank = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        init_nccl(dist, local_rank)
     line = sharded_measure(args.layers if args.layers != 16 else PRUNED["layers"], args.steps, args.warmup, rank, local_rank, world)
     if rank == 0:
         print(json.dumps(line), flush=True)
@@ -785,7 +802,7 @@ def shift_main(args) -> None:
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        init_nccl(dist, local_rank)
     from snntome_b200.native import fill_normal_f16
     c = dict(SHIFT)
     c["max_shift"] = max(0, min(8, args.max_shift))
@@ -926,7 +943,7 @@ def whitepaper_main(args) -> None:
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        init_nccl(dist, local_rank)
     row = WHITEPAPER_ROWS[args.wp_row]
     cin = max(1 << 16, int(80_000_000 * args.scale))
     plan, _ = build_whitepaper_plan(row, cin, local_rank, args.wp_gen, not args.wp_unmerged)
@@ -1189,9 +1206,6 @@ def image_main(args) -> None:
 
 
 def main() -> None:
-    # stdout carries one JSON line and nothing else: NCCL's version banner (printed at NCCL_DEBUG=VERSION) goes to a level that keeps quiet
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None, help="timed steps (default: 10; 2000 / 1000 / 500 for the decode, decode-full and token-shift workloads, whose steps are 1 - 2 ms, so that the clock sampler sees the timed region)")
@@ -1264,7 +1278,7 @@ def main() -> None:
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        init_nccl(dist, local_rank)
 
     def barrier():
         if dist is not None:
